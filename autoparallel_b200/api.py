@@ -1,0 +1,330 @@
+"""Public entry points: ``AutoParallel`` (context manager) and ``auto_parallel`` (one call).
+
+    with AutoParallel(model, input_fn, mesh, mp_policy) as autop:
+        autop.add_parameter_memory_constraint()            # FSDP knob
+        autop.add_input_constraints([(Shard(0),), ...])
+        placement = autop.optimize_placement()
+        parallel = autop.apply_placement(placement)
+    parallel.to_empty(device="cuda"); parallel.init_weights()
+    loss = parallel(local_tokens, labels=local_labels); loss.backward()
+
+``model`` lives on the meta device and ``input_fn`` returns *global* example inputs; the returned
+module takes this rank's *local* shards, returns local tensors, and owns ``DTensor`` parameters
+(so ``torch.distributed.checkpoint`` and ``torch.optim`` work on it unchanged).
+
+Behavioural parity target: autoparallel/api.py:231-774.  What differs is everything under the
+API: the ILP runs on HiGHS with node/edge variables, lowering builds the per-rank graph directly,
+partitioning is tag-driven, and the per-rank graph is executed by this framework's runtime
+(``runtime/executor.py``) on its own sm_100a kernels and collectives.
+"""
+from __future__ import annotations
+
+import contextlib
+import copy
+import logging
+import time
+from typing import Any, Callable, Optional, Sequence
+
+import torch
+import torch.fx as fx
+import torch.nn as nn
+from torch._subclasses import FakeTensorMode
+from torch.distributed.tensor import DTensor
+from torch.distributed.tensor.placement_types import Placement, Replicate, Shard
+from torch.utils._pytree import tree_flatten, tree_unflatten
+
+from .parallel.cost import comm as comm_cost
+from .parallel.cost import device as device_cost
+from .parallel.frontend import mp_cast
+from .parallel.frontend.trace import ForwardInputs, JointGraph, build_joint_graph, clone_model_for_tracing, move_to_fake
+from .parallel.lower import inputs as input_utils
+from .parallel.lower.apply import LoweredGraph, lower_to_local_graph
+from .parallel.lower.init_weights import wrap_init_weights
+from .parallel.lower.module_build import make_parallel_module
+from .parallel.lower.partition import extract_forward, partition_joint
+from .parallel.passes.act_ckpt import apply_activation_checkpointing, mark_fsdp_recompute
+from .parallel.solver.ilp import InfeasibleError, ShardingOptimizer
+
+logger = logging.getLogger(__name__)
+
+
+def _mesh_device(mesh) -> torch.device:
+    if mesh.device_type == "cuda":
+        return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    return torch.device(mesh.device_type)
+
+
+class AutoParallel:
+    """Trace ``model``, search placements, and build the parallel module.
+
+    Args:
+        model: module on the meta device (it is deep-copied, never modified).
+        input_fn: returns global example inputs – a tensor, a tuple, or ``ForwardInputs``.
+        mesh: ``DeviceMesh`` whose dims are the axes placements refer to.
+        mp_policy: object with ``param_dtype / reduce_dtype / output_dtype / cast_forward_inputs``.
+        reshard_after_forward: re-gather FSDP parameters in backward instead of keeping them.
+        cost_model: ``"auto"`` (NVLink-5 α–β model or CPU loopback by mesh device), a
+            ``comm.Topology``, or a path to a calibration table (JSON).
+        repeated_subgraphs: share ILP variables between structurally identical layers.
+        activation_checkpointing: ``"none" | "selective" | "full"``.
+    """
+
+    def __init__(
+        self,
+        model: nn.Module,
+        input_fn: Callable,
+        mesh,
+        mp_policy: Any = None,
+        reshard_after_forward: bool = True,
+        dynamic: bool = False,
+        cost_model: Any = "auto",
+        repeated_subgraphs: bool = True,
+        activation_checkpointing: str = "none",
+        plan_device: Optional[str] = None,
+    ):
+        if dynamic:
+            raise NotImplementedError(
+                "dynamic=True (symbolic batch) is not supported: graphs are specialised to static shapes so they can "
+                "be replayed as CUDA graphs"
+            )
+        self.fake_mode = FakeTensorMode()
+        self.mp_policy = mp_cast.canonicalize_mp(mp_policy)
+        self.mesh = mesh
+        self.input_fn = input_fn
+        self.reshard_after_forward = reshard_after_forward
+        self.repeated_subgraphs = repeated_subgraphs
+        self.cost_model = cost_model
+        self.activation_checkpointing = activation_checkpointing
+        self.plan_device = plan_device
+        model = clone_model_for_tracing(model)
+        if self.mp_policy is not None:
+            mp_cast.apply_dtype_cast(model, self.mp_policy)
+        # fake tensors live on CPU: planning never touches a device
+        self.model = move_to_fake(model, self.fake_mode, "cpu")
+        self.active: Optional[bool] = False
+        self.input_constraints = None
+        self.output_constraints = None
+        self.timings: dict[str, float] = {}
+
+    # ------------------------------------------------------------------ context management
+    def __enter__(self):
+        if self.active is not False:
+            raise RuntimeError("AutoParallel is not re-entrant")
+        self._stack = contextlib.ExitStack()
+        try:
+            self._prev_topology = comm_cost._topology
+            self._prev_limit = device_cost._override
+            if isinstance(self.cost_model, comm_cost.Topology):
+                comm_cost.set_topology(self.cost_model)
+            else:
+                topo = comm_cost.Topology.for_mesh(self.mesh)
+                if self.plan_device is not None:
+                    topo = comm_cost.Topology([comm_cost.NVLINK5] * self.mesh.ndim)
+                if isinstance(self.cost_model, str) and self.cost_model not in ("auto", "nccl"):
+                    topo.load_table(self.cost_model)
+                comm_cost.set_topology(topo)
+            if self.plan_device is not None:
+                device_cost.set_device_limit(device_cost.DEVICE_LIMITS[self.plan_device])
+            self._stack.enter_context(self.mesh)
+            t0 = time.perf_counter()
+            self.joint = build_joint_graph(self.model, self.input_fn, self.fake_mode)
+            self.gm = self.joint.gm
+            self.timings["trace"] = time.perf_counter() - t0
+            force_hp = (
+                self.mp_policy is not None
+                and self.mp_policy.reduce_dtype is not None
+                and self.mp_policy.param_dtype is not None
+                and self.mp_policy.reduce_dtype.itemsize > self.mp_policy.param_dtype.itemsize
+            )
+            t0 = time.perf_counter()
+            self.sharding_optimizer = ShardingOptimizer(
+                self.joint,
+                self.mesh,
+                force_grad_reduce_in_higher_precision=force_hp,
+                repeated_subgraphs=self.repeated_subgraphs,
+            )
+            self.timings["build_optimizer"] = time.perf_counter() - t0
+            self.active = True
+        except BaseException:
+            self._restore()
+            self._stack.close()
+            raise
+        return self
+
+    def _restore(self):
+        comm_cost.set_topology(self._prev_topology)
+        device_cost.set_device_limit(self._prev_limit)
+
+    def __exit__(self, exc_type, exc, tb):
+        self._restore()
+        self.active = None
+        return self._stack.__exit__(exc_type, exc, tb)
+
+    def _assert_entered(self):
+        if self.active is False:
+            raise RuntimeError("use AutoParallel as a context manager: `with AutoParallel(...) as autop:`")
+        if self.active is None:
+            raise RuntimeError("this AutoParallel context has exited; it is not re-entrant")
+
+    # ------------------------------------------------------------------ constraints
+    def add_parameter_memory_constraint(self, low: Optional[float] = None, high: Optional[float] = None):
+        self._assert_entered()
+        low = 0.0 if low is None else low
+        high = 1.0 / self.mesh.size() if high is None else high
+        if low > high:
+            raise ValueError(f"low must be <= high, got low={low}, high={high}")
+        return self.sharding_optimizer.add_parameter_memory_constraint(low, high)
+
+    def add_input_constraints(self, constraints: Sequence[Optional[Sequence[Placement]]]):
+        self._assert_entered()
+        if self.input_constraints is not None:
+            raise AssertionError("input constraints have already been set")
+        self.sharding_optimizer.add_sharded_input_constraint(constraints)
+        self.input_constraints = list(constraints)
+
+    def add_output_constraints(self, constraints: Sequence[Optional[Sequence[Placement]]]):
+        self._assert_entered()
+        if self.output_constraints is not None:
+            raise AssertionError("output constraints have already been set")
+        self.sharding_optimizer.add_sharded_output_constraint(constraints)
+        self.output_constraints = list(constraints)
+
+    # ------------------------------------------------------------------ solve / apply
+    def optimize_placement(self, verbose: bool = False):
+        self._assert_entered()
+        t0 = time.perf_counter()
+        try:
+            self.sharding_placement = self.sharding_optimizer.get_solution(verbose=False)
+        except InfeasibleError as e:
+            raise RuntimeError(
+                "The sharding optimizer could not find a feasible solution. This usually means the constraints "
+                "contradict each other or the mesh is too large for the tensors being sharded. " + str(e)
+            ) from e
+        self.timings["solve"] = time.perf_counter() - t0
+        if verbose:
+            logger.info(self.sharding_optimizer.get_log(verbose=True))
+        return self.sharding_placement
+
+    def lower(self, sharding_placement=None) -> LoweredGraph:
+        self._assert_entered()
+        sol = sharding_placement if sharding_placement is not None else self.sharding_placement
+        t0 = time.perf_counter()
+        lowered = lower_to_local_graph(self.joint, sol, self.mesh)
+        mark_fsdp_recompute(lowered.joint, self.reshard_after_forward)
+        if self.activation_checkpointing != "none":
+            apply_activation_checkpointing(lowered.joint, self.activation_checkpointing)
+        self.timings["lower"] = time.perf_counter() - t0
+        self.lowered = lowered
+        self.parallel_gm = lowered.gm
+        return lowered
+
+    def apply_placement(self, sharding_placement=None, *, executor: Optional[str] = None) -> nn.Module:
+        """Build the parallel module.  ``executor``: ``None``/"graph" runs the generated FX code,
+        "streams" runs it through the multi-stream overlap executor."""
+        from .runtime.executor import build_runtime
+
+        lowered = self.lower(sharding_placement)
+        t0 = time.perf_counter()
+        parts = partition_joint(lowered.joint)
+        fwd_only = extract_forward(lowered.joint)
+        self.partitioned = parts
+        runtime = build_runtime(lowered, parts, fwd_only, self.mesh, executor=executor)
+        sharded_params, sharded_buffers = _meta_state(self.model, lowered, self.mesh)
+        expected = input_utils.expected_local_inputs(self.joint.traced_inputs, lowered.input_placements, self.mesh)
+        traced = self.joint.traced_inputs
+        param_names = list(lowered.joint.param_nodes)
+        buffer_names = list(lowered.joint.buffer_nodes)
+        out_spec = _user_out_spec(self.joint)
+
+        def forward(module, *args, **kwargs):
+            flat = input_utils.flatten_call(traced, args, kwargs)
+            input_utils.check_forward_args(flat, expected)
+            params = [_local(module.get_parameter(n)) for n in param_names]
+            buffers = [_local(module.get_buffer(n)) for n in buffer_names]
+            tensors = [a for a, e in zip(flat, expected) if e[0] == "tensor"]
+            outs = runtime(params, buffers, tensors, torch.is_grad_enabled())
+            if out_spec is not None:
+                return tree_unflatten(list(outs), out_spec)
+            return outs[0] if len(outs) == 1 else tuple(outs)
+
+        module = make_parallel_module(self.model, sharded_params, sharded_buffers, forward)
+        module.__dict__["_apb200_runtime"] = runtime
+        module.__dict__["_apb200_lowered"] = lowered
+        wrap_init_weights(module)
+        self.timings["apply"] = time.perf_counter() - t0
+        return module
+
+
+def _local(t):
+    return t.to_local() if isinstance(t, DTensor) else t
+
+
+def _user_out_spec(joint: JointGraph):
+    spec = joint.out_spec
+    return spec
+
+
+def _meta_state(model: nn.Module, lowered: LoweredGraph, mesh):
+    """Meta-device DTensor parameters / buffers with the solved placements (the caller
+    materialises them with ``to_empty`` + ``init_weights``)."""
+    from torch.distributed.tensor._dtensor_spec import DTensorSpec, TensorMeta
+
+    params, buffers = {}, {}
+
+    def make(t: torch.Tensor, placements, requires_grad):
+        placements = placements or (Replicate(),) * mesh.ndim
+        from .parallel.strategies.dtensor_adapter import local_shape
+
+        ls = local_shape(t.shape, mesh.shape, placements)
+        local = torch.empty(ls, dtype=t.dtype, device="meta")
+        return DTensor.from_local(local, mesh, placements, run_check=False, shape=t.shape, stride=_contig_stride(t.shape))
+
+    for fqn, p in model.named_parameters():
+        dt = make(p, lowered.param_placements.get(fqn), p.requires_grad)
+        params[fqn] = nn.Parameter(dt, requires_grad=p.requires_grad)
+    for fqn, b in model.named_buffers():
+        buffers[fqn] = make(b, lowered.buffer_placements.get(fqn), False)
+    return params, buffers
+
+
+def _contig_stride(shape):
+    stride, acc = [], 1
+    for s in reversed(shape):
+        stride.append(acc)
+        acc *= s
+    return tuple(reversed(stride))
+
+
+def auto_parallel(
+    model: nn.Module,
+    mesh,
+    sample_inputs,
+    *,
+    sample_kwargs: Optional[dict] = None,
+    out_shardings=None,
+    mp_policy=None,
+    parameter_memory: Optional[tuple] = (None, None),
+    reshard_after_forward: bool = True,
+    **kwargs,
+) -> nn.Module:
+    """One-call API: placements of DTensor sample inputs become input constraints, plain tensors are
+    replicated, ``out_shardings`` (a placement tuple or a pytree of them) become output
+    constraints, and the FSDP memory band is applied unless ``parameter_memory=None``.
+    Reference: autoparallel/api.py:667-774."""
+    if not isinstance(sample_inputs, tuple):
+        sample_inputs = (sample_inputs,)
+    input_fn, in_pl = input_utils.input_fn_from_samples(sample_inputs, sample_kwargs)
+    with AutoParallel(model, input_fn, mesh, mp_policy=mp_policy, reshard_after_forward=reshard_after_forward, **kwargs) as ap:
+        rep = (Replicate(),) * mesh.ndim
+        cons = []
+        for node, pl in zip(ap.joint.input_nodes, in_pl):
+            cons.append(None if node is None else (pl if pl is not None else rep))
+        ap.add_input_constraints(cons)
+        if parameter_memory is not None:
+            ap.add_parameter_memory_constraint(*parameter_memory)
+        if out_shardings is not None:
+            ap.add_output_constraints(
+                input_utils.flatten_out_shardings(out_shardings, len(ap.joint.fwd_outputs), mesh)
+            )
+        ap.optimize_placement()
+        return ap.apply_placement()

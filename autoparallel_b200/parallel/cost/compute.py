@@ -1,0 +1,135 @@
+"""Compute-time estimate of one node under one sharding strategy (microseconds).
+
+``time = max(FLOPs / tensor throughput, bytes moved / HBM bandwidth)`` on the *local* (sharded)
+shapes, with a launch-latency floor; metadata-only ops cost nothing.  FLOPs come from closed
+forms per op (GEMM-shaped ops, attention) rather than a FlopCounterMode run per candidate,
+which keeps strategy pricing out of the planner's critical path.  Reference:
+autoparallel/cost_models/compute_estimation.py:391-493.
+"""
+from __future__ import annotations
+
+import math
+import operator
+from typing import Optional, Sequence
+
+import torch
+
+from ..strategies.dtensor_adapter import DTensorSpec, OpSpec, Partial, Shard, local_shape
+from .device import DeviceLimit, get_device_limit
+
+aten = torch.ops.aten
+apb = torch.ops.apb200
+
+_ZERO_COST = {
+    aten.view.default,
+    aten._unsafe_view.default,
+    aten.reshape.default,
+    aten.alias.default,
+    aten.detach.default,
+    aten.permute.default,
+    aten.t.default,
+    aten.transpose.int,
+    aten.expand.default,
+    aten.unsqueeze.default,
+    aten.squeeze.dim,
+    aten.squeeze.dims,
+    aten.slice.Tensor,
+    aten.select.int,
+    aten.split_with_sizes.default,
+    aten.split.Tensor,
+    aten.unbind.int,
+    operator.getitem,
+}
+
+_cache: dict = {}
+
+
+def reset_cache() -> None:
+    _cache.clear()
+
+
+def _numel(shape: Sequence[int]) -> int:
+    return math.prod(shape) if len(shape) else 1
+
+
+def _local(spec: Optional[DTensorSpec]) -> Optional[list[int]]:
+    if spec is None or spec.tensor_meta is None:
+        return None
+    return local_shape(spec.tensor_meta.shape, spec.mesh.shape, spec.placements)
+
+
+def _flops(op, args, in_shapes: list[list[int]], out_shapes: list[list[int]]) -> float:
+    if op is apb.mm_nd.default:
+        a, b = in_shapes[0], in_shapes[1]
+        n = b[0] if args[2] else b[1]
+        return 2.0 * _numel(a) * n
+    if op is apb.mm_wgrad.default:
+        a, b = in_shapes[0], in_shapes[1]
+        return 2.0 * _numel(a) * b[-1]
+    if op is apb.gemm.default or op is aten.mm.default:
+        a = in_shapes[0]
+        return 2.0 * _numel(a) * out_shapes[0][-1] if op is aten.mm.default else 2.0 * _numel(a) * out_shapes[0][-1]
+    if op is aten.bmm.default or op is aten.baddbmm.default:
+        a = in_shapes[-2]
+        return 2.0 * _numel(a) * out_shapes[0][-1]
+    if op is aten.addmm.default:
+        return 2.0 * _numel(in_shapes[1]) * out_shapes[0][-1]
+    if op is apb.attention.default:
+        b, s, h, d = in_shapes[0]
+        sk = in_shapes[1][1]
+        causal = 0.5 if args[3] else 1.0
+        return 4.0 * b * h * s * sk * d * causal
+    if op is apb.attention_bwd.default:
+        b, s, h, d = in_shapes[1]
+        sk = in_shapes[2][1]
+        causal = 0.5 if args[6] else 1.0
+        return 10.0 * b * h * s * sk * d * causal
+    name = str(op)
+    if "scaled_dot_product" in name or "_attention" in name:
+        q = in_shapes[1] if "backward" in name else in_shapes[0]
+        if len(q) == 4:
+            b, h, s, d = q
+            mult = 10.0 if "backward" in name else 4.0
+            return mult * b * h * s * s * d * 0.5
+    return 0.0
+
+
+def strategy_compute_cost(node, spec: OpSpec, limit: Optional[DeviceLimit] = None) -> float:
+    """Microseconds for ``node`` when run with ``spec``'s local shapes."""
+    op = node.target
+    if op in _ZERO_COST or not isinstance(op, torch._ops.OpOverload):
+        return 0.0
+    limit = limit or get_device_limit(spec.mesh.device_type)
+    outs = spec.output_specs if isinstance(spec.output_specs, (tuple, list)) else [spec.output_specs]
+    in_shapes, out_shapes = [], []
+    nbytes = 0.0
+    dtype = None
+    for s in spec.input_specs or []:
+        ls = _local(s)
+        if ls is None:
+            continue
+        in_shapes.append(ls)
+        nbytes += _numel(ls) * s.tensor_meta.dtype.itemsize
+        if dtype is None and s.tensor_meta.dtype.is_floating_point:
+            dtype = s.tensor_meta.dtype
+    for s in outs:
+        ls = _local(s)
+        if ls is None:
+            continue
+        out_shapes.append(ls)
+        nbytes += _numel(ls) * s.tensor_meta.dtype.itemsize
+        if dtype is None and s.tensor_meta.dtype.is_floating_point:
+            dtype = s.tensor_meta.dtype
+    key = (op, repr(in_shapes), repr(out_shapes), dtype, limit.name, repr([a for a in node.args if isinstance(a, (bool, int, float))]))
+    hit = _cache.get(key)
+    if hit is not None:
+        return hit
+    try:
+        flops = _flops(op, node.args, in_shapes, out_shapes)
+    except Exception:
+        flops = 0.0
+    t_flops = flops / limit.flops_per_us(dtype or torch.float32)
+    t_mem = nbytes / limit.bytes_per_us()
+    cost = max(t_flops, t_mem, limit.launch_us)
+    _cache[key] = cost
+    return cost

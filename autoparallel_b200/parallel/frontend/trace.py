@@ -1,0 +1,276 @@
+"""Joint forward+backward graph capture on fake tensors.
+
+``build_joint_graph`` turns a meta-device ``nn.Module`` plus an ``input_fn`` describing the
+*global* inputs into one ATen-level FX graph that computes the forward outputs and the
+gradients of every parameter, together with an index of which placeholder / output is
+which (parameter, buffer, user input, tangent; forward output, gradient).  Reference call
+stack: autoparallel/api.py:157-228 and autoparallel/tracing.py:14-137.
+
+The capture itself uses the same upstream entry points as the reference (Dynamo functional
+export + AOTAutograd joint export); everything downstream of the captured graph – partitioning,
+execution, scheduling – is this framework's own, so the AOT ``ExitStack`` is closed as soon as
+the graph is in hand.
+"""
+from __future__ import annotations
+
+import contextlib
+import copy
+import dataclasses
+import logging
+import time
+from typing import Any, Callable, Optional
+
+import torch
+import torch.fx as fx
+import torch.nn as nn
+from torch._subclasses import FakeTensorMode
+
+from .mp_cast import cast_reads
+
+logger = logging.getLogger(__name__)
+
+
+@dataclasses.dataclass
+class ForwardInputs:
+    """Positional and keyword inputs of ``model.forward`` (reference: input_validation.py:13-24)."""
+
+    args: tuple = ()
+    kwargs: dict = dataclasses.field(default_factory=dict)
+
+
+@dataclasses.dataclass
+class JointGraph:
+    gm: fx.GraphModule
+    #: fqn -> placeholder node
+    param_nodes: dict[str, fx.Node]
+    buffer_nodes: dict[str, fx.Node]
+    #: user inputs in flat (tree_flatten((args, kwargs))) order; None where the leaf is not a graph input
+    input_nodes: list[Optional[fx.Node]]
+    tangent_nodes: list[fx.Node]
+    #: forward outputs in flat order (fx.Node or constant)
+    fwd_outputs: list[Any]
+    #: fqn -> gradient node (None when the parameter gets no gradient)
+    param_grads: dict[str, Optional[fx.Node]]
+    input_grads: list[Optional[fx.Node]]
+    out_spec: Any  # pytree spec of the user-visible forward output
+    traced_inputs: ForwardInputs
+    #: number of forward outputs at the head of the output tuple
+    num_fwd_outputs: int = 0
+
+    def tangent_of(self, out_idx: int) -> Optional[fx.Node]:
+        for n in self.tangent_nodes:
+            if n.meta["apb200_tangent_of"] == out_idx:
+                return n
+        return None
+
+
+def normalize_inputs(raw) -> ForwardInputs:
+    if isinstance(raw, ForwardInputs):
+        return ForwardInputs(tuple(raw.args), dict(raw.kwargs))
+    if isinstance(raw, tuple):
+        return ForwardInputs(raw)
+    return ForwardInputs((raw,))
+
+
+def move_to_fake(model: nn.Module, mode: FakeTensorMode, device) -> nn.Module:
+    """Swap every meta parameter/buffer for a fake tensor on ``device``, preserving aliases.
+
+    Tied weights (one tensor reachable under two names) map to one fake tensor, so the traced
+    graph has a single placeholder for them (reference: tracing.py:39-85).
+    """
+    memo: dict[int, torch.Tensor] = {}
+    for mod in model.modules():
+        for store, is_param in ((mod._parameters, True), (mod._buffers, False)):
+            for name, t in list(store.items()):
+                if t is None:
+                    continue
+                if id(t) not in memo:
+                    if t.device.type != "meta":
+                        raise AssertionError(
+                            f"{type(mod).__name__}.{name} must live on the meta device (found {t.device}); "
+                            "build the model under `with torch.device('meta')`"
+                        )
+                    with mode:
+                        f = torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=device)
+                    if is_param:
+                        f = nn.Parameter(f, requires_grad=t.requires_grad)
+                    memo[id(t)] = f
+                    memo[id(f)] = f
+                store[name] = memo[id(t)]
+    return model
+
+
+def decomposition_table():
+    """Core ATen decompositions minus the ops the planner wants to see whole.
+
+    Kept whole (they have sharding rules and fused kernels): layer norm fwd/bwd, softmax fwd/bwd,
+    embedding backward, threshold_backward, full_like/empty_like, stack.  ``addmm`` becomes
+    ``bias + a @ b`` so linear layers with bias still expose an ``mm`` to tensor parallelism
+    (reference: tracing.py:14-36).
+    """
+    from torch._decomp import core_aten_decompositions
+
+    aten = torch.ops.aten
+    table = dict(core_aten_decompositions())
+    for op in (
+        aten.full_like.default,
+        aten.empty_like.default,
+        aten.threshold_backward.default,
+        aten.native_layer_norm.default,
+        aten.native_layer_norm_backward.default,
+        aten.embedding_dense_backward.default,
+        aten._softmax.default,
+        aten._softmax_backward_data.default,
+        aten.stack.default,
+        aten.addmm.default,
+        aten._scaled_dot_product_flash_attention_for_cpu.default,
+    ):
+        table.pop(op, None)
+
+    def addmm(self, mat1, mat2, beta=1, alpha=1):
+        out = mat1 @ mat2
+        if alpha != 1:
+            out = out * alpha
+        return (self if beta == 1 else self * beta) + out
+
+    table[aten.addmm.default] = addmm
+    return table
+
+
+@contextlib.contextmanager
+def _local_map_capture():
+    """Make Dynamo keep ``local_map`` regions as one higher-order node (if this torch can)."""
+    try:
+        from torch._dynamo.variables.higher_order_ops import LocalMapWrappedHigherOrderVariable as vt
+        from torch._higher_order_ops import local_map as lm
+
+        with vt.enable(), lm.defer_inlining():
+            yield
+    except ImportError:  # pragma: no cover - older torch
+        yield
+
+
+def _add_unused_state(model: nn.Module, gm: fx.GraphModule) -> None:
+    """Dynamo drops parameters ``forward`` never reads; re-attach them so they are sharded,
+    initialised and checkpointed like the others (reference: tracing.py:99-137)."""
+    from torch.fx.graph_module import _assign_attr
+
+    have = set(dict(gm.named_parameters(remove_duplicate=False))) | set(dict(gm.named_buffers(remove_duplicate=False)))
+    first = next((n for n in gm.graph.nodes if n.op not in ("placeholder", "get_attr")), None)
+    added = False
+    for fqn, t in list(model.named_parameters()) + list(model.named_buffers()):
+        if fqn in have:
+            continue
+        _assign_attr(t, gm, fqn)
+        with gm.graph.inserting_before(first):
+            n = gm.graph.create_node("get_attr", target=fqn)
+            n.meta["val"] = t
+        added = True
+    if added:
+        gm.recompile()
+
+
+def build_joint_graph(
+    model: nn.Module, input_fn: Callable, fake_mode: FakeTensorMode, canonicalize: bool = True
+) -> JointGraph:
+    from torch._dynamo.functional_export import _dynamo_graph_capture_for_export
+    from torch._functorch.aot_autograd import aot_export_joint_with_descriptors
+    from torch.export._trace import _restore_state_dict
+
+    t0 = time.perf_counter()
+    with fake_mode:
+        traced_inputs = normalize_inputs(input_fn())
+
+    with contextlib.ExitStack() as stack:
+        with cast_reads(True), _local_map_capture(), torch._dynamo.utils._disable_saved_tensors_hooks_during_tracing():
+            captured = _dynamo_graph_capture_for_export(model)(*traced_inputs.args, **traced_inputs.kwargs)
+            _restore_state_dict(model, captured)
+            _add_unused_state(model, captured)
+            jd = aot_export_joint_with_descriptors(
+                stack,
+                captured,
+                traced_inputs.args,
+                traced_inputs.kwargs or None,
+                decompositions=decomposition_table(),
+            )
+        gm = jd.graph_module
+        out_spec = getattr(jd, "out_spec", None)
+    if canonicalize:
+        from .graph_canon import canonicalize as _canon
+
+        _canon(gm)
+    joint = index_joint_graph(gm, traced_inputs, out_spec)
+    logger.info("joint graph captured in %.3fs (%d nodes)", time.perf_counter() - t0, len(gm.graph.nodes))
+    return joint
+
+
+def index_joint_graph(gm: fx.GraphModule, traced_inputs: ForwardInputs, out_spec=None) -> JointGraph:
+    """Classify placeholders and outputs from the descriptors AOTAutograd attached to them."""
+    from torch._functorch._aot_autograd import descriptors as D
+    from torch.utils._pytree import tree_flatten
+
+    params: dict[str, fx.Node] = {}
+    buffers: dict[str, fx.Node] = {}
+    n_flat = len(tree_flatten((traced_inputs.args, traced_inputs.kwargs))[0])
+    inputs: list[Optional[fx.Node]] = [None] * n_flat
+    tangents: list[fx.Node] = []
+    for n in gm.graph.nodes:
+        if n.op != "placeholder":
+            continue
+        d = n.meta.get("desc")
+        if isinstance(d, D.ParamAOTInput):
+            params[d.target] = n
+            n.meta["apb200_kind"] = ("param", d.target)
+        elif isinstance(d, D.BufferAOTInput):
+            buffers[d.target] = n
+            n.meta["apb200_kind"] = ("buffer", d.target)
+        elif isinstance(d, D.PlainAOTInput):
+            if d.idx >= len(inputs):
+                inputs.extend([None] * (d.idx + 1 - len(inputs)))
+            inputs[d.idx] = n
+            n.meta["apb200_kind"] = ("input", d.idx)
+        elif isinstance(d, D.TangentAOTInput):
+            tangents.append(n)
+            out_idx = d.output.idx if isinstance(d.output, D.PlainAOTOutput) else -1
+            n.meta["apb200_tangent_of"] = out_idx
+            n.meta["apb200_kind"] = ("tangent", out_idx)
+        else:
+            raise NotImplementedError(f"unsupported joint-graph input {n.name}: {d!r}")
+
+    out_node = next(n for n in gm.graph.nodes if n.op == "output")
+    out_vals = list(out_node.args[0])
+    out_descs = out_node.meta.get("desc")
+    fwd_outputs: list[Any] = []
+    param_grads: dict[str, Optional[fx.Node]] = {k: None for k in params}
+    input_grads: list[Optional[fx.Node]] = [None] * len(inputs)
+    for v, d in zip(out_vals, out_descs):
+        if isinstance(d, D.PlainAOTOutput):
+            fwd_outputs.append(v)
+        elif isinstance(d, D.GradAOTOutput):
+            src = d.grad_of
+            if isinstance(src, D.ParamAOTInput):
+                param_grads[src.target] = v
+            elif isinstance(src, D.PlainAOTInput):
+                input_grads[src.idx] = v
+        elif v is None:
+            continue  # gradient slot of an input that does not require grad
+        else:
+            raise NotImplementedError(f"unsupported joint-graph output descriptor {d!r}")
+    return JointGraph(
+        gm=gm,
+        param_nodes=params,
+        buffer_nodes=buffers,
+        input_nodes=inputs,
+        tangent_nodes=tangents,
+        fwd_outputs=fwd_outputs,
+        param_grads=param_grads,
+        input_grads=input_grads,
+        out_spec=out_spec,
+        traced_inputs=traced_inputs,
+        num_fwd_outputs=len(fwd_outputs),
+    )
+
+
+def clone_model_for_tracing(model: nn.Module) -> nn.Module:
+    """Deep copy that keeps parameter aliasing (``copy.deepcopy`` memoises shared tensors)."""
+    return copy.deepcopy(model)

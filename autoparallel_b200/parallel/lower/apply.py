@@ -1,0 +1,235 @@
+"""Lowering: global joint graph + chosen placements → per-rank graph with collectives.
+
+For every node, each tensor argument is moved from its producer's chosen output placement to the
+placement this node's chosen strategy requires (``Shard→Replicate`` all-gather, ``Partial→
+Replicate`` all-reduce, ``Partial→Shard`` reduce-scatter, ``Shard→Shard`` all-to-all,
+``Replicate→Shard`` local slice), shape arguments of views / factories are rewritten to local
+shapes, and the op itself is emitted unchanged on local tensors.  Redistributions of one tensor
+to one target placement are emitted once and shared.  The result contains ``apb200_comm``
+collective nodes (see ``runtime/comm_ops.py``).
+
+Reference: autoparallel/apply_sharding.py:84-293 (``ApplyShardingInterpreter``) – which re-traces
+with ``make_fx`` over DTensor's redistribute; here the per-rank graph is constructed directly.
+"""
+from __future__ import annotations
+
+import dataclasses
+import logging
+import math
+import operator
+from typing import Any, Optional
+
+import torch
+import torch.fx as fx
+
+from ...runtime import comm_ops
+from ..frontend.graph_canon import all_input_nodes
+from ..frontend.trace import JointGraph
+from ..strategies.dtensor_adapter import DTensorSpec, OpSpec, Partial, Replicate, Shard, local_shape
+
+logger = logging.getLogger(__name__)
+aten = torch.ops.aten
+comm = comm_ops.ops
+
+# op -> position of the "size" argument that must be rewritten to the local output shape
+_SIZE_ARG = {
+    aten.view.default: 1,
+    aten._unsafe_view.default: 1,
+    aten.reshape.default: 1,
+    aten.expand.default: 1,
+    aten.zeros.default: 0,
+    aten.ones.default: 0,
+    aten.full.default: 0,
+    aten.empty.memory_format: 0,
+    aten.rand.default: 0,
+    aten.randn.default: 0,
+    aten.new_zeros.default: 1,
+    aten.new_ones.default: 1,
+    aten.new_empty.default: 1,
+    aten.new_full.default: 1,
+}
+
+
+@dataclasses.dataclass
+class LoweredGraph:
+    gm: fx.GraphModule
+    joint: JointGraph  # re-indexed over ``gm``
+    #: placements of parameters / buffers / inputs / outputs in the solution
+    param_placements: dict[str, tuple]
+    buffer_placements: dict[str, tuple]
+    input_placements: list[Optional[tuple]]
+    output_placements: list[Optional[tuple]]
+    num_collectives: dict[str, int]
+
+
+def _spec_for_input(producer_spec: OpSpec, consumer: fx.Node) -> Optional[DTensorSpec]:
+    o = producer_spec.output_specs
+    if isinstance(o, DTensorSpec):
+        return o
+    if consumer.op == "call_function" and consumer.target is operator.getitem:
+        return o[consumer.args[1]]
+    return next((x for x in o if x is not None), None)
+
+
+class _Redistributor:
+    def __init__(self, graph: fx.Graph, mesh):
+        self.g = graph
+        self.mesh = mesh
+        self.groups = []
+        for i in range(mesh.ndim):
+            pg = mesh.get_group(i)
+            self.groups.append((pg.group_name, mesh.shape[i]))
+        self.cache: dict[tuple, fx.Node] = {}
+        self.counts = {"all_gather": 0, "reduce_scatter": 0, "all_reduce": 0, "all_to_all": 0, "local_chunk": 0}
+
+    def _emit(self, kind: str, args: tuple, like: fx.Node, shape) -> fx.Node:
+        n = self.g.call_function(getattr(comm, kind).default, args)
+        v = like.meta["val"]
+        n.meta["val"] = v.new_empty(shape)
+        for k in ("stack_trace", "nn_module_stack", "seq_nr", "autograd_backward", "apb200_phase"):
+            if k in like.meta:
+                n.meta[k] = like.meta[k]
+        self.counts[kind] += 1
+        return n
+
+    def __call__(self, x: fx.Node, key_node: fx.Node, src: DTensorSpec, dst: DTensorSpec) -> fx.Node:
+        """Emit (or reuse) the collectives taking local tensor ``x`` from ``src`` to ``dst``."""
+        if src.placements == dst.placements:
+            return x
+        key = (key_node, tuple(dst.placements))
+        hit = self.cache.get(key)
+        if hit is not None:
+            return hit
+        from .redistribute import plan_redistribution
+
+        cur = x
+        shape = list(x.meta["val"].shape)
+        for st in plan_redistribution(src.placements, dst.placements, self.mesh.shape):
+            gname, n = self.groups[st.mesh_dim]
+            if st.kind == "all_gather":
+                shape[st.dim] *= n
+                cur = self._emit("all_gather", (cur, st.dim, gname, n), x, shape)
+            elif st.kind == "all_reduce":
+                cur = self._emit("all_reduce", (cur, gname, n), x, shape)
+            elif st.kind == "reduce_scatter":
+                shape[st.dim] //= n
+                cur = self._emit("reduce_scatter", (cur, st.dim, gname, n), x, shape)
+            elif st.kind == "all_to_all":
+                shape[st.dim2] *= n
+                shape[st.dim] //= n
+                cur = self._emit("all_to_all", (cur, st.dim, st.dim2, gname, n), x, shape)
+            elif st.kind == "local_chunk":
+                shape[st.dim] //= n
+                cur = self._emit("local_chunk", (cur, st.dim, gname, n), x, shape)
+        self.cache[key] = cur
+        return cur
+
+
+def _local_val(val, spec: Optional[DTensorSpec], mesh):
+    if not isinstance(val, torch.Tensor) or spec is None:
+        return val
+    ls = local_shape(val.shape, mesh.shape, spec.placements)
+    return val.new_empty(ls)
+
+
+def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mesh) -> LoweredGraph:
+    from ..frontend.trace import index_joint_graph
+
+    old_g = joint.gm.graph
+    new_g = fx.Graph()
+    env: dict[fx.Node, fx.Node] = {}
+    redis = _Redistributor(new_g, mesh)
+
+    for node in old_g.nodes:
+        if node.op == "placeholder":
+            nn_ = new_g.placeholder(node.target)
+            nn_.meta = dict(node.meta)
+            spec = solution[node].output_spec if node in solution else None
+            nn_.meta["val"] = _local_val(node.meta.get("val"), spec, mesh)
+            if spec is not None:
+                nn_.meta["apb200_placements"] = tuple(spec.placements)
+            env[node] = nn_
+        elif node.op == "get_attr":
+            nn_ = new_g.get_attr(node.target)
+            nn_.meta = dict(node.meta)
+            env[node] = nn_
+        elif node.op == "output":
+            def conv_out(a):
+                return env[a] if isinstance(a, fx.Node) else a
+
+            out = new_g.output(fx.node.map_arg(node.args[0], conv_out))
+            out.meta = dict(node.meta)
+        elif node.op == "call_function":
+            if node not in solution:
+                # shape arithmetic etc.: copy verbatim
+                nn_ = new_g.node_copy(node, lambda a: env[a])
+                env[node] = nn_
+                continue
+            spec = solution[node]
+            slot = 0
+            tensor_inputs = [i for i in all_input_nodes(node) if i in solution]
+            it = iter(range(len(tensor_inputs)))
+
+            def conv(a):
+                nonlocal slot
+                if a not in solution:
+                    return env[a]
+                s = next(it)
+                src = _spec_for_input(solution[a], node)
+                dst = spec.input_specs[s] if spec.input_specs else None
+                if src is None or dst is None:
+                    return env[a]
+                return redis(env[a], a, src, dst)
+
+            new_args, new_kwargs = fx.node.map_arg((node.args, node.kwargs), conv)
+            out_spec = spec.output_specs
+            val = node.meta.get("val")
+            if isinstance(out_spec, DTensorSpec):
+                lval = _local_val(val, out_spec, mesh)
+            elif isinstance(val, (tuple, list)):
+                lval = tuple(_local_val(v, s, mesh) for v, s in zip(val, out_spec))
+            else:
+                lval = val
+            if node.target in _SIZE_ARG and isinstance(lval, torch.Tensor):
+                pos = _SIZE_ARG[node.target]
+                new_args = list(new_args)
+                if node.target is aten.expand.default:
+                    old = list(node.args[pos])
+                    new_args[pos] = [-1 if o == -1 else l for o, l in zip(old, lval.shape)]
+                else:
+                    new_args[pos] = list(lval.shape)
+                new_args = tuple(new_args)
+            nn_ = new_g.call_function(node.target, new_args, new_kwargs)
+            nn_.meta = dict(node.meta)
+            nn_.meta["val"] = lval
+            nn_.meta["apb200_placements"] = (
+                tuple(out_spec.placements)
+                if isinstance(out_spec, DTensorSpec)
+                else tuple(tuple(s.placements) if s is not None else None for s in out_spec)
+            )
+            env[node] = nn_
+        else:
+            raise NotImplementedError(node.op)
+
+    new_gm = fx.GraphModule(joint.gm, new_g)
+    # aliases were only redistribution points for the solver
+    from ..frontend.graph_canon import strip_redistribution_points
+
+    strip_redistribution_points(new_gm)
+    new_gm.graph.eliminate_dead_code()
+    new_gm.graph.lint()
+    new_gm.recompile()
+    new_joint = index_joint_graph(new_gm, joint.traced_inputs, joint.out_spec)
+
+    def pl(n):
+        return tuple(solution[n].output_spec.placements) if isinstance(n, fx.Node) and n in solution else None
+
+    return LoweredGraph(
+        gm=new_gm,
+        joint=new_joint,
+        param_placements={k: pl(v) for k, v in joint.param_nodes.items()},
+        buffer_placements={k: pl(v) for k, v in joint.buffer_nodes.items()},
+        input_placements=[pl(n) for n in joint.input_nodes],
+        output_placements=[pl(n) for n in joint.fwd_outputs],
+        num_collectives=dict(redis.counts),
+    )

@@ -1,0 +1,95 @@
+"""Planning of one placement change as an ordered list of per-mesh-dim collectives.
+
+The same plan is priced by the cost model and emitted by the lowering, so what the solver pays
+for is what runs.  Ordering rules (a tensor dim sharded over several mesh dims is split
+outer-mesh-dim first):
+
+1. *unshard* steps (all-gather, all-to-all) run from the innermost mesh dim outwards;
+2. a mesh dim whose shard sits *inside* a shard that changes (same tensor dim, outer mesh dim)
+   is gathered first and re-sharded afterwards, so chunks stay contiguous;
+3. *shard* steps (local slice, reduce-scatter) and all-reduces run from the outermost mesh dim
+   inwards.
+
+Reference: DTensor's ``redistribute_local_tensor`` as driven by
+autoparallel/shardings/ordered_sharding.py:70-102 and priced by
+autoparallel/cost_models/collective_runtime_estimation.py:115-229.
+"""
+from __future__ import annotations
+
+from typing import NamedTuple, Optional, Sequence
+
+from torch.distributed.tensor.placement_types import Partial, Placement, Replicate, Shard
+
+
+class Step(NamedTuple):
+    kind: str  # all_gather | all_reduce | reduce_scatter | all_to_all | local_chunk
+    mesh_dim: int
+    dim: Optional[int] = None  # gather / scatter / chunk dim (all_to_all: new shard dim)
+    dim2: Optional[int] = None  # all_to_all: old shard dim (concat dim)
+
+
+class RedistributeError(RuntimeError):
+    pass
+
+
+def plan_redistribution(src: Sequence[Placement], dst: Sequence[Placement], mesh_shape: Sequence[int]) -> list[Step]:
+    nd = len(mesh_shape)
+    cur = list(src)
+    steps: list[Step] = []
+    for q, p in zip(dst, src):
+        if isinstance(q, Partial) and not isinstance(p, Partial):
+            raise RedistributeError(f"cannot create a pending reduction: {p} -> {q}")
+
+    def changes(i):
+        return cur[i] != dst[i] and mesh_shape[i] > 1
+
+    # tensor dims touched by a change on mesh dim i (as source shard or target shard)
+    def touched(i):
+        dims = set()
+        if isinstance(cur[i], Shard):
+            dims.add(cur[i].dim)
+        if isinstance(dst[i], Shard):
+            dims.add(dst[i].dim)
+        return dims
+
+    must_unshard = set()
+    for i in range(nd):
+        if not changes(i):
+            continue
+        if isinstance(cur[i], Shard):
+            must_unshard.add(i)
+        for j in range(i + 1, nd):
+            if isinstance(cur[j], Shard) and cur[j].dim in touched(i) and mesh_shape[j] > 1:
+                must_unshard.add(j)
+    # phase 1: inner -> outer
+    for i in sorted(must_unshard, reverse=True):
+        p, q = cur[i], dst[i]
+        simple_a2a = (
+            isinstance(q, Shard)
+            and q.dim != p.dim
+            and not any(isinstance(cur[j], Shard) and cur[j].dim == q.dim for j in range(nd) if j != i)
+            and not any(isinstance(dst[j], Shard) and dst[j].dim == q.dim for j in range(nd) if j != i)
+            and not any(isinstance(cur[j], Shard) and cur[j].dim == p.dim for j in range(i + 1, nd))
+        )
+        if simple_a2a:
+            steps.append(Step("all_to_all", i, q.dim, p.dim))
+            cur[i] = q
+        else:
+            steps.append(Step("all_gather", i, p.dim))
+            cur[i] = Replicate()
+    # phase 2: outer -> inner
+    for i in range(nd):
+        p, q = cur[i], dst[i]
+        if p == q or mesh_shape[i] == 1:
+            cur[i] = q
+            continue
+        if isinstance(p, Partial) and isinstance(q, Replicate):
+            steps.append(Step("all_reduce", i))
+        elif isinstance(p, Partial) and isinstance(q, Shard):
+            steps.append(Step("reduce_scatter", i, q.dim))
+        elif isinstance(p, Replicate) and isinstance(q, Shard):
+            steps.append(Step("local_chunk", i, q.dim))
+        else:
+            raise RedistributeError(f"cannot redistribute {p} -> {q} on mesh dim {i}")
+        cur[i] = q
+    return steps

@@ -1,0 +1,442 @@
+"""Sharding rules owned by the framework.
+
+A rule maps ``(mesh, node, input strategies, input values, output value)`` to an
+``OpStrategy``.  Rules exist for (a) every ``apb200`` operator – written as tables of
+single-mesh-dim placements and expanded to the full mesh, (b) ATen ops where the planner wants
+different behaviour from DTensor's default (``alias`` as a free redistribution point, factory
+ops shardable at zero cost, ``getitem`` mirroring its producer, casts as pass-through).
+Reference: autoparallel/shardings/propagation_rules.py:56-680.
+"""
+from __future__ import annotations
+
+import itertools
+import operator
+from typing import Callable, Optional, Sequence
+
+import torch
+
+from .dtensor_adapter import (
+    DTensorSpec,
+    OpSpec,
+    OpStrategy,
+    Partial,
+    Placement,
+    Replicate,
+    Shard,
+    all_options,
+    is_valid_spec,
+    tensor_meta_of,
+)
+
+aten = torch.ops.aten
+apb = torch.ops.apb200
+
+R = Replicate()
+P = Partial()
+
+
+def S(d: int) -> Shard:
+    return Shard(d)
+
+
+_RULES: dict[object, Callable] = {}
+
+
+def register_rule(*ops):
+    def deco(fn):
+        for op in ops:
+            _RULES[op] = fn
+        return fn
+
+    return deco
+
+
+def get_rule(op) -> Optional[Callable]:
+    return _RULES.get(op)
+
+
+def registered_ops():
+    return list(_RULES)
+
+
+class RuleCtx:
+    """What a rule sees: the mesh, tensor input values/strategies (in argument order), the
+    node's full args (for flags) and its output value(s)."""
+
+    def __init__(self, mesh, op, args, kwargs, in_vals, in_strats, out_val, even_only):
+        self.mesh, self.op, self.args, self.kwargs = mesh, op, args, kwargs
+        self.in_vals, self.in_strats, self.out_val, self.even_only = in_vals, in_strats, out_val, even_only
+
+    @property
+    def out_vals(self):
+        return list(self.out_val) if isinstance(self.out_val, (tuple, list)) else [self.out_val]
+
+
+def expand_rows(ctx: RuleCtx, rows: Sequence[Sequence[Optional[Placement]]]) -> OpStrategy:
+    """``rows[i] = (out_0, .., out_{m-1}, in_0, .., in_{n-1})`` placements for ONE mesh dim;
+    the full-mesh strategy set is the product over mesh dims, filtered for shard validity."""
+    mesh = ctx.mesh
+    outs, ins = ctx.out_vals, ctx.in_vals
+    n_out = len(outs)
+    rep_row = tuple([R if isinstance(v, torch.Tensor) else None for v in outs] + [R] * len(ins))
+    rows = [tuple(r) for r in rows]
+    if rep_row not in rows:
+        rows = [rep_row] + rows
+    out_tms = [tensor_meta_of(v) if isinstance(v, torch.Tensor) else None for v in outs]
+    in_tms = [tensor_meta_of(v) for v in ins]
+    specs = []
+    seen = set()
+    for combo in itertools.product(rows, repeat=mesh.ndim):
+        per_tensor = list(zip(*combo))  # per tensor: placements over mesh dims
+        key = tuple(per_tensor)
+        if key in seen:
+            continue
+        seen.add(key)
+        o_specs = [
+            DTensorSpec(mesh, tuple(pl), tensor_meta=tm) if tm is not None else None
+            for pl, tm in zip(per_tensor[:n_out], out_tms)
+        ]
+        i_specs = [DTensorSpec(mesh, tuple(pl), tensor_meta=tm) for pl, tm in zip(per_tensor[n_out:], in_tms)]
+        if not all(is_valid_spec(s, mesh, ctx.even_only) for s in o_specs + i_specs):
+            continue
+        out = o_specs[0] if not isinstance(ctx.out_val, (tuple, list)) else tuple(o_specs)
+        specs.append(OpSpec(out, input_specs=i_specs))
+    return OpStrategy(specs)
+
+
+def _lead_dims(v: torch.Tensor, keep_last: int = 1):
+    return range(v.ndim - keep_last)
+
+
+# ------------------------------------------------------------------------------ apb200 operators
+@register_rule(apb.rms_norm.default)
+def _rms_norm(ctx):
+    x = ctx.in_vals[0]
+    return expand_rows(ctx, [(S(i), S(i), S(i), R) for i in _lead_dims(x)])
+
+
+@register_rule(apb.rms_norm_bwd.default)
+def _rms_norm_bwd(ctx):
+    x = ctx.in_vals[1]
+    return expand_rows(ctx, [(S(i), P, S(i), S(i), R, S(i)) for i in _lead_dims(x)])
+
+
+@register_rule(apb.rope.default)
+def _rope(ctx):
+    # x [B, S, H, D]; cos/sin [S, D/2]
+    return expand_rows(ctx, [(S(0), S(0), R, R), (S(1), S(1), S(0), S(0)), (S(2), S(2), R, R)])
+
+
+@register_rule(apb.swiglu.default)
+def _swiglu(ctx):
+    return expand_rows(ctx, [(S(i), S(i), S(i)) for i in range(ctx.in_vals[0].ndim)])
+
+
+@register_rule(apb.swiglu_bwd.default)
+def _swiglu_bwd(ctx):
+    return expand_rows(ctx, [(S(i),) * 5 for i in range(ctx.in_vals[0].ndim)])
+
+
+@register_rule(apb.attention.default)
+def _attention(ctx):
+    # q [B,S,H,D], k/v [B,S,Hkv,D] -> o [B,S,H,D], lse [B,H,S]; batch- and head-parallel.
+    return expand_rows(ctx, [(S(0), S(0), S(0), S(0), S(0)), (S(2), S(1), S(2), S(2), S(2))])
+
+
+@register_rule(apb.attention_bwd.default)
+def _attention_bwd(ctx):
+    # (dout, q, k, v, out, lse) -> (dq, dk, dv)
+    return expand_rows(
+        ctx,
+        [
+            (S(0), S(0), S(0), S(0), S(0), S(0), S(0), S(0), S(0)),
+            (S(2), S(2), S(2), S(2), S(2), S(2), S(2), S(2), S(1)),
+        ],
+    )
+
+
+@register_rule(apb.cross_entropy.default)
+def _xent(ctx):
+    logits = ctx.in_vals[0]
+    return expand_rows(ctx, [(S(i), S(i), S(i), S(i)) for i in _lead_dims(logits)])
+
+
+@register_rule(apb.cross_entropy_bwd.default)
+def _xent_bwd(ctx):
+    logits = ctx.in_vals[1]
+    return expand_rows(ctx, [(S(i), S(i), S(i), S(i), S(i)) for i in _lead_dims(logits)])
+
+
+@register_rule(apb.mm_nd.default)
+def _mm_nd(ctx):
+    a, b = ctx.in_vals
+    trans_b = ctx.args[2]
+    last = a.ndim - 1
+    kdim, ndim = (1, 0) if trans_b else (0, 1)
+    rows = [(S(i), S(i), R) for i in range(last)]
+    rows += [(P, S(last), S(kdim)), (S(last), R, S(ndim))]
+    return expand_rows(ctx, rows)
+
+
+@register_rule(apb.mm_wgrad.default)
+def _mm_wgrad(ctx):
+    a, b = ctx.in_vals
+    la, lb = a.ndim - 1, b.ndim - 1
+    rows = [(P, S(i), S(i)) for i in range(la)]
+    rows += [(S(0), S(la), R), (S(1), R, S(lb))]
+    return expand_rows(ctx, rows)
+
+
+@register_rule(apb.gemm.default)
+def _gemm(ctx):
+    ta, tb = ctx.args[2], ctx.args[3]
+    am, ak = (1, 0) if ta else (0, 1)
+    bk, bn = (1, 0) if tb else (0, 1)
+    return expand_rows(ctx, [(S(0), S(am), R), (S(1), R, S(bn)), (P, S(ak), S(bk))])
+
+
+@register_rule(apb.embedding_bwd.default)
+def _embedding_bwd(ctx):
+    dy, ids = ctx.in_vals
+    rows = [(P, S(i), S(i)) for i in range(ids.ndim)]
+    rows.append((S(1), S(dy.ndim - 1), R))
+    return expand_rows(ctx, rows)
+
+
+# ------------------------------------------------------------------------------ pass-through ops
+def passthrough(ctx: RuleCtx, allow_partial: bool = True) -> OpStrategy:
+    """One strategy per input option: output placement == input placement."""
+    (strat,) = ctx.in_strats
+    out_tm = tensor_meta_of(ctx.out_val)
+    specs = []
+    for s in strat.strategies:
+        src = s.output_spec
+        if not allow_partial and any(isinstance(p, Partial) for p in src.placements):
+            continue
+        specs.append(
+            OpSpec(
+                DTensorSpec(ctx.mesh, src.placements, tensor_meta=out_tm),
+                input_specs=[DTensorSpec(ctx.mesh, src.placements, tensor_meta=src.tensor_meta)],
+            )
+        )
+    return OpStrategy(specs)
+
+
+@register_rule(apb.dtype_cast.default, torch.ops.prims.convert_element_type.default)
+def _cast(ctx):
+    return passthrough(ctx, allow_partial=True)
+
+
+@register_rule(aten.alias.default)
+def _alias(ctx):
+    """Every placement in, same placement out: a zero-cost node whose *incoming edge* is where
+    the solver pays for a redistribution shared by all consumers."""
+    return all_options(ctx.mesh, ctx.out_val, ctx.even_only)
+
+
+# ------------------------------------------------------------------------------ factory ops
+FACTORY_OPS = [
+    aten.zeros.default,
+    aten.ones.default,
+    aten.full.default,
+    aten.empty.memory_format,
+    aten.rand.default,
+    aten.randn.default,
+]
+REPLICATED_FACTORY_OPS = [
+    aten.arange.default,
+    aten.arange.start,
+    aten.arange.start_step,
+    aten.scalar_tensor.default,
+    torch.ops.prims.iota.default,
+]
+
+
+@register_rule(*FACTORY_OPS)
+def _factory(ctx):
+    """No tensor inputs: any sharding of the output is free (each rank creates its shard)."""
+    strat = all_options(ctx.mesh, ctx.out_val, ctx.even_only)
+    for s in strat.strategies:
+        s.input_specs = []
+    return strat
+
+
+@register_rule(*REPLICATED_FACTORY_OPS)
+def _replicated_factory(ctx):
+    spec = DTensorSpec(ctx.mesh, (R,) * ctx.mesh.ndim, tensor_meta=tensor_meta_of(ctx.out_val))
+    return OpStrategy([OpSpec(spec, input_specs=[])])
+
+
+@register_rule(operator.getitem)
+def _getitem(ctx):
+    """Mirrors the producer 1:1 – strategy *i* of ``getitem`` is element ``idx`` of the
+    producer's strategy *i* (the solver ties the two indices together)."""
+    (strat,) = ctx.in_strats
+    idx = ctx.args[1]
+    specs = []
+    for s in strat.strategies:
+        spec = s.output_specs[idx]
+        specs.append(OpSpec(spec, input_specs=[spec]))
+    return OpStrategy(specs)
+
+
+# ------------------------------------------------------------------------------ view / reshape
+def _view_groups(in_shape, out_shape):
+    """Split both shapes into aligned groups with equal element counts:
+    ``[8, 64, 256] -> [8, 64, 8, 32]`` gives ``([0],[0]), ([1],[1]), ([2],[2,3])``."""
+    groups = []
+    i = j = 0
+    ni, nj = len(in_shape), len(out_shape)
+    while i < ni or j < nj:
+        gi, gj = [], []
+        pi = pj = 1
+        if i < ni:
+            gi.append(i)
+            pi *= in_shape[i]
+            i += 1
+        if j < nj:
+            gj.append(j)
+            pj *= out_shape[j]
+            j += 1
+        while pi != pj:
+            if pi < pj:
+                if i >= ni:
+                    return None
+                gi.append(i)
+                pi *= in_shape[i]
+                i += 1
+            else:
+                if j >= nj:
+                    return None
+                gj.append(j)
+                pj *= out_shape[j]
+                j += 1
+        # absorb trailing size-1 dims
+        while i < ni and in_shape[i] == 1 and (j >= nj or out_shape[j] != 1):
+            gi.append(i)
+            i += 1
+        while j < nj and out_shape[j] == 1 and (i >= ni or in_shape[i] != 1):
+            gj.append(j)
+            j += 1
+        groups.append((gi, gj))
+    return groups
+
+
+def view_placement_map(in_shape, out_shape, mesh_shape, placements):
+    """Output placements of ``x.view(out_shape)`` for a given input placement, or None when the
+    view cannot be done shard-locally.  A shard on the *leading* non-unit dim of a group maps to
+    the leading non-unit output dim of that group when the sizes divide."""
+    groups = _view_groups(list(in_shape), list(out_shape))
+    if groups is None:
+        return None
+    in_to_group = {}
+    for g in groups:
+        for d in g[0]:
+            in_to_group[d] = g
+    rem_out = list(out_shape)  # remaining (local) size of each out dim as mesh dims shard it
+    rem_in = list(in_shape)
+    out = []
+    for n, p in zip(mesh_shape, placements):
+        if not isinstance(p, Shard):
+            out.append(p)
+            continue
+        d = p.dim
+        gi, gj = in_to_group[d]
+        lead_in = next((x for x in gi if in_shape[x] != 1), gi[0])
+        if d != lead_in:
+            return None
+        lead_out = next((x for x in gj if out_shape[x] != 1), gj[0] if gj else None)
+        if lead_out is None:
+            return None
+        if rem_in[d] % n != 0 or rem_out[lead_out] % n != 0:
+            return None
+        rem_in[d] //= n
+        rem_out[lead_out] //= n
+        out.append(Shard(lead_out))
+    return tuple(out)
+
+
+@register_rule(aten.view.default, aten._unsafe_view.default, aten.reshape.default)
+def _view(ctx):
+    (strat,) = ctx.in_strats
+    x = ctx.in_vals[0]
+    out_tm = tensor_meta_of(ctx.out_val)
+    specs = []
+    for s in strat.strategies:
+        src = s.output_spec
+        mapped = view_placement_map(x.shape, ctx.out_val.shape, ctx.mesh.shape, src.placements)
+        if mapped is None:
+            continue
+        specs.append(
+            OpSpec(
+                DTensorSpec(ctx.mesh, mapped, tensor_meta=out_tm),
+                input_specs=[DTensorSpec(ctx.mesh, src.placements, tensor_meta=src.tensor_meta)],
+            )
+        )
+    return OpStrategy(specs)
+
+
+# ------------------------------------------------------------------------------ layer norm
+@register_rule(aten.native_layer_norm.default)
+def _layer_norm(ctx):
+    """(x, normalized_shape, weight?, bias?, eps) -> (out, mean, rstd); shard only outside the
+    normalised dims.  (DTensor's own strategy indexes weight options by the input's option
+    index and breaks when the two lists differ in length.)"""
+    x = ctx.in_vals[0]
+    n_norm = len(ctx.args[1])
+    n_extra = len(ctx.in_vals) - 1
+    rows = [(S(i), S(i), S(i), S(i)) + (R,) * n_extra for i in range(x.ndim - n_norm)]
+    return expand_rows(ctx, rows)
+
+
+@register_rule(aten.native_layer_norm_backward.default)
+def _layer_norm_bwd(ctx):
+    """(dy, x, normalized_shape, mean, rstd, weight?, bias?, mask) -> (dx, dw?, db?)."""
+    x = ctx.in_vals[1]
+    n_norm = len(ctx.args[2])
+    n_extra = len(ctx.in_vals) - 4
+    outs = ctx.out_vals
+    rows = []
+    for i in range(x.ndim - n_norm):
+        o = [S(i)] + [P if isinstance(v, torch.Tensor) else None for v in outs[1:]]
+        rows.append(tuple(o) + (S(i), S(i), S(i), S(i)) + (R,) * n_extra)
+    return expand_rows(ctx, rows)
+
+
+# ------------------------------------------------------------------------------ misc ATen gaps
+@register_rule(aten._scaled_dot_product_flash_attention_for_cpu.default)
+def _sdpa_cpu(ctx):
+    # q,k,v [B,H,S,D] (+ optional mask) -> (out [B,H,S,D], lse [B,H,S]); batch- and head-parallel
+    extra = (R,) * (len(ctx.in_vals) - 3)
+    return expand_rows(ctx, [(S(0), S(0), S(0), S(0), S(0)) + extra, (S(1), S(1), S(1), S(1), S(1)) + extra])
+
+
+@register_rule(aten._scaled_dot_product_flash_attention_for_cpu_backward.default)
+def _sdpa_cpu_bwd(ctx):
+    # (dout, q, k, v, out, lse, ...) -> (dq, dk, dv)
+    extra = (R,) * (len(ctx.in_vals) - 6)
+    return expand_rows(ctx, [(S(0),) * 9 + extra, (S(1),) * 9 + extra])
+
+
+@register_rule(aten.squeeze.dims, aten.squeeze.dim)
+def _squeeze(ctx):
+    x = ctx.in_vals[0]
+    dims = ctx.args[1]
+    dims = [dims] if isinstance(dims, int) else list(dims)
+    dims = {d % x.ndim for d in dims if x.shape[d % x.ndim] == 1}
+    rows, new = [], 0
+    for d in range(x.ndim):
+        if d in dims:
+            continue
+        rows.append((S(new), S(d)))
+        new += 1
+    return expand_rows(ctx, rows)
+
+
+@register_rule(aten.scatter.value, aten.scatter.src, aten.gather.default)
+def _scatter_gather(ctx):
+    """Shardable on every dim except the scatter/gather dim (all tensor operands alike)."""
+    x = ctx.in_vals[0]
+    dim = ctx.args[1] % x.ndim
+    n = len(ctx.in_vals)
+    return expand_rows(ctx, [(S(i),) * (1 + n) for i in range(x.ndim) if i != dim])

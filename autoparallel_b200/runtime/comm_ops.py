@@ -1,0 +1,176 @@
+"""Collective operators that the lowered (per-rank) graph contains.
+
+The planner's lowering emits these – one node per collective, synchronous in graph semantics –
+instead of c10d functional collectives, so the scheduler and the fusion passes have a single
+vocabulary to pattern-match (all-gather → GEMM, GEMM → reduce-scatter, ...), and so the same
+graph runs on three back-ends:
+
+* ``nccl`` / ``gloo`` / ``fake`` process groups through c10d functional collectives (the
+  NCCL-only baseline plan, CPU tests, planning on fake ranks),
+* this framework's symmetric-memory kernels (``runtime/symm.py``) when a group has been enabled
+  for them – P2P loads over NVLink inside the kernel, no NCCL on the path.
+
+Every op takes the tensor dim it acts on, so gathers / scatters on inner dims need no
+``chunk + cat`` round trip through HBM in the graph.  ``group`` is a c10d group name
+(``mesh.get_group(i).group_name``).  Reference: the reference lowers through DTensor's
+``redistribute_local_tensor`` to ``_c10d_functional`` ops (autoparallel/shardings/
+ordered_sharding.py:70-102) and wraps them for users in autoparallel/collectives.py:89-229.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.distributed._functional_collectives as funcol
+
+NS = "apb200_comm"
+lib = torch.library.Library(NS, "DEF")  # noqa: TOR901
+
+lib.define("all_gather(Tensor x, int dim, str group, int group_size) -> Tensor")
+lib.define("reduce_scatter(Tensor x, int dim, str group, int group_size) -> Tensor")
+lib.define("all_reduce(Tensor x, str group, int group_size) -> Tensor")
+lib.define("all_to_all(Tensor x, int split_dim, int concat_dim, str group, int group_size) -> Tensor")
+lib.define("local_chunk(Tensor x, int dim, str group, int group_size) -> Tensor")
+
+#: group name -> symmetric-memory communicator (set by runtime.symm.enable_for_group)
+_symm_backends: dict[str, object] = {}
+
+
+def _wait(t):
+    return funcol.wait_tensor(t) if hasattr(funcol, "wait_tensor") else t
+
+
+def _rank_in_group(group: str) -> int:
+    pg = dist.distributed_c10d._resolve_process_group(group)
+    return dist.get_rank(pg)
+
+
+def _all_gather(x, dim, group, n):
+    be = _symm_backends.get(group)
+    if be is not None and x.is_cuda:
+        return be.all_gather(x, dim)
+    x = x.contiguous()
+    out = torch.ops._c10d_functional.all_gather_into_tensor(x, n, group)
+    out = torch.ops._c10d_functional.wait_tensor(out)
+    if dim == 0:
+        return out
+    # [n*d0, ...] -> [n, d0, ...] -> move n next to ``dim`` -> merge
+    out = out.view(n, *x.shape).movedim(0, dim)
+    shape = list(x.shape)
+    shape[dim] *= n
+    return out.reshape(shape)
+
+
+def _reduce_scatter(x, dim, group, n):
+    be = _symm_backends.get(group)
+    if be is not None and x.is_cuda:
+        return be.reduce_scatter(x, dim)
+    shape = list(x.shape)
+    shape[dim] //= n
+    if dim != 0:
+        x = x.view(*x.shape[:dim], n, shape[dim], *x.shape[dim + 1 :]).movedim(dim, 0)
+    flat = x.reshape(-1) if x.is_contiguous() else x.contiguous().view(-1)
+    out = torch.ops._c10d_functional.reduce_scatter_tensor(flat, "sum", n, group)
+    return torch.ops._c10d_functional.wait_tensor(out).view(shape)
+
+
+def _all_reduce(x, group, n):
+    be = _symm_backends.get(group)
+    if be is not None and x.is_cuda:
+        return be.all_reduce(x)
+    out = torch.ops._c10d_functional.all_reduce(x.contiguous(), "sum", group)
+    return torch.ops._c10d_functional.wait_tensor(out)
+
+
+def _all_to_all(x, split_dim, concat_dim, group, n):
+    """Each rank splits ``x`` into n chunks along ``split_dim``, sends chunk r to rank r, and
+    concatenates what it receives along ``concat_dim`` (Shard(concat_dim) -> Shard(split_dim))."""
+    be = _symm_backends.get(group)
+    if be is not None and x.is_cuda:
+        return be.all_to_all(x, split_dim, concat_dim)
+    chunks = x.chunk(n, dim=split_dim)
+    send = torch.stack([c.contiguous() for c in chunks], 0)  # [n, ...chunk]
+    flat = send.reshape(n * send.shape[1], *send.shape[2:]) if send.ndim > 1 else send
+    rows = flat.shape[0] // n
+    out = torch.ops._c10d_functional.all_to_all_single(flat, [rows] * n, [rows] * n, group)
+    out = torch.ops._c10d_functional.wait_tensor(out)
+    recv = out.view(n, *chunks[0].shape)
+    return torch.cat(list(recv.unbind(0)), dim=concat_dim)
+
+
+def _local_chunk(x, dim, group, n):
+    r = _rank_in_group(group)
+    size = x.shape[dim] // n
+    return x.narrow(dim, r * size, size).contiguous()
+
+
+for _name, _fn in (
+    ("all_gather", _all_gather),
+    ("reduce_scatter", _reduce_scatter),
+    ("all_reduce", _all_reduce),
+    ("all_to_all", _all_to_all),
+    ("local_chunk", _local_chunk),
+):
+    lib.impl(_name, _fn, "CPU")
+    lib.impl(_name, _fn, "CUDA")
+
+
+def _shape_mul(x, dim, n):
+    s = list(x.shape)
+    s[dim] *= n
+    return x.new_empty(s)
+
+
+def _shape_div(x, dim, n):
+    s = list(x.shape)
+    s[dim] //= n
+    return x.new_empty(s)
+
+
+lib.impl("all_gather", lambda x, dim, group, n: _shape_mul(x, dim, n), "Meta")
+lib.impl("reduce_scatter", lambda x, dim, group, n: _shape_div(x, dim, n), "Meta")
+lib.impl("all_reduce", lambda x, group, n: torch.empty_like(x), "Meta")
+lib.impl("local_chunk", lambda x, dim, group, n: _shape_div(x, dim, n), "Meta")
+
+
+def _a2a_meta(x, split_dim, concat_dim, group, n):
+    s = list(x.shape)
+    s[split_dim] //= n
+    s[concat_dim] *= n
+    return x.new_empty(s)
+
+
+lib.impl("all_to_all", _a2a_meta, "Meta")
+
+ops = getattr(torch.ops, NS)
+
+
+# ---------------------------------------------------------------------------- autograd pairs
+def _setup(ctx, inputs, output):
+    ctx.args = inputs[1:]
+
+
+torch.library.register_autograd(
+    f"{NS}::all_gather", lambda ctx, g: (ops.reduce_scatter(g, *ctx.args), None, None, None), setup_context=_setup, lib=lib
+)
+torch.library.register_autograd(
+    f"{NS}::reduce_scatter", lambda ctx, g: (ops.all_gather(g, *ctx.args), None, None, None), setup_context=_setup, lib=lib
+)
+torch.library.register_autograd(
+    f"{NS}::all_reduce", lambda ctx, g: (ops.all_reduce(g, *ctx.args), None, None), setup_context=_setup, lib=lib
+)
+torch.library.register_autograd(
+    f"{NS}::all_to_all",
+    lambda ctx, g: (ops.all_to_all(g, ctx.args[1], ctx.args[0], ctx.args[2], ctx.args[3]), None, None, None, None),
+    setup_context=_setup,
+    lib=lib,
+)
+torch.library.register_autograd(
+    f"{NS}::local_chunk", lambda ctx, g: (ops.all_gather(g, *ctx.args), None, None, None), setup_context=_setup, lib=lib
+)
+
+COLLECTIVE_OPS = {
+    ops.all_gather.default,
+    ops.reduce_scatter.default,
+    ops.all_reduce.default,
+    ops.all_to_all.default,
+}
