@@ -1,0 +1,118 @@
+"""Per-kernel timing against the machine's measured roofline.
+
+``python -m autoparallel_b200.ops.bench_kernels [--json out.json]`` times each sm_100a kernel at
+the Llama-3 8B shapes with CUDA events (3 warm-ups, inputs rotated through a pool larger than the
+126 MB L2 so every timed launch reads cold data) and prints achieved TFLOP/s or GB/s next to the
+fraction of the measured peak (``MEASURED_PEAKS.json`` beside the repo root if present, else
+6.65 TB/s and 1.59 PFLOP/s).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        m = json.load(open(p))
+        return m["hbm_gbs"], m["bf16_tflops"], m.get("bf16_tflops_sustained", m["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+def time_fn(make_args, fn, iters=10, pool=4):
+    argsets = [make_args() for _ in range(pool)]
+    for i in range(3):
+        fn(*argsets[i % pool])
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for i, (s, e) in enumerate(evs):
+        s.record()
+        fn(*argsets[i % pool])
+        e.record()
+    torch.cuda.synchronize()
+    ts = sorted(s.elapsed_time(e) for s, e in evs)
+    return ts[len(ts) // 2], ts[0]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--quick", action="store_true")
+    args = ap.parse_args()
+    from autoparallel_b200.ops import cuda_impl, library as L
+
+    cuda_impl.ensure_loaded()
+    hbm, tf_burst, tf_sus, src = _peaks()
+    dev = "cuda"
+    bf = torch.bfloat16
+    rows = []
+
+    def rec(name, ms, best, flops=None, nbytes=None):
+        r = {"kernel": name, "ms_median": ms, "ms_best": best}
+        if flops:
+            r["tflops"] = flops / best / 1e9
+            r["frac_of_burst_gemm_peak"] = r["tflops"] / tf_burst
+        if nbytes:
+            r["gbs"] = nbytes / best / 1e6
+            r["frac_of_copy_peak"] = r["gbs"] / hbm
+        rows.append(r)
+        extra = f"{r.get('tflops', 0):8.1f} TF/s ({r.get('frac_of_burst_gemm_peak', 0):.2f} of {src} burst)" if flops else \
+            f"{r.get('gbs', 0):8.1f} GB/s ({r.get('frac_of_copy_peak', 0):.2f} of {src} copy)"
+        print(f"{name:44s} {best:8.3f} ms  {extra}", flush=True)
+
+    M = 8192
+    shapes = [(M, 4096, 4096), (M, 14336, 4096), (M, 4096, 14336), (M, 1024, 4096)]
+    if not args.quick:
+        shapes.append((M, 128256, 4096))
+    for (m, n, k) in shapes:
+        for tag, ta, tb in (("nt", False, True), ("nn", False, False), ("tn", True, False)):
+            if tag == "tn":
+                mk = lambda: (torch.randn(k, m, device=dev, dtype=bf), torch.randn(k, n, device=dev, dtype=bf))
+            elif tag == "nn":
+                mk = lambda: (torch.randn(m, k, device=dev, dtype=bf), torch.randn(k, n, device=dev, dtype=bf))
+            else:
+                mk = lambda: (torch.randn(m, k, device=dev, dtype=bf), torch.randn(n, k, device=dev, dtype=bf))
+            ms, best = time_fn(mk, lambda a, b: L.ops.gemm(a, b, ta, tb, bf), pool=3)
+            rec(f"gemm_{tag} {m}x{n}x{k}", ms, best, flops=2.0 * m * n * k)
+            if tag == "nt":
+                ms, best = time_fn(mk, lambda a, b: torch.matmul(a, b.t()), pool=3)
+                rec(f"  cublas_nt {m}x{n}x{k}", ms, best, flops=2.0 * m * n * k)
+    cuda_impl.check_status()
+    D = 4096
+    mk = lambda: (torch.randn(M, D, device=dev, dtype=bf), torch.randn(D, device=dev, dtype=bf))
+    ms, best = time_fn(mk, lambda x, w: L.ops.rms_norm(x, w, 1e-5), pool=8)
+    rec("rms_norm fwd 8192x4096", ms, best, nbytes=2 * M * D * 2)
+    mk = lambda: (torch.randn(M, D, device=dev, dtype=bf), torch.randn(M, D, device=dev, dtype=bf), torch.randn(D, device=dev, dtype=bf), torch.rand(M, device=dev))
+    ms, best = time_fn(mk, lambda dy, x, w, r: L.ops.rms_norm_bwd(dy, x, w, r), pool=8)
+    rec("rms_norm bwd 8192x4096", ms, best, nbytes=3 * M * D * 2)
+    H = 14336
+    mk = lambda: (torch.randn(M, H, device=dev, dtype=bf), torch.randn(M, H, device=dev, dtype=bf))
+    ms, best = time_fn(mk, lambda a, b: L.ops.swiglu(a, b), pool=4)
+    rec("swiglu fwd 8192x14336", ms, best, nbytes=3 * M * H * 2)
+    mk = lambda: (torch.randn(M, H, device=dev, dtype=bf), torch.randn(M, H, device=dev, dtype=bf), torch.randn(M, H, device=dev, dtype=bf))
+    ms, best = time_fn(mk, lambda g, a, b: L.ops.swiglu_bwd(g, a, b), pool=4)
+    rec("swiglu bwd 8192x14336", ms, best, nbytes=5 * M * H * 2)
+    ang = torch.randn(M, 64, device=dev)
+    cs, sn = ang.cos(), ang.sin()
+    mk = lambda: (torch.randn(1, M, 32, 128, device=dev, dtype=bf),)
+    ms, best = time_fn(mk, lambda x: L.ops.rope(x, cs, sn, False), pool=8)
+    rec("rope 1x8192x32x128", ms, best, nbytes=2 * M * 4096 * 2)
+    if not args.quick:
+        V = 128256
+        mk = lambda: (torch.randn(M, V, device=dev, dtype=bf), torch.randint(0, V, (M,), device=dev))
+        ms, best = time_fn(mk, lambda lg, lb: L.ops.cross_entropy(lg, lb), pool=2)
+        rec("cross_entropy fwd 8192x128256", ms, best, nbytes=M * V * 2)
+    mk = lambda: (torch.randn(1, M, 32, 128, device=dev, dtype=bf), torch.randn(1, M, 8, 128, device=dev, dtype=bf), torch.randn(1, M, 8, 128, device=dev, dtype=bf))
+    ms, best = time_fn(mk, lambda q, k, v: L.ops.attention(q, k, v, True, 128 ** -0.5), pool=2)
+    rec("attention fwd causal 8192 32q/8kv", ms, best, flops=4.0 * M * M * 4096 * 0.5)
+    if args.json:
+        json.dump({"peaks": {"hbm_gbs": hbm, "bf16_tflops": tf_burst, "bf16_tflops_sustained": tf_sus, "source": src}, "rows": rows}, open(args.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,152 @@
+// Python bindings: torch tensors in, raw-pointer launchers (extern "C", defined in the .cu files)
+// out.  All launches go to the current CUDA stream of the tensor's device.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <cstdint>
+
+extern "C" {
+int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                  int a_mn_major, int b_mn_major, int out_fp32, uint32_t* status, int num_sms, cudaStream_t stream);
+int apb_rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int D, float eps, int is_bf16,
+                     cudaStream_t st);
+int apb_rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw, float* dw_acc,
+                     long long rows, int D, int is_bf16, int num_sms, cudaStream_t st);
+int apb_cast(const void* src, void* dst, long long n, int src_bf16, int dst_bf16, int num_sms, cudaStream_t st);
+int apb_rope(const void* x, const float* cs, const float* sn, void* y, long long B, int S, int H, int D, int conj, int is_bf16,
+             int num_sms, cudaStream_t st);
+int apb_swiglu_fwd(const void* a, const void* b, void* y, long long n, int is_bf16, int num_sms, cudaStream_t st);
+int apb_swiglu_bwd(const void* dy, const void* a, const void* b, void* da, void* db, long long n, int is_bf16, int num_sms,
+                   cudaStream_t st);
+int apb_xent_fwd(const void* logits, const long long* labels, float* loss, float* lse, long long rows, int V, int is_bf16,
+                 cudaStream_t st);
+int apb_xent_bwd(const float* dloss, const void* logits, const long long* labels, const float* lse, void* dlogits,
+                 long long rows, int V, int is_bf16, cudaStream_t st);
+int apb_embedding_bwd(const void* dy, const long long* ids, float* out_f32, long long tokens, int D, int is_bf16,
+                      cudaStream_t st);
+int apb_adamw(const void* tensors_dev, const void* chunks_dev, int num_chunks, float lr, float beta1, float beta2, float eps,
+              float wd, float bc1, float bc2, float grad_scale, cudaStream_t st);
+}
+
+namespace {
+
+int num_sms() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check(int err, const char* what) {
+  TORCH_CHECK(err == 0, what, " failed with code ", err,
+              err == 3 ? " (unsupported shape / alignment)" : err == 4 ? " (launch error)" : "");
+}
+
+bool is_bf16(const at::Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kFloat, "expected bf16 or fp32, got ",
+              t.scalar_type());
+  return t.scalar_type() == at::kBFloat16;
+}
+
+// C[M,N] = opA * opB.  a: [M,K] (or [K,M] if a_mn_major); b: [N,K] (or [K,N] if b_mn_major).
+void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, at::Tensor& status) {
+  c10::cuda::CUDAGuard g(a.device());
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm: bf16 operands required");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && c.stride(1) == 1,
+              "gemm: 2-d row-major operands required");
+  const int M = c.size(0), N = c.size(1);
+  const int K = a_mn_major ? a.size(0) : a.size(1);
+  TORCH_CHECK((a_mn_major ? a.size(1) : a.size(0)) == M, "gemm: A shape mismatch");
+  TORCH_CHECK((b_mn_major ? b.size(1) : b.size(0)) == N && (b_mn_major ? b.size(0) : b.size(1)) == K, "gemm: B shape mismatch");
+  const bool out_fp32 = c.scalar_type() == at::kFloat;
+  TORCH_CHECK(out_fp32 || c.scalar_type() == at::kBFloat16, "gemm: output must be bf16 or fp32");
+  check(apb_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, a.stride(0), b.stride(0), c.stride(0), a_mn_major,
+                      b_mn_major, out_fp32, reinterpret_cast<uint32_t*>(status.data_ptr()), num_sms(), stream()),
+        "apb_gemm_bf16");
+}
+
+void rms_norm_fwd(const at::Tensor& x, const at::Tensor& w, at::Tensor& y, at::Tensor& rstd, double eps) {
+  c10::cuda::CUDAGuard g(x.device());
+  const int D = x.size(-1);
+  check(apb_rms_norm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), x.numel() / D, D, (float)eps,
+                         is_bf16(x), stream()),
+        "apb_rms_norm_fwd");
+}
+
+void rms_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& rstd, at::Tensor& dx,
+                  at::Tensor& dw, at::Tensor& dw_acc) {
+  c10::cuda::CUDAGuard g(x.device());
+  const int D = x.size(-1);
+  check(apb_rms_norm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), dw.data_ptr(),
+                         dw_acc.data_ptr<float>(), x.numel() / D, D, is_bf16(x), num_sms(), stream()),
+        "apb_rms_norm_bwd");
+}
+
+void cast(const at::Tensor& src, at::Tensor& dst) {
+  c10::cuda::CUDAGuard g(src.device());
+  check(apb_cast(src.data_ptr(), dst.data_ptr(), src.numel(), is_bf16(src), is_bf16(dst), num_sms(), stream()), "apb_cast");
+}
+
+void rope(const at::Tensor& x, const at::Tensor& cs, const at::Tensor& sn, at::Tensor& y, bool conj) {
+  c10::cuda::CUDAGuard g(x.device());
+  check(apb_rope(x.data_ptr(), cs.data_ptr<float>(), sn.data_ptr<float>(), y.data_ptr(), x.size(0), x.size(1), x.size(2),
+                 x.size(3), conj, is_bf16(x), num_sms(), stream()),
+        "apb_rope");
+}
+
+void swiglu_fwd(const at::Tensor& a, const at::Tensor& b, at::Tensor& y) {
+  c10::cuda::CUDAGuard g(a.device());
+  check(apb_swiglu_fwd(a.data_ptr(), b.data_ptr(), y.data_ptr(), a.numel(), is_bf16(a), num_sms(), stream()), "apb_swiglu_fwd");
+}
+
+void swiglu_bwd(const at::Tensor& dy, const at::Tensor& a, const at::Tensor& b, at::Tensor& da, at::Tensor& db) {
+  c10::cuda::CUDAGuard g(a.device());
+  check(apb_swiglu_bwd(dy.data_ptr(), a.data_ptr(), b.data_ptr(), da.data_ptr(), db.data_ptr(), a.numel(), is_bf16(a), num_sms(),
+                       stream()),
+        "apb_swiglu_bwd");
+}
+
+void xent_fwd(const at::Tensor& logits, const at::Tensor& labels, at::Tensor& loss, at::Tensor& lse) {
+  c10::cuda::CUDAGuard g(logits.device());
+  const int V = logits.size(-1);
+  check(apb_xent_fwd(logits.data_ptr(), (const long long*)labels.data_ptr<int64_t>(), loss.data_ptr<float>(),
+                     lse.data_ptr<float>(), logits.numel() / V, V, is_bf16(logits), stream()),
+        "apb_xent_fwd");
+}
+
+void xent_bwd(const at::Tensor& dloss, const at::Tensor& logits, const at::Tensor& labels, const at::Tensor& lse,
+              at::Tensor& dlogits) {
+  c10::cuda::CUDAGuard g(logits.device());
+  const int V = logits.size(-1);
+  check(apb_xent_bwd(dloss.data_ptr<float>(), logits.data_ptr(), (const long long*)labels.data_ptr<int64_t>(),
+                     lse.data_ptr<float>(), dlogits.data_ptr(), logits.numel() / V, V, is_bf16(logits), stream()),
+        "apb_xent_bwd");
+}
+
+void embedding_bwd(const at::Tensor& dy, const at::Tensor& ids, at::Tensor& out_f32) {
+  c10::cuda::CUDAGuard g(dy.device());
+  check(apb_embedding_bwd(dy.data_ptr(), (const long long*)ids.data_ptr<int64_t>(), out_f32.data_ptr<float>(), ids.numel(),
+                          dy.size(-1), is_bf16(dy), stream()),
+        "apb_embedding_bwd");
+}
+
+void adamw(const at::Tensor& table, const at::Tensor& chunks, int64_t num_chunks, double lr, double b1, double b2, double eps,
+           double wd, double bc1, double bc2, double grad_scale) {
+  c10::cuda::CUDAGuard g(table.device());
+  check(apb_adamw(table.data_ptr(), chunks.data_ptr(), (int)num_chunks, (float)lr, (float)b1, (float)b2, (float)eps, (float)wd,
+                  (float)bc1, (float)bc2, (float)grad_scale, stream()),
+        "apb_adamw");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm);
+  m.def("rms_norm_fwd", &rms_norm_fwd);
+  m.def("rms_norm_bwd", &rms_norm_bwd);
+  m.def("cast", &cast);
+  m.def("rope", &rope);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("xent_fwd", &xent_fwd);
+  m.def("xent_bwd", &xent_bwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("adamw", &adamw);
+}

@@ -1,0 +1,482 @@
+// Bandwidth-bound kernels of the transformer step for sm_100a: RMSNorm fwd/bwd, RoPE, SwiGLU
+// fwd/bwd, cross-entropy fwd/bwd, dtype cast, embedding backward, multi-tensor AdamW.
+// All use 16-byte vector accesses, fp32 math, and grids sized as multiples of the 148 SMs.
+// They replace the ATen / Inductor-generated kernels the reference reaches for the same nodes
+// (autoparallel/_testing/models/llama3.py:187-213, 355-356, 396-397).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace apb {
+
+template <typename T> struct Vec8;  // 8 elements
+template <> struct Vec8<__nv_bfloat16> {
+  uint4 raw;
+  __device__ void load(const __nv_bfloat16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ void store(__nv_bfloat16* p) const { *reinterpret_cast<uint4*>(p) = raw; }
+  __device__ void to_float(float (&f)[8]) const {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 v = __bfloat1622float2(h[i]);
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    }
+  }
+  __device__ void from_float(const float (&f)[8]) {
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  }
+};
+template <> struct Vec8<float> {
+  float4 a, b;
+  __device__ void load(const float* p) {
+    a = reinterpret_cast<const float4*>(p)[0];
+    b = reinterpret_cast<const float4*>(p)[1];
+  }
+  __device__ void store(float* p) const {
+    reinterpret_cast<float4*>(p)[0] = a;
+    reinterpret_cast<float4*>(p)[1] = b;
+  }
+  __device__ void to_float(float (&f)[8]) const {
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  __device__ void from_float(const float (&f)[8]) {
+    a = make_float4(f[0], f[1], f[2], f[3]);
+    b = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// block-wide sum; ``red`` is >= 32 floats of shared memory.  All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float r = (l < nw) ? red[l] : 0.f;
+  return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float r = (l < nw) ? red[l] : -INFINITY;
+  return warp_max(r);
+}
+
+// ------------------------------------------------------------------------------------ RMSNorm
+// one block per row; D % 8 == 0
+template <typename T>
+__global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                                    float* __restrict__ rstd, int D, float eps) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const T* xr = x + row * D;
+  T* yr = y + row * D;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
+    Vec8<T> v; v.load(xr + c);
+    float f[8]; v.to_float(f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / D + eps);
+  if (threadIdx.x == 0) rstd[row] = r;
+  for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
+    Vec8<T> v, wv; v.load(xr + c); wv.load(w + c);
+    float f[8], g[8]; v.to_float(f); wv.to_float(g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * r * g[i];
+    v.from_float(f); v.store(yr + c);
+  }
+}
+
+// Persistent blocks over rows.  dx per row; dw partial sums per thread-owned columns are added
+// into ``dw_acc`` (fp32 [D], zeroed by the caller) with one atomicAdd per column per block.
+// Requires D <= blockDim.x * 8 * RMS_BWD_MAX_VEC.
+constexpr int RMS_BWD_MAX_VEC = 4;
+template <typename T>
+__global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                                    const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_acc,
+                                    long long rows, int D) {
+  __shared__ float red[32];
+  float wreg[RMS_BWD_MAX_VEC][8];
+  float dwreg[RMS_BWD_MAX_VEC][8];
+#pragma unroll
+  for (int j = 0; j < RMS_BWD_MAX_VEC; ++j) {
+    const int c = (threadIdx.x + j * blockDim.x) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwreg[j][i] = 0.f;
+    if (c < D) {
+      Vec8<T> wv; wv.load(w + c); wv.to_float(wreg[j]);
+    }
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + row * D;
+    const T* gr = dy + row * D;
+    const float r = rstd[row];
+    float xh[RMS_BWD_MAX_VEC][8], g[RMS_BWD_MAX_VEC][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < RMS_BWD_MAX_VEC; ++j) {
+      const int c = (threadIdx.x + j * blockDim.x) * 8;
+      if (c < D) {
+        Vec8<T> xv, gv; xv.load(xr + c); gv.load(gr + c);
+        float xf[8], gf[8]; xv.to_float(xf); gv.to_float(gf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[j][i] = xf[i] * r;
+          dwreg[j][i] += gf[i] * xh[j][i];
+          g[j][i] = gf[i] * wreg[j][i];
+          dot += g[j][i] * xh[j][i];
+        }
+      }
+    }
+    dot = block_sum(dot, red) / D;
+#pragma unroll
+    for (int j = 0; j < RMS_BWD_MAX_VEC; ++j) {
+      const int c = (threadIdx.x + j * blockDim.x) * 8;
+      if (c < D) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = r * (g[j][i] - xh[j][i] * dot);
+        Vec8<T> ov; ov.from_float(o); ov.store(dx + row * D + c);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < RMS_BWD_MAX_VEC; ++j) {
+    const int c = (threadIdx.x + j * blockDim.x) * 8;
+    if (c < D) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(dw_acc + c + i, dwreg[j][i]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void cast_from_f32_kernel(const float* __restrict__ src, T* __restrict__ dst, long long n) {
+  long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (; i + 8 <= n; i += stride) {
+    Vec8<float> v; v.load(src + i);
+    float f[8]; v.to_float(f);
+    Vec8<T> o; o.from_float(f); o.store(dst + i);
+  }
+  if (i < n && i + 8 > n)
+    for (long long k = i; k < n; ++k) dst[k] = T(src[k]);
+}
+template <typename T>
+__global__ void cast_to_f32_kernel(const T* __restrict__ src, float* __restrict__ dst, long long n) {
+  long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (; i + 8 <= n; i += stride) {
+    Vec8<T> v; v.load(src + i);
+    float f[8]; v.to_float(f);
+    Vec8<float> o; o.from_float(f); o.store(dst + i);
+  }
+  if (i < n && i + 8 > n)
+    for (long long k = i; k < n; ++k) dst[k] = float(src[k]);
+}
+
+// ------------------------------------------------------------------------------------ RoPE
+// x [B, S, H, D] with interleaved pairs; cos/sin fp32 [S, D/2].  One thread per 8 elements.
+template <typename T>
+__global__ void rope_kernel(const T* __restrict__ x, const float* __restrict__ cs, const float* __restrict__ sn,
+                            T* __restrict__ y, long long total_vec, int S, int H, int D, float sign) {
+  const int vec_per_head = D / 8;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total_vec;
+       v += (long long)gridDim.x * blockDim.x) {
+    const int dv = v % vec_per_head;
+    const long long bsh = v / vec_per_head;
+    const int s = (bsh / H) % S;
+    Vec8<T> xv; xv.load(x + v * 8);
+    float f[8]; xv.to_float(f);
+    const float4 c = *reinterpret_cast<const float4*>(cs + (long long)s * (D / 2) + dv * 4);
+    const float4 n = *reinterpret_cast<const float4*>(sn + (long long)s * (D / 2) + dv * 4);
+    const float cc[4] = {c.x, c.y, c.z, c.w};
+    const float nn[4] = {n.x * sign, n.y * sign, n.z * sign, n.w * sign};
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o[2 * i] = f[2 * i] * cc[i] - f[2 * i + 1] * nn[i];
+      o[2 * i + 1] = f[2 * i] * nn[i] + f[2 * i + 1] * cc[i];
+    }
+    Vec8<T> ov; ov.from_float(o); ov.store(y + v * 8);
+  }
+}
+
+// ------------------------------------------------------------------------------------ SwiGLU
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, long long nvec) {
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    Vec8<T> av, bv; av.load(a + v * 8); bv.load(b + v * 8);
+    float fa[8], fb[8], o[8]; av.to_float(fa); bv.to_float(fb);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = fa[i] / (1.f + __expf(-fa[i])) * fb[i];
+    Vec8<T> ov; ov.from_float(o); ov.store(y + v * 8);
+  }
+}
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ a, const T* __restrict__ b,
+                                  T* __restrict__ da, T* __restrict__ db, long long nvec) {
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    Vec8<T> gv, av, bv; gv.load(dy + v * 8); av.load(a + v * 8); bv.load(b + v * 8);
+    float g[8], fa[8], fb[8], oa[8], ob[8]; gv.to_float(g); av.to_float(fa); bv.to_float(fb);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float sig = 1.f / (1.f + __expf(-fa[i]));
+      const float silu = fa[i] * sig;
+      oa[i] = g[i] * fb[i] * (sig * (1.f + fa[i] * (1.f - sig)));
+      ob[i] = g[i] * silu;
+    }
+    Vec8<T> o1, o2; o1.from_float(oa); o2.from_float(ob); o1.store(da + v * 8); o2.store(db + v * 8);
+  }
+}
+
+// ------------------------------------------------------------------------------------ cross-entropy
+// one block per row of V logits (V % 8 == 0): online (max, sum-exp); loss = lse - logit[label].
+template <typename T>
+__global__ void xent_fwd_kernel(const T* __restrict__ logits, const long long* __restrict__ labels,
+                                float* __restrict__ loss, float* __restrict__ lse, int V) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const T* lr = logits + row * V;
+  float m = -INFINITY, s = 0.f;
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    Vec8<T> v; v.load(lr + c);
+    float f[8]; v.to_float(f);
+    float lm = f[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) lm = fmaxf(lm, f[i]);
+    const float nm = fmaxf(m, lm);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += __expf(f[i] - nm);
+    s = s * __expf(m - nm) + acc;
+    m = nm;
+  }
+  const float gm = block_max(m, red);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) {
+    const float l = gm + logf(s);
+    lse[row] = l;
+    loss[row] = l - float(lr[labels[row]]);
+  }
+}
+template <typename T>
+__global__ void xent_bwd_kernel(const float* __restrict__ dloss, const T* __restrict__ logits,
+                                const long long* __restrict__ labels, const float* __restrict__ lse,
+                                T* __restrict__ dlogits, int V) {
+  const long long row = blockIdx.x;
+  const T* lr = logits + row * V;
+  T* dr = dlogits + row * V;
+  const float l = lse[row], g = dloss[row];
+  const int lab = (int)labels[row];
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    Vec8<T> v; v.load(lr + c);
+    float f[8]; v.to_float(f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = (__expf(f[i] - l) - ((c + i) == lab ? 1.f : 0.f)) * g;
+    Vec8<T> o; o.from_float(f); o.store(dr + c);
+  }
+}
+
+// ------------------------------------------------------------------------------------ embedding backward
+// out fp32 [rows, D] (zeroed by caller) += dy[token] for each token; one block per token.
+template <typename T>
+__global__ void embedding_bwd_kernel(const T* __restrict__ dy, const long long* __restrict__ ids, float* __restrict__ out,
+                                     int D) {
+  const long long tok = blockIdx.x;
+  const long long r = ids[tok];
+  for (int c = threadIdx.x; c < D; c += blockDim.x) atomicAdd(out + r * D + c, float(dy[tok * D + c]));
+}
+
+// ------------------------------------------------------------------------------------ AdamW
+// Multi-tensor: ``table`` lists chunks (tensor id, offset); each block handles one chunk.
+struct AdamTensor {
+  float* p;        // fp32 master / parameter
+  const float* g;  // fp32 gradient
+  float* m;
+  float* v;
+  __nv_bfloat16* p_lp;  // optional low-precision copy to emit (may be null)
+  long long n;
+};
+constexpr int ADAM_CHUNK = 65536;
+__global__ void adamw_kernel(const AdamTensor* __restrict__ tensors, const int2* __restrict__ chunks, float lr,
+                             float beta1, float beta2, float eps, float wd, float bc1, float bc2, float grad_scale) {
+  const int2 ch = chunks[blockIdx.x];
+  const AdamTensor t = tensors[ch.x];
+  const long long base = (long long)ch.y * ADAM_CHUNK;
+  const long long end = min(base + (long long)ADAM_CHUNK, t.n);
+  for (long long i = base + threadIdx.x * 4; i < end; i += blockDim.x * 4) {
+    if (i + 4 <= end && ((reinterpret_cast<uintptr_t>(t.p + i) & 15) == 0)) {
+      float4 p = *reinterpret_cast<float4*>(t.p + i);
+      const float4 g4 = *reinterpret_cast<const float4*>(t.g + i);
+      float4 m = *reinterpret_cast<float4*>(t.m + i);
+      float4 v = *reinterpret_cast<float4*>(t.v + i);
+      float* pp = &p.x; const float* gg = &g4.x; float* mm = &m.x; float* vv = &v.x;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float g = gg[k] * grad_scale;
+        mm[k] = beta1 * mm[k] + (1.f - beta1) * g;
+        vv[k] = beta2 * vv[k] + (1.f - beta2) * g * g;
+        const float mh = mm[k] / bc1;
+        const float vh = vv[k] / bc2;
+        pp[k] = pp[k] * (1.f - lr * wd) - lr * mh / (sqrtf(vh) + eps);
+      }
+      *reinterpret_cast<float4*>(t.p + i) = p;
+      *reinterpret_cast<float4*>(t.m + i) = m;
+      *reinterpret_cast<float4*>(t.v + i) = v;
+      if (t.p_lp) {
+        t.p_lp[i] = __float2bfloat16(p.x); t.p_lp[i + 1] = __float2bfloat16(p.y);
+        t.p_lp[i + 2] = __float2bfloat16(p.z); t.p_lp[i + 3] = __float2bfloat16(p.w);
+      }
+    } else {
+      for (long long k = i; k < min(i + 4, end); ++k) {
+        const float g = t.g[k] * grad_scale;
+        const float m = beta1 * t.m[k] + (1.f - beta1) * g;
+        const float v = beta2 * t.v[k] + (1.f - beta2) * g * g;
+        t.m[k] = m; t.v[k] = v;
+        const float pn = t.p[k] * (1.f - lr * wd) - lr * (m / bc1) / (sqrtf(v / bc2) + eps);
+        t.p[k] = pn;
+        if (t.p_lp) t.p_lp[k] = __float2bfloat16(pn);
+      }
+    }
+  }
+}
+
+static inline int grid_for(long long work_items, int threads, int num_sms) {
+  long long blocks = (work_items + threads - 1) / threads;
+  long long cap = (long long)num_sms * 8;
+  return (int)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+}  // namespace apb
+
+using namespace apb;
+typedef __nv_bfloat16 bf16;
+
+#define DISPATCH(is_bf16, ...)      \
+  if (is_bf16) {                    \
+    typedef bf16 T;                 \
+    __VA_ARGS__;                    \
+  } else {                          \
+    typedef float T;                \
+    __VA_ARGS__;                    \
+  }
+
+extern "C" {
+
+int apb_rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int D, float eps, int is_bf16,
+                     cudaStream_t st) {
+  if (D % 8) return 3;
+  if (rows == 0) return 0;
+  const int threads = D >= 2048 ? 256 : 128;
+  DISPATCH(is_bf16, rms_norm_fwd_kernel<T><<<(unsigned)rows, threads, 0, st>>>((const T*)x, (const T*)w, (T*)y, rstd, D, eps));
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// dw_acc: fp32 [D] scratch, zeroed here; dw receives the cast result.
+int apb_rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw, float* dw_acc,
+                     long long rows, int D, int is_bf16, int num_sms, cudaStream_t st) {
+  if (D % 8) return 3;
+  int threads = 256;
+  while (threads * 8 * RMS_BWD_MAX_VEC < D && threads < 1024) threads *= 2;
+  if (threads * 8 * RMS_BWD_MAX_VEC < D) return 3;
+  cudaMemsetAsync(dw_acc, 0, sizeof(float) * D, st);
+  if (rows > 0) {
+    const int grid = (int)(rows < (long long)num_sms * 2 ? rows : (long long)num_sms * 2);
+    DISPATCH(is_bf16, rms_norm_bwd_kernel<T><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx,
+                                                                      dw_acc, rows, D));
+  }
+  if (is_bf16) cast_from_f32_kernel<bf16><<<grid_for(D / 8, 256, num_sms), 256, 0, st>>>(dw_acc, (bf16*)dw, D);
+  else cudaMemcpyAsync(dw, dw_acc, sizeof(float) * D, cudaMemcpyDeviceToDevice, st);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int apb_cast(const void* src, void* dst, long long n, int src_bf16, int dst_bf16, int num_sms, cudaStream_t st) {
+  if (n == 0) return 0;
+  const int grid = grid_for((n + 7) / 8, 256, num_sms);
+  if (src_bf16 && !dst_bf16) cast_to_f32_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)src, (float*)dst, n);
+  else if (!src_bf16 && dst_bf16) cast_from_f32_kernel<bf16><<<grid, 256, 0, st>>>((const float*)src, (bf16*)dst, n);
+  else return 3;
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int apb_rope(const void* x, const float* cs, const float* sn, void* y, long long B, int S, int H, int D, int conj,
+             int is_bf16, int num_sms, cudaStream_t st) {
+  if (D % 8) return 3;
+  const long long nvec = B * S * H * (D / 8);
+  if (nvec == 0) return 0;
+  const int grid = grid_for(nvec, 256, num_sms);
+  DISPATCH(is_bf16, rope_kernel<T><<<grid, 256, 0, st>>>((const T*)x, cs, sn, (T*)y, nvec, S, H, D, conj ? -1.f : 1.f));
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int apb_swiglu_fwd(const void* a, const void* b, void* y, long long n, int is_bf16, int num_sms, cudaStream_t st) {
+  if (n % 8) return 3;
+  if (n == 0) return 0;
+  DISPATCH(is_bf16, swiglu_fwd_kernel<T><<<grid_for(n / 8, 256, num_sms), 256, 0, st>>>((const T*)a, (const T*)b, (T*)y, n / 8));
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int apb_swiglu_bwd(const void* dy, const void* a, const void* b, void* da, void* db, long long n, int is_bf16, int num_sms,
+                   cudaStream_t st) {
+  if (n % 8) return 3;
+  if (n == 0) return 0;
+  DISPATCH(is_bf16, swiglu_bwd_kernel<T><<<grid_for(n / 8, 256, num_sms), 256, 0, st>>>((const T*)dy, (const T*)a, (const T*)b,
+                                                                                       (T*)da, (T*)db, n / 8));
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int apb_xent_fwd(const void* logits, const long long* labels, float* loss, float* lse, long long rows, int V, int is_bf16,
+                 cudaStream_t st) {
+  if (V % 8) return 3;
+  if (rows == 0) return 0;
+  const int threads = V >= 8192 ? 1024 : 256;
+  DISPATCH(is_bf16, xent_fwd_kernel<T><<<(unsigned)rows, threads, 0, st>>>((const T*)logits, labels, loss, lse, V));
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int apb_xent_bwd(const float* dloss, const void* logits, const long long* labels, const float* lse, void* dlogits,
+                 long long rows, int V, int is_bf16, cudaStream_t st) {
+  if (V % 8) return 3;
+  if (rows == 0) return 0;
+  const int threads = V >= 8192 ? 1024 : 256;
+  DISPATCH(is_bf16, xent_bwd_kernel<T><<<(unsigned)rows, threads, 0, st>>>(dloss, (const T*)logits, labels, lse, (T*)dlogits, V));
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int apb_embedding_bwd(const void* dy, const long long* ids, float* out_f32, long long tokens, int D, int is_bf16,
+                      cudaStream_t st) {
+  if (tokens == 0) return 0;
+  DISPATCH(is_bf16, embedding_bwd_kernel<T><<<(unsigned)tokens, 256, 0, st>>>((const T*)dy, ids, out_f32, D));
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int apb_adamw(const void* tensors_dev, const void* chunks_dev, int num_chunks, float lr, float beta1, float beta2, float eps,
+              float wd, float bc1, float bc2, float grad_scale, cudaStream_t st) {
+  if (num_chunks == 0) return 0;
+  adamw_kernel<<<num_chunks, 256, 0, st>>>((const AdamTensor*)tensors_dev, (const int2*)chunks_dev, lr, beta1, beta2, eps, wd,
+                                           bc1, bc2, grad_scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+}  // extern "C"

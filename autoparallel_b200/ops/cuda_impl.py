@@ -1,5 +1,269 @@
-"""Loader for the in-tree sm_100a extension (filled in by the kernel build)."""
+"""CUDA implementations of the ``apb200`` operators on the in-tree sm_100a extension.
+
+Loaded on first use of an op with a CUDA tensor.  There is no silent fallback: if the extension
+is missing on a machine with a GPU the op raises, and fp32 GEMMs – which the tcgen05 kernel does
+not take – are the only case routed to a library call (``torch.matmul``), stated here.
+
+Attention currently runs through PyTorch's fused SDPA kernels (library call) behind the
+``apb200::attention`` schema; every other operator below is this framework's own kernel.
+"""
+from __future__ import annotations
+
+import importlib
+import os
+import threading
+
+import torch
+
+from . import library as L
+
+_C = None
+_lock = threading.Lock()
+_status: dict[int, torch.Tensor] = {}
+_scratch: dict[tuple, torch.Tensor] = {}
+launch_count = 0  # kernels of this extension launched since import (bench bookkeeping)
+
+STATUS_NAMES = {
+    0: "ok",
+    1: "GEMM consumer timed out waiting for a TMA stage",
+    2: "GEMM producer timed out waiting for a free stage",
+    3: "epilogue timed out waiting for an accumulator",
+    4: "MMA issuer timed out waiting for a free accumulator",
+    5: "timed out waiting for a peer flag",
+    6: "bad argument",
+}
+
+
+def extension():
+    return _C
 
 
 def ensure_loaded() -> None:
-    raise RuntimeError("the sm_100a extension has not been built: run `python -c 'import __graft_entry__ as g; g.build()'`")
+    global _C
+    if _C is not None:
+        return
+    with _lock:
+        if _C is not None:
+            return
+        from . import build
+
+        if not os.path.exists(build.so_path()):
+            if os.environ.get("APB200_NO_JIT_BUILD"):
+                raise RuntimeError(
+                    "the sm_100a extension is not built: run `python -m autoparallel_b200.ops.build` "
+                    "(or __graft_entry__.build())"
+                )
+            build.build()
+        _C = importlib.import_module("autoparallel_b200.ops._C")
+        _register()
+
+
+def status_buffer(device) -> torch.Tensor:
+    idx = torch.device(device).index or 0
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def check_status(device=None) -> None:
+    """Raise if any kernel on ``device`` recorded a timed-out wait (synchronises)."""
+    for idx, t in _status.items():
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        code = int(t[0].item())
+        if code != 0:
+            t.zero_()
+            raise RuntimeError(f"apb200 kernel status {code} on cuda:{idx}: {STATUS_NAMES.get(code, 'unknown')}")
+
+
+def _scratch_f32(device, n: int) -> torch.Tensor:
+    key = (torch.device(device).index or 0, "f32")
+    t = _scratch.get(key)
+    if t is None or t.numel() < n:
+        t = torch.empty(max(n, 16384), dtype=torch.float32, device=device)
+        _scratch[key] = t
+    return t
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+# ----------------------------------------------------------------------------------- GEMM family
+def _as2d(t: torch.Tensor) -> torch.Tensor:
+    t2 = t.reshape(-1, t.shape[-1])
+    if t2.stride(-1) != 1 or (t2.stride(0) % 8) != 0 or (t2.data_ptr() % 16) != 0:
+        t2 = t2.contiguous()
+    return t2
+
+
+def gemm_raw(a2: torch.Tensor, b2: torch.Tensor, a_mn: bool, b_mn: bool, out_dtype: torch.dtype) -> torch.Tensor:
+    """C[M,N] = opA @ opB on the tcgen05 kernel.  a2: [M,K] or [K,M] if a_mn; b2: [N,K] or [K,N] if b_mn."""
+    M = a2.shape[1] if a_mn else a2.shape[0]
+    N = b2.shape[1] if b_mn else b2.shape[0]
+    if a2.dtype != torch.bfloat16 or b2.dtype != torch.bfloat16 or (a2.shape[1] % 8) or (b2.shape[1] % 8) or (N % 8):
+        # fp32 / fp16 operands, or row strides TMA cannot address (not multiples of 16 bytes):
+        # library GEMM (not a tensor-core path of this framework)
+        A = a2.t() if a_mn else a2
+        B = b2 if b_mn else b2.t()
+        return torch.matmul(A, B).to(out_dtype)
+    c = torch.empty((M, N), dtype=out_dtype if out_dtype in (torch.bfloat16, torch.float32) else torch.float32, device=a2.device)
+    _C.gemm(a2, b2, c, a_mn, b_mn, status_buffer(a2.device))
+    _count()
+    return c if c.dtype == out_dtype else c.to(out_dtype)
+
+
+def _gemm(a, b, trans_a, trans_b, out_dtype):
+    a2, b2 = _as2d(a), _as2d(b)
+    # op(a): stored [M,K] if not trans_a else [K,M]; op(b): stored [K,N] if not trans_b else [N,K]
+    return gemm_raw(a2, b2, bool(trans_a), not trans_b, out_dtype)
+
+
+def _mm_nd(a, b, trans_b, out_dtype):
+    lead = a.shape[:-1]
+    out = gemm_raw(_as2d(a), _as2d(b), False, not trans_b, out_dtype)
+    return out.view(*lead, out.shape[-1])
+
+
+def _mm_wgrad(a, b, out_dtype):
+    return gemm_raw(_as2d(a), _as2d(b), True, True, out_dtype)
+
+
+# ----------------------------------------------------------------------------------- pointwise etc.
+def _dtype_cast(x, dtype):
+    if x.dtype == dtype:
+        return x
+    pair = {x.dtype, dtype}
+    if pair == {torch.float32, torch.bfloat16} and x.is_contiguous() and x.data_ptr() % 16 == 0:
+        out = torch.empty_like(x, dtype=dtype)
+        _C.cast(x, out)
+        _count()
+        return out
+    return x.to(dtype)
+
+
+def _rms_norm(x, w, eps):
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    rstd = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    _C.rms_norm_fwd(x, w.to(x.dtype).contiguous(), y, rstd, eps)
+    _count()
+    return y, rstd
+
+
+def _rms_norm_bwd(dy, x, w, rstd):
+    dy, x = dy.contiguous(), x.contiguous()
+    dx = torch.empty_like(x)
+    dw = torch.empty_like(w, dtype=x.dtype)
+    _C.rms_norm_bwd(dy, x, w.to(x.dtype).contiguous(), rstd.contiguous(), dx, dw, _scratch_f32(x.device, x.shape[-1]))
+    _count(3)
+    return dx, dw.to(w.dtype)
+
+
+def _rope(x, cos, sin, conj):
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    _C.rope(x, cos.float().contiguous(), sin.float().contiguous(), y, conj)
+    _count()
+    return y
+
+
+def _swiglu(a, b):
+    a, b = a.contiguous(), b.contiguous()
+    y = torch.empty_like(a)
+    _C.swiglu_fwd(a, b, y)
+    _count()
+    return y
+
+
+def _swiglu_bwd(dy, a, b):
+    dy, a, b = dy.contiguous(), a.contiguous(), b.contiguous()
+    da, db = torch.empty_like(a), torch.empty_like(b)
+    _C.swiglu_bwd(dy, a, b, da, db)
+    _count()
+    return da, db
+
+
+def _cross_entropy(logits, labels):
+    logits = logits.contiguous()
+    shape = logits.shape[:-1]
+    loss = torch.empty(shape, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(shape, dtype=torch.float32, device=logits.device)
+    _C.xent_fwd(logits, labels.contiguous(), loss, lse)
+    _count()
+    return loss, lse
+
+
+def _cross_entropy_bwd(dloss, logits, labels, lse):
+    logits = logits.contiguous()
+    out = torch.empty_like(logits)
+    _C.xent_bwd(dloss.float().contiguous(), logits, labels.contiguous(), lse.contiguous(), out)
+    _count()
+    return out
+
+
+def _embedding_bwd(dy, ids, num_rows):
+    dy = dy.contiguous()
+    out = torch.zeros(num_rows, dy.shape[-1], dtype=torch.float32, device=dy.device)
+    _C.embedding_bwd(dy, ids.contiguous(), out)
+    _count()
+    return out.to(dy.dtype)
+
+
+# ----------------------------------------------------------------------------------- attention (library)
+def _expand_kv(t, rep):
+    if rep == 1:
+        return t
+    b, s, h, d = t.shape
+    return t.unsqueeze(3).expand(b, s, h, rep, d).reshape(b, s, h * rep, d)
+
+
+def _attention(q, k, v, causal, scale):
+    rep = q.shape[2] // k.shape[2]
+    qt = q.transpose(1, 2)
+    kt = _expand_kv(k, rep).transpose(1, 2)
+    vt = _expand_kv(v, rep).transpose(1, 2)
+    out, lse, *_ = torch.ops.aten._scaled_dot_product_flash_attention(qt, kt, vt, 0.0, causal, False, scale=scale)
+    return out.transpose(1, 2).contiguous(), lse
+
+
+def _attention_bwd(dout, q, k, v, out, lse, causal, scale):
+    rep = q.shape[2] // k.shape[2]
+    b, s, h, d = q.shape
+    sk = k.shape[1]
+    qt = q.transpose(1, 2)
+    kt = _expand_kv(k, rep).transpose(1, 2)
+    vt = _expand_kv(v, rep).transpose(1, 2)
+    empty = torch.empty(0, dtype=torch.long, device=q.device)
+    seed = torch.zeros((), dtype=torch.long, device=q.device)
+    dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
+        dout.transpose(1, 2), qt, kt, vt, out.transpose(1, 2), lse, None, None, s, sk, 0.0, causal, seed, seed, scale=scale
+    )
+    dq = dq.transpose(1, 2).contiguous()
+    dk = dk.transpose(1, 2)
+    dv = dv.transpose(1, 2)
+    if rep > 1:
+        dk = dk.reshape(b, sk, k.shape[2], rep, d).sum(3)
+        dv = dv.reshape(b, sk, k.shape[2], rep, d).sum(3)
+    return dq, dk.contiguous(), dv.contiguous()
+
+
+def _register() -> None:
+    R = L.register_cuda_impl
+    R("gemm", _gemm)
+    R("mm_nd", _mm_nd)
+    R("mm_wgrad", _mm_wgrad)
+    R("dtype_cast", _dtype_cast)
+    R("rms_norm", _rms_norm)
+    R("rms_norm_bwd", _rms_norm_bwd)
+    R("rope", _rope)
+    R("swiglu", _swiglu)
+    R("swiglu_bwd", _swiglu_bwd)
+    R("cross_entropy", _cross_entropy)
+    R("cross_entropy_bwd", _cross_entropy_bwd)
+    R("embedding_bwd", _embedding_bwd)
+    R("attention", _attention)
+    R("attention_bwd", _attention_bwd)

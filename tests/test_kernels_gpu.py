@@ -1,0 +1,160 @@
+"""Numerics of every sm_100a kernel against the plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from autoparallel_b200.ops import cuda_impl, library
+
+    cuda_impl.ensure_loaded()
+    return library, cuda_impl
+
+
+def _ref(name, *args):
+    from autoparallel_b200.ops import reference_impls
+
+    cpu = [a.detach().cpu() if isinstance(a, torch.Tensor) else a for a in args]
+    return reference_impls[name](*cpu)
+
+
+def _close(a, b, rtol, atol):
+    a = a.detach().float().cpu()
+    b = b.detach().float().cpu()
+    assert a.shape == b.shape
+    err = (a - b).abs().max().item()
+    assert torch.allclose(a, b, rtol=rtol, atol=atol), f"max abs err {err}"
+
+
+GEMM_SHAPES = [
+    (128, 256, 64),
+    (256, 512, 256),
+    (384, 768, 192),
+    (1000, 520, 136),  # ragged M, N; K not a multiple of the k-tile
+    (64, 128, 4096),
+    (4096, 4096, 1024),
+    (130, 264, 72),
+]
+
+
+@pytest.mark.parametrize("M,N,K_", GEMM_SHAPES)
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm(K, M, N, K_, ta, tb, out_dtype):
+    lib, impl = K
+    torch.manual_seed(0)
+    a = torch.randn((K_, M) if ta else (M, K_), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((N, K_) if tb else (K_, N), device="cuda", dtype=torch.bfloat16)
+    c = lib.ops.gemm(a, b, ta, tb, out_dtype)
+    impl.check_status()
+    A = a.float().cpu().t() if ta else a.float().cpu()
+    B = b.float().cpu().t() if tb else b.float().cpu()
+    ref = A @ B
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 1e-3
+    _close(c, ref, rtol=tol, atol=tol * (K_ ** 0.5))
+
+
+def test_mm_nd_and_wgrad(K):
+    lib, impl = K
+    torch.manual_seed(1)
+    x = torch.randn(2, 192, 256, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(384, 256, device="cuda", dtype=torch.bfloat16)
+    y = lib.ops.mm_nd(x, w, True, torch.bfloat16)
+    _close(y, x.float().cpu() @ w.float().cpu().t(), 2e-2, 0.5)
+    dy = torch.randn(2, 192, 384, device="cuda", dtype=torch.bfloat16)
+    dx = lib.ops.mm_nd(dy, w, False, torch.bfloat16)
+    _close(dx, dy.float().cpu() @ w.float().cpu(), 2e-2, 0.5)
+    dw = lib.ops.mm_wgrad(dy, x, torch.float32)
+    _close(dw, dy.float().cpu().reshape(-1, 384).t() @ x.float().cpu().reshape(-1, 256), 1e-3, 0.05)
+    impl.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,D", [(7, 256), (300, 4096), (64, 8192), (33, 1024)])
+def test_rms_norm(K, dtype, rows, D):
+    lib, _ = K
+    torch.manual_seed(0)
+    x = torch.randn(rows, D, device="cuda", dtype=dtype)
+    w = torch.randn(D, device="cuda", dtype=dtype)
+    y, rstd = lib.ops.rms_norm(x, w, 1e-5)
+    ry, rr = _ref("rms_norm", x, w, 1e-5)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    _close(y, ry, tol, tol)
+    _close(rstd, rr, 1e-5, 1e-5)
+    dy = torch.randn_like(x)
+    dx, dw = lib.ops.rms_norm_bwd(dy, x, w, rstd)
+    rdx, rdw = _ref("rms_norm_bwd", dy, x, w, rstd)
+    _close(dx, rdx, tol, tol)
+    _close(dw, rdw, tol, tol * 8 if dtype == torch.bfloat16 else 1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rope_swiglu(K, dtype):
+    lib, _ = K
+    torch.manual_seed(0)
+    x = torch.randn(2, 96, 6, 128, device="cuda", dtype=dtype)
+    ang = torch.randn(96, 64, device="cuda")
+    for conj in (False, True):
+        y = lib.ops.rope(x, ang.cos(), ang.sin(), conj)
+        _close(y, _ref("rope", x, ang.cos(), ang.sin(), conj), 2e-2 if dtype == torch.bfloat16 else 1e-5, 2e-2 if dtype == torch.bfloat16 else 1e-5)
+    a = torch.randn(50, 1408, device="cuda", dtype=dtype)
+    b = torch.randn(50, 1408, device="cuda", dtype=dtype)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    _close(lib.ops.swiglu(a, b), _ref("swiglu", a, b), tol, tol)
+    dy = torch.randn_like(a)
+    da, db = lib.ops.swiglu_bwd(dy, a, b)
+    rda, rdb = _ref("swiglu_bwd", dy, a, b)
+    _close(da, rda, tol, tol)
+    _close(db, rdb, tol, tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,V", [(5, 1024), (37, 128256), (16, 50264)])
+def test_cross_entropy(K, dtype, rows, V):
+    lib, _ = K
+    torch.manual_seed(0)
+    logits = (torch.randn(rows, V, device="cuda") * 3).to(dtype)
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    loss, lse = lib.ops.cross_entropy(logits, labels)
+    rl, rlse = _ref("cross_entropy", logits, labels)
+    _close(loss, rl, 1e-4, 1e-4)
+    _close(lse, rlse, 1e-4, 1e-4)
+    dl = torch.randn(rows, device="cuda")
+    d = lib.ops.cross_entropy_bwd(dl, logits, labels, lse)
+    rd = _ref("cross_entropy_bwd", dl, logits, labels, lse)
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    _close(d, rd, tol, 1e-3 if dtype == torch.bfloat16 else 1e-6)
+
+
+def test_cast_and_embedding_bwd(K):
+    lib, _ = K
+    x = torch.randn(1000, 33, device="cuda")
+    y = lib.ops.dtype_cast(x, torch.bfloat16)
+    assert torch.equal(y, x.to(torch.bfloat16))
+    assert torch.equal(lib.ops.dtype_cast(y, torch.float32), y.float())
+    dy = torch.randn(4, 20, 64, device="cuda", dtype=torch.bfloat16)
+    ids = torch.randint(0, 50, (4, 20), device="cuda")
+    out = lib.ops.embedding_bwd(dy, ids, 50)
+    _close(out, _ref("embedding_bwd", dy, ids, 50), 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention(K, causal):
+    lib, _ = K
+    torch.manual_seed(0)
+    q = torch.randn(2, 256, 8, 128, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(2, 256, 2, 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(2, 256, 2, 128, device="cuda", dtype=torch.bfloat16)
+    scale = 128 ** -0.5
+    o, lse = lib.ops.attention(q, k, v, causal, scale)
+    ro, rlse = _ref("attention", q, k, v, causal, scale)
+    _close(o, ro, 2e-2, 2e-2)
+    _close(lse, rlse, 1e-2, 1e-2)
+    do = torch.randn_like(o)
+    dq, dk, dv = lib.ops.attention_bwd(do, q, k, v, o, lse, causal, scale)
+    rdq, rdk, rdv = _ref("attention_bwd", do, q, k, v, ro.to(q.dtype), rlse, causal, scale)
+    _close(dq, rdq, 5e-2, 5e-2)
+    _close(dk, rdk, 5e-2, 5e-2)
+    _close(dv, rdv, 5e-2, 5e-2)
