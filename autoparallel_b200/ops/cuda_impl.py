@@ -109,6 +109,8 @@ def gemm_raw(a2: torch.Tensor, b2: torch.Tensor, a_mn: bool, b_mn: bool, out_dty
         # library GEMM (not a tensor-core path of this framework)
         A = a2.t() if a_mn else a2
         B = b2 if b_mn else b2.t()
+        if out_dtype == torch.float32 and A.dtype != torch.float32:
+            return torch.matmul(A.float(), B.float())
         return torch.matmul(A, B).to(out_dtype)
     c = torch.empty((M, N), dtype=out_dtype if out_dtype in (torch.bfloat16, torch.float32) else torch.float32, device=a2.device)
     _C.gemm(a2, b2, c, a_mn, b_mn, status_buffer(a2.device))
