@@ -210,6 +210,12 @@ class AutoParallel:
         sol = sharding_placement if sharding_placement is not None else self.sharding_placement
         t0 = time.perf_counter()
         lowered = lower_to_local_graph(self.joint, sol, self.mesh)
+        from .parallel.passes.peephole import fuse_cast_into_gemm
+
+        if fuse_cast_into_gemm(lowered.gm):
+            from .parallel.frontend.trace import index_joint_graph
+
+            lowered.joint = index_joint_graph(lowered.gm, self.joint.traced_inputs, self.joint.out_spec)
         mark_fsdp_recompute(lowered.joint, self.reshard_after_forward)
         if self.activation_checkpointing != "none":
             apply_activation_checkpointing(lowered.joint, self.activation_checkpointing)

@@ -216,6 +216,10 @@ def _embedding_bwd(dy, ids, num_rows):
 
 
 # ----------------------------------------------------------------------------------- attention (library)
+ATTENTION_BACKEND = os.environ.get("APB200_ATTENTION", "cudnn")  # "cudnn" | "flash"
+_cudnn_lse_ndim = [3]
+
+
 def _expand_kv(t, rep):
     if rep == 1:
         return t
@@ -225,25 +229,40 @@ def _expand_kv(t, rep):
 
 def _attention(q, k, v, causal, scale):
     rep = q.shape[2] // k.shape[2]
+    if ATTENTION_BACKEND == "cudnn":
+        rep = 1  # cuDNN takes grouped-query heads natively
     qt = q.transpose(1, 2)
     kt = _expand_kv(k, rep).transpose(1, 2)
     vt = _expand_kv(v, rep).transpose(1, 2)
-    out, lse, *_ = torch.ops.aten._scaled_dot_product_flash_attention(qt, kt, vt, 0.0, causal, False, scale=scale)
+    if ATTENTION_BACKEND == "cudnn":
+        out, lse, *_ = torch.ops.aten._scaled_dot_product_cudnn_attention(qt, kt, vt, None, True, 0.0, causal, False, scale=scale)
+        _cudnn_lse_ndim[0] = lse.ndim
+        lse = lse.reshape(q.shape[0], q.shape[2], q.shape[1])
+    else:
+        out, lse, *_ = torch.ops.aten._scaled_dot_product_flash_attention(qt, kt, vt, 0.0, causal, False, scale=scale)
     return out.transpose(1, 2).contiguous(), lse
 
 
 def _attention_bwd(dout, q, k, v, out, lse, causal, scale):
     rep = q.shape[2] // k.shape[2]
+    if ATTENTION_BACKEND == "cudnn":
+        rep = 1
     b, s, h, d = q.shape
     sk = k.shape[1]
     qt = q.transpose(1, 2)
     kt = _expand_kv(k, rep).transpose(1, 2)
     vt = _expand_kv(v, rep).transpose(1, 2)
-    empty = torch.empty(0, dtype=torch.long, device=q.device)
     seed = torch.zeros((), dtype=torch.long, device=q.device)
-    dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
-        dout.transpose(1, 2), qt, kt, vt, out.transpose(1, 2), lse, None, None, s, sk, 0.0, causal, seed, seed, scale=scale
-    )
+    if ATTENTION_BACKEND == "cudnn":
+        lse_c = lse.unsqueeze(-1) if _cudnn_lse_ndim[0] == 4 else lse
+        dq, dk, dv = torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
+            dout.transpose(1, 2), qt, kt, vt, out.transpose(1, 2), lse_c, seed, seed, None, None, None, s, sk, 0.0, causal,
+            scale=scale,
+        )
+    else:
+        dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
+            dout.transpose(1, 2), qt, kt, vt, out.transpose(1, 2), lse, None, None, s, sk, 0.0, causal, seed, seed, scale=scale
+        )
     dq = dq.transpose(1, 2).contiguous()
     dk = dk.transpose(1, 2)
     dv = dv.transpose(1, 2)

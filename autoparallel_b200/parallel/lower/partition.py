@@ -82,6 +82,11 @@ def partition_joint(joint: JointGraph) -> PartitionedGraph:
     def need(n: fx.Node):
         if n.op != "call_function" or n in B or n in clone:
             return
+        if n.target is _op.getitem:
+            src = n.args[0]
+            # an element of a multi-output node is recomputed only together with its producer
+            if not (src.op == "call_function" and src.meta.get(RECOMPUTE) and not src.meta.get(MUST_SAVE)):
+                return
         if n.meta.get(RECOMPUTE) and not n.meta.get(MUST_SAVE):
             clone.add(n)
             for i in n.all_input_nodes:
@@ -152,7 +157,9 @@ def partition_joint(joint: JointGraph) -> PartitionedGraph:
         if isinstance(gn, fx.Node):
             grad_of_input.append(len(grads))
             # a gradient that is itself a forward value / primal (rare) is passed through
-            grads.append(benv[gn] if gn in benv else None)
+            if gn not in benv:
+                raise RuntimeError(f"gradient node {gn.name} of {p.name} is not part of the backward graph (stale graph index?)")
+            grads.append(benv[gn])
         else:
             grad_of_input.append(None)
     bw_g.output(tuple(grads))

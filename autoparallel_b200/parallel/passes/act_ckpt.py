@@ -101,8 +101,15 @@ def apply_activation_checkpointing(
     fwd = [n for n in g.nodes if n.op == "call_function" and n not in T]
     n_rec = n_save = 0
     mm_seen = 0
+    import operator
+
     for n in fwd:
         if n.meta.get(RECOMPUTE) or n.meta.get(MUST_SAVE):
+            continue
+        if n.target is operator.getitem:
+            src = n.args[0]
+            if src.meta.get(RECOMPUTE) and not src.meta.get(MUST_SAVE):
+                n.meta[RECOMPUTE] = True
             continue
         expensive = n.target in _EXPENSIVE or n.target in comm_ops.COLLECTIVE_OPS
         if mode == "selective":
