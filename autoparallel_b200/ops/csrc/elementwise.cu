@@ -480,3 +480,83 @@ int apb_adamw(const void* tensors_dev, const void* chunks_dev, int num_chunks, f
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (see apb_noalloc.h for the contract).
+// ------------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "apb_noalloc.h"
+
+// The weight-gradient accumulator.  In host code this name is only a handle for the runtime's
+// symbol table, never a pointer a kernel could use: its device address is fetched once per device
+// with cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_noalloc_dw_acc[APB_NOALLOC_MAX_D];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+int g_noalloc_sms[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+// One-time per-device set-up; the caller's current device is the one being set up.
+int noalloc_setup(int dev) {
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] != nullptr) return APB_NOALLOC_OK;
+  float* p = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dw_acc) != cudaSuccess || p == nullptr) {
+    (void)cudaGetLastError();
+    return APB_NOALLOC_ERR_SETUP;
+  }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+    (void)cudaGetLastError();
+    return APB_NOALLOC_ERR_SETUP;
+  }
+  g_noalloc_sms[dev] = sms;
+  g_noalloc_ptr[dev] = p;
+  return APB_NOALLOC_OK;
+}
+}  // namespace
+
+extern "C" int apb_rms_norm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw,
+                                        long long rows, int D, int is_bf16, cudaStream_t st) {
+  if (D <= 0 || rows < 0 || (D % 8) != 0) return APB_NOALLOC_ERR_BAD_SHAPE;
+  if (D > APB_NOALLOC_MAX_D) return APB_NOALLOC_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return APB_NOALLOC_ERR_SETUP;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    const int e = noalloc_setup(dev);
+    if (e != APB_NOALLOC_OK) return e;
+  }
+  float* acc = g_noalloc_ptr[dev];
+  const int num_sms = g_noalloc_sms[dev];
+  int threads = 256;
+  while (threads * 8 * RMS_BWD_MAX_VEC < D && threads < 1024) threads *= 2;
+  if (threads * 8 * RMS_BWD_MAX_VEC < D) return APB_NOALLOC_ERR_BAD_SHAPE;
+  // the array keeps the previous call's sums: start from zero
+  if (cudaMemsetAsync(acc, 0, sizeof(float) * D, st) != cudaSuccess) return APB_NOALLOC_ERR_LAUNCH;
+  if (rows > 0) {
+    const int grid = (int)(rows < (long long)num_sms * 2 ? rows : (long long)num_sms * 2);
+    DISPATCH(is_bf16, rms_norm_bwd_kernel<T><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx,
+                                                                      acc, rows, D));
+  }
+  if (is_bf16) {
+    cast_from_f32_kernel<bf16><<<grid_for(D / 8, 256, num_sms), 256, 0, st>>>(acc, (bf16*)dw, D);
+  } else {
+    if (cudaMemcpyAsync(dw, acc, sizeof(float) * D, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+      return APB_NOALLOC_ERR_LAUNCH;
+  }
+  return cudaGetLastError() == cudaSuccess ? APB_NOALLOC_OK : APB_NOALLOC_ERR_LAUNCH;
+}
+
+extern "C" const char* apb_noalloc_strerror(int code) {
+  switch (code) {
+    case APB_NOALLOC_OK: return "ok";
+    case APB_NOALLOC_ERR_BAD_SHAPE: return "bad shape: D must be a positive multiple of 8 and rows >= 0";
+    case APB_NOALLOC_ERR_LAUNCH: return "CUDA launch failed";
+    case APB_NOALLOC_ERR_TOO_LARGE: return "D exceeds APB_NOALLOC_MAX_D (16384): the built-in scratch array is too small";
+    case APB_NOALLOC_ERR_SETUP: return "could not obtain the device address of the built-in scratch array";
+    default: return "unknown error code";
+  }
+}
