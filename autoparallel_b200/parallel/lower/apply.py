@@ -217,6 +217,7 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
 
     strip_redistribution_points(new_gm)
     new_gm.graph.eliminate_dead_code()
+    sink_input_chains(new_gm)
     new_gm.graph.lint()
     new_gm.recompile()
     new_joint = index_joint_graph(new_gm, joint.traced_inputs, joint.out_spec)
@@ -233,3 +234,37 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
         output_placements=[pl(n) for n in joint.fwd_outputs],
         num_collectives=dict(redis.counts),
     )
+
+
+def sink_input_chains(gm: fx.GraphModule) -> int:
+    """Move computations that depend only on graph inputs (parameter → cast → all-gather → view
+    chains) down to just before their first consumer.
+
+    The solver's redistribution points sit right after the placeholders, so without this every
+    parameter gather would run – and its full-size result stay alive – from the top of the
+    graph.  Sinking restores "gather right before use" (what FSDP does), which bounds memory and
+    gives the overlap scheduler a meaningful first-use position to prefetch towards.
+    """
+    g = gm.graph
+    nodes = list(g.nodes)
+    input_only = {n for n in nodes if n.op == "placeholder"}
+    chain = []
+    for n in nodes:
+        if n.op == "call_function" and n.all_input_nodes and all(i in input_only for i in n.all_input_nodes):
+            input_only.add(n)
+            chain.append(n)
+    moved = 0
+    for n in reversed(chain):
+        users = list(n.users)
+        if not users:
+            continue
+        pos = {x: i for i, x in enumerate(g.nodes)}
+        first = min(users, key=lambda u: pos[u])
+        if first.op == "output":
+            continue
+        if pos[first] - pos[n] > 1:
+            first.prepend(n)
+            moved += 1
+    g.lint()
+    gm.recompile()
+    return moved

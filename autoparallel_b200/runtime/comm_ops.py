@@ -174,3 +174,70 @@ COLLECTIVE_OPS = {
     ops.all_reduce.default,
     ops.all_to_all.default,
 }
+
+
+# --------------------------------------------------------------------------------------------------
+# Split-phase forms used by the overlap scheduler: ``*_start`` issues the collective on the
+# communication stream and returns the (not yet valid) result; ``comm_wait`` makes the compute stream
+# wait for it.  Between the two nodes the scheduler places independent compute.
+# --------------------------------------------------------------------------------------------------
+lib.define("all_gather_start(Tensor x, int dim, str group, int group_size) -> Tensor")
+lib.define("reduce_scatter_start(Tensor x, int dim, str group, int group_size) -> Tensor")
+lib.define("all_reduce_start(Tensor x, str group, int group_size) -> Tensor")
+lib.define("comm_wait(Tensor x) -> Tensor")
+
+
+def _ag_start(x, dim, group, n):
+    be = _symm_backends.get(group)
+    if be is not None and x.is_cuda:
+        return be.all_gather_start(x, dim)
+    if dim != 0:
+        return _all_gather(x, dim, group, n)  # inner-dim gathers need a post-permute: keep synchronous
+    return torch.ops._c10d_functional.all_gather_into_tensor(x.contiguous(), n, group)
+
+
+def _rs_start(x, dim, group, n):
+    be = _symm_backends.get(group)
+    if be is not None and x.is_cuda:
+        return be.reduce_scatter_start(x, dim)
+    if dim != 0:
+        return _reduce_scatter(x, dim, group, n)
+    shape = list(x.shape)
+    shape[0] //= n
+    out = torch.ops._c10d_functional.reduce_scatter_tensor(x.contiguous().view(-1), "sum", n, group)
+    return out.view(shape)
+
+
+def _ar_start(x, group, n):
+    be = _symm_backends.get(group)
+    if be is not None and x.is_cuda:
+        return be.all_reduce_start(x)
+    return torch.ops._c10d_functional.all_reduce(x.contiguous(), "sum", group)
+
+
+def _comm_wait(x):
+    be = _symm_pending.pop(x.data_ptr(), None) if _symm_pending else None
+    if be is not None:
+        be.wait(x)
+        return x
+    return torch.ops._c10d_functional.wait_tensor(x)
+
+
+#: data_ptr -> backend for results of symmetric-memory ``*_start`` calls still in flight
+_symm_pending: dict[int, object] = {}
+
+for _name, _fn in (("all_gather_start", _ag_start), ("reduce_scatter_start", _rs_start), ("all_reduce_start", _ar_start),
+                   ("comm_wait", _comm_wait)):
+    lib.impl(_name, _fn, "CPU")
+    lib.impl(_name, _fn, "CUDA")
+lib.impl("all_gather_start", lambda x, dim, group, n: _shape_mul(x, dim, n), "Meta")
+lib.impl("reduce_scatter_start", lambda x, dim, group, n: _shape_div(x, dim, n), "Meta")
+lib.impl("all_reduce_start", lambda x, group, n: torch.empty_like(x), "Meta")
+lib.impl("comm_wait", lambda x: torch.empty_like(x), "Meta")
+
+START_OF = {
+    ops.all_gather.default: ops.all_gather_start.default,
+    ops.reduce_scatter.default: ops.reduce_scatter_start.default,
+    ops.all_reduce.default: ops.all_reduce_start.default,
+}
+START_OPS = set(START_OF.values())

@@ -24,14 +24,14 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture(scope="session")
 def fake_world():
-    """256 fake ranks in one process: collectives are shape-only no-ops, so planning, lowering and
+    """8 fake ranks in one process: collectives are shape-only no-ops, so planning, lowering and
     even execution of rank 0's graph run without any device (the reference's test harness does the
     same, tests/conftest.py:43-82 there)."""
     import torch.distributed as dist
     from torch.testing._internal.distributed.fake_pg import FakeStore
 
     if not dist.is_initialized():
-        dist.init_process_group("fake", store=FakeStore(), rank=0, world_size=256)
+        dist.init_process_group("fake", store=FakeStore(), rank=0, world_size=8)
     yield
     # left initialised for the whole session
 
@@ -40,14 +40,14 @@ def fake_world():
 def mesh_1d(fake_world):
     from torch.distributed.device_mesh import init_device_mesh
 
-    return init_device_mesh("cpu", (256,), mesh_dim_names=("dp",))
+    return init_device_mesh("cpu", (8,), mesh_dim_names=("dp",))
 
 
 @pytest.fixture()
 def mesh_2d(fake_world):
     from torch.distributed.device_mesh import init_device_mesh
 
-    return init_device_mesh("cpu", (32, 8), mesh_dim_names=("dp", "tp"))
+    return init_device_mesh("cpu", (2, 4), mesh_dim_names=("dp", "tp"))
 
 
 @pytest.fixture(autouse=True)

@@ -1,0 +1,101 @@
+"""CPU reference implementations of the operator library against PyTorch's own autograd."""
+import torch
+import torch.nn.functional as F
+
+from autoparallel_b200.ops import library as L
+
+
+def test_rms_norm_matches_torch():
+    torch.manual_seed(0)
+    x = torch.randn(4, 6, 32, requires_grad=True)
+    w = torch.randn(32, requires_grad=True)
+    g = torch.randn(4, 6, 32)
+    L.rms_norm(x, w, 1e-5).backward(g)
+    x2, w2 = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    F.rms_norm(x2, (32,), w2, 1e-5).backward(g)
+    assert torch.allclose(x.grad, x2.grad, atol=1e-5)
+    assert torch.allclose(w.grad, w2.grad, atol=1e-5)
+
+
+def test_rope_matches_complex_rotation():
+    torch.manual_seed(0)
+    x = torch.randn(2, 8, 4, 16, requires_grad=True)
+    ang = torch.randn(8, 8)
+    y = L.rope(x, ang.cos(), ang.sin())
+    xc = torch.view_as_complex(x.detach().reshape(2, 8, 4, 8, 2))
+    ref = torch.view_as_real(xc * torch.polar(torch.ones_like(ang), ang)[None, :, None, :]).flatten(3)
+    assert torch.allclose(y, ref, atol=1e-5)
+    # backward of a rotation is the inverse rotation
+    g = torch.randn_like(y)
+    y.backward(g)
+    assert torch.allclose(x.grad, L.ops.rope(g, ang.cos(), ang.sin(), True), atol=1e-6)
+
+
+def test_attention_gqa_matches_sdpa():
+    torch.manual_seed(0)
+    q = torch.randn(2, 16, 4, 8, requires_grad=True)
+    k = torch.randn(2, 16, 2, 8, requires_grad=True)
+    v = torch.randn(2, 16, 2, 8, requires_grad=True)
+    o = L.attention(q, k, v, causal=True)
+    g = torch.randn_like(o)
+    o.backward(g)
+    q2, k2, v2 = (t.detach().clone().requires_grad_() for t in (q, k, v))
+    o2 = F.scaled_dot_product_attention(
+        q2.transpose(1, 2), k2.transpose(1, 2).repeat_interleave(2, 1), v2.transpose(1, 2).repeat_interleave(2, 1), is_causal=True
+    ).transpose(1, 2)
+    o2.backward(g)
+    for a, b in ((o, o2), (q.grad, q2.grad), (k.grad, k2.grad), (v.grad, v2.grad)):
+        assert torch.allclose(a, b, atol=1e-5)
+
+
+def test_swiglu_and_cross_entropy():
+    torch.manual_seed(0)
+    a = torch.randn(5, 16, requires_grad=True)
+    b = torch.randn(5, 16, requires_grad=True)
+    g = torch.randn(5, 16)
+    L.swiglu(a, b).backward(g)
+    a2, b2 = a.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+    (F.silu(a2) * b2).backward(g)
+    assert torch.allclose(a.grad, a2.grad, atol=1e-6) and torch.allclose(b.grad, b2.grad, atol=1e-6)
+    lg = torch.randn(7, 11, requires_grad=True)
+    lab = torch.randint(0, 11, (7,))
+    L.cross_entropy(lg, lab).backward()
+    lg2 = lg.detach().clone().requires_grad_()
+    F.cross_entropy(lg2, lab).backward()
+    assert torch.allclose(lg.grad, lg2.grad, atol=1e-6)
+
+
+def test_gemm_family_autograd():
+    torch.manual_seed(0)
+    for ta, tb in ((False, False), (False, True), (True, False), (True, True)):
+        a = torch.randn((6, 5) if ta else (5, 6), requires_grad=True)
+        b = torch.randn((7, 6) if tb else (6, 7), requires_grad=True)
+        g = torch.randn(5, 7)
+        L.ops.gemm(a, b, ta, tb, torch.float32).backward(g)
+        a2, b2 = a.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+        ((a2.t() if ta else a2) @ (b2.t() if tb else b2)).backward(g)
+        assert torch.allclose(a.grad, a2.grad, atol=1e-5) and torch.allclose(b.grad, b2.grad, atol=1e-5)
+    x = torch.randn(2, 3, 6, requires_grad=True)
+    w = torch.randn(4, 6, requires_grad=True)
+    g = torch.randn(2, 3, 4)
+    L.ops.mm_nd(x, w, True, torch.float32).backward(g)
+    x2, w2 = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    (x2 @ w2.t()).backward(g)
+    assert torch.allclose(x.grad, x2.grad, atol=1e-5) and torch.allclose(w.grad, w2.grad, atol=1e-5)
+
+
+def test_models_run_on_cpu():
+    from autoparallel_b200.models.gpt2 import GPT2, gpt2_debug
+    from autoparallel_b200.models.llama3 import Transformer, llama3_debug
+
+    m = Transformer(llama3_debug())
+    m.init_weights(0)
+    t = torch.randint(0, 1024, (2, 32))
+    loss = m(t, t)
+    loss.backward()
+    assert torch.isfinite(loss)
+    g = GPT2(gpt2_debug())
+    g.init_weights(0)
+    t = torch.randint(0, 512, (2, 16))
+    assert torch.isfinite(g(t, t))
+    assert g.lm_head.weight is g.wte.weight
