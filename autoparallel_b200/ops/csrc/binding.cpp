@@ -25,6 +25,10 @@ int apb_xent_bwd(const float* dloss, const void* logits, const long long* labels
                  long long rows, int V, int is_bf16, cudaStream_t st);
 int apb_embedding_bwd(const void* dy, const long long* ids, float* out_f32, long long tokens, int D, int is_bf16,
                       cudaStream_t st);
+int apb_symm_header_bytes();
+int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank, int n, unsigned epoch, const void* src,
+                        void* dst, long long outer, long long inner_bytes, int elem_kind, float scale, long long stage_capacity,
+                        uint32_t* status, int num_ctas, cudaStream_t st);
 int apb_adamw(const void* tensors_dev, const void* chunks_dev, int num_chunks, float lr, float beta1, float beta2, float eps,
               float wd, float bc1, float bc2, float grad_scale, cudaStream_t st);
 }
@@ -135,6 +139,20 @@ void adamw(const at::Tensor& table, const at::Tensor& chunks, int64_t num_chunks
         "apb_adamw");
 }
 
+int64_t symm_header_bytes() { return apb_symm_header_bytes(); }
+
+// One collective on a symmetric workspace (see symm_comm.cu).  src/dst are ordinary device tensors.
+void symm_collective(int64_t mode, const std::vector<int64_t>& peer_ptrs, int64_t rank, int64_t epoch, const at::Tensor& src,
+                     at::Tensor& dst, int64_t outer, int64_t inner_bytes, int64_t elem_kind, double scale,
+                     int64_t stage_capacity, at::Tensor& status, int64_t num_ctas) {
+  c10::cuda::CUDAGuard g(src.device());
+  std::vector<unsigned long long> ptrs(peer_ptrs.begin(), peer_ptrs.end());
+  check(apb_symm_collective((int)mode, ptrs.data(), (int)rank, (int)ptrs.size(), (unsigned)epoch, src.data_ptr(), dst.data_ptr(),
+                            outer, inner_bytes, (int)elem_kind, (float)scale, stage_capacity,
+                            reinterpret_cast<uint32_t*>(status.data_ptr()), (int)num_ctas, stream()),
+        "apb_symm_collective");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -149,4 +167,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("xent_bwd", &xent_bwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("adamw", &adamw);
+  m.def("symm_header_bytes", &symm_header_bytes);
+  m.def("symm_collective", &symm_collective);
 }

@@ -1,0 +1,71 @@
+"""This framework's NVLink collectives (symmetric-memory kernels) against NCCL, on 2+ GPUs.
+
+Runs as child processes (one per GPU) so the pytest process itself never joins a process group.
+NVLS is off in NCCL for these tests and the kernels use plain peer loads only.
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+from autoparallel_b200.runtime import symm, comm_ops
+from autoparallel_b200.ops import cuda_impl
+g = symm.enable_for_group(dist.group.WORLD, workspace_bytes=256 << 20)
+name = dist.group.WORLD.group_name
+def nccl(fn, *a):
+    be = comm_ops._symm_backends.pop(name)
+    try: return fn(*a)
+    finally: comm_ops._symm_backends[name] = be
+torch.manual_seed(rank)
+errs = []
+for it in range(3):
+    for dtype in (torch.bfloat16, torch.float32):
+        x = torch.randn(64 * world, 96, 40, device="cuda", dtype=dtype)
+        for dim in (0, 1, 2):
+            shape = list(x.shape); 
+            a = comm_ops.ops.all_gather(x, dim, name, world); b = nccl(comm_ops._all_gather, x, dim, name, world)
+            errs.append(("ag", dim, dtype, (a.float() - b.float()).abs().max().item()))
+        for dim in (0, 1):
+            xs = torch.randn(64 * world, 96 * world, 40, device="cuda", dtype=dtype)
+            a = comm_ops.ops.reduce_scatter(xs, dim, name, world); b = nccl(comm_ops._reduce_scatter, xs, dim, name, world)
+            tol = 0.1 if dtype == torch.bfloat16 else 1e-4
+            errs.append(("rs", dim, dtype, (a.float() - b.float()).abs().max().item() / tol * 1e-6))
+        xs = torch.randn(16 * world, 24 * world, 8, device="cuda", dtype=dtype)
+        a = comm_ops.ops.all_to_all(xs, 1, 0, name, world); b = nccl(comm_ops._all_to_all, xs, 1, 0, name, world)
+        errs.append(("a2a", 1, dtype, (a.float() - b.float()).abs().max().item()))
+        a = comm_ops.ops.all_reduce(x, name, world); b = nccl(comm_ops._all_reduce, x, name, world)
+        errs.append(("ar", 0, dtype, (a.float() - b.float()).abs().max().item() / (0.1 if dtype == torch.bfloat16 else 1e-4) * 1e-6))
+    # split-phase
+    x = torch.randn(1024, 512, device="cuda")
+    h = comm_ops.ops.all_gather_start(x, 0, name, world); y = comm_ops.ops.comm_wait(h)
+    errs.append(("ag_async", 0, torch.float32, (y - nccl(comm_ops._all_gather, x, 0, name, world)).abs().max().item()))
+torch.cuda.synchronize(); cuda_impl.check_status()
+bad = [e for e in errs if e[3] > 1e-6]
+print("RESULT", rank, "bad", bad[:5], "n", len(errs), flush=True)
+dist.barrier(); dist.destroy_process_group()
+sys.exit(1 if bad else 0)
+'''
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_symm_collectives_match_nccl(tmp_path):
+    n = min(torch.cuda.device_count(), 4)
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    r = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+         "--master-port", "29571", str(script)],
+        env=env, capture_output=True, text=True, timeout=300,
+    )
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("bad []") == n, r.stdout[-2000:]
