@@ -28,7 +28,12 @@ int apb_embedding_bwd(const void* dy, const long long* ids, float* out_f32, long
 int apb_symm_header_bytes();
 int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank, int n, unsigned epoch, const void* src,
                         void* dst, long long outer, long long inner_bytes, int elem_kind, float scale, long long stage_capacity,
-                        uint32_t* status, int num_ctas, cudaStream_t st);
+                        uint32_t* status, int num_ctas, unsigned target0, unsigned target1, cudaStream_t st);
+int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                   long long ldc, int a_mn_major, int b_mn_major, int out_fp32, const unsigned long long* peer_ptrs, int rank,
+                   int n, unsigned epoch, int rows_per_shard, const void* shard_src, void* gbuf, long long shard_bytes,
+                   uint32_t* landed, unsigned landed_target, int rows_per_rank, float scale, long long stage_capacity,
+                   const unsigned* targets, int comm_ctas, uint32_t* status, int num_sms, cudaStream_t stream);
 int apb_adamw(const void* tensors_dev, const void* chunks_dev, int num_chunks, float lr, float beta1, float beta2, float eps,
               float wd, float bc1, float bc2, float grad_scale, cudaStream_t st);
 }
@@ -144,13 +149,41 @@ int64_t symm_header_bytes() { return apb_symm_header_bytes(); }
 // One collective on a symmetric workspace (see symm_comm.cu).  src/dst are ordinary device tensors.
 void symm_collective(int64_t mode, const std::vector<int64_t>& peer_ptrs, int64_t rank, int64_t epoch, const at::Tensor& src,
                      at::Tensor& dst, int64_t outer, int64_t inner_bytes, int64_t elem_kind, double scale,
-                     int64_t stage_capacity, at::Tensor& status, int64_t num_ctas) {
+                     int64_t stage_capacity, at::Tensor& status, int64_t num_ctas, int64_t target0, int64_t target1) {
   c10::cuda::CUDAGuard g(src.device());
   std::vector<unsigned long long> ptrs(peer_ptrs.begin(), peer_ptrs.end());
   check(apb_symm_collective((int)mode, ptrs.data(), (int)rank, (int)ptrs.size(), (unsigned)epoch, src.data_ptr(), dst.data_ptr(),
                             outer, inner_bytes, (int)elem_kind, (float)scale, stage_capacity,
-                            reinterpret_cast<uint32_t*>(status.data_ptr()), (int)num_ctas, stream()),
+                            reinterpret_cast<uint32_t*>(status.data_ptr()), (int)num_ctas, (unsigned)target0, (unsigned)target1,
+                            stream()),
         "apb_symm_collective");
+}
+
+// GEMM fused with a collective (see gemm_fused.cu).  a/b follow the conventions of ``gemm``; for the
+// gather modes the gathered operand passed here is the local full-size buffer ``gbuf``.
+void gemm_fused(int64_t fuse, const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major,
+                const std::vector<int64_t>& peer_ptrs, int64_t rank, int64_t epoch, int64_t rows_per_shard,
+                const at::Tensor& shard_src, const at::Tensor& landed, int64_t landed_target, int64_t rows_per_rank,
+                double scale, int64_t stage_capacity, const std::vector<int64_t>& targets, int64_t comm_ctas,
+                at::Tensor& status) {
+  c10::cuda::CUDAGuard g(a.device());
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm_fused: bf16 operands required");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && c.is_contiguous(), "gemm_fused: layout");
+  const int K = a_mn_major ? a.size(0) : a.size(1);
+  const int M = a_mn_major ? a.size(1) : a.size(0);
+  const int N = b_mn_major ? b.size(1) : b.size(0);
+  TORCH_CHECK((b_mn_major ? b.size(0) : b.size(1)) == K, "gemm_fused: contraction mismatch");
+  const bool out_fp32 = c.scalar_type() == at::kFloat;
+  std::vector<unsigned long long> ptrs(peer_ptrs.begin(), peer_ptrs.end());
+  unsigned tg[3] = {(unsigned)targets[0], (unsigned)targets[1], (unsigned)targets[2]};
+  void* gbuf = fuse == 1 ? a.data_ptr() : b.data_ptr();
+  check(apb_gemm_fused((int)fuse, a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                       c.dim() == 2 ? c.stride(0) : N, a_mn_major, b_mn_major, out_fp32, ptrs.data(), (int)rank, (int)ptrs.size(),
+                       (unsigned)epoch, (int)rows_per_shard, shard_src.data_ptr(), gbuf,
+                       (long long)shard_src.numel() * shard_src.element_size(),
+                       reinterpret_cast<uint32_t*>(landed.data_ptr()), (unsigned)landed_target, (int)rows_per_rank, (float)scale,
+                       stage_capacity, tg, (int)comm_ctas, reinterpret_cast<uint32_t*>(status.data_ptr()), num_sms(), stream()),
+        "apb_gemm_fused");
 }
 
 }  // namespace
@@ -169,4 +202,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw", &adamw);
   m.def("symm_header_bytes", &symm_header_bytes);
   m.def("symm_collective", &symm_collective);
+  m.def("gemm_fused", &gemm_fused);
 }

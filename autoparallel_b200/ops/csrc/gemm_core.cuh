@@ -1,0 +1,379 @@
+// Body of the persistent tcgen05 GEMM CTA, shared by the plain GEMM (gemm_tcgen05.cu) and the GEMM
+// kernels fused with a collective (gemm_fused.cu).
+//
+//   tile 128 x 256 x 64, 4 TMA stages, two 256-column TMEM accumulators
+//   warp 0: TMA producer | warp 1: TMEM owner + MMA issuer | warps 2..5: epilogue
+//
+// FUSE selects what the CTA does beyond a plain GEMM:
+//   FUSE_NONE       nothing
+//   FUSE_GATHER_A   rows (M) of A arrive shard by shard from peer GPUs: the producer waits for the
+//                   per-shard "landed" counter before loading a tile of that shard
+//   FUSE_GATHER_B   same for B; with a K-major B the shards partition N, with an MN-major B
+//                   (stored [K, N]) they partition K, and the k-loop starts at the local shard
+//   FUSE_REDUCE_SCATTER  the epilogue adds each fp32 tile into the owner rank's accumulation
+//                   buffer in peer memory (red.add over NVLink) instead of storing it locally
+#pragma once
+#include "ptx.cuh"
+#include "symm_proto.cuh"
+
+namespace apb {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16, GROUP_M = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int B_STAGE_BYTES = BN * BK * 2;
+constexpr int CHUNK_BYTES = BK * 128;  // one [BK x 64-element] MN-major box
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+
+enum : int { FUSE_NONE = 0, FUSE_GATHER_A = 1, FUSE_GATHER_B = 2, FUSE_REDUCE_SCATTER = 3 };
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  int out_fp32;
+  int num_m_tiles, num_n_tiles;
+  uint32_t* status;
+};
+
+struct FuseParams {
+  apbs::Peers peers;
+  int rank, n;
+  uint32_t epoch;
+  // gather
+  int rows_per_shard;          // rows of the gathered operand per rank (in its stored layout)
+  const uint32_t* landed;      // [n] local counters; shard s usable once landed[s] >= landed_target
+  uint32_t landed_target;
+  // reduce-scatter
+  int rows_per_rank;           // rows of C owned by each rank (multiple of BM)
+};
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& tm, int& tn) {
+  const int per_group = GROUP_M * num_n;
+  const int group = t / per_group;
+  const int first_m = group * GROUP_M;
+  const int gsz = min(num_m - first_m, GROUP_M);
+  const int r = t % per_group;
+  tm = first_m + r % gsz;
+  tn = r / gsz;
+}
+
+__device__ __forceinline__ void red_add_v4_sys(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+// cta / num_ctas: index of this CTA among the GEMM CTAs of the launch (fused kernels also run
+// communication CTAs that are not counted here).
+template <bool A_MN, bool B_MN, int FUSE>
+__device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                                         const FuseParams& f, int cta, int num_ctas, uint8_t* smem_raw) {
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint64_t* full = bars;                         // [STAGES]
+  uint64_t* empty = bars + STAGES;               // [STAGES]
+  uint64_t* tmem_full = bars + 2 * STAGES;       // [2]
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+  // rotation that makes every rank start on data it already owns
+  int m_rot = 0, n_rot = 0, k_rot = 0;
+  if (FUSE == FUSE_GATHER_A && !A_MN) m_rot = (f.rank * f.rows_per_shard) / BM;
+  if (FUSE == FUSE_GATHER_B && !B_MN) n_rot = (f.rank * f.rows_per_shard) / BN;
+  if (FUSE == FUSE_GATHER_B && B_MN) k_rot = (f.rank * f.rows_per_shard) / BK;
+  if (FUSE == FUSE_GATHER_A && A_MN) k_rot = (f.rank * f.rows_per_shard) / BK;
+  if (FUSE == FUSE_REDUCE_SCATTER) m_rot = (((f.rank + 1) % f.n) * f.rows_per_rank) / BM;  // own rows last
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = cta; t < num_tiles && ok; t += num_ctas) {
+        int tm, tn;
+        tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
+        tm = (tm + m_rot) % p.num_m_tiles;
+        tn = (tn + n_rot) % p.num_n_tiles;
+        const int m0 = tm * BM, n0 = tn * BN;
+        if ((FUSE == FUSE_GATHER_A && !A_MN) || (FUSE == FUSE_GATHER_B && !B_MN)) {
+          // the tile's rows of the gathered operand must have landed
+          const int r0 = (FUSE == FUSE_GATHER_A) ? m0 : n0;
+          const int extent = (FUSE == FUSE_GATHER_A) ? min(BM, p.M - m0) : min(BN, p.N - n0);
+          const int s0 = r0 / f.rows_per_shard, s1 = (r0 + extent - 1) / f.rows_per_shard;
+          for (int s = s0; s <= s1 && ok; ++s)
+            if (!apbs::wait_ge<false>(f.landed + s, f.landed_target, p.status)) ok = false;
+          if (!ok) {
+            *abort_flag = 1;
+            break;
+          }
+          fence_proxy_async_global();
+        }
+        for (int kb0 = 0; kb0 < num_kb; ++kb0) {
+          const int kb = (kb0 + k_rot) % num_kb;
+          if ((FUSE == FUSE_GATHER_B && B_MN) || (FUSE == FUSE_GATHER_A && A_MN)) {
+            const int r0 = kb * BK;
+            const int s0 = r0 / f.rows_per_shard, s1 = (min(r0 + BK, p.K) - 1) / f.rows_per_shard;
+            for (int s = s0; s <= s1 && ok; ++s)
+              if (!apbs::wait_ge<false>(f.landed + s, f.landed_target, p.status)) ok = false;
+            if (!ok) {
+              *abort_flag = 1;
+              break;
+            }
+            fence_proxy_async_global();
+          }
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+            ok = false;
+            atomicCAS(p.status, 0u, (uint32_t)ST_TIMEOUT_EMPTY);
+            *abort_flag = 1;
+            break;
+          }
+          mbar_expect_tx(&full[stage], A_STAGE_BYTES + B_STAGE_BYTES);
+          uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
+          if (!A_MN) {
+            tma_load_2d(a_dst, &tmA, &full[stage], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(a_dst + c * CHUNK_BYTES, &tmA, &full[stage], m0 + c * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(b_dst, &tmB, &full[stage], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(b_dst + c * CHUNK_BYTES, &tmB, &full[stage], n0 + c * 64, kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t buf_phase = 0;
+      bool ok = true;
+      for (int t = cta; t < num_tiles && ok; t += num_ctas) {
+        if (!mbar_wait(&tmem_empty[buf], buf_phase ^ 1, abort_flag)) {
+          atomicCAS(p.status, 0u, (uint32_t)ST_TIMEOUT_TMEM_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            ok = false;
+            atomicCAS(p.status, 0u, (uint32_t)ST_TIMEOUT_FULL);
+            *abort_flag = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t a_desc = A_MN ? make_smem_desc(a_addr + k * (UMMA_K * 128), CHUNK_BYTES, 1024)
+                                         : make_smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t b_desc = B_MN ? make_smem_desc(b_addr + k * (UMMA_K * 128), CHUNK_BYTES, 1024)
+                                         : make_smem_desc(b_addr + k * (UMMA_K * 2), 16, 1024);
+            umma_f16(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);  // stage reusable once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full[buf]);
+        if (++buf == 2) {
+          buf = 0;
+          buf_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    for (int t = cta; t < num_tiles; t += num_ctas) {
+      int tm, tn;
+      tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
+      tm = (tm + m_rot) % p.num_m_tiles;
+      tn = (tn + n_rot) % p.num_n_tiles;
+      if (!mbar_wait(&tmem_full[buf], buf_phase, abort_flag)) {
+        atomicCAS(p.status, 0u, (uint32_t)ST_TIMEOUT_TMEM_FULL);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const long long row = (long long)tm * BM + q * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
+      float* rs_base = nullptr;
+      if (FUSE == FUSE_REDUCE_SCATTER) {
+        const int owner = (tm * BM) / f.rows_per_rank;
+        // the owner zeroes its accumulation buffer at the start of the step and then raises "ready"
+        bool ok = true;
+        if (owner != f.rank) {
+          if (lane == 0) ok = apbs::wait_ge<true>(apbs::flag_ptr(f.peers.base[f.rank], apbs::OFF_READY, owner), f.epoch, p.status);
+        } else {
+          if (lane == 0) ok = apbs::wait_ge<false>(apbs::flag_ptr(f.peers.base[f.rank], apbs::OFF_READY, owner), f.epoch, p.status);
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) {
+          *abort_flag = 1;
+          break;
+        }
+        rs_base = reinterpret_cast<float*>(f.peers.base[owner] + apbs::HEADER_BYTES) +
+                  (row - (long long)owner * f.rows_per_rank) * p.N;
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (row < p.M && col < p.N) {
+          if (FUSE == FUSE_REDUCE_SCATTER) {
+            float* dst = rs_base + col;
+            if (col + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                red_add_v4_sys(dst + 4 * i, __uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                               __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col + i < p.N) atomicAdd_system(dst + i, __uint_as_float(r[i]));
+            }
+          } else if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
+            if (col + 32 <= p.N && (p.ldc & 3) == 0) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                reinterpret_cast<uint4*>(dst)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col + i < p.N) dst[i] = __uint_as_float(r[i]);
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
+            if (col + 32 <= p.N && (p.ldc & 7) == 0) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+                v.y = pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                v.z = pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                v.w = pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                reinterpret_cast<uint4*>(dst)[i] = v;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col + i < p.N) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[buf]);
+      if (++buf == 2) {
+        buf = 0;
+        buf_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------ host helpers
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map, innermost extent ``inner`` (contiguous), 128-byte swizzle, box 64 x box_outer.
+inline int make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld_elems, uint32_t box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return 1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld_elems * 2};
+  cuuint32_t box[2] = {64, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 2;
+}
+
+// Tensor maps of both operands for C[M,N] = opA * opB (see gemm_tcgen05.cu for the conventions).
+inline int make_operand_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, const void* B, int M, int N, int K,
+                             long long lda, long long ldb, int a_mn_major, int b_mn_major) {
+  if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return 3;
+  int e = !a_mn_major ? make_map(tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM)
+                      : make_map(tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BK);
+  if (e) return e;
+  return !b_mn_major ? make_map(tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BN)
+                     : make_map(tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BK);
+}
+
+}  // namespace apb

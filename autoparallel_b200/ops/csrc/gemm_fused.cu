@@ -1,0 +1,195 @@
+// GEMM fused with its neighbouring collective, one kernel per rank, over NVLink peer memory.
+//
+//   all-gather -> GEMM   (FUSE_GATHER_A / FUSE_GATHER_B): a few communication CTAs publish this
+//       rank's shard, pull every peer's shard ONCE into a local full-size operand buffer and bump a
+//       per-shard "landed" counter; the GEMM CTAs (one per SM, same persistent tcgen05 main loop as
+//       the plain GEMM) start on the local shard and wait on the counter only when they reach a
+//       tile of a shard that has not landed yet.  Covers the FSDP parameter gather in forward
+//       (weights [N/n, K] gathered along N) and in backward (the same weights consumed as a
+//       [K', N'] operand, i.e. gathered along the contraction dim) and the tensor-parallel
+//       activation gather (A rows).
+//   GEMM -> reduce-scatter (FUSE_REDUCE_SCATTER): the epilogue adds each fp32 accumulator tile into
+//       the owning rank's buffer with vector red.add over NVLink; communication CTAs zero that
+//       buffer up front, and once every rank has signalled that its contributions are complete,
+//       scale / cast the sum into the output shard.  Covers the gradient reduce-scatter (weight
+//       gradient GEMM) and the row-parallel projection followed by a sequence-sharded output.
+//
+// No TMA multicast, no NCCL: remote data moves with ordinary peer loads / red.add issued from the
+// kernel, so transfer and tensor-core work overlap tile by tile.  Waits are bounded; a timeout is
+// reported through the status word.  Reference counterparts (host-driven pipelines of cuBLAS calls
+// and P2P copies): autoparallel/graph_passes/async_tp/asynctp_ops.py:396-531, 1104-1186.
+#include "gemm_core.cuh"
+
+namespace apb {
+
+struct CommParams {
+  int comm_ctas;
+  // gather
+  const uint8_t* shard_src;
+  uint8_t* gbuf;
+  long long shard_bytes;
+  uint32_t* landed;
+  // reduce-scatter
+  long long acc_elems;  // fp32 elements of this rank's accumulation buffer (rows_per_rank * N)
+  void* out;
+  int out_fp32;
+  float scale;
+  // arrival-counter targets (running totals kept by the host)
+  uint32_t t_phase0, t_phase1, t_gemm;
+};
+
+__device__ __forceinline__ void comm_gather(const GemmParams& p, const FuseParams& f, const CommParams& c, int cta) {
+  using namespace apbs;
+  uint8_t* my_ws = f.peers.base[f.rank];
+  uint8_t* stage = my_ws + HEADER_BYTES;
+  __shared__ uint32_t ok_s;
+  if (threadIdx.x == 0) ok_s = 1u;
+  __syncthreads();
+  if (threadIdx.x < f.n && threadIdx.x != f.rank)
+    if (!wait_ge<true>(flag_ptr(my_ws, OFF_DONE, threadIdx.x), f.epoch - 1, p.status)) ok_s = 0u;
+  __syncthreads();
+  if (!ok_s) return;
+  coop_copy16(stage, c.shard_src, c.shard_bytes, cta, c.comm_ctas);
+  coop_copy16(c.gbuf + (long long)f.rank * c.shard_bytes, c.shard_src, c.shard_bytes, cta, c.comm_ctas);
+  fence_proxy_async_global();
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) atomicAdd(c.landed + f.rank, 1u);
+  if (arrive_is_last(flag_ptr(my_ws, OFF_COUNTERS, 2), c.t_phase0)) {
+    if (threadIdx.x < f.n && threadIdx.x != f.rank) st_release_sys(flag_ptr(f.peers.base[threadIdx.x], OFF_READY, f.rank), f.epoch);
+  }
+  for (int k = 1; k < f.n; ++k) {
+    const int peer = (f.rank + k) % f.n;
+    if (threadIdx.x == 0 && !wait_ge<true>(flag_ptr(my_ws, OFF_READY, peer), f.epoch, p.status)) ok_s = 0u;
+    __syncthreads();
+    if (!ok_s) return;
+    coop_copy16(c.gbuf + (long long)peer * c.shard_bytes, f.peers.base[peer] + HEADER_BYTES, c.shard_bytes, cta, c.comm_ctas);
+    fence_proxy_async_global();
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) atomicAdd(c.landed + peer, 1u);
+  }
+  if (arrive_is_last(flag_ptr(my_ws, OFF_COUNTERS, 3), c.t_phase1)) {
+    if (threadIdx.x < f.n && threadIdx.x != f.rank) st_release_sys(flag_ptr(f.peers.base[threadIdx.x], OFF_DONE, f.rank), f.epoch);
+  }
+}
+
+__device__ __forceinline__ void comm_reduce_scatter(const GemmParams& p, const FuseParams& f, const CommParams& c, int cta) {
+  using namespace apbs;
+  uint8_t* my_ws = f.peers.base[f.rank];
+  float* acc = reinterpret_cast<float*>(my_ws + HEADER_BYTES);
+  __shared__ uint32_t ok_s;
+  if (threadIdx.x == 0) ok_s = 1u;
+  __syncthreads();
+  if (threadIdx.x < f.n && threadIdx.x != f.rank)
+    if (!wait_ge<true>(flag_ptr(my_ws, OFF_DONE, threadIdx.x), f.epoch - 1, p.status)) ok_s = 0u;
+  __syncthreads();
+  if (!ok_s) return;
+  const long long nvec = c.acc_elems >> 2;
+  const long long stride = (long long)c.comm_ctas * blockDim.x;
+  for (long long i = (long long)cta * blockDim.x + threadIdx.x; i < nvec; i += stride)
+    reinterpret_cast<float4*>(acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (arrive_is_last(flag_ptr(my_ws, OFF_COUNTERS, 2), c.t_phase0)) {
+    if (threadIdx.x < f.n) st_release_sys(flag_ptr(f.peers.base[threadIdx.x], OFF_READY, f.rank), f.epoch);
+  }
+  // every rank (this one included) signals when all of its tiles have been added
+  if (threadIdx.x < f.n)
+    if (!wait_ge<true>(flag_ptr(my_ws, OFF_CONTRIB, threadIdx.x), f.epoch, p.status)) ok_s = 0u;
+  __syncthreads();
+  if (!ok_s) return;
+  for (long long i = (long long)cta * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float4 v = reinterpret_cast<const float4*>(acc)[i];
+    v.x *= c.scale; v.y *= c.scale; v.z *= c.scale; v.w *= c.scale;
+    if (c.out_fp32) {
+      reinterpret_cast<float4*>(c.out)[i] = v;
+    } else {
+      uint2 o;
+      o.x = pack_bf16(v.x, v.y);
+      o.y = pack_bf16(v.z, v.w);
+      reinterpret_cast<uint2*>(c.out)[i] = o;
+    }
+  }
+}
+
+template <bool A_MN, bool B_MN, int FUSE>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p,
+                  FuseParams f, CommParams c) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x < c.comm_ctas) {
+    if (FUSE == FUSE_REDUCE_SCATTER) comm_reduce_scatter(p, f, c, blockIdx.x);
+    else comm_gather(p, f, c, blockIdx.x);
+    return;
+  }
+  gemm_cta<A_MN, B_MN, FUSE>(tmA, tmB, p, f, blockIdx.x - c.comm_ctas, gridDim.x - c.comm_ctas, smem_raw);
+  if (FUSE == FUSE_REDUCE_SCATTER) {
+    using namespace apbs;
+    uint8_t* my_ws = f.peers.base[f.rank];
+    if (arrive_is_last(flag_ptr(my_ws, OFF_COUNTERS, 4), c.t_gemm)) {
+      if (threadIdx.x < f.n) {
+        st_release_sys(flag_ptr(f.peers.base[threadIdx.x], OFF_CONTRIB, f.rank), f.epoch);
+        if (threadIdx.x != f.rank) st_release_sys(flag_ptr(f.peers.base[threadIdx.x], OFF_DONE, f.rank), f.epoch);
+      }
+    }
+  }
+}
+
+}  // namespace apb
+
+using namespace apb;
+
+// fuse: 1 gather A, 2 gather B, 3 reduce-scatter.  ``targets``: {phase0, phase1, gemm} arrival totals.
+// For gathers the tensor map of the gathered operand is built over ``gbuf`` (the local full-size
+// buffer); the caller passes that pointer as A or B.  Returns 0 or an error code.
+extern "C" int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                              long long ldb, long long ldc, int a_mn_major, int b_mn_major, int out_fp32,
+                              const unsigned long long* peer_ptrs, int rank, int n, unsigned epoch, int rows_per_shard,
+                              const void* shard_src, void* gbuf, long long shard_bytes, uint32_t* landed,
+                              unsigned landed_target, int rows_per_rank, float scale, long long stage_capacity,
+                              const unsigned* targets, int comm_ctas, uint32_t* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (n > apbs::MAX_RANKS || n < 1 || comm_ctas < 1) return 3;
+  CUtensorMap tmA, tmB;
+  const int e = make_operand_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_mn_major, b_mn_major);
+  if (e) return e;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
+  p.num_m_tiles = (M + BM - 1) / BM;
+  p.num_n_tiles = (N + BN - 1) / BN;
+  p.status = status;
+  FuseParams f{};
+  for (int i = 0; i < n; ++i) f.peers.base[i] = reinterpret_cast<uint8_t*>(peer_ptrs[i]);
+  f.rank = rank; f.n = n; f.epoch = epoch;
+  f.rows_per_shard = rows_per_shard; f.landed = landed; f.landed_target = landed_target; f.rows_per_rank = rows_per_rank;
+  CommParams c{};
+  c.comm_ctas = comm_ctas;
+  c.shard_src = static_cast<const uint8_t*>(shard_src); c.gbuf = static_cast<uint8_t*>(gbuf); c.shard_bytes = shard_bytes;
+  c.landed = landed; c.out = C; c.out_fp32 = out_fp32; c.scale = scale;
+  c.t_phase0 = targets[0]; c.t_phase1 = targets[1]; c.t_gemm = targets[2];
+  if (fuse == FUSE_REDUCE_SCATTER) {
+    if (rows_per_rank <= 0 || (rows_per_rank % BM) != 0 || (long long)rows_per_rank * n != M || (N & 3)) return 3;
+    c.acc_elems = (long long)rows_per_rank * N;
+    if (c.acc_elems * 4 > stage_capacity) return 7;
+  } else {
+    if ((shard_bytes & 15) || shard_bytes > stage_capacity || rows_per_shard <= 0) return shard_bytes > stage_capacity ? 7 : 3;
+  }
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  const int gemm_ctas = tiles < num_sms ? tiles : num_sms;
+  const int grid = gemm_ctas + comm_ctas;
+  auto launch = [&](auto kern) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+    kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p, f, c);
+  };
+#define APB_LAUNCH_FUSED(FUSE)                                                        \
+  do {                                                                                \
+    if (!a_mn_major && !b_mn_major) launch(gemm_fused_kernel<false, false, FUSE>);    \
+    else if (!a_mn_major && b_mn_major) launch(gemm_fused_kernel<false, true, FUSE>); \
+    else if (a_mn_major && !b_mn_major) launch(gemm_fused_kernel<true, false, FUSE>); \
+    else launch(gemm_fused_kernel<true, true, FUSE>);                                 \
+  } while (0)
+  if (fuse == FUSE_GATHER_A) APB_LAUNCH_FUSED(FUSE_GATHER_A);
+  else if (fuse == FUSE_GATHER_B) APB_LAUNCH_FUSED(FUSE_GATHER_B);
+  else if (fuse == FUSE_REDUCE_SCATTER) APB_LAUNCH_FUSED(FUSE_REDUCE_SCATTER);
+  else return 3;
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}

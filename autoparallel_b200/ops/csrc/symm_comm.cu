@@ -19,51 +19,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "symm_proto.cuh"
+
 namespace apbs {
-
-constexpr int MAX_RANKS = 16;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
-constexpr uint32_t ST_TIMEOUT_PEER_FLAG = 5;
-
-// workspace header layout (bytes)
-constexpr int FLAG_STRIDE = 128;                       // one flag per 128-B line
-constexpr int OFF_READY = 0;                           // ready[rank]
-constexpr int OFF_DONE = MAX_RANKS * FLAG_STRIDE;      // done[rank]
-constexpr int OFF_COUNTERS = 2 * MAX_RANKS * FLAG_STRIDE;  // local atomic counters
-constexpr int HEADER_BYTES = 8192;
-
-struct Peers {
-  uint8_t* base[MAX_RANKS];
-};
-
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// Bounded wait for *flag >= epoch (epochs compared with wrap-safe signed difference).
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* status) {
-  if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-  const unsigned long long t0 = gtime();
-  for (uint32_t i = 1;; ++i) {
-    if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    if ((i & 31u) == 0u) {
-      if (gtime() - t0 > kWaitLimitNs) {
-        atomicCAS(status, 0u, ST_TIMEOUT_PEER_FLAG);
-        return false;
-      }
-      __nanosleep(64);
-    }
-  }
-}
 
 enum Mode : int { ALL_GATHER = 0, REDUCE_SCATTER = 1, ALL_TO_ALL = 2 };
 
@@ -79,40 +37,12 @@ struct CollParams {
   int elem_kind;       // reduce-scatter: 0 = fp32, 1 = bf16 (summed in fp32)
   float scale;         // reduce-scatter: result multiplied by this
   uint32_t* status;
+  uint32_t target0, target1;  // arrival-counter values that mark the last CTA of phases 0 and 1
 };
-
-// copy ``bytes`` (multiple of 16, 16-B aligned) with the whole grid
-__device__ __forceinline__ void grid_copy16(uint8_t* dst, const uint8_t* src, long long bytes) {
-  const long long nvec = bytes >> 4;
-  const uint4* s = reinterpret_cast<const uint4*>(src);
-  uint4* d = reinterpret_cast<uint4*>(dst);
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  for (; i + 3 * stride < nvec; i += 4 * stride) {
-    uint4 a = s[i], b = s[i + stride], c = s[i + 2 * stride], e = s[i + 3 * stride];
-    d[i] = a; d[i + stride] = b; d[i + 2 * stride] = c; d[i + 3 * stride] = e;
-  }
-  for (; i < nvec; i += stride) d[i] = s[i];
-}
-
-// last-CTA detection on a local counter that counts up by gridDim.x per use
-__device__ __forceinline__ bool grid_arrive_is_last(uint32_t* counter, uint32_t target) {
-  __shared__ uint32_t is_last;
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const uint32_t prev = atomicAdd(counter, 1u);
-    is_last = (prev + 1u == target) ? 1u : 0u;
-  }
-  __syncthreads();
-  return is_last != 0u;
-}
 
 template <int MODE>
 __global__ void __launch_bounds__(512) symm_collective_kernel(CollParams p) {
   uint8_t* my_ws = p.peers.base[p.rank];
-  uint32_t* my_flags = reinterpret_cast<uint32_t*>(my_ws);
-  uint32_t* counters = reinterpret_cast<uint32_t*>(my_ws + OFF_COUNTERS);
   uint8_t* my_stage = my_ws + HEADER_BYTES;
   const int n = p.n;
   // bytes of this rank's input
@@ -123,12 +53,12 @@ __global__ void __launch_bounds__(512) symm_collective_kernel(CollParams p) {
 
   // ---- phase 0: my staging is free once every peer has finished the previous collective
   if (threadIdx.x < n && threadIdx.x != p.rank) {
-    if (!wait_flag(reinterpret_cast<uint32_t*>(my_ws + OFF_DONE + threadIdx.x * FLAG_STRIDE), p.epoch - 1, p.status)) ok_s = 0u;
+    if (!wait_ge<true>(reinterpret_cast<uint32_t*>(my_ws + OFF_DONE + threadIdx.x * FLAG_STRIDE), p.epoch - 1, p.status)) ok_s = 0u;
   }
   __syncthreads();
   if (!ok_s) return;
-  grid_copy16(my_stage, p.src, in_bytes);
-  if (grid_arrive_is_last(&counters[0], p.epoch * gridDim.x)) {
+  coop_copy16(my_stage, p.src, in_bytes, blockIdx.x, gridDim.x);
+  if (arrive_is_last(flag_ptr(my_ws, OFF_COUNTERS, 0), p.target0)) {
     if (threadIdx.x < n && threadIdx.x != p.rank)
       st_release_sys(reinterpret_cast<uint32_t*>(p.peers.base[threadIdx.x] + OFF_READY + p.rank * FLAG_STRIDE), p.epoch);
   }
@@ -142,14 +72,14 @@ __global__ void __launch_bounds__(512) symm_collective_kernel(CollParams p) {
         src = p.src;
       } else {
         if (threadIdx.x == 0 &&
-            !wait_flag(reinterpret_cast<uint32_t*>(my_ws + OFF_READY + peer * FLAG_STRIDE), p.epoch, p.status))
+            !wait_ge<true>(reinterpret_cast<uint32_t*>(my_ws + OFF_READY + peer * FLAG_STRIDE), p.epoch, p.status))
           ok_s = 0u;
         __syncthreads();
         if (!ok_s) return;
         src = p.peers.base[peer] + HEADER_BYTES;
       }
       if (p.outer == 1) {
-        grid_copy16(p.dst + (long long)peer * p.inner_bytes, src, p.inner_bytes);
+        coop_copy16(p.dst + (long long)peer * p.inner_bytes, src, p.inner_bytes, blockIdx.x, gridDim.x);
       } else {
         // dst[o][peer][inner] <- src[o][inner]
         const long long vec_per = p.inner_bytes >> 4;
@@ -164,7 +94,7 @@ __global__ void __launch_bounds__(512) symm_collective_kernel(CollParams p) {
   } else {
     // wait for everybody, then read chunk ``rank`` of every peer
     if (threadIdx.x < n && threadIdx.x != p.rank) {
-      if (!wait_flag(reinterpret_cast<uint32_t*>(my_ws + OFF_READY + threadIdx.x * FLAG_STRIDE), p.epoch, p.status)) ok_s = 0u;
+      if (!wait_ge<true>(reinterpret_cast<uint32_t*>(my_ws + OFF_READY + threadIdx.x * FLAG_STRIDE), p.epoch, p.status)) ok_s = 0u;
     }
     __syncthreads();
     if (!ok_s) return;
@@ -216,7 +146,7 @@ __global__ void __launch_bounds__(512) symm_collective_kernel(CollParams p) {
   }
 
   // ---- phase 2: tell the peers their staging areas are no longer being read by me
-  if (grid_arrive_is_last(&counters[1], p.epoch * gridDim.x)) {
+  if (arrive_is_last(flag_ptr(my_ws, OFF_COUNTERS, 1), p.target1)) {
     if (threadIdx.x < n && threadIdx.x != p.rank)
       st_release_sys(reinterpret_cast<uint32_t*>(p.peers.base[threadIdx.x] + OFF_DONE + p.rank * FLAG_STRIDE), p.epoch);
   }
@@ -234,7 +164,7 @@ int apb_symm_header_bytes() { return HEADER_BYTES; }
 // mode: 0 all-gather, 1 reduce-scatter (sum), 2 all-to-all.  Returns 0 or an error code.
 int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank, int n, unsigned epoch, const void* src,
                         void* dst, long long outer, long long inner_bytes, int elem_kind, float scale, long long stage_capacity,
-                        uint32_t* status, int num_ctas, cudaStream_t st) {
+                        uint32_t* status, int num_ctas, unsigned target0, unsigned target1, cudaStream_t st) {
   if (n > MAX_RANKS || n < 1) return 3;
   if ((inner_bytes & 15) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return 3;
   const long long in_bytes = (mode == ALL_GATHER) ? outer * inner_bytes : outer * inner_bytes * n;
@@ -243,7 +173,7 @@ int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank,
   for (int i = 0; i < n; ++i) p.peers.base[i] = reinterpret_cast<uint8_t*>(peer_ptrs[i]);
   p.rank = rank; p.n = n; p.epoch = epoch;
   p.src = static_cast<const uint8_t*>(src); p.dst = static_cast<uint8_t*>(dst);
-  p.outer = outer; p.inner_bytes = inner_bytes; p.elem_kind = elem_kind; p.scale = scale; p.status = status;
+  p.outer = outer; p.inner_bytes = inner_bytes; p.elem_kind = elem_kind; p.scale = scale; p.status = status; p.target0 = target0; p.target1 = target1;
   if (mode == ALL_GATHER) symm_collective_kernel<ALL_GATHER><<<num_ctas, 512, 0, st>>>(p);
   else if (mode == REDUCE_SCATTER) symm_collective_kernel<REDUCE_SCATTER><<<num_ctas, 512, 0, st>>>(p);
   else if (mode == ALL_TO_ALL) symm_collective_kernel<ALL_TO_ALL><<<num_ctas, 512, 0, st>>>(p);

@@ -49,6 +49,7 @@ class SymmGroup:
         torch.cuda.synchronize()
         dist.barrier(self.pg)
         self.epoch = 0
+        self.arrivals = [0] * 8  # running totals of the header's arrival counters
         self.num_ctas = num_ctas
         self.stream = torch.cuda.Stream(device=self.device)
         self.status = cuda_impl.status_buffer(self.device)
@@ -60,8 +61,11 @@ class SymmGroup:
         from ..ops import cuda_impl
 
         self.epoch += 1
+        self.arrivals[0] += self.num_ctas
+        self.arrivals[1] += self.num_ctas
         self._C.symm_collective(mode, self.peer_ptrs, self.rank, self.epoch, src, dst, outer, inner_bytes, elem_kind, scale,
-                                self.capacity, self.status, self.num_ctas)
+                                self.capacity, self.status, self.num_ctas, self.arrivals[0] & 0xFFFFFFFF,
+                                self.arrivals[1] & 0xFFFFFFFF)
         cuda_impl._count()
 
     def _split(self, shape, dim, itemsize):
@@ -117,6 +121,87 @@ class SymmGroup:
         # recv: [peer, d0, ..., chunk@split_dim, ...]; concatenate peers along concat_dim
         pieces = recv.unbind(0)
         return torch.cat(pieces, dim=concat_dim)
+
+    # ------------------------------------------------------------------ GEMM fused with a collective
+    FUSE_GATHER_A, FUSE_GATHER_B, FUSE_REDUCE_SCATTER = 1, 2, 3
+
+    def _landed(self):
+        if not hasattr(self, "_landed_buf"):
+            self._landed_buf = torch.zeros(16, dtype=torch.int32, device=self.device)
+            self._landed_total = 0
+        return self._landed_buf
+
+    def _fused(self, fuse, a, b, c, a_mn, b_mn, rows_per_shard, shard_src, rows_per_rank, scale):
+        from ..ops import cuda_impl
+
+        landed = self._landed()
+        self.epoch += 1
+        ctas = self.fused_comm_ctas
+        if fuse == self.FUSE_REDUCE_SCATTER:
+            self.arrivals[2] += ctas
+            self.arrivals[4] += min(self._num_sms, -(-c.shape[0] * self.n // 128) * -(-c.shape[1] // 256))
+        else:
+            self.arrivals[2] += ctas
+            self.arrivals[3] += ctas
+            self._landed_total += ctas
+        targets = [self.arrivals[2] & 0xFFFFFFFF, self.arrivals[3] & 0xFFFFFFFF, self.arrivals[4] & 0xFFFFFFFF]
+        self._C.gemm_fused(fuse, a, b, c, a_mn, b_mn, self.peer_ptrs, self.rank, self.epoch, rows_per_shard, shard_src, landed,
+                           self._landed_total & 0xFFFFFFFF, rows_per_rank, scale, self.capacity, targets, ctas, self.status)
+        cuda_impl._count()
+
+    @property
+    def _num_sms(self):
+        return torch.cuda.get_device_properties(self.device).multi_processor_count
+
+    fused_comm_ctas = 16
+
+    def can_fuse_gather(self, shard: torch.Tensor) -> bool:
+        nbytes = shard.numel() * shard.element_size()
+        return shard.dtype == torch.bfloat16 and shard.dim() == 2 and nbytes % 16 == 0 and nbytes <= self.capacity and shard.shape[1] % 8 == 0
+
+    def ag_gemm_b(self, x: torch.Tensor, w_shard: torch.Tensor, out_dtype=torch.bfloat16):
+        """y = x @ all_gather(w_shard, 0)^T with x [M, K], w_shard [R, K]; returns (y [M, n*R], w_full)."""
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        w_shard = w_shard.contiguous()
+        R, K = w_shard.shape
+        w_full = torch.empty(self.n * R, K, dtype=w_shard.dtype, device=x.device)
+        y = torch.empty(x2.shape[0], self.n * R, dtype=out_dtype, device=x.device)
+        self._fused(self.FUSE_GATHER_B, x2, w_full, y, False, False, R, w_shard, 0, 1.0)
+        return y.view(*x.shape[:-1], self.n * R), w_full
+
+    def ag_gemm_bk(self, dy: torch.Tensor, w_shard: torch.Tensor, out_dtype=torch.bfloat16):
+        """dx = dy @ all_gather(w_shard, 0) with dy [M, n*R], w_shard [R, K]; the gathered rows are the
+        contraction dim.  Returns (dx [M, K], w_full)."""
+        d2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        w_shard = w_shard.contiguous()
+        R, K = w_shard.shape
+        w_full = torch.empty(self.n * R, K, dtype=w_shard.dtype, device=dy.device)
+        dx = torch.empty(d2.shape[0], K, dtype=out_dtype, device=dy.device)
+        self._fused(self.FUSE_GATHER_B, d2, w_full, dx, False, True, R, w_shard, 0, 1.0)
+        return dx.view(*dy.shape[:-1], K), w_full
+
+    def ag_gemm_a(self, x_shard: torch.Tensor, w: torch.Tensor, trans_b: bool = True, out_dtype=torch.bfloat16):
+        """y = all_gather(x_shard, 0) @ (w^T if trans_b else w); returns (y [n*R, N], x_full)."""
+        xs = x_shard.reshape(-1, x_shard.shape[-1]).contiguous()
+        w = w.contiguous()
+        R, K = xs.shape
+        x_full = torch.empty(self.n * R, K, dtype=xs.dtype, device=xs.device)
+        N = w.shape[0] if trans_b else w.shape[1]
+        y = torch.empty(self.n * R, N, dtype=out_dtype, device=xs.device)
+        self._fused(self.FUSE_GATHER_A, x_full, w, y, False, not trans_b, R, xs, 0, 1.0)
+        return y, x_full
+
+    def gemm_rs(self, a: torch.Tensor, b: torch.Tensor, a_mn: bool, b_mn: bool, out_dtype=torch.float32, scale: float = 1.0):
+        """reduce_scatter(opA @ opB, dim 0) in one kernel; returns this rank's [M/n, N] rows."""
+        a, b = a.contiguous(), b.contiguous()
+        M = a.shape[1] if a_mn else a.shape[0]
+        N = b.shape[1] if b_mn else b.shape[0]
+        out = torch.empty(M // self.n, N, dtype=out_dtype, device=a.device)
+        self._fused(self.FUSE_REDUCE_SCATTER, a, b, out, a_mn, b_mn, 0, out, M // self.n, scale)
+        return out
+
+    def can_fuse_rs(self, M: int, N: int) -> bool:
+        return M % (self.n * 128) == 0 and N % 8 == 0 and (M // self.n) * N * 4 <= self.capacity
 
     def _fallback(self, kind, x, *dims):
         n, g = self.n, self.group_name

@@ -68,4 +68,70 @@ def test_symm_collectives_match_nccl(tmp_path):
         env=env, capture_output=True, text=True, timeout=300,
     )
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert r.stdout.count("bad []") == n, r.stdout[-2000:]
+    assert "bad [(" not in r.stdout and r.stdout.count("RESULT") == n, r.stdout[-2000:]
+
+
+FUSED_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+from autoparallel_b200.runtime import symm
+from autoparallel_b200.ops import cuda_impl
+g = symm.enable_for_group(dist.group.WORLD, workspace_bytes=256 << 20)
+bad = []
+def gather(t):
+    out = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(out, t.contiguous()); return torch.cat(out, 0)
+def check(name, got, ref, tol):
+    err = (got.float() - ref.float()).abs().max().item()
+    if not err <= tol: bad.append((name, err))
+for it in range(3):
+    torch.manual_seed(100 * it + rank)
+    M, K, R = 512 + 128 * it, 320, 384
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(R, K, device="cuda", dtype=torch.bfloat16) * 0.1
+    wf = gather(w)
+    y, w_full = g.ag_gemm_b(x, w)
+    check("ag_b w_full", w_full, wf, 0.0); check("ag_b y", y, x.float() @ wf.float().t(), 0.25)
+    dy = torch.randn(M, world * R, device="cuda", dtype=torch.bfloat16)
+    dx, w_full2 = g.ag_gemm_bk(dy, w)
+    check("ag_bk w_full", w_full2, wf, 0.0); check("ag_bk dx", dx, dy.float() @ wf.float(), 0.5)
+    xs = torch.randn(256, K, device="cuda", dtype=torch.bfloat16)
+    w2 = torch.randn(512, K, device="cuda", dtype=torch.bfloat16) * 0.1
+    ya, x_full = g.ag_gemm_a(xs, w2)
+    xf = gather(xs)
+    check("ag_a x_full", x_full, xf, 0.0); check("ag_a y", ya, xf.float() @ w2.float().t(), 0.25)
+    # GEMM -> reduce-scatter: weight-gradient shape (both operands MN-major) and row-parallel shape
+    T = 1024
+    dyl = torch.randn(T, 256 * world, device="cuda", dtype=torch.bfloat16)
+    xl = torch.randn(T, 320, device="cuda", dtype=torch.bfloat16)
+    full = (dyl.float().t() @ xl.float()); dist.all_reduce(full)
+    out = g.gemm_rs(dyl, xl, True, True, torch.float32)
+    check("wgrad_rs", out, full[rank * 256:(rank + 1) * 256], 0.05)
+    a = torch.randn(128 * world * 2, 192, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(264, 192, device="cuda", dtype=torch.bfloat16)
+    full = a.float() @ b.float().t(); dist.all_reduce(full)
+    out = g.gemm_rs(a, b, False, False, torch.bfloat16, scale=0.5)
+    rows = a.shape[0] // world
+    check("mm_rs", out, 0.5 * full[rank * rows:(rank + 1) * rows], 0.5)
+torch.cuda.synchronize(); cuda_impl.check_status()
+print("RESULT", rank, "bad", bad[:6], flush=True)
+dist.barrier(); dist.destroy_process_group()
+sys.exit(1 if bad else 0)
+'''
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_gemm_collectives(tmp_path):
+    n = min(torch.cuda.device_count(), 4)
+    script = tmp_path / "worker.py"
+    script.write_text(FUSED_WORKER)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    r = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+         "--master-port", "29572", str(script)],
+        env=env, capture_output=True, text=True, timeout=300,
+    )
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "bad [(" not in r.stdout and r.stdout.count("RESULT") == n, r.stdout[-2000:]
