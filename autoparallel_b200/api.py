@@ -81,6 +81,7 @@ class AutoParallel:
         repeated_subgraphs: bool = True,
         activation_checkpointing: str = "none",
         plan_device: Optional[str] = None,
+        fuse_collectives: bool = True,
     ):
         if dynamic:
             raise NotImplementedError(
@@ -96,6 +97,8 @@ class AutoParallel:
         self.cost_model = cost_model
         self.activation_checkpointing = activation_checkpointing
         self.plan_device = plan_device
+        self.fuse_collectives = fuse_collectives
+        self.fusion_stats = {}
         model = clone_model_for_tracing(model)
         if self.mp_policy is not None:
             mp_cast.apply_dtype_cast(model, self.mp_policy)
@@ -212,9 +215,14 @@ class AutoParallel:
         lowered = lower_to_local_graph(self.joint, sol, self.mesh)
         from .parallel.passes.peephole import fuse_cast_into_gemm
 
-        if fuse_cast_into_gemm(lowered.gm):
-            from .parallel.frontend.trace import index_joint_graph
+        from .parallel.frontend.trace import index_joint_graph
+        from .parallel.passes.fuse_collectives import fuse_collectives
 
+        changed = fuse_cast_into_gemm(lowered.gm)
+        if self.fuse_collectives:
+            self.fusion_stats = fuse_collectives(lowered.gm, lowered.joint.tangent_nodes, self.reshard_after_forward)
+            changed += sum(self.fusion_stats.values())
+        if changed:
             lowered.joint = index_joint_graph(lowered.gm, self.joint.traced_inputs, self.joint.out_spec)
         mark_fsdp_recompute(lowered.joint, self.reshard_after_forward)
         if self.activation_checkpointing != "none":

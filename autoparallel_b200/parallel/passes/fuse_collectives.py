@@ -1,0 +1,129 @@
+"""Graph pass that merges a collective with the GEMM next to it into one fused node.
+
+Patterns on the lowered per-rank graph:
+
+* ``mm_nd(x, all_gather(w, 0))``  – FSDP parameter gather feeding a projection (forward: weight
+  used transposed; backward dgrad: weight used as stored, the gathered rows are the contraction
+  dim) → ``apb200_comm::ag_mm`` modes 0 / 1.  Every GEMM consumer of a gathered parameter gets its
+  own fused node, i.e. the parameter is re-gathered where it is used (reshard-after-forward); with
+  ``reshard_after_forward=False`` later consumers reuse the gathered operand the first node returns.
+* ``mm_nd(all_gather(x, rows), w)`` – sequence-sharded activations entering a column-parallel
+  projection → ``ag_mm`` modes 2 / 3 (several projections of the same gathered activation share the
+  gathered operand returned by the first).
+* ``reduce_scatter(mm_nd(..), rows)`` and ``reduce_scatter(mm_wgrad(..), 0)`` – row-parallel
+  projection with a sequence-sharded result, and weight gradient with gradient reduce-scatter →
+  ``apb200_comm::mm_rs`` modes 0 / 1 / 2.
+
+Reference counterpart: ``micro_pipeline_tp_pass`` (autoparallel/graph_passes/async_tp/asynctp.py:
+1265-1329), which only handles gathered *activations* and decomposes into host-side pipelines; this
+pass also covers gathered weights and targets single-kernel implementations.
+"""
+from __future__ import annotations
+
+import operator
+
+import torch
+import torch.fx as fx
+
+from ...runtime import comm_ops
+
+apb = torch.ops.apb200
+comm = comm_ops.ops
+
+
+def _rows_leading(shape, dim) -> bool:
+    """True when ``dim`` is the outermost non-unit dim of ``shape[:-1]`` (row blocks stay contiguous
+    after flattening the leading dims)."""
+    lead = list(shape[:-1])
+    if dim >= len(lead):
+        return False
+    return all(s == 1 for s in lead[:dim])
+
+
+def _tangent_dependent(gm: fx.GraphModule, tangents) -> set:
+    T = set(tangents)
+    for n in gm.graph.nodes:
+        if n.op == "call_function" and any(i in T for i in n.all_input_nodes):
+            T.add(n)
+    return T
+
+
+def fuse_collectives(gm: fx.GraphModule, tangents=(), reshard_after_forward: bool = True) -> dict:
+    g = gm.graph
+    stats = {"ag_mm": 0, "mm_rs": 0}
+    T = _tangent_dependent(gm, tangents)
+    order = {n: i for i, n in enumerate(g.nodes)}
+
+    def make_getitem(node, idx, like):
+        with g.inserting_after(node):
+            gi = g.call_function(operator.getitem, (node, idx))
+        gi.meta = dict(like.meta)
+        return gi
+
+    # ---- GEMM -> reduce-scatter
+    for rs in [n for n in g.nodes if n.op == "call_function" and n.target is comm.reduce_scatter.default]:
+        src, dim, group, n_ranks = rs.args
+        if not (isinstance(src, fx.Node) and src.op == "call_function" and len(src.users) == 1):
+            continue
+        if src.target is apb.mm_wgrad.default and dim == 0:
+            a, b, dt = src.args
+            mode = 2
+        elif src.target is apb.mm_nd.default and _rows_leading(src.meta["val"].shape, dim):
+            a, b, trans_b, dt = src.args
+            mode = 0 if trans_b else 1
+        else:
+            continue
+        with g.inserting_before(rs):
+            fused = g.call_function(comm.mm_rs.default, (a, b, mode, dt, 1.0, group, n_ranks))
+        fused.meta = dict(rs.meta)
+        rs.replace_all_uses_with(fused)
+        g.erase_node(rs)
+        g.erase_node(src)
+        stats["mm_rs"] += 1
+
+    # ---- all-gather -> GEMM
+    for ag in [n for n in g.nodes if n.op == "call_function" and n.target is comm.all_gather.default]:
+        x, dim, group, n_ranks = ag.args
+        users = sorted(ag.users, key=lambda u: order.get(u, 1 << 30))
+        val = ag.meta["val"]
+        shared = None  # node whose second output is the gathered operand, reusable by later users
+        for u in users:
+            if u.op != "call_function" or u.target is not apb.mm_nd.default:
+                continue
+            a, b, trans_b, dt = u.args
+            if b is ag and a is not ag and val.ndim == 2 and dim == 0:
+                mode = 0 if trans_b else 1
+                args = (a, x, mode, dt, group, n_ranks)
+                is_weight = True
+            elif a is ag and b is not ag and _rows_leading(val.shape, dim):
+                mode = 2 if trans_b else 3
+                args = (x, b, mode, dt, group, n_ranks)
+                is_weight = False
+            else:
+                continue
+            regather = is_weight and reshard_after_forward
+            if shared is not None and not regather and order[shared] < order[u] and (u in T) == (shared in T):
+                # reuse the operand gathered by an earlier fused node in the same pass direction
+                with g.inserting_before(u):
+                    full = g.call_function(operator.getitem, (shared, 1))
+                full.meta = dict(ag.meta)
+                u.replace_input_with(ag, full)
+                continue
+            with g.inserting_before(u):
+                fused = g.call_function(comm.ag_mm.default, args)
+            fused.meta = dict(u.meta)
+            fused.meta["val"] = (u.meta["val"], ag.meta["val"])
+            order[fused] = order[u]
+            if u in T:
+                T.add(fused)
+            y = make_getitem(fused, 0, u)
+            u.replace_all_uses_with(y)
+            g.erase_node(u)
+            stats["ag_mm"] += 1
+            if not regather:
+                shared = fused
+        if len(ag.users) == 0:
+            g.erase_node(ag)
+    g.lint()
+    gm.recompile()
+    return stats

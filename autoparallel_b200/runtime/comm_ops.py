@@ -241,3 +241,95 @@ START_OF = {
     ops.all_reduce.default: ops.all_reduce_start.default,
 }
 START_OPS = set(START_OF.values())
+
+
+# --------------------------------------------------------------------------------------------------
+# GEMM fused with the neighbouring collective.  One graph node = one kernel per rank when the group
+# has a symmetric-memory communicator (runtime/symm.py: communication CTAs + tcgen05 GEMM CTAs in
+# the same launch); otherwise the unfused composition below, which is also the CPU semantics.
+#   ag_mm  mode 0: y = x @ all_gather(w, 0)^T          (FSDP forward; w [N/n, K])
+#          mode 1: y = x @ all_gather(w, 0)            (FSDP backward dgrad; gathered rows = contraction)
+#          mode 2: y = all_gather(x, rows) @ w^T       (sequence-parallel activations -> column-parallel weight)
+#          mode 3: y = all_gather(x, rows) @ w
+#          returns (y, gathered operand)
+#   mm_rs  mode 0: reduce_scatter(a @ b^T, rows)   mode 1: reduce_scatter(a @ b, rows)
+#          mode 2: reduce_scatter(a^T @ b, rows)       (weight gradient + gradient reduce-scatter)
+# --------------------------------------------------------------------------------------------------
+lib.define("ag_mm(Tensor x, Tensor w, int mode, ScalarType out_dtype, str group, int group_size) -> (Tensor, Tensor)")
+lib.define("mm_rs(Tensor a, Tensor b, int mode, ScalarType out_dtype, float scale, str group, int group_size) -> Tensor")
+
+_apb = torch.ops.apb200
+
+
+def _ag_mm(x, w, mode, out_dtype, group, n):
+    be = _symm_backends.get(group)
+    if be is not None and x.is_cuda:
+        if mode in (0, 1) and be.can_fuse_gather(w) and x.dtype == torch.bfloat16:
+            return be.ag_gemm_b(x, w, out_dtype) if mode == 0 else be.ag_gemm_bk(x, w, out_dtype)
+        if mode in (2, 3) and x.dtype == torch.bfloat16 and be.can_fuse_gather(x.reshape(-1, x.shape[-1])):
+            lead = list(x.shape[:-1])
+            y, xf = be.ag_gemm_a(x, w, trans_b=(mode == 2), out_dtype=out_dtype)
+            d = next((i for i, s in enumerate(lead) if s != 1), 0)
+            lead[d] *= n
+            return y.view(*lead, y.shape[-1]), xf.view(*lead, x.shape[-1])
+    if mode in (0, 1):
+        wf = _all_gather(w, 0, group, n)
+        return _apb.mm_nd(x, wf, mode == 0, out_dtype), wf
+    d = next((i for i, s in enumerate(x.shape[:-1]) if s != 1), 0)
+    xf = _all_gather(x, d, group, n)
+    return _apb.mm_nd(xf, w, mode == 2, out_dtype), xf
+
+
+def _mm_rs(a, b, mode, out_dtype, scale, group, n):
+    be = _symm_backends.get(group)
+    if be is not None and a.is_cuda and a.dtype == torch.bfloat16 and out_dtype in (torch.float32, torch.bfloat16):
+        if mode == 2:
+            a2, b2 = a.reshape(-1, a.shape[-1]), b.reshape(-1, b.shape[-1])
+            if be.can_fuse_rs(a2.shape[1], b2.shape[1]) and a2.shape[1] % 8 == 0 and b2.shape[1] % 8 == 0:
+                return be.gemm_rs(a2, b2, True, True, out_dtype, scale)
+        else:
+            a2 = a.reshape(-1, a.shape[-1])
+            N = b.shape[0] if mode == 0 else b.shape[1]
+            if be.can_fuse_rs(a2.shape[0], N) and b.shape[1] % 8 == 0:
+                out = be.gemm_rs(a2, b, False, mode == 1, out_dtype, scale)
+                lead = list(a.shape[:-1])
+                d = next((i for i, s in enumerate(lead) if s != 1), 0)
+                lead[d] //= n
+                return out.view(*lead, N)
+    if mode == 2:
+        full = _apb.mm_wgrad(a, b, out_dtype)
+        d = 0
+    else:
+        full = _apb.mm_nd(a, b, mode == 0, out_dtype)
+        d = next((i for i, s in enumerate(a.shape[:-1]) if s != 1), 0)
+    out = _reduce_scatter(full, d, group, n)
+    return out * scale if scale != 1.0 else out
+
+
+def _ag_mm_meta(x, w, mode, out_dtype, group, n):
+    if mode in (0, 1):
+        wf = w.new_empty((w.shape[0] * n, w.shape[1]))
+        nn_ = wf.shape[0] if mode == 0 else wf.shape[1]
+        return x.new_empty((*x.shape[:-1], nn_), dtype=out_dtype), wf
+    lead = list(x.shape[:-1])
+    d = next((i for i, s in enumerate(lead) if s != 1), 0)
+    lead[d] *= n
+    nn_ = w.shape[0] if mode == 2 else w.shape[1]
+    return x.new_empty((*lead, nn_), dtype=out_dtype), x.new_empty((*lead, x.shape[-1]))
+
+
+def _mm_rs_meta(a, b, mode, out_dtype, scale, group, n):
+    if mode == 2:
+        return a.new_empty((a.shape[-1] // n, b.shape[-1]), dtype=out_dtype)
+    lead = list(a.shape[:-1])
+    d = next((i for i, s in enumerate(lead) if s != 1), 0)
+    lead[d] //= n
+    return a.new_empty((*lead, b.shape[0] if mode == 0 else b.shape[1]), dtype=out_dtype)
+
+
+for _name, _fn in (("ag_mm", _ag_mm), ("mm_rs", _mm_rs)):
+    lib.impl(_name, _fn, "CPU")
+    lib.impl(_name, _fn, "CUDA")
+lib.impl("ag_mm", _ag_mm_meta, "Meta")
+lib.impl("mm_rs", _mm_rs_meta, "Meta")
+FUSED_OPS = {ops.ag_mm.default, ops.mm_rs.default}

@@ -54,6 +54,7 @@ class SymmGroup:
         self.stream = torch.cuda.Stream(device=self.device)
         self.status = cuda_impl.status_buffer(self.device)
         self._pending: dict[int, torch.cuda.Event] = {}
+        self.async_twin: Optional[SymmGroup] = None
         self.bytes_moved = 0
 
     # ------------------------------------------------------------------ synchronous forms
@@ -218,6 +219,10 @@ class SymmGroup:
 
     # ------------------------------------------------------------------ split-phase forms
     def _async(self, fn, x, *args):
+        if self.async_twin is not None:
+            # split-phase collectives run on the communication stream with their own workspace and
+            # epoch sequence, so they never interleave with main-stream (fused / synchronous) ops
+            return getattr(self.async_twin, "_async")(getattr(self.async_twin, fn.__name__), x, *args)
         cur = torch.cuda.current_stream()
         self.stream.wait_stream(cur)
         with torch.cuda.stream(self.stream):
@@ -241,6 +246,8 @@ class SymmGroup:
 
     def wait(self, out: torch.Tensor) -> None:
         ev = self._pending.pop(out.data_ptr(), None)
+        if ev is None and self.async_twin is not None:
+            ev = self.async_twin._pending.pop(out.data_ptr(), None)
         if ev is not None:
             torch.cuda.current_stream().wait_event(ev)
 
@@ -253,6 +260,7 @@ def enable_for_group(group, workspace_bytes: int = 1 << 30, num_ctas: int = 32) 
     name = pg.group_name
     if name not in _groups:
         _groups[name] = SymmGroup(pg, workspace_bytes, num_ctas)
+        _groups[name].async_twin = SymmGroup(pg, workspace_bytes, num_ctas)
         comm_ops._symm_backends[name] = _groups[name]
     return _groups[name]
 
