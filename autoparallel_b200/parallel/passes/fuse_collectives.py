@@ -74,7 +74,7 @@ def fuse_collectives(gm: fx.GraphModule, tangents=(), reshard_after_forward: boo
         else:
             continue
         with g.inserting_before(rs):
-            fused = g.call_function(comm.mm_rs.default, (a, b, mode, dt, 1.0, group, n_ranks))
+            fused = g.call_function(comm.mm_rs.default, (a, b, mode, dim, dt, 1.0, group, n_ranks))
         fused.meta = dict(rs.meta)
         rs.replace_all_uses_with(fused)
         g.erase_node(rs)
@@ -93,11 +93,11 @@ def fuse_collectives(gm: fx.GraphModule, tangents=(), reshard_after_forward: boo
             a, b, trans_b, dt = u.args
             if b is ag and a is not ag and val.ndim == 2 and dim == 0:
                 mode = 0 if trans_b else 1
-                args = (a, x, mode, dt, group, n_ranks)
+                args = (a, x, mode, 0, dt, group, n_ranks)
                 is_weight = True
             elif a is ag and b is not ag and _rows_leading(val.shape, dim):
                 mode = 2 if trans_b else 3
-                args = (x, b, mode, dt, group, n_ranks)
+                args = (x, b, mode, dim, dt, group, n_ranks)
                 is_weight = False
             else:
                 continue

@@ -251,17 +251,18 @@ START_OPS = set(START_OF.values())
 #          mode 1: y = x @ all_gather(w, 0)            (FSDP backward dgrad; gathered rows = contraction)
 #          mode 2: y = all_gather(x, rows) @ w^T       (sequence-parallel activations -> column-parallel weight)
 #          mode 3: y = all_gather(x, rows) @ w
-#          returns (y, gathered operand)
+#          returns (y, gathered operand); ``dim`` is the gather dim of x (modes 2/3; 0 for modes 0/1)
 #   mm_rs  mode 0: reduce_scatter(a @ b^T, rows)   mode 1: reduce_scatter(a @ b, rows)
 #          mode 2: reduce_scatter(a^T @ b, rows)       (weight gradient + gradient reduce-scatter)
+#          ``dim`` is the scatter dim of the result; every dim before it has extent 1
 # --------------------------------------------------------------------------------------------------
-lib.define("ag_mm(Tensor x, Tensor w, int mode, ScalarType out_dtype, str group, int group_size) -> (Tensor, Tensor)")
-lib.define("mm_rs(Tensor a, Tensor b, int mode, ScalarType out_dtype, float scale, str group, int group_size) -> Tensor")
+lib.define("ag_mm(Tensor x, Tensor w, int mode, int dim, ScalarType out_dtype, str group, int group_size) -> (Tensor, Tensor)")
+lib.define("mm_rs(Tensor a, Tensor b, int mode, int dim, ScalarType out_dtype, float scale, str group, int group_size) -> Tensor")
 
 _apb = torch.ops.apb200
 
 
-def _ag_mm(x, w, mode, out_dtype, group, n):
+def _ag_mm(x, w, mode, dim, out_dtype, group, n):
     be = _symm_backends.get(group)
     if be is not None and x.is_cuda:
         if mode in (0, 1) and be.can_fuse_gather(w) and x.dtype == torch.bfloat16:
@@ -269,18 +270,16 @@ def _ag_mm(x, w, mode, out_dtype, group, n):
         if mode in (2, 3) and x.dtype == torch.bfloat16 and be.can_fuse_gather(x.reshape(-1, x.shape[-1])):
             lead = list(x.shape[:-1])
             y, xf = be.ag_gemm_a(x, w, trans_b=(mode == 2), out_dtype=out_dtype)
-            d = next((i for i, s in enumerate(lead) if s != 1), 0)
-            lead[d] *= n
+            lead[dim] *= n
             return y.view(*lead, y.shape[-1]), xf.view(*lead, x.shape[-1])
     if mode in (0, 1):
         wf = _all_gather(w, 0, group, n)
         return _apb.mm_nd(x, wf, mode == 0, out_dtype), wf
-    d = next((i for i, s in enumerate(x.shape[:-1]) if s != 1), 0)
-    xf = _all_gather(x, d, group, n)
+    xf = _all_gather(x, dim, group, n)
     return _apb.mm_nd(xf, w, mode == 2, out_dtype), xf
 
 
-def _mm_rs(a, b, mode, out_dtype, scale, group, n):
+def _mm_rs(a, b, mode, dim, out_dtype, scale, group, n):
     be = _symm_backends.get(group)
     if be is not None and a.is_cuda and a.dtype == torch.bfloat16 and out_dtype in (torch.float32, torch.bfloat16):
         if mode == 2:
@@ -290,40 +289,35 @@ def _mm_rs(a, b, mode, out_dtype, scale, group, n):
         else:
             a2 = a.reshape(-1, a.shape[-1])
             N = b.shape[0] if mode == 0 else b.shape[1]
-            if be.can_fuse_rs(a2.shape[0], N) and b.shape[1] % 8 == 0:
+            if be.can_fuse_rs(a2.shape[0], N) and b.shape[1] % 8 == 0 and a2.shape[1] % 8 == 0:
                 out = be.gemm_rs(a2, b, False, mode == 1, out_dtype, scale)
                 lead = list(a.shape[:-1])
-                d = next((i for i, s in enumerate(lead) if s != 1), 0)
-                lead[d] //= n
+                lead[dim] //= n
                 return out.view(*lead, N)
     if mode == 2:
         full = _apb.mm_wgrad(a, b, out_dtype)
-        d = 0
     else:
         full = _apb.mm_nd(a, b, mode == 0, out_dtype)
-        d = next((i for i, s in enumerate(a.shape[:-1]) if s != 1), 0)
-    out = _reduce_scatter(full, d, group, n)
+    out = _reduce_scatter(full, dim, group, n)
     return out * scale if scale != 1.0 else out
 
 
-def _ag_mm_meta(x, w, mode, out_dtype, group, n):
+def _ag_mm_meta(x, w, mode, dim, out_dtype, group, n):
     if mode in (0, 1):
         wf = w.new_empty((w.shape[0] * n, w.shape[1]))
         nn_ = wf.shape[0] if mode == 0 else wf.shape[1]
         return x.new_empty((*x.shape[:-1], nn_), dtype=out_dtype), wf
     lead = list(x.shape[:-1])
-    d = next((i for i, s in enumerate(lead) if s != 1), 0)
-    lead[d] *= n
+    lead[dim] *= n
     nn_ = w.shape[0] if mode == 2 else w.shape[1]
     return x.new_empty((*lead, nn_), dtype=out_dtype), x.new_empty((*lead, x.shape[-1]))
 
 
-def _mm_rs_meta(a, b, mode, out_dtype, scale, group, n):
+def _mm_rs_meta(a, b, mode, dim, out_dtype, scale, group, n):
     if mode == 2:
         return a.new_empty((a.shape[-1] // n, b.shape[-1]), dtype=out_dtype)
     lead = list(a.shape[:-1])
-    d = next((i for i, s in enumerate(lead) if s != 1), 0)
-    lead[d] //= n
+    lead[dim] //= n
     return a.new_empty((*lead, b.shape[0] if mode == 0 else b.shape[1]), dtype=out_dtype)
 
 
