@@ -10,8 +10,9 @@
 //                   per-shard "landed" counter before loading a tile of that shard
 //   FUSE_GATHER_B   same for B; with a K-major B the shards partition N, with an MN-major B
 //                   (stored [K, N]) they partition K, and the k-loop starts at the local shard
-//   FUSE_REDUCE_SCATTER  the epilogue adds each fp32 tile into the owner rank's accumulation
-//                   buffer in peer memory (red.add over NVLink) instead of storing it locally
+//   FUSE_REDUCE_SCATTER  the epilogue stores each fp32 tile into this rank's slot of the OWNER
+//                   rank's staging area in peer memory (16-byte stores over NVLink); the owner
+//                   sums the n slots once every rank has signalled completion
 #pragma once
 #include "ptx.cuh"
 #include "symm_proto.cuh"
@@ -24,6 +25,8 @@ constexpr int B_STAGE_BYTES = BN * BK * 2;
 constexpr int CHUNK_BYTES = BK * 128;  // one [BK x 64-element] MN-major box
 constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int EPI_STAGE_FLOATS = 32 * 33;  // per epilogue warp: one 32x32 fp32 block, padded
+constexpr int GEMM_FUSED_RS_SMEM_BYTES = GEMM_SMEM_BYTES + 4 * EPI_STAGE_FLOATS * 4;
 
 enum : int { FUSE_NONE = 0, FUSE_GATHER_A = 1, FUSE_GATHER_B = 2, FUSE_REDUCE_SCATTER = 3 };
 
@@ -121,6 +124,14 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      uint32_t landed_mask = 0;  // shards already seen as landed: checked once, never polled again
+      auto shard_ready = [&](int s) -> bool {
+        if (landed_mask & (1u << s)) return true;
+        if (!apbs::wait_ge<false>(f.landed + s, f.landed_target, p.status)) return false;
+        fence_proxy_async_global();
+        landed_mask |= 1u << s;
+        return true;
+      };
       for (int t = cta; t < num_tiles && ok; t += num_ctas) {
         int tm, tn;
         tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
@@ -132,26 +143,22 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
           const int r0 = (FUSE == FUSE_GATHER_A) ? m0 : n0;
           const int extent = (FUSE == FUSE_GATHER_A) ? min(BM, p.M - m0) : min(BN, p.N - n0);
           const int s0 = r0 / f.rows_per_shard, s1 = (r0 + extent - 1) / f.rows_per_shard;
-          for (int s = s0; s <= s1 && ok; ++s)
-            if (!apbs::wait_ge<false>(f.landed + s, f.landed_target, p.status)) ok = false;
+          for (int s = s0; s <= s1 && ok; ++s) ok = shard_ready(s);
           if (!ok) {
             *abort_flag = 1;
             break;
           }
-          fence_proxy_async_global();
         }
         for (int kb0 = 0; kb0 < num_kb; ++kb0) {
           const int kb = (kb0 + k_rot) % num_kb;
           if ((FUSE == FUSE_GATHER_B && B_MN) || (FUSE == FUSE_GATHER_A && A_MN)) {
             const int r0 = kb * BK;
             const int s0 = r0 / f.rows_per_shard, s1 = (min(r0 + BK, p.K) - 1) / f.rows_per_shard;
-            for (int s = s0; s <= s1 && ok; ++s)
-              if (!apbs::wait_ge<false>(f.landed + s, f.landed_target, p.status)) ok = false;
+            for (int s = s0; s <= s1 && ok; ++s) ok = shard_ready(s);
             if (!ok) {
               *abort_flag = 1;
               break;
             }
-            fence_proxy_async_global();
           }
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             ok = false;
@@ -264,8 +271,9 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
           *abort_flag = 1;
           break;
         }
+        // slot ``rank`` of the owner's staging area: [n][rows_per_rank][N] fp32
         rs_base = reinterpret_cast<float*>(f.peers.base[owner] + apbs::HEADER_BYTES) +
-                  (row - (long long)owner * f.rows_per_rank) * p.N;
+                  ((long long)f.rank * f.rows_per_rank + (row - (long long)owner * f.rows_per_rank)) * p.N;
       }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -273,19 +281,36 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
         const int col = n0 + c * 32;
+        if (FUSE == FUSE_REDUCE_SCATTER) {
+          // Transpose the warp's 32x32 block through shared memory so that every store instruction
+          // writes four 128-byte row segments: NVLink moves full segments instead of 16-byte crumbs.
+          float* stg = reinterpret_cast<float*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256) + (warp - 2) * EPI_STAGE_FLOATS;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) stg[lane * 33 + i] = __uint_as_float(r[i]);
+          __syncwarp();
+          const long long row0 = (long long)tm * BM + q * 32;  // first row of this warp's block
+          float* blk = rs_base - (long long)lane * p.N;         // rs_base points at this lane's row
+          const int sub = lane >> 3, seg = (lane & 7) * 4;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int rr = sub + 4 * j;
+            if (row0 + rr < p.M) {
+              const float* sp = stg + rr * 33 + seg;
+              float* dst = blk + (long long)rr * p.N + col + seg;
+              if (col + seg + 4 <= p.N) {
+                *reinterpret_cast<float4*>(dst) = make_float4(sp[0], sp[1], sp[2], sp[3]);
+              } else {
+                for (int e = 0; e < 4; ++e)
+                  if (col + seg + e < p.N) dst[e] = sp[e];
+              }
+            }
+          }
+          __syncwarp();
+          continue;
+        }
         if (row < p.M && col < p.N) {
           if (FUSE == FUSE_REDUCE_SCATTER) {
-            float* dst = rs_base + col;
-            if (col + 32 <= p.N && (p.N & 3) == 0) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                red_add_v4_sys(dst + 4 * i, __uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                               __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (col + i < p.N) atomicAdd_system(dst + i, __uint_as_float(r[i]));
-            }
+            // handled below (needs the whole warp)
           } else if (p.out_fp32) {
             float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
             if (col + 32 <= p.N && (p.ldc & 3) == 0) {

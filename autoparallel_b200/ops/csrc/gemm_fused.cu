@@ -8,10 +8,10 @@
 //       (weights [N/n, K] gathered along N) and in backward (the same weights consumed as a
 //       [K', N'] operand, i.e. gathered along the contraction dim) and the tensor-parallel
 //       activation gather (A rows).
-//   GEMM -> reduce-scatter (FUSE_REDUCE_SCATTER): the epilogue adds each fp32 accumulator tile into
-//       the owning rank's buffer with vector red.add over NVLink; communication CTAs zero that
-//       buffer up front, and once every rank has signalled that its contributions are complete,
-//       scale / cast the sum into the output shard.  Covers the gradient reduce-scatter (weight
+//   GEMM -> reduce-scatter (FUSE_REDUCE_SCATTER): the epilogue stores each fp32 accumulator tile into
+//       this rank's slot of the OWNING rank's staging area with 16-byte stores over NVLink; once
+//       every rank has signalled that its tiles are complete, the owner's communication CTAs sum
+//       the n slots, scale / cast, and write the output shard.  Covers the gradient reduce-scatter (weight
 //       gradient GEMM) and the row-parallel projection followed by a sequence-sharded output.
 //
 // No TMA multicast, no NCCL: remote data moves with ordinary peer loads / red.add issued from the
@@ -77,28 +77,31 @@ __device__ __forceinline__ void comm_gather(const GemmParams& p, const FuseParam
 __device__ __forceinline__ void comm_reduce_scatter(const GemmParams& p, const FuseParams& f, const CommParams& c, int cta) {
   using namespace apbs;
   uint8_t* my_ws = f.peers.base[f.rank];
-  float* acc = reinterpret_cast<float*>(my_ws + HEADER_BYTES);
+  const float* slots = reinterpret_cast<const float*>(my_ws + HEADER_BYTES);  // [n][rows_per_rank * N]
   __shared__ uint32_t ok_s;
   if (threadIdx.x == 0) ok_s = 1u;
   __syncthreads();
+  // my staging area is free once every peer has finished the previous collective
   if (threadIdx.x < f.n && threadIdx.x != f.rank)
     if (!wait_ge<true>(flag_ptr(my_ws, OFF_DONE, threadIdx.x), f.epoch - 1, p.status)) ok_s = 0u;
   __syncthreads();
   if (!ok_s) return;
-  const long long nvec = c.acc_elems >> 2;
-  const long long stride = (long long)c.comm_ctas * blockDim.x;
-  for (long long i = (long long)cta * blockDim.x + threadIdx.x; i < nvec; i += stride)
-    reinterpret_cast<float4*>(acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   if (arrive_is_last(flag_ptr(my_ws, OFF_COUNTERS, 2), c.t_phase0)) {
     if (threadIdx.x < f.n) st_release_sys(flag_ptr(f.peers.base[threadIdx.x], OFF_READY, f.rank), f.epoch);
   }
-  // every rank (this one included) signals when all of its tiles have been added
+  // every rank (this one included) signals when all of its tiles have been stored
   if (threadIdx.x < f.n)
     if (!wait_ge<true>(flag_ptr(my_ws, OFF_CONTRIB, threadIdx.x), f.epoch, p.status)) ok_s = 0u;
   __syncthreads();
   if (!ok_s) return;
+  const long long nvec = c.acc_elems >> 2;
+  const long long stride = (long long)c.comm_ctas * blockDim.x;
   for (long long i = (long long)cta * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    float4 v = reinterpret_cast<const float4*>(acc)[i];
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < f.n; ++k) {
+      const float4 x = reinterpret_cast<const float4*>(slots + (long long)k * c.acc_elems)[i];
+      v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+    }
     v.x *= c.scale; v.y *= c.scale; v.z *= c.scale; v.w *= c.scale;
     if (c.out_fp32) {
       reinterpret_cast<float4*>(c.out)[i] = v;
@@ -169,16 +172,17 @@ extern "C" int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, i
   if (fuse == FUSE_REDUCE_SCATTER) {
     if (rows_per_rank <= 0 || (rows_per_rank % BM) != 0 || (long long)rows_per_rank * n != M || (N & 3)) return 3;
     c.acc_elems = (long long)rows_per_rank * N;
-    if (c.acc_elems * 4 > stage_capacity) return 7;
+    if (c.acc_elems * 4 * n > stage_capacity) return 7;  // one fp32 slot per source rank
   } else {
     if ((shard_bytes & 15) || shard_bytes > stage_capacity || rows_per_shard <= 0) return shard_bytes > stage_capacity ? 7 : 3;
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int gemm_ctas = tiles < num_sms ? tiles : num_sms;
   const int grid = gemm_ctas + comm_ctas;
+  const int smem_bytes = fuse == FUSE_REDUCE_SCATTER ? GEMM_FUSED_RS_SMEM_BYTES : GEMM_SMEM_BYTES;
   auto launch = [&](auto kern) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
-    kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p, f, c);
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, p, f, c);
   };
 #define APB_LAUNCH_FUSED(FUSE)                                                        \
   do {                                                                                \

@@ -101,18 +101,27 @@ __global__ void __launch_bounds__(512) symm_collective_kernel(CollParams p) {
     const long long vec_per = p.inner_bytes >> 4;  // 16-B vectors per chunk per outer slice
     const long long total = p.outer * vec_per;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-      const long long o = i / vec_per, v = i % vec_per;
+      long long o = 0, v = i;
+      if (p.outer != 1) {
+        o = i / vec_per;
+        v = i - o * vec_per;
+      }
       const long long src_off = (o * n + p.rank) * p.inner_bytes + (v << 4);
       if (MODE == REDUCE_SCATTER) {
         if (p.elem_kind == 0) {
-          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-          for (int k = 0; k < n; ++k) {
-            const int peer = (p.rank + k) % n;
-            const uint8_t* base = (peer == p.rank) ? p.src : p.peers.base[peer] + HEADER_BYTES;
-            const float4 x = *reinterpret_cast<const float4*>(base + src_off);
-            acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+          float4 xs[MAX_RANKS];
+#pragma unroll
+          for (int k = 0; k < MAX_RANKS; ++k) {  // all loads issued before the first add
+            if (k < n) {
+              const int peer = (p.rank + k) % n;
+              const uint8_t* base = (peer == p.rank) ? p.src : p.peers.base[peer] + HEADER_BYTES;
+              xs[k] = *reinterpret_cast<const float4*>(base + src_off);
+            }
           }
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int k = 0; k < MAX_RANKS; ++k)
+            if (k < n) { acc.x += xs[k].x; acc.y += xs[k].y; acc.z += xs[k].z; acc.w += xs[k].w; }
           acc.x *= p.scale; acc.y *= p.scale; acc.z *= p.scale; acc.w *= p.scale;
           reinterpret_cast<float4*>(p.dst + o * p.inner_bytes)[v] = acc;
         } else {

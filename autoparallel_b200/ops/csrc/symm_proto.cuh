@@ -79,16 +79,21 @@ __device__ __forceinline__ bool arrive_is_last(uint32_t* counter, uint32_t targe
   return is_last_s != 0u;
 }
 
-// copy ``bytes`` (multiple of 16, both 16-B aligned) with CTAs [cta, cta+ncta) of ``nthreads`` threads
+// copy ``bytes`` (multiple of 16, both 16-B aligned) with CTAs [cta, cta+ncta) of this launch.
+// Eight independent 16-byte loads are in flight per thread before the first store, which is what
+// keeps an NVLink pull (about 2 us round trip) near link bandwidth with a few dozen CTAs.
 __device__ __forceinline__ void coop_copy16(uint8_t* dst, const uint8_t* src, long long bytes, int cta, int ncta) {
   const long long nvec = bytes >> 4;
   const uint4* s = reinterpret_cast<const uint4*>(src);
   uint4* d = reinterpret_cast<uint4*>(dst);
   const long long stride = (long long)ncta * blockDim.x;
   long long i = (long long)cta * blockDim.x + threadIdx.x;
-  for (; i + 3 * stride < nvec; i += 4 * stride) {
-    const uint4 a = s[i], b = s[i + stride], c = s[i + 2 * stride], e = s[i + 3 * stride];
-    d[i] = a; d[i + stride] = b; d[i + 2 * stride] = c; d[i + 3 * stride] = e;
+  for (; i + 7 * stride < nvec; i += 8 * stride) {
+    uint4 v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = s[i + k * stride];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) d[i + k * stride] = v[k];
   }
   for (; i < nvec; i += stride) d[i] = s[i];
 }

@@ -154,7 +154,7 @@ class SymmGroup:
     def _num_sms(self):
         return torch.cuda.get_device_properties(self.device).multi_processor_count
 
-    fused_comm_ctas = 16
+    fused_comm_ctas = 64
 
     def can_fuse_gather(self, shard: torch.Tensor) -> bool:
         nbytes = shard.numel() * shard.element_size()
@@ -202,7 +202,7 @@ class SymmGroup:
         return out
 
     def can_fuse_rs(self, M: int, N: int) -> bool:
-        return M % (self.n * 128) == 0 and N % 8 == 0 and (M // self.n) * N * 4 <= self.capacity
+        return M % (self.n * 128) == 0 and N % 8 == 0 and M * N * 4 <= self.capacity  # n fp32 slots of [M/n, N]
 
     def _fallback(self, kind, x, *dims):
         n, g = self.n, self.group_name
