@@ -1,0 +1,204 @@
+"""Mixture-of-experts decoder with expert parallelism through ``local_map``.
+
+Config of record: 12 layers, d_model 2048, 16 query / 4 KV heads, RoPE, RMSNorm, vocab 102400;
+every FFN is MoE with 64 routed SwiGLU experts (hidden 1408), softmax top-8 router, plus one
+always-on shared expert.  The dense parts (attention, shared expert, norms, embeddings) are sharded
+by the planner; the routed-expert block is one ``local_map`` region – route → dispatch all-to-all →
+expert FFN on the local experts → combine all-to-all → weighted scatter-add – with tokens
+``Shard(0)`` and expert weights ``Shard(0)`` on the expert-parallel mesh axis.
+
+Dispatch is **capacity based**: each (source rank, expert) pair owns a fixed slot count
+``C = ceil(capacity_factor · tokens · top_k / num_experts)``; assignments beyond the slot count are
+dropped (their gate weight contributes nothing).  Shapes are therefore static – no device→host
+sync for split sizes in any layer and the step is CUDA-graph capturable – where the reference
+exchanges counts and then syncs to the host for variable all-to-all splits
+(autoparallel/_testing/models/dsv3.py:552-616; routing :388-444; region :620-703).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.distributed.tensor.placement_types import Replicate, Shard
+
+from .. import ops as K
+from ..collectives import all_to_all, axis_size, local_map
+from .llama3 import Attention, LlamaConfig, RMSNorm, rope_tables
+
+
+@dataclass
+class MoEConfig:
+    dim: int = 2048
+    n_layers: int = 12
+    n_heads: int = 16
+    n_kv_heads: int = 4
+    vocab_size: int = 102400
+    num_experts: int = 64
+    top_k: int = 8
+    expert_hidden: int = 1408
+    shared_hidden: int = 1408
+    capacity_factor: float = 1.25
+    norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    max_seq_len: int = 4096
+    init_std: float = 0.02
+    ep_axis: str = "ep"
+    router_bias_zipf: Optional[float] = None  # s of a Zipf(s) bias over experts (skewed-load runs)
+
+    def attn_cfg(self) -> LlamaConfig:
+        return LlamaConfig(dim=self.dim, n_layers=self.n_layers, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
+                           vocab_size=self.vocab_size, norm_eps=self.norm_eps, rope_theta=self.rope_theta,
+                           max_seq_len=self.max_seq_len, init_std=self.init_std)
+
+
+def moe_reference_config(**kw) -> MoEConfig:
+    return MoEConfig(**kw)
+
+
+def moe_debug(**kw) -> MoEConfig:
+    base = dict(dim=128, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=512, num_experts=8, top_k=2, expert_hidden=64,
+                shared_hidden=64, max_seq_len=64)
+    base.update(kw)
+    return MoEConfig(**base)
+
+
+def _expert_region(x, gate_w, gate_idx, w1, w3, w2, *, ep_axis: str, num_experts: int, capacity: int):
+    """Runs on local shards.  x [T, d] tokens of this rank; gate_w / gate_idx [T, k]; w1, w3
+    [E_loc, d, h], w2 [E_loc, h, d] local experts.  Returns [T, d]."""
+    T, d = x.shape
+    k = gate_idx.shape[1]
+    n = axis_size(ep_axis)
+    e_loc = num_experts // n
+    flat_e = gate_idx.reshape(-1)                                   # [T*k] expert of each assignment
+    order = torch.argsort(flat_e, stable=True)
+    sorted_e = flat_e[order]
+    counts = torch.zeros(num_experts, dtype=torch.long, device=x.device).index_add(0, flat_e, torch.ones_like(flat_e))
+    starts = torch.cumsum(counts, 0) - counts
+    pos_sorted = torch.arange(T * k, device=x.device) - starts[sorted_e]
+    pos = torch.empty_like(pos_sorted)
+    pos[order] = pos_sorted                                         # slot of each assignment inside its expert
+    keep = pos < capacity
+    slot = torch.where(keep, flat_e * capacity + pos, torch.full_like(pos, num_experts * capacity))
+    tok = torch.arange(T * k, device=x.device) // k
+    send = x.new_zeros(num_experts * capacity + 1, d)
+    send = send.index_copy(0, slot, x[tok])[:-1]                    # [E*C, d]; dropped rows land in the spare row
+    send = send.view(n, e_loc * capacity, d)
+    recv = all_to_all(send.reshape(n * e_loc * capacity, d), ep_axis, 0, 0).view(n, e_loc, capacity, d)
+    h = recv.permute(1, 0, 2, 3).reshape(e_loc, n * capacity, d)    # expert-major
+    a = torch.bmm(h, w1)
+    b = torch.bmm(h, w3)
+    y = torch.bmm(F.silu(a) * b, w2)                                # [E_loc, n*C, d]
+    back = y.view(e_loc, n, capacity, d).permute(1, 0, 2, 3).reshape(n * e_loc * capacity, d)
+    got = all_to_all(back, ep_axis, 0, 0)                           # [E*C, d] in this rank's slot order
+    got = torch.cat([got, got.new_zeros(1, d)], 0)
+    per_assign = got[slot] * (gate_w.reshape(-1, 1) * keep.unsqueeze(1)).to(got.dtype)
+    out = torch.zeros_like(x).index_add(0, tok, per_assign)
+    return out
+
+
+class MoEFFN(nn.Module):
+    def __init__(self, cfg: MoEConfig):
+        super().__init__()
+        self.cfg = cfg
+        E, d, h = cfg.num_experts, cfg.dim, cfg.expert_hidden
+        self.router = nn.Linear(d, E, bias=False)
+        self.register_buffer("router_bias", torch.zeros(E), persistent=True)
+        self.w1 = nn.Parameter(torch.empty(E, d, h))
+        self.w3 = nn.Parameter(torch.empty(E, d, h))
+        self.w2 = nn.Parameter(torch.empty(E, h, d))
+        self.shared_w1 = nn.Linear(d, cfg.shared_hidden, bias=False)
+        self.shared_w3 = nn.Linear(d, cfg.shared_hidden, bias=False)
+        self.shared_w2 = nn.Linear(cfg.shared_hidden, d, bias=False)
+
+    def forward(self, x):
+        cfg = self.cfg
+        b, s, d = x.shape
+        scores = torch.softmax((self.router(x).float() + self.router_bias), dim=-1)
+        gate_w, gate_idx = torch.topk(scores, cfg.top_k, dim=-1)
+        gate_w = gate_w / gate_w.sum(-1, keepdim=True)
+        shared = self.shared_w2(K.swiglu(self.shared_w1(x), self.shared_w3(x)))
+        tokens_per_rank = (b * s) // axis_size(cfg.ep_axis)
+        capacity = max(1, math.ceil(cfg.capacity_factor * tokens_per_rank * cfg.top_k / cfg.num_experts))
+
+        # Argument order = order of first use inside the region: the graph capture lists the region's
+        # inputs in that order and insists that the declared placements line up with it.
+        def region(gi, xf, w1, w3, w2, gw):
+            return _expert_region(xf, gw, gi, w1, w3, w2, ep_axis=cfg.ep_axis, num_experts=cfg.num_experts, capacity=capacity)
+
+        tok_pl = (Shard(0),)
+        routed = local_map(region, out_placements=(tok_pl,), in_placements=(tok_pl,) * 6)(
+            gate_idx.reshape(b * s, -1), x.reshape(b * s, d), self.w1, self.w3, self.w2, gate_w.to(x.dtype).reshape(b * s, -1))
+        return shared + routed.view(b, s, d)
+
+    def init_weights(self, std: float):
+        nn.init.normal_(self.router.weight, mean=0.0, std=std)
+        for w in (self.w1, self.w3, self.w2):
+            nn.init.normal_(w, mean=0.0, std=std)
+        for lin in (self.shared_w1, self.shared_w3, self.shared_w2):
+            nn.init.normal_(lin.weight, mean=0.0, std=std)
+        if self.cfg.router_bias_zipf:
+            ranks = torch.arange(1, self.cfg.num_experts + 1, dtype=torch.float32, device=self.router_bias.device)
+            p = ranks.pow(-self.cfg.router_bias_zipf)
+            self.router_bias = (p / p.sum()).log() - (p / p.sum()).log().mean()
+        else:
+            self.router_bias = torch.zeros_like(self.router_bias)
+
+
+class MoEBlock(nn.Module):
+    def __init__(self, cfg: MoEConfig):
+        super().__init__()
+        self.attention = Attention(cfg.attn_cfg())
+        self.moe = MoEFFN(cfg)
+        self.attention_norm = RMSNorm(cfg.dim, cfg.norm_eps)
+        self.ffn_norm = RMSNorm(cfg.dim, cfg.norm_eps)
+        self.std = cfg.init_std
+
+    def forward(self, x, cos, sin):
+        h = x + self.attention(self.attention_norm(x), cos, sin)
+        return h + self.moe(self.ffn_norm(h))
+
+    def init_weights(self):
+        self.attention_norm.init_weights()
+        self.ffn_norm.init_weights()
+        self.attention.init_weights(self.std, self.std)
+        self.moe.init_weights(self.std)
+
+
+class MoETransformer(nn.Module):
+    def __init__(self, cfg: MoEConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.tok_embeddings = nn.Embedding(cfg.vocab_size, cfg.dim)
+        self.layers = nn.ModuleDict({str(i): MoEBlock(cfg) for i in range(cfg.n_layers)})
+        self.norm = RMSNorm(cfg.dim, cfg.norm_eps)
+        self.output = nn.Linear(cfg.dim, cfg.vocab_size, bias=False)
+        cos, sin = rope_tables(cfg.dim // cfg.n_heads, cfg.max_seq_len, cfg.rope_theta)
+        self.register_buffer("rope_cos", cos, persistent=False)
+        self.register_buffer("rope_sin", sin, persistent=False)
+
+    def forward(self, tokens, labels=None):
+        s = tokens.shape[1]
+        cos, sin = self.rope_cos[:s], self.rope_sin[:s]
+        h = self.tok_embeddings(tokens)
+        for layer in self.layers.values():
+            h = layer(h, cos, sin)
+        logits = self.output(self.norm(h))
+        if labels is None:
+            return logits
+        return K.cross_entropy(logits, labels)
+
+    def init_weights(self, seed: Optional[int] = None):
+        if seed is not None:
+            torch.manual_seed(seed)
+        cfg = self.cfg
+        cos, sin = rope_tables(cfg.dim // cfg.n_heads, cfg.max_seq_len, cfg.rope_theta, device=self.rope_cos.device)
+        self.rope_cos, self.rope_sin = cos, sin
+        nn.init.normal_(self.tok_embeddings.weight, mean=0.0, std=cfg.init_std)
+        for layer in self.layers.values():
+            layer.init_weights()
+        self.norm.init_weights()
+        nn.init.normal_(self.output.weight, mean=0.0, std=cfg.init_std)

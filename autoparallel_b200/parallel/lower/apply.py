@@ -125,6 +125,29 @@ class _Redistributor:
         return cur
 
 
+def _inline_region(g: fx.Graph, body: fx.GraphModule, args) -> fx.Node:
+    """Copy the body of a ``local_map`` region (already traced on local shapes) into ``g`` and return
+    a node producing the tuple of its outputs."""
+    env: dict[fx.Node, Any] = {}
+    it = iter(args)
+    out = None
+    for n in body.graph.nodes:
+        if n.op == "placeholder":
+            env[n] = next(it)
+        elif n.op == "output":
+            vals = fx.node.map_arg(n.args[0], lambda a: env[a])
+            out = g.call_function(_make_tuple, tuple(vals) if isinstance(vals, (tuple, list)) else (vals,))
+        elif n.op == "get_attr":
+            raise NotImplementedError("local_map bodies that close over tensors are not supported; pass them as arguments")
+        else:
+            env[n] = g.node_copy(n, lambda a: env[a])
+    return out
+
+
+def _make_tuple(*xs):
+    return tuple(xs)
+
+
 def _local_val(val, spec: Optional[DTensorSpec], mesh):
     if not isinstance(val, torch.Tensor) or spec is None:
         return val
@@ -199,7 +222,12 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
                 else:
                     new_args[pos] = list(lval.shape)
                 new_args = tuple(new_args)
-            nn_ = new_g.call_function(node.target, new_args, new_kwargs)
+            from ..strategies.local_map_rules import is_local_map_node, local_map_body
+
+            if is_local_map_node(node):
+                nn_ = _inline_region(new_g, local_map_body(node), new_args)
+            else:
+                nn_ = new_g.call_function(node.target, new_args, new_kwargs)
             nn_.meta = dict(node.meta)
             nn_.meta["val"] = lval
             nn_.meta["apb200_placements"] = (

@@ -182,7 +182,7 @@ class ShardingOptimizer:
     def _build_costs(self) -> None:
         for n in self.nodes:
             st = self.strats[n].strategies
-            if n.op == "call_function":
+            if n.op == "call_function" and isinstance(n.target, torch._ops.OpOverload):
                 self._node_cost[n] = np.array([compute_cost.strategy_compute_cost(n, s) for s in st], dtype=np.float64)
             else:
                 self._node_cost[n] = np.zeros(len(st))

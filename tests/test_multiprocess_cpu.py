@@ -1,0 +1,203 @@
+"""Numerical equivalence of the parallel module with the single-device model, on real (gloo)
+process groups: loss and every parameter gradient, 1-D and 2-D meshes, both executors, the MoE
+model with expert parallelism, and a checkpoint round trip through torch.distributed.checkpoint."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _init(rank, ws, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(ws))
+    dist.init_process_group("gloo", rank=rank, world_size=ws)
+
+
+def _llama_worker(rank, ws, shape, executor, mp_policy, port, q):
+    _init(rank, ws, port)
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Replicate, Shard
+
+    from autoparallel_b200 import AutoParallel, ForwardInputs
+    from autoparallel_b200.models.llama3 import Transformer, llama3_debug
+    from autoparallel_b200.parallel.frontend.mp_cast import MPPolicy
+
+    mesh = init_device_mesh("cpu", shape, mesh_dim_names=("dp", "tp")[: len(shape)])
+    cfg = llama3_debug()
+    B, S = 8, 64
+    with torch.device("meta"):
+        m = Transformer(cfg)
+
+    def input_fn():
+        return ForwardInputs((torch.randint(0, cfg.vocab_size, (B, S)),), {"labels": torch.randint(0, cfg.vocab_size, (B, S))})
+
+    pol = MPPolicy(torch.bfloat16, torch.float32) if mp_policy else None
+    with AutoParallel(m, input_fn, mesh, pol) as ap:
+        ap.add_parameter_memory_constraint()
+        ap.add_input_constraints([(Shard(0),) + (Replicate(),) * (mesh.ndim - 1)] * 2)
+        ap.optimize_placement()
+        pm = ap.apply_placement(executor=executor)
+    pm.to_empty(device="cpu")
+    pm.init_weights(seed=0)
+    torch.manual_seed(1)
+    tok = torch.randint(0, cfg.vocab_size, (B, S))
+    lab = torch.randint(0, cfg.vocab_size, (B, S))
+    r0 = mesh.get_local_rank(0)
+    loss = pm(tok.chunk(shape[0], 0)[r0], labels=lab.chunk(shape[0], 0)[r0])
+    loss.backward()
+    ref = Transformer(cfg)
+    ref.init_weights(seed=0)
+    rl = ref(tok, lab)
+    rl.backward()
+    worst = 0.0
+    for (n, p), (n2, p2) in zip(pm.named_parameters(), ref.named_parameters()):
+        assert n == n2
+        assert torch.equal(p.full_tensor(), p2), n  # init_weights gives the same values under any plan
+        g = p.grad.full_tensor().float()
+        worst = max(worst, ((g - p2.grad).abs().max() / (p2.grad.abs().max() + 1e-12)).item())
+    with torch.no_grad():
+        inf = pm(tok.chunk(shape[0], 0)[r0], labels=lab.chunk(shape[0], 0)[r0])
+    if rank == 0:
+        q.put((loss.item(), rl.item(), worst, inf.item(), isinstance(pm, Transformer)))
+    dist.destroy_process_group()
+
+
+def _run(fn, ws, *args):
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = 29600 + (os.getpid() % 300)
+    mp.spawn(fn, args=(ws, *args, port, q), nprocs=ws, join=True)
+    return q.get()
+
+
+@pytest.mark.parametrize("shape,executor", [((2,), "graph"), ((4,), "streams"), ((2, 2), "graph")])
+def test_llama_matches_single_device(shape, executor):
+    ws = 1
+    for s in shape:
+        ws *= s
+    loss, ref, worst, inf, is_user_class = _run(_llama_worker, ws, shape, executor, False)
+    assert abs(loss - ref) < 1e-5
+    assert worst < 1e-4
+    assert abs(inf - ref) < 1e-5  # forward-only graph under no_grad agrees with the training graph
+    assert is_user_class
+
+
+def test_llama_mixed_precision_close_to_fp32():
+    loss, ref, worst, inf, _ = _run(_llama_worker, 2, (2,), "graph", True)
+    assert abs(loss - ref) < 5e-2
+    assert worst < 0.15
+
+
+def _moe_worker(rank, ws, port, q):
+    _init(rank, ws, port)
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Shard
+
+    from autoparallel_b200 import AutoParallel, ForwardInputs
+    from autoparallel_b200.models.moe import MoETransformer, moe_debug
+
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("ep",))
+    cfg = moe_debug(capacity_factor=8.0)  # room for every assignment: nothing is dropped
+    B, S = 4, 32
+    with torch.device("meta"):
+        m = MoETransformer(cfg)
+
+    def input_fn():
+        return ForwardInputs((torch.randint(0, cfg.vocab_size, (B, S)),), {"labels": torch.randint(0, cfg.vocab_size, (B, S))})
+
+    with AutoParallel(m, input_fn, mesh) as ap:
+        ap.add_parameter_memory_constraint()
+        ap.add_input_constraints([(Shard(0),)] * 2)
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+        n_a2a = ap.lowered.num_collectives["all_to_all"]
+    pm.to_empty(device="cpu")
+    pm.init_weights(seed=0)
+    torch.manual_seed(1)
+    tok = torch.randint(0, cfg.vocab_size, (B, S))
+    lab = torch.randint(0, cfg.vocab_size, (B, S))
+    loss = pm(tok.chunk(ws, 0)[rank], labels=lab.chunk(ws, 0)[rank])
+    loss.backward()
+    gn = sum(p.grad.full_tensor().float().pow(2).sum() for p in pm.parameters()).sqrt().item()
+    if rank == 0:
+        q.put((loss.item(), gn, n_a2a))
+    dist.destroy_process_group()
+
+
+def test_moe_expert_parallel_matches_one_rank():
+    l2, g2, _ = _run(_moe_worker, 2)
+    l1, g1, _ = _run(_moe_worker, 1)
+    assert abs(l2 - l1) < 1e-4
+    assert abs(g2 - g1) / g1 < 1e-3
+
+
+def _dcp_worker(rank, ws, tmp, port, q):
+    _init(rank, ws, port)
+    import torch.distributed.checkpoint as dcp
+    from torch.distributed.checkpoint.state_dict import get_state_dict, set_state_dict
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Shard
+
+    from autoparallel_b200 import AutoParallel, ForwardInputs
+    from autoparallel_b200.models.llama3 import Transformer, llama3_debug
+    from autoparallel_b200.optim import AdamW
+
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("dp",))
+    cfg = llama3_debug()
+    B, S = 4, 32
+
+    def build():
+        with torch.device("meta"):
+            m = Transformer(cfg)
+
+        def input_fn():
+            return ForwardInputs((torch.randint(0, cfg.vocab_size, (B, S)),), {"labels": torch.randint(0, cfg.vocab_size, (B, S))})
+
+        with AutoParallel(m, input_fn, mesh) as ap:
+            ap.add_parameter_memory_constraint()
+            ap.add_input_constraints([(Shard(0),)] * 2)
+            ap.optimize_placement()
+            pm = ap.apply_placement()
+        pm.to_empty(device="cpu")
+        return pm
+
+    torch.manual_seed(3)
+    tok = torch.randint(0, cfg.vocab_size, (B, S)).chunk(ws, 0)[rank]
+    pm = build()
+    pm.init_weights(seed=0)
+    opt = AdamW(pm.parameters(), lr=1e-2)
+    for _ in range(2):
+        pm(tok, labels=tok).backward()
+        opt.step()
+        opt.zero_grad()
+    msd, osd = get_state_dict(pm, opt)
+    dcp.save({"model": msd, "optim": osd}, checkpoint_id=tmp)
+    pm(tok, labels=tok).backward()
+    opt.step()
+    opt.zero_grad()
+    want = pm(tok, labels=tok).item()
+    # fresh module + optimizer, load, repeat the third step
+    pm2 = build()
+    pm2.init_weights(seed=123)
+    opt2 = AdamW(pm2.parameters(), lr=1e-2)
+    pm2(tok, labels=tok).backward()
+    opt2.step()
+    opt2.zero_grad()  # materialise optimizer state so it can be loaded into
+    msd2, osd2 = get_state_dict(pm2, opt2)
+    state = {"model": msd2, "optim": osd2}
+    dcp.load(state, checkpoint_id=tmp)
+    set_state_dict(pm2, opt2, model_state_dict=state["model"], optim_state_dict=state["optim"])
+    pm2(tok, labels=tok).backward()
+    opt2.step()
+    opt2.zero_grad()
+    got = pm2(tok, labels=tok).item()
+    if rank == 0:
+        q.put((want, got))
+    dist.destroy_process_group()
+
+
+def test_dcp_round_trip_of_sharded_params_and_optimizer_state(tmp_path):
+    want, got = _run(_dcp_worker, 2, str(tmp_path / "ckpt"))
+    assert abs(want - got) < 1e-5
