@@ -82,6 +82,7 @@ class AutoParallel:
         activation_checkpointing: str = "none",
         plan_device: Optional[str] = None,
         fuse_collectives: bool = True,
+        bucket_collectives: bool = False,
     ):
         if dynamic:
             raise NotImplementedError(
@@ -98,6 +99,8 @@ class AutoParallel:
         self.activation_checkpointing = activation_checkpointing
         self.plan_device = plan_device
         self.fuse_collectives = fuse_collectives
+        self.bucket_collectives = bucket_collectives
+        self.bucket_stats = {}
         self.fusion_stats = {}
         model = clone_model_for_tracing(model)
         if self.mp_policy is not None:
@@ -222,6 +225,11 @@ class AutoParallel:
         if self.fuse_collectives:
             self.fusion_stats = fuse_collectives(lowered.gm, lowered.joint.tangent_nodes, self.reshard_after_forward)
             changed += sum(self.fusion_stats.values())
+        if self.bucket_collectives:
+            from .parallel.passes.bucketing import bucket_collectives
+
+            self.bucket_stats = bucket_collectives(lowered.gm)
+            changed += self.bucket_stats["members"]
         if changed:
             lowered.joint = index_joint_graph(lowered.gm, self.joint.traced_inputs, self.joint.out_spec)
         mark_fsdp_recompute(lowered.joint, self.reshard_after_forward)

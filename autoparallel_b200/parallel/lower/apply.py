@@ -278,7 +278,9 @@ def sink_input_chains(gm: fx.GraphModule) -> int:
     input_only = {n for n in nodes if n.op == "placeholder"}
     chain = []
     for n in nodes:
-        if n.op == "call_function" and n.all_input_nodes and all(i in input_only for i in n.all_input_nodes):
+        # single-input chains only (cast / gather / view of one graph input): anything that joins two
+        # tensors is real computation, not parameter preparation
+        if n.op == "call_function" and len(n.all_input_nodes) == 1 and n.all_input_nodes[0] in input_only:
             input_only.add(n)
             chain.append(n)
     moved = 0

@@ -69,7 +69,8 @@ def schedule_for_streams(gm: fx.GraphModule, mesh=None, config: Optional[Overlap
     # ---- input-only chains (everything a prefetchable start depends on)
     input_only: set[fx.Node] = set(placeholders)
     for n in body:
-        if n.op == "get_attr" or all(i in input_only for i in n.all_input_nodes):
+        # single-input chains from a graph input (parameter -> cast -> gather -> view)
+        if n.op == "get_attr" or (len(n.all_input_nodes) == 1 and n.all_input_nodes[0] in input_only):
             if n.op == "get_attr" or n.target is not comm_ops.ops.comm_wait.default:
                 input_only.add(n)
     ag_start = comm_ops.ops.all_gather_start.default
