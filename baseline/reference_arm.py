@@ -1,15 +1,156 @@
-"""Reference arm of the benchmark: the unmodified reference package from ``baseline/_ref``."""
+"""Reference arm of the benchmark: the unmodified reference package (``baseline/_ref/autoparallel``)
+driven through its own public API on the same metric and config as ``bench.py``'s own arm.
+
+Nothing of this framework is on that path: the model is the reference's own Llama-3
+(``autoparallel._testing.models.llama3.Transformer``), compute is ATen / cuBLAS / cuDNN, collectives
+are c10d functional collectives on NCCL, the optimizer is ``torch.optim.AdamW``.  The only foreign
+piece is ``baseline/shims/pulp.py``: the reference needs PuLP + the CBC binary for its ILP, neither
+exists in this offline image, so a PuLP-compatible layer over HiGHS stands in for the *solver*.
+If anything in the reference fails to import or run here, one ``unavailable`` line is printed.
+"""
+from __future__ import annotations
+
 import json
 import os
 import sys
+import time
+import traceback
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _unavailable(why: str) -> None:
+    if int(os.environ.get("RANK", 0)) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why[:300]}), flush=True)
 
 
 def run(args) -> None:
-    ref = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref")
-    rank = int(os.environ.get("RANK", 0))
+    ref = os.path.join(HERE, "_ref")
     if not os.path.isdir(os.path.join(ref, "autoparallel")):
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "reference is not installed under baseline/_ref"}))
-        return
+        return _unavailable("reference is not installed under baseline/_ref")
+    sys.path.insert(0, ref)
+    try:
+        import pulp  # noqa: F401
+    except ImportError:
+        sys.path.insert(0, os.path.join(HERE, "shims"))
+    try:
+        _run(args)
+    except Exception as e:  # the reference could not run in this image
+        tb = traceback.format_exc().strip().splitlines()
+        where = next((l.strip() for l in reversed(tb) if "autoparallel" in l and "File" in l), "")
+        _unavailable(f"{type(e).__name__}: {str(e)[:160]} {where[:100]}")
+        try:
+            import torch.distributed as dist
+
+            if dist.is_initialized():
+                dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def _run(args) -> None:
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+    from torch.distributed.tensor.placement_types import Shard
+
+    from autoparallel._testing.models.llama3 import Transformer, TransformerModelArgs
+    from autoparallel.api import AutoParallel
+
+    import bench  # clock sampler only
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29500")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    S = args.seq_len
+    margs = TransformerModelArgs(dim=4096, n_layers=args.layers or 32, n_heads=32, n_kv_heads=8, ffn_dim_multiplier=1.3,
+                                 multiple_of=1024, rope_theta=500000, vocab_size=128256, max_seq_len=S)
+    B_global = world
+    with torch.device("meta"):
+        model = Transformer(margs)
+
+    def input_fn():
+        return torch.randint(0, margs.vocab_size, (B_global, S), device="cuda")
+
+    mp_policy = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+    t0 = time.perf_counter()
+    with AutoParallel(model, input_fn, mesh, mp_policy) as autop:
+        autop.add_parameter_memory_constraint(low=None, high=None)
+        autop.add_input_constraints([(Shard(0),)])
+        autop.add_output_constraints([(Shard(0),)])
+        t1 = time.perf_counter()
+        placement = autop.optimize_placement()
+        ilp_s = time.perf_counter() - t1
+        parallel_mod = autop.apply_placement(placement)
+    plan_s = time.perf_counter() - t0
+    parallel_mod.to_empty(device="cuda")
+    parallel_mod.init_weights()
+    opt = torch.optim.AdamW(parallel_mod.parameters(), lr=3e-4, weight_decay=0.1)
+    g = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    host = [(torch.randint(0, margs.vocab_size, (1, S), generator=g).pin_memory(),
+             torch.randint(0, margs.vocab_size, (1, S), generator=g).pin_memory()) for _ in range(4)]
+    devs = [(t.cuda(), l.cuda()) for t, l in host]
+
+    def step(tok, lab):
+        logits = parallel_mod(tok)
+        loss = F.cross_entropy(logits.flatten(0, 1).float(), lab.flatten())
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def step_device(i):
+        return step(*devs[i % 4])
+
+    def step_e2e(i):
+        t, l = host[i % 4]
+        return step(t.cuda(non_blocking=True), l.cuda(non_blocking=True)).item()
+
+    for i in range(args.warmup):
+        step_device(i)
+    torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        last = None
+        for i in range(steps):
+            last = fn(i)
+        e.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = torch.tensor([s.elapsed_time(e)], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item(), last
+
+    sampler = bench.ClockSampler(local_rank)
     if rank == 0:
-        print(json.dumps({"impl": "reference", "unavailable": "reference arm not wired yet"}))
+        sampler.start()
+    ms_dev, _ = timed(step_device, args.steps)
+    ms_e2e, last = timed(step_e2e, args.steps)
+    clocks = sampler.stop() if rank == 0 else {}
+    tokens = B_global * S * args.steps
+    if rank == 0:
+        print(json.dumps({
+            "metric": "Llama-3-8B train tokens/s (auto plan)" if not args.layers else "llama3_8b reduced layers (NOT the headline config)",
+            "value": tokens / (ms_dev / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "impl": "reference",
+            "config": {"model": "llama3_8b" if not args.layers else f"llama3_8b[{args.layers} layers]", "global_batch": B_global, "seq_len": S,
+                       "parallelism": f"dp{world} (reference ILP; eager apply_placement; NCCL + cuBLAS/cuDNN)",
+                       "optimizer": "torch.optim.AdamW", "ilp_backend": "HiGHS behind a PuLP-compatible shim (CBC/PuLP absent offline)"},
+            "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": 2 * S * 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": 0, "clocks": clocks, "ilp_solve_s": ilp_s, "plan_total_s": round(plan_s, 2),
+            "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 1), "final_loss": float(last),
+        }), flush=True)
+    dist.destroy_process_group()
