@@ -1,0 +1,93 @@
+"""Offline what-if tool for the overlap scheduler.
+
+    python -m autoparallel_b200.tools.overlap_simulator --model llama3_8b --mesh 8 [--layers 4]
+        [--prefetch-depth 12] [--max-in-flight-gb 2] [--bucket] [--table colls.json] [--trace out.json]
+
+Plans the model on fake ranks (no GPU, no process group traffic), lowers it, partitions it, applies
+the bucketing / overlap passes with the given knobs and reports, for forward and backward: number
+of collectives by kind, simulated total / compute / communication / exposed-communication time and
+peak live bytes – before and after scheduling.  Collective times come from the α–β NVLink-5 model or
+from a measured table (``--table``, the format written by ``parallel.cost.calibrate``).
+Reference: autoparallel/tools/overlap_simulator/run.py (replays captured graphs through Inductor's
+scheduler with measured collective tables).
+"""
+from __future__ import annotations
+
+import argparse
+import copy
+import json
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "llama3_70b", "llama3_debug"])
+    ap.add_argument("--mesh", default="8", help="comma separated mesh shape, e.g. 8 or 2,4")
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--prefetch-depth", type=int, default=12)
+    ap.add_argument("--max-in-flight-gb", type=float, default=2.0)
+    ap.add_argument("--max-pending-reductions", type=int, default=6)
+    ap.add_argument("--bucket", action="store_true")
+    ap.add_argument("--table", default=None)
+    ap.add_argument("--trace", default=None)
+    ap.add_argument("--device", default="B200")
+    args = ap.parse_args(argv)
+
+    import torch
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Replicate, Shard
+    from torch.testing._internal.distributed.fake_pg import FakeStore
+
+    from .. import AutoParallel, ForwardInputs
+    from ..models import llama3
+    from ..parallel.frontend.mp_cast import MPPolicy
+    from ..parallel.lower.partition import partition_joint
+    from ..parallel.passes.overlap import OverlapConfig, exposed_collectives, schedule_for_streams
+    from ..utils.trace_sim import create_execution_trace, estimate_graph_metrics
+
+    shape = tuple(int(x) for x in args.mesh.split(","))
+    world = 1
+    for s in shape:
+        world *= s
+    if not dist.is_initialized():
+        dist.init_process_group("fake", store=FakeStore(), rank=0, world_size=world)
+    mesh = init_device_mesh("cpu", shape, mesh_dim_names=("dp", "tp", "cp")[: len(shape)])
+    cfg = getattr(llama3, args.model)(max_seq_len=args.seq_len)
+    if args.layers:
+        cfg.n_layers = args.layers
+    batch = args.batch or shape[0]
+    with torch.device("meta"):
+        model = llama3.Transformer(cfg)
+
+    def input_fn():
+        return ForwardInputs((torch.randint(0, cfg.vocab_size, (batch, args.seq_len)),),
+                             {"labels": torch.randint(0, cfg.vocab_size, (batch, args.seq_len))})
+
+    with AutoParallel(model, input_fn, mesh, MPPolicy(torch.bfloat16, torch.float32), plan_device=args.device,
+                      cost_model=args.table or "auto", bucket_collectives=args.bucket) as apx:
+        apx.add_parameter_memory_constraint()
+        apx.add_input_constraints([(Shard(0),) + (Replicate(),) * (mesh.ndim - 1)] * 2)
+        apx.optimize_placement()
+        lowered = apx.lower()
+        parts = partition_joint(lowered.joint)
+        ocfg = OverlapConfig(args.prefetch_depth, int(args.max_in_flight_gb * 2**30), args.max_pending_reductions)
+        report = {"plan": {"collectives": lowered.num_collectives, "fused": apx.fusion_stats, "buckets": apx.bucket_stats,
+                           "ilp_solve_s": apx.sharding_optimizer.timings.get("solve")}}
+        for name, gm in (("forward", parts.fw), ("backward", parts.bw)):
+            before = estimate_graph_metrics(gm, mesh, args.device)
+            sched = schedule_for_streams(copy.deepcopy(gm), mesh, ocfg)
+            after = estimate_graph_metrics(sched, mesh, args.device)
+            report[name] = {
+                "before": before.__dict__, "after": after.__dict__,
+                "exposed_collectives_after": exposed_collectives(sched),
+            }
+            if args.trace:
+                create_execution_trace(sched, mesh, args.trace.replace(".json", f"_{name}.json"), args.device)
+    print(json.dumps(report, indent=1, default=float))
+    return report
+
+
+if __name__ == "__main__":
+    main()
