@@ -93,6 +93,7 @@ def save_optimizer(optimizer, path: str) -> None:
         "edges": [(idx[c], slot, idx[p]) for c, slot, p in optimizer.edges],
         "edge_cost": [np.asarray(optimizer._edge_cost[(c, slot)]) for c, slot, p in optimizer.edges],
         "pairs": [(idx[a], idx[b]) for a, b in optimizer._pairs],
+        "param_ratios": _param_ratios(optimizer, idx),
         "classes": [optimizer._classes()[n] for n in optimizer.nodes] if optimizer.repeated_subgraphs else None,
         "constraints": [
             {"name": c.name, "kind": c.kind, "node": idx.get(c.node) if c.node is not None else None, "allowed": c.allowed,
@@ -106,6 +107,26 @@ def save_optimizer(optimizer, path: str) -> None:
     }
     torch.save(state, path)
     optimizer.timings["save"] = time.perf_counter() - t0
+
+
+def _param_ratios(optimizer, idx) -> list:
+    """(node index, [local/global element ratio per candidate placement]) for every parameter."""
+    import math
+
+    from ..parallel.strategies.dtensor_adapter import local_shape
+
+    out = []
+    for p in optimizer.joint.param_nodes.values():
+        if p not in idx:
+            continue
+        shape = list(p.meta["val"].shape)
+        total = max(1, math.prod(shape))
+        ratios = []
+        for s in optimizer.strats[p].strategies:
+            ls = local_shape(shape, optimizer.mesh.shape, s.output_spec.placements)
+            ratios.append(math.prod(ls) / total if ls is not None else 1.0)
+        out.append((idx[p], ratios))
+    return out
 
 
 class LoadedOptimizer:
@@ -179,6 +200,45 @@ class LoadedOptimizer:
                 vals += [1.0] * nc + [-1.0]
                 lo.append(0.0)
                 hi.append(0.0)
+                r += 1
+        # forward/backward twins share a placement
+        for a, b in st.get("pairs", []):
+            pa, pb = st["nodes"][a]["placements"], st["nodes"][b]["placements"]
+            for pl in set(pa) | set(pb):
+                ia = [k for k, x in enumerate(pa) if x == pl]
+                ib = [k for k, x in enumerate(pb) if x == pl]
+                if ia and ib:
+                    rows += [r] * (len(ia) + len(ib))
+                    cols += [y_off[a] + k for k in ia] + [y_off[b] + k for k in ib]
+                    vals += [1.0] * len(ia) + [-1.0] * len(ib)
+                    lo.append(0.0)
+                    hi.append(0.0)
+                    r += 1
+                else:
+                    for k in ia:
+                        ub[y_off[a] + k] = 0.0
+                    for k in ib:
+                        ub[y_off[b] + k] = 0.0
+        # parameters pinned by the user (saved constraints or ``extra_fixed``) do not count towards the memory band
+        pinned = {c["node"] for c in st["constraints"] if c["kind"] == "node"} | {self.names.index(n) for n in (extra_fixed or {})}
+        for cst in st["constraints"]:
+            if cst["kind"] != "memory":
+                continue
+            lo_sum = hi_sum = 0.0
+            first = True
+            for i, ratios in st.get("param_ratios", []):
+                if i in pinned:
+                    continue
+                best = min(ratios)
+                lo_sum += max(best, cst["low"])
+                hi_sum += max(best, cst["high"])
+                rows += [r] * len(ratios)
+                cols += [y_off[i] + k for k in range(len(ratios))]
+                vals += list(ratios)
+                first = False
+            if not first:
+                lo.append(lo_sum - 1e-6)
+                hi.append(hi_sum + 1e-6)
                 r += 1
         for cst in st["constraints"]:
             if cst["kind"] == "node" and cst["node"] is not None:
