@@ -43,6 +43,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--only", default=None, choices=["gemm_nt", "gemm_tn", "rms_norm_bwd", "xent_bwd"],
+                    help="run a single small case (what a profiler capture is taken on)")
     args = ap.parse_args()
     from autoparallel_b200.ops import cuda_impl, library as L
 
@@ -66,6 +68,25 @@ def main():
         print(f"{name:44s} {best:8.3f} ms  {extra}", flush=True)
 
     M = 8192
+    if args.only:
+        # one kernel, inputs larger than the 126 MB L2 but well under a GB, a handful of launches
+        if args.only in ("gemm_nt", "gemm_tn"):
+            ta = args.only == "gemm_tn"
+            mk = (lambda: (torch.randn(4096, M, device=dev, dtype=bf), torch.randn(4096, 4096, device=dev, dtype=bf))) if ta else \
+                (lambda: (torch.randn(M, 4096, device=dev, dtype=bf), torch.randn(4096, 4096, device=dev, dtype=bf)))
+            ms, best = time_fn(mk, lambda a, b: L.ops.gemm(a, b, ta, not ta, bf), iters=3, pool=2)
+            rec(f"{args.only} 8192x4096x4096", ms, best, flops=2.0 * M * 4096 * 4096)
+        elif args.only == "rms_norm_bwd":
+            mk = lambda: (torch.randn(M, 4096, device=dev, dtype=bf), torch.randn(M, 4096, device=dev, dtype=bf), torch.randn(4096, device=dev, dtype=bf), torch.rand(M, device=dev))
+            ms, best = time_fn(mk, lambda dy, x, w, r: L.ops.rms_norm_bwd(dy, x, w, r), iters=3, pool=2)
+            rec("rms_norm bwd 8192x4096", ms, best, nbytes=3 * M * 4096 * 2)
+        else:
+            V = 32064
+            mk = lambda: (torch.randn(M, device=dev), torch.randn(M, V, device=dev, dtype=bf), torch.randint(0, V, (M,), device=dev), torch.rand(M, device=dev) + 10)
+            ms, best = time_fn(mk, lambda g, lg, lb, lse: L.ops.cross_entropy_bwd(g, lg, lb, lse), iters=3, pool=2)
+            rec("cross_entropy bwd 8192x32064", ms, best, nbytes=2 * M * V * 2)
+        cuda_impl.check_status()
+        return
     shapes = [(M, 4096, 4096), (M, 14336, 4096), (M, 4096, 14336), (M, 1024, 4096)]
     if not args.quick:
         shapes.append((M, 128256, 4096))

@@ -110,15 +110,15 @@ __global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict
 // into ``dw_acc`` (fp32 [D], zeroed by the caller) with one atomicAdd per column per block.
 // Requires D <= blockDim.x * 8 * RMS_BWD_MAX_VEC.
 constexpr int RMS_BWD_MAX_VEC = 4;
-template <typename T>
+template <typename T, int NVEC>
 __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                                     const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_acc,
                                     long long rows, int D) {
   __shared__ float red[32];
-  float wreg[RMS_BWD_MAX_VEC][8];
-  float dwreg[RMS_BWD_MAX_VEC][8];
+  float wreg[NVEC][8];
+  float dwreg[NVEC][8];
 #pragma unroll
-  for (int j = 0; j < RMS_BWD_MAX_VEC; ++j) {
+  for (int j = 0; j < NVEC; ++j) {
     const int c = (threadIdx.x + j * blockDim.x) * 8;
 #pragma unroll
     for (int i = 0; i < 8; ++i) dwreg[j][i] = 0.f;
@@ -130,10 +130,10 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
     const T* xr = x + row * D;
     const T* gr = dy + row * D;
     const float r = rstd[row];
-    float xh[RMS_BWD_MAX_VEC][8], g[RMS_BWD_MAX_VEC][8];
+    float xh[NVEC][8], g[NVEC][8];
     float dot = 0.f;
 #pragma unroll
-    for (int j = 0; j < RMS_BWD_MAX_VEC; ++j) {
+    for (int j = 0; j < NVEC; ++j) {
       const int c = (threadIdx.x + j * blockDim.x) * 8;
       if (c < D) {
         Vec8<T> xv, gv; xv.load(xr + c); gv.load(gr + c);
@@ -149,7 +149,7 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
     }
     dot = block_sum(dot, red) / D;
 #pragma unroll
-    for (int j = 0; j < RMS_BWD_MAX_VEC; ++j) {
+    for (int j = 0; j < NVEC; ++j) {
       const int c = (threadIdx.x + j * blockDim.x) * 8;
       if (c < D) {
         float o[8];
@@ -160,7 +160,7 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
     }
   }
 #pragma unroll
-  for (int j = 0; j < RMS_BWD_MAX_VEC; ++j) {
+  for (int j = 0; j < NVEC; ++j) {
     const int c = (threadIdx.x + j * blockDim.x) * 8;
     if (c < D) {
 #pragma unroll
@@ -362,6 +362,25 @@ __global__ void adamw_kernel(const AdamTensor* __restrict__ tensors, const int2*
   }
 }
 
+// Launch configuration of rms_norm_bwd_kernel: as many threads as 8-element vectors in a row (up to
+// 1024) so each thread keeps ONE vector per operand in registers; that keeps the register count low
+// enough for several resident blocks per SM, which is what a latency-bound row loop needs.
+template <typename T>
+static inline int launch_rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_acc,
+                                      long long rows, int D, int num_sms, cudaStream_t st) {
+  int threads = 128;
+  while (threads * 8 < D && threads < 1024) threads *= 2;
+  const int nvec = (D + threads * 8 - 1) / (threads * 8);
+  if (nvec > RMS_BWD_MAX_VEC) return 3;
+  const int per_sm = threads >= 1024 ? 2 : (threads >= 512 ? 4 : 8);
+  const long long cap = (long long)num_sms * per_sm;
+  const int grid = (int)(rows < cap ? rows : cap);
+  if (nvec == 1) rms_norm_bwd_kernel<T, 1><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_acc, rows, D);
+  else if (nvec == 2) rms_norm_bwd_kernel<T, 2><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_acc, rows, D);
+  else rms_norm_bwd_kernel<T, 4><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_acc, rows, D);
+  return 0;
+}
+
 static inline int grid_for(long long work_items, int threads, int num_sms) {
   long long blocks = (work_items + threads - 1) / threads;
   long long cap = (long long)num_sms * 8;
@@ -397,14 +416,12 @@ int apb_rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, long lo
 int apb_rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw, float* dw_acc,
                      long long rows, int D, int is_bf16, int num_sms, cudaStream_t st) {
   if (D % 8) return 3;
-  int threads = 256;
-  while (threads * 8 * RMS_BWD_MAX_VEC < D && threads < 1024) threads *= 2;
-  if (threads * 8 * RMS_BWD_MAX_VEC < D) return 3;
+  if (D > 1024 * 8 * RMS_BWD_MAX_VEC) return 3;
   cudaMemsetAsync(dw_acc, 0, sizeof(float) * D, st);
   if (rows > 0) {
-    const int grid = (int)(rows < (long long)num_sms * 2 ? rows : (long long)num_sms * 2);
-    DISPATCH(is_bf16, rms_norm_bwd_kernel<T><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx,
-                                                                      dw_acc, rows, D));
+    int e;
+    DISPATCH(is_bf16, e = launch_rms_norm_bwd<T>(dy, x, w, rstd, dx, dw_acc, rows, D, num_sms, st));
+    if (e) return e;
   }
   if (is_bf16) cast_from_f32_kernel<bf16><<<grid_for(D / 8, 256, num_sms), 256, 0, st>>>(dw_acc, (bf16*)dw, D);
   else cudaMemcpyAsync(dw, dw_acc, sizeof(float) * D, cudaMemcpyDeviceToDevice, st);
@@ -531,15 +548,12 @@ extern "C" int apb_rms_norm_bwd_noalloc(const void* dy, const void* x, const voi
   }
   float* acc = g_noalloc_ptr[dev];
   const int num_sms = g_noalloc_sms[dev];
-  int threads = 256;
-  while (threads * 8 * RMS_BWD_MAX_VEC < D && threads < 1024) threads *= 2;
-  if (threads * 8 * RMS_BWD_MAX_VEC < D) return APB_NOALLOC_ERR_BAD_SHAPE;
   // the array keeps the previous call's sums: start from zero
   if (cudaMemsetAsync(acc, 0, sizeof(float) * D, st) != cudaSuccess) return APB_NOALLOC_ERR_LAUNCH;
   if (rows > 0) {
-    const int grid = (int)(rows < (long long)num_sms * 2 ? rows : (long long)num_sms * 2);
-    DISPATCH(is_bf16, rms_norm_bwd_kernel<T><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx,
-                                                                      acc, rows, D));
+    int e;
+    DISPATCH(is_bf16, e = launch_rms_norm_bwd<T>(dy, x, w, rstd, dx, acc, rows, D, num_sms, st));
+    if (e) return APB_NOALLOC_ERR_BAD_SHAPE;
   }
   if (is_bf16) {
     cast_from_f32_kernel<bf16><<<grid_for(D / 8, 256, num_sms), 256, 0, st>>>(acc, (bf16*)dw, D);

@@ -40,7 +40,7 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=None, help="debugging only: override the layer count (invalidates the metric)")
     ap.add_argument("--ac", default="auto", choices=["auto", "none", "selective", "full"])
-    ap.add_argument("--executor", default="graph", choices=["graph", "streams"])
+    ap.add_argument("--executor", default="streams", choices=["graph", "streams"])
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "symm"])
     return ap.parse_args()
 
