@@ -74,10 +74,57 @@ __device__ __forceinline__ void comm_gather(const GemmParams& p, const FuseParam
   }
 }
 
-__device__ __forceinline__ void comm_reduce_scatter(const GemmParams& p, const FuseParams& f, const CommParams& c, int cta) {
+// Final phase of GEMM -> reduce-scatter, executed by the GEMM CTAs once their tiles are done: wait
+// until every rank has signalled that its tiles are stored, then sum the n slots of this rank's
+// staging area into the output shard.  (All GEMM CTAs are resident at that point: one per SM.)
+__device__ __forceinline__ void rs_final_reduce(const GemmParams& p, const FuseParams& f, const CommParams& c, int cta, int ncta) {
   using namespace apbs;
   uint8_t* my_ws = f.peers.base[f.rank];
   const float* slots = reinterpret_cast<const float*>(my_ws + HEADER_BYTES);  // [n][rows_per_rank * N]
+  __shared__ uint32_t ok_r;
+  if (threadIdx.x == 0) ok_r = 1u;
+  __syncthreads();
+  if (threadIdx.x < f.n)
+    if (!wait_ge<true>(flag_ptr(my_ws, OFF_CONTRIB, threadIdx.x), f.epoch, p.status)) ok_r = 0u;
+  __syncthreads();
+  if (!ok_r) return;
+  const long long nvec = c.acc_elems >> 2;
+  const long long stride = (long long)ncta * blockDim.x;
+  for (long long i0 = (long long)cta * blockDim.x + threadIdx.x; i0 < nvec; i0 += 4 * stride) {
+    float4 acc[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < f.n; ++k) {
+      const float4* sl = reinterpret_cast<const float4*>(slots + (long long)k * c.acc_elems);
+      float4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * stride < nvec) x[u] = sl[i0 + u * stride];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * stride < nvec) { acc[u].x += x[u].x; acc[u].y += x[u].y; acc[u].z += x[u].z; acc[u].w += x[u].w; }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+      float4 v = acc[u];
+      v.x *= c.scale; v.y *= c.scale; v.z *= c.scale; v.w *= c.scale;
+      if (c.out_fp32) {
+        reinterpret_cast<float4*>(c.out)[i] = v;
+      } else {
+        uint2 o;
+        o.x = pack_bf16(v.x, v.y);
+        o.y = pack_bf16(v.z, v.w);
+        reinterpret_cast<uint2*>(c.out)[i] = o;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void comm_reduce_scatter(const GemmParams& p, const FuseParams& f, const CommParams& c, int cta) {
+  using namespace apbs;
+  uint8_t* my_ws = f.peers.base[f.rank];
   __shared__ uint32_t ok_s;
   if (threadIdx.x == 0) ok_s = 1u;
   __syncthreads();
@@ -89,29 +136,8 @@ __device__ __forceinline__ void comm_reduce_scatter(const GemmParams& p, const F
   if (arrive_is_last(flag_ptr(my_ws, OFF_COUNTERS, 2), c.t_phase0)) {
     if (threadIdx.x < f.n) st_release_sys(flag_ptr(f.peers.base[threadIdx.x], OFF_READY, f.rank), f.epoch);
   }
-  // every rank (this one included) signals when all of its tiles have been stored
-  if (threadIdx.x < f.n)
-    if (!wait_ge<true>(flag_ptr(my_ws, OFF_CONTRIB, threadIdx.x), f.epoch, p.status)) ok_s = 0u;
-  __syncthreads();
-  if (!ok_s) return;
-  const long long nvec = c.acc_elems >> 2;
-  const long long stride = (long long)c.comm_ctas * blockDim.x;
-  for (long long i = (long long)cta * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int k = 0; k < f.n; ++k) {
-      const float4 x = reinterpret_cast<const float4*>(slots + (long long)k * c.acc_elems)[i];
-      v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
-    }
-    v.x *= c.scale; v.y *= c.scale; v.z *= c.scale; v.w *= c.scale;
-    if (c.out_fp32) {
-      reinterpret_cast<float4*>(c.out)[i] = v;
-    } else {
-      uint2 o;
-      o.x = pack_bf16(v.x, v.y);
-      o.y = pack_bf16(v.z, v.w);
-      reinterpret_cast<uint2*>(c.out)[i] = o;
-    }
-  }
+  // Return at once: every CTA of the launch requests the GEMM's shared memory, so only one CTA
+  // fits per SM and a communication CTA that lingered would keep a GEMM CTA off its SM.
 }
 
 template <bool A_MN, bool B_MN, int FUSE>
@@ -134,6 +160,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (threadIdx.x != f.rank) st_release_sys(flag_ptr(f.peers.base[threadIdx.x], OFF_DONE, f.rank), f.epoch);
       }
     }
+    rs_final_reduce(p, f, c, blockIdx.x - c.comm_ctas, gridDim.x - c.comm_ctas);
   }
 }
 

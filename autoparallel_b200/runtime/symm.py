@@ -154,7 +154,7 @@ class SymmGroup:
     def _num_sms(self):
         return torch.cuda.get_device_properties(self.device).multi_processor_count
 
-    fused_comm_ctas = 64
+    fused_comm_ctas = 32  # every CTA of a fused launch owns an SM (GEMM-sized shared memory): keep the copy crew small
 
     def can_fuse_gather(self, shard: torch.Tensor) -> bool:
         nbytes = shard.numel() * shard.element_size()
