@@ -3,11 +3,14 @@
 //
 //   tile 128 x 256 x 64, 4 TMA stages, two 256-column TMEM accumulators
 //   warp 0: TMA producer | warp 1: TMEM owner + MMA issuer | warps 2..5: epilogue
+//   warp 6 (gather-fused kernels only): copy engine driver, see gather_comm_warp
 //
 // FUSE selects what the CTA does beyond a plain GEMM:
 //   FUSE_NONE       nothing
-//   FUSE_GATHER_A   rows (M) of A arrive shard by shard from peer GPUs: the producer waits for the
-//                   per-shard "landed" counter before loading a tile of that shard
+//   FUSE_GATHER_A   rows (M) of A arrive shard by shard from peer GPUs: a seventh warp of every CTA
+//                   pulls this CTA's share of each shard with bulk copies (TMA engine, no SM taken
+//                   from the GEMM) and the producer waits for the per-shard "landed" counter
+//                   before loading a tile of that shard
 //   FUSE_GATHER_B   same for B; with a K-major B the shards partition N, with an MN-major B
 //                   (stored [K, N]) they partition K, and the k-loop starts at the local shard
 //   FUSE_REDUCE_SCATTER  the epilogue stores each fp32 tile into this rank's slot of the OWNER
@@ -27,6 +30,9 @@ constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int EPI_STAGE_FLOATS = 32 * 33;  // per epilogue warp: one 32x32 fp32 block, padded
 constexpr int GEMM_FUSED_RS_SMEM_BYTES = GEMM_SMEM_BYTES + 4 * EPI_STAGE_FLOATS * 4;
+constexpr int AG_NBUF = 4, AG_CHUNK = 8192;  // bounce ring of the gather warp: 3 bulk loads in flight per CTA
+constexpr int GEMM_FUSED_AG_SMEM_BYTES = GEMM_SMEM_BYTES + AG_NBUF * AG_CHUNK;
+constexpr int GEMM_AG_THREADS = GEMM_THREADS + 32;
 
 enum : int { FUSE_NONE = 0, FUSE_GATHER_A = 1, FUSE_GATHER_B = 2, FUSE_REDUCE_SCATTER = 3 };
 
@@ -45,8 +51,12 @@ struct FuseParams {
   uint32_t epoch;
   // gather
   int rows_per_shard;          // rows of the gathered operand per rank (in its stored layout)
-  const uint32_t* landed;      // [n] local counters; shard s usable once landed[s] >= landed_target
+  uint32_t* landed;            // [n] local counters; shard s usable once landed[s] >= landed_target
   uint32_t landed_target;
+  const uint8_t* shard_src;    // this rank's shard (any local memory)
+  uint8_t* gbuf;               // local full-size operand, [n][shard_bytes]
+  long long shard_bytes;
+  uint32_t t_publish, t_pulled;  // running totals of the two arrival counters
   // reduce-scatter
   int rows_per_rank;           // rows of C owned by each rank (multiple of BM)
 };
@@ -67,6 +77,95 @@ __device__ __forceinline__ void red_add_v4_sys(float* addr, float a, float b, fl
 }
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
+// ---------------------------------------------------------------------------- gather warp
+// One lane per CTA drives the copy engine: it publishes this CTA's share of the local shard into the
+// rank's symmetric staging area (and into the local full-size operand), then pulls the same share of
+// every peer's staging area over NVLink.  Data moves global -> shared -> global as bulk copies through
+// a ring of AG_NBUF bounce buffers, so AG_NBUF-1 loads are in flight per CTA (one per SM: a few MB
+// in flight on the GPU, enough to cover the NVLink round trip) while the tensor cores run.
+struct BounceRing {
+  uint8_t* buf;
+  uint64_t* bars;  // [AG_NBUF]
+  uint32_t it;     // chunks moved so far by this CTA (buffer = it % AG_NBUF, parity from it / AG_NBUF)
+};
+
+// Copies chunks cta, cta+ncta, ... of [src, src+bytes) to dst0 (and dst1 if non-null); returns after
+// every store has completed.  False on a timed-out load.
+__device__ __forceinline__ bool ring_copy(BounceRing& r, const uint8_t* src, uint8_t* dst0, uint8_t* dst1, long long bytes,
+                                          int cta, int ncta, volatile uint32_t* abort_flag) {
+  const long long nchunks = (bytes + AG_CHUNK - 1) / AG_CHUNK;
+  const int total = cta < nchunks ? (int)((nchunks - cta + ncta - 1) / ncta) : 0;
+  auto off_of = [&](int j) { return ((long long)cta + (long long)j * ncta) * AG_CHUNK; };
+  auto size_of = [&](long long off) { return (uint32_t)min((long long)AG_CHUNK, bytes - off); };
+  auto issue_load = [&](int j) {
+    const long long off = off_of(j);
+    const uint32_t sz = size_of(off);
+    const uint32_t b = (r.it + j) % AG_NBUF;
+    mbar_expect_tx(&r.bars[b], sz);
+    bulk_load(r.buf + b * AG_CHUNK, src + off, sz, &r.bars[b]);
+  };
+  for (int j = 0; j < AG_NBUF - 1 && j < total; ++j) issue_load(j);
+  bool ok = true;
+  for (int j = 0; j < total; ++j) {
+    const uint32_t it = r.it + j, b = it % AG_NBUF, parity = (it / AG_NBUF) & 1u;
+    if (!mbar_wait(&r.bars[b], parity, abort_flag)) {
+      ok = false;
+      break;
+    }
+    const long long off = off_of(j);
+    const uint32_t sz = size_of(off);
+    bulk_store(dst0 + off, r.buf + b * AG_CHUNK, sz);
+    if (dst1 != nullptr) bulk_store(dst1 + off, r.buf + b * AG_CHUNK, sz);
+    tma_store_commit();
+    if (j + AG_NBUF - 1 < total) {
+      bulk_store_wait_read_1();  // the buffer stored one iteration ago has been read: refill it
+      issue_load(j + AG_NBUF - 1);
+    }
+  }
+  r.it += total;
+  tma_store_wait_all();
+  return ok;
+}
+
+// Called by one lane.  ``cta`` / ``ncta``: this CTA among the GEMM CTAs (all of them resident).
+__device__ __forceinline__ void gather_comm_warp(const GemmParams& p, const FuseParams& f, int cta, int ncta, BounceRing& ring,
+                                                 volatile uint32_t* abort_flag) {
+  using namespace apbs;
+  uint8_t* my_ws = f.peers.base[f.rank];
+  uint8_t* stage = my_ws + HEADER_BYTES;
+  auto fail = [&]() {
+    atomicCAS(p.status, 0u, (uint32_t)ST_TIMEOUT_PEER_FLAG);
+    *abort_flag = 1;
+  };
+  // my staging area may be overwritten once every peer has finished pulling the previous epoch
+  for (int k = 1; k < f.n; ++k)
+    if (!wait_ge<true>(flag_ptr(my_ws, OFF_DONE, (f.rank + k) % f.n), f.epoch - 1, p.status)) return fail();
+  if (!ring_copy(ring, f.shard_src, stage, f.gbuf + (long long)f.rank * f.shard_bytes, f.shard_bytes, cta, ncta, abort_flag)) return fail();
+  fence_proxy_async_global();
+  __threadfence_system();
+  atomicAdd(f.landed + f.rank, 1u);
+  if (atomicAdd(flag_ptr(my_ws, OFF_COUNTERS, 2), 1u) + 1u == f.t_publish) {
+    __threadfence_system();  // every other CTA's share was fenced before its arrival
+    for (int k = 1; k < f.n; ++k) st_release_sys(flag_ptr(f.peers.base[(f.rank + k) % f.n], OFF_READY, f.rank), f.epoch);
+  }
+  for (int k = 1; k < f.n; ++k) {
+    const int peer = (f.rank + k) % f.n;
+    if (!wait_ge<true>(flag_ptr(my_ws, OFF_READY, peer), f.epoch, p.status)) return fail();
+    fence_proxy_async_global();
+    if (!ring_copy(ring, f.peers.base[peer] + HEADER_BYTES, f.gbuf + (long long)peer * f.shard_bytes, nullptr, f.shard_bytes, cta, ncta,
+                   abort_flag))
+      return fail();
+    fence_proxy_async_global();
+    __threadfence();
+    atomicAdd(f.landed + peer, 1u);
+  }
+  __threadfence_system();
+  if (atomicAdd(flag_ptr(my_ws, OFF_COUNTERS, 3), 1u) + 1u == f.t_pulled) {
+    __threadfence_system();
+    for (int k = 1; k < f.n; ++k) st_release_sys(flag_ptr(f.peers.base[(f.rank + k) % f.n], OFF_DONE, f.rank), f.epoch);
+  }
+}
+
 // cta / num_ctas: index of this CTA among the GEMM CTAs of the launch (fused kernels also run
 // communication CTAs that are not counted here).
 template <bool A_MN, bool B_MN, int FUSE>
@@ -82,6 +181,8 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
   uint64_t* tmem_empty = bars + 2 * STAGES + 2;  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint64_t* ring_bars = bars + 2 * STAGES + 6;   // [AG_NBUF], gather-fused kernels only
+  constexpr bool GATHER = FUSE == FUSE_GATHER_A || FUSE == FUSE_GATHER_B;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -104,6 +205,8 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
       mbar_init(&tmem_full[b], 1);
       mbar_init(&tmem_empty[b], 128);
     }
+    if (GATHER)
+      for (int b = 0; b < AG_NBUF; ++b) mbar_init(&ring_bars[b], 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -236,6 +339,12 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
           buf_phase ^= 1;
         }
       }
+    }
+  } else if (GATHER && warp == 6) {
+    // ------------------------------------------------------------------ gather warp
+    if (lane == 0) {
+      BounceRing ring{smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256, ring_bars, 0u};
+      gather_comm_warp(p, f, cta, num_ctas, ring, abort_flag);
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)

@@ -1,10 +1,12 @@
 // GEMM fused with its neighbouring collective, one kernel per rank, over NVLink peer memory.
 //
-//   all-gather -> GEMM   (FUSE_GATHER_A / FUSE_GATHER_B): a few communication CTAs publish this
-//       rank's shard, pull every peer's shard ONCE into a local full-size operand buffer and bump a
-//       per-shard "landed" counter; the GEMM CTAs (one per SM, same persistent tcgen05 main loop as
-//       the plain GEMM) start on the local shard and wait on the counter only when they reach a
-//       tile of a shard that has not landed yet.  Covers the FSDP parameter gather in forward
+//   all-gather -> GEMM   (FUSE_GATHER_A / FUSE_GATHER_B): a seventh warp in every GEMM CTA drives
+//       the copy engine: it publishes the CTA's share of this rank's shard, pulls the same share of
+//       every peer's shard ONCE into a local full-size operand buffer (bulk copies through a ring of
+//       bounce buffers in shared memory) and bumps a per-shard "landed" counter; the GEMM warps
+//       (one CTA per SM, same persistent tcgen05 main loop as the plain GEMM) start on the local
+//       shard and wait on the counter only when they reach a tile of a shard that has not landed
+//       yet.  No SM is taken from the GEMM.  Covers the FSDP parameter gather in forward
 //       (weights [N/n, K] gathered along N) and in backward (the same weights consumed as a
 //       [K', N'] operand, i.e. gathered along the contraction dim) and the tensor-parallel
 //       activation gather (A rows).
@@ -14,8 +16,8 @@
 //       the n slots, scale / cast, and write the output shard.  Covers the gradient reduce-scatter (weight
 //       gradient GEMM) and the row-parallel projection followed by a sequence-sharded output.
 //
-// No TMA multicast, no NCCL: remote data moves with ordinary peer loads / red.add issued from the
-// kernel, so transfer and tensor-core work overlap tile by tile.  Waits are bounded; a timeout is
+// No NCCL: remote data moves with plain (unicast) bulk loads and 16-byte peer stores issued from
+// the kernel, so transfer and tensor-core work overlap tile by tile.  Waits are bounded; a timeout is
 // reported through the status word.  Reference counterparts (host-driven pipelines of cuBLAS calls
 // and P2P copies): autoparallel/graph_passes/async_tp/asynctp_ops.py:396-531, 1104-1186.
 #include "gemm_core.cuh"
@@ -23,13 +25,7 @@
 namespace apb {
 
 struct CommParams {
-  int comm_ctas;
-  // gather
-  const uint8_t* shard_src;
-  uint8_t* gbuf;
-  long long shard_bytes;
-  uint32_t* landed;
-  // reduce-scatter
+  int comm_ctas;  // reduce-scatter only: CTAs that wait for the peers and publish "slots free"
   long long acc_elems;  // fp32 elements of this rank's accumulation buffer (rows_per_rank * N)
   void* out;
   int out_fp32;
@@ -37,42 +33,6 @@ struct CommParams {
   // arrival-counter targets (running totals kept by the host)
   uint32_t t_phase0, t_phase1, t_gemm;
 };
-
-__device__ __forceinline__ void comm_gather(const GemmParams& p, const FuseParams& f, const CommParams& c, int cta) {
-  using namespace apbs;
-  uint8_t* my_ws = f.peers.base[f.rank];
-  uint8_t* stage = my_ws + HEADER_BYTES;
-  __shared__ uint32_t ok_s;
-  if (threadIdx.x == 0) ok_s = 1u;
-  __syncthreads();
-  if (threadIdx.x < f.n && threadIdx.x != f.rank)
-    if (!wait_ge<true>(flag_ptr(my_ws, OFF_DONE, threadIdx.x), f.epoch - 1, p.status)) ok_s = 0u;
-  __syncthreads();
-  if (!ok_s) return;
-  coop_copy16(stage, c.shard_src, c.shard_bytes, cta, c.comm_ctas);
-  coop_copy16(c.gbuf + (long long)f.rank * c.shard_bytes, c.shard_src, c.shard_bytes, cta, c.comm_ctas);
-  fence_proxy_async_global();
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) atomicAdd(c.landed + f.rank, 1u);
-  if (arrive_is_last(flag_ptr(my_ws, OFF_COUNTERS, 2), c.t_phase0)) {
-    if (threadIdx.x < f.n && threadIdx.x != f.rank) st_release_sys(flag_ptr(f.peers.base[threadIdx.x], OFF_READY, f.rank), f.epoch);
-  }
-  for (int k = 1; k < f.n; ++k) {
-    const int peer = (f.rank + k) % f.n;
-    if (threadIdx.x == 0 && !wait_ge<true>(flag_ptr(my_ws, OFF_READY, peer), f.epoch, p.status)) ok_s = 0u;
-    __syncthreads();
-    if (!ok_s) return;
-    coop_copy16(c.gbuf + (long long)peer * c.shard_bytes, f.peers.base[peer] + HEADER_BYTES, c.shard_bytes, cta, c.comm_ctas);
-    fence_proxy_async_global();
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) atomicAdd(c.landed + peer, 1u);
-  }
-  if (arrive_is_last(flag_ptr(my_ws, OFF_COUNTERS, 3), c.t_phase1)) {
-    if (threadIdx.x < f.n && threadIdx.x != f.rank) st_release_sys(flag_ptr(f.peers.base[threadIdx.x], OFF_DONE, f.rank), f.epoch);
-  }
-}
 
 // Final phase of GEMM -> reduce-scatter, executed by the GEMM CTAs once their tiles are done: wait
 // until every rank has signalled that its tiles are stored, then sum the n slots of this rank's
@@ -141,13 +101,12 @@ __device__ __forceinline__ void comm_reduce_scatter(const GemmParams& p, const F
 }
 
 template <bool A_MN, bool B_MN, int FUSE>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(FUSE == FUSE_REDUCE_SCATTER ? GEMM_THREADS : GEMM_AG_THREADS, 1)
 gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p,
                   FuseParams f, CommParams c) {
   extern __shared__ uint8_t smem_raw[];
-  if ((int)blockIdx.x < c.comm_ctas) {
-    if (FUSE == FUSE_REDUCE_SCATTER) comm_reduce_scatter(p, f, c, blockIdx.x);
-    else comm_gather(p, f, c, blockIdx.x);
+  if (FUSE == FUSE_REDUCE_SCATTER && (int)blockIdx.x < c.comm_ctas) {
+    comm_reduce_scatter(p, f, c, blockIdx.x);
     return;
   }
   gemm_cta<A_MN, B_MN, FUSE>(tmA, tmB, p, f, blockIdx.x - c.comm_ctas, gridDim.x - c.comm_ctas, smem_raw);
@@ -168,7 +127,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 using namespace apb;
 
-// fuse: 1 gather A, 2 gather B, 3 reduce-scatter.  ``targets``: {phase0, phase1, gemm} arrival totals.
+// fuse: 1 gather A, 2 gather B, 3 reduce-scatter.  ``targets``: {phase0, phase1, gemm} arrival totals
+// (gathers: one arrival per GEMM CTA in phases 0 and 1; reduce-scatter: comm_ctas in phase 0, GEMM CTAs in 'gemm').
 // For gathers the tensor map of the gathered operand is built over ``gbuf`` (the local full-size
 // buffer); the caller passes that pointer as A or B.  Returns 0 or an error code.
 extern "C" int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, int M, int N, int K, long long lda,
@@ -193,8 +153,9 @@ extern "C" int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, i
   f.rows_per_shard = rows_per_shard; f.landed = landed; f.landed_target = landed_target; f.rows_per_rank = rows_per_rank;
   CommParams c{};
   c.comm_ctas = comm_ctas;
-  c.shard_src = static_cast<const uint8_t*>(shard_src); c.gbuf = static_cast<uint8_t*>(gbuf); c.shard_bytes = shard_bytes;
-  c.landed = landed; c.out = C; c.out_fp32 = out_fp32; c.scale = scale;
+  f.shard_src = static_cast<const uint8_t*>(shard_src); f.gbuf = static_cast<uint8_t*>(gbuf); f.shard_bytes = shard_bytes;
+  f.t_publish = targets[0]; f.t_pulled = targets[1];
+  c.out = C; c.out_fp32 = out_fp32; c.scale = scale;
   c.t_phase0 = targets[0]; c.t_phase1 = targets[1]; c.t_gemm = targets[2];
   if (fuse == FUSE_REDUCE_SCATTER) {
     if (rows_per_rank <= 0 || (rows_per_rank % BM) != 0 || (long long)rows_per_rank * n != M || (N & 3)) return 3;
@@ -202,14 +163,17 @@ extern "C" int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, i
     if (c.acc_elems * 4 * n > stage_capacity) return 7;  // one fp32 slot per source rank
   } else {
     if ((shard_bytes & 15) || shard_bytes > stage_capacity || rows_per_shard <= 0) return shard_bytes > stage_capacity ? 7 : 3;
+    if ((reinterpret_cast<uintptr_t>(shard_src) & 15) || (reinterpret_cast<uintptr_t>(gbuf) & 15)) return 3;  // bulk copies
+    c.comm_ctas = 0;
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int gemm_ctas = tiles < num_sms ? tiles : num_sms;
-  const int grid = gemm_ctas + comm_ctas;
-  const int smem_bytes = fuse == FUSE_REDUCE_SCATTER ? GEMM_FUSED_RS_SMEM_BYTES : GEMM_SMEM_BYTES;
+  const int grid = gemm_ctas + c.comm_ctas;
+  const int smem_bytes = fuse == FUSE_REDUCE_SCATTER ? GEMM_FUSED_RS_SMEM_BYTES : GEMM_FUSED_AG_SMEM_BYTES;
+  const int threads = fuse == FUSE_REDUCE_SCATTER ? GEMM_THREADS : GEMM_AG_THREADS;
   auto launch = [&](auto kern) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, p, f, c);
+    kern<<<grid, threads, smem_bytes, stream>>>(tmA, tmB, p, f, c);
   };
 #define APB_LAUNCH_FUSED(FUSE)                                                        \
   do {                                                                                \

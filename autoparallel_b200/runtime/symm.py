@@ -138,13 +138,16 @@ class SymmGroup:
         landed = self._landed()
         self.epoch += 1
         ctas = self.fused_comm_ctas
+        # the kernel runs min(#SMs, #tiles) GEMM CTAs over 128 x 256 output tiles
         if fuse == self.FUSE_REDUCE_SCATTER:
             self.arrivals[2] += ctas
             self.arrivals[4] += min(self._num_sms, -(-c.shape[0] * self.n // 128) * -(-c.shape[1] // 256))
         else:
-            self.arrivals[2] += ctas
-            self.arrivals[3] += ctas
-            self._landed_total += ctas
+            # every GEMM CTA carries a gather warp that arrives once per phase and once per shard
+            gemm_ctas = min(self._num_sms, -(-c.shape[0] // 128) * -(-c.shape[1] // 256))
+            self.arrivals[2] += gemm_ctas
+            self.arrivals[3] += gemm_ctas
+            self._landed_total += gemm_ctas
         targets = [self.arrivals[2] & 0xFFFFFFFF, self.arrivals[3] & 0xFFFFFFFF, self.arrivals[4] & 0xFFFFFFFF]
         self._C.gemm_fused(fuse, a, b, c, a_mn, b_mn, self.peer_ptrs, self.rank, self.epoch, rows_per_shard, shard_src, landed,
                            self._landed_total & 0xFFFFFFFF, rows_per_rank, scale, self.capacity, targets, ctas, self.status)
@@ -154,11 +157,12 @@ class SymmGroup:
     def _num_sms(self):
         return torch.cuda.get_device_properties(self.device).multi_processor_count
 
-    fused_comm_ctas = 32  # every CTA of a fused launch owns an SM (GEMM-sized shared memory): keep the copy crew small
+    fused_comm_ctas = 2  # GEMM -> reduce-scatter only: CTAs that wait for the peers' "done" and publish "slots free"
 
     def can_fuse_gather(self, shard: torch.Tensor) -> bool:
         nbytes = shard.numel() * shard.element_size()
-        return shard.dtype == torch.bfloat16 and shard.dim() == 2 and nbytes % 16 == 0 and nbytes <= self.capacity and shard.shape[1] % 8 == 0
+        return (shard.dtype == torch.bfloat16 and shard.dim() == 2 and nbytes % 16 == 0 and nbytes <= self.capacity
+                and shard.shape[1] % 8 == 0 and shard.data_ptr() % 16 == 0)
 
     def ag_gemm_b(self, x: torch.Tensor, w_shard: torch.Tensor, out_dtype=torch.bfloat16):
         """y = x @ all_gather(w_shard, 0)^T with x [M, K], w_shard [R, K]; returns (y [M, n*R], w_full)."""
