@@ -81,7 +81,7 @@ class AutoParallel:
         repeated_subgraphs: bool = True,
         activation_checkpointing: str = "none",
         plan_device: Optional[str] = None,
-        fuse_collectives: bool = True,
+        fuse_collectives: Any = None,
         bucket_collectives: bool = False,
     ):
         if dynamic:
@@ -222,8 +222,18 @@ class AutoParallel:
         from .parallel.passes.fuse_collectives import fuse_collectives
 
         changed = fuse_cast_into_gemm(lowered.gm)
-        if self.fuse_collectives:
-            self.fusion_stats = fuse_collectives(lowered.gm, lowered.joint.tangent_nodes, self.reshard_after_forward)
+        fuse = self.fuse_collectives
+        if fuse is None:
+            # A fused node is one kernel only where the mesh has symmetric-memory communicators; over
+            # NCCL it would run gather-then-GEMM back to back and hide the gather from the overlap
+            # scheduler, so the separate nodes are kept there.
+            from .runtime import symm
+
+            fuse = symm.enabled_for_mesh(self.mesh)
+        if fuse:
+            # "all" also fuses gathers along the contraction dim (kept apart by default: they cannot overlap tile by tile)
+            self.fusion_stats = fuse_collectives(lowered.gm, lowered.joint.tangent_nodes, self.reshard_after_forward,
+                                                 fuse_contraction_gather=(fuse == "all"))
             changed += sum(self.fusion_stats.values())
         if self.bucket_collectives:
             from .parallel.passes.bucketing import bucket_collectives

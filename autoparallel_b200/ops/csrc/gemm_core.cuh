@@ -59,6 +59,7 @@ struct FuseParams {
   uint32_t t_publish, t_pulled;  // running totals of the two arrival counters
   // reduce-scatter
   int rows_per_rank;           // rows of C owned by each rank (multiple of BM)
+  int slot_bf16;               // partial tiles travel as bf16 (bf16 result) instead of fp32
 };
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& tm, int& tn) {
@@ -148,16 +149,60 @@ __device__ __forceinline__ void gather_comm_warp(const GemmParams& p, const Fuse
     __threadfence_system();  // every other CTA's share was fenced before its arrival
     for (int k = 1; k < f.n; ++k) st_release_sys(flag_ptr(f.peers.base[(f.rank + k) % f.n], OFF_READY, f.rank), f.epoch);
   }
-  for (int k = 1; k < f.n; ++k) {
-    const int peer = (f.rank + k) % f.n;
-    if (!wait_ge<true>(flag_ptr(my_ws, OFF_READY, peer), f.epoch, p.status)) return fail();
-    fence_proxy_async_global();
-    if (!ring_copy(ring, f.peers.base[peer] + HEADER_BYTES, f.gbuf + (long long)peer * f.shard_bytes, nullptr, f.shard_bytes, cta, ncta,
-                   abort_flag))
-      return fail();
-    fence_proxy_async_global();
-    __threadfence();
-    atomicAdd(f.landed + peer, 1u);
+  // Pull: one chunk sequence over all peers, so that loads from the next peer are already in flight
+  // while the last stores of the previous one complete (a shard is only a few chunks per CTA).
+  {
+    const long long nchunks = (f.shard_bytes + AG_CHUNK - 1) / AG_CHUNK;
+    const int per = cta < nchunks ? (int)((nchunks - cta + ncta - 1) / ncta) : 0;  // my chunks of each shard
+    const int total = per * (f.n - 1);
+    auto peer_of = [&](int q) { return (f.rank + 1 + q / per) % f.n; };
+    auto off_of = [&](int q) { return ((long long)cta + (long long)(q % per) * ncta) * AG_CHUNK; };
+    auto size_of = [&](long long off) { return (uint32_t)min((long long)AG_CHUNK, f.shard_bytes - off); };
+    bool ok = true;
+    auto issue_load = [&](int q) {
+      const int peer = peer_of(q);
+      if (q % per == 0) {  // first chunk of this peer: its staging area must be complete
+        if (!wait_ge<true>(flag_ptr(my_ws, OFF_READY, peer), f.epoch, p.status)) {
+          ok = false;
+          return;
+        }
+        fence_proxy_async_global();
+      }
+      const long long off = off_of(q);
+      const uint32_t sz = size_of(off);
+      const uint32_t b = (ring.it + q) % AG_NBUF;
+      mbar_expect_tx(&ring.bars[b], sz);
+      bulk_load(ring.buf + b * AG_CHUNK, f.peers.base[peer] + HEADER_BYTES + off, sz, &ring.bars[b]);
+    };
+    int issued = 0;
+    for (; issued < AG_NBUF - 1 && issued < total && ok; ++issued) issue_load(issued);
+    for (int q = 0; q < total && ok; ++q) {
+      const uint32_t it = ring.it + q, b = it % AG_NBUF, parity = (it / AG_NBUF) & 1u;
+      if (!mbar_wait(&ring.bars[b], parity, abort_flag)) {
+        ok = false;
+        break;
+      }
+      const int peer = peer_of(q);
+      const long long off = off_of(q);
+      bulk_store(f.gbuf + (long long)peer * f.shard_bytes + off, ring.buf + b * AG_CHUNK, size_of(off));
+      tma_store_commit();
+      if (issued < total) {
+        bulk_store_wait_read_1();  // the buffer stored one iteration ago has been read: refill it
+        issue_load(issued++);
+      }
+      if (q % per == per - 1) {  // last chunk of this peer: publish the shard once its stores are complete
+        tma_store_wait_all();
+        fence_proxy_async_global();
+        __threadfence();
+        atomicAdd(f.landed + peer, 1u);
+      }
+    }
+    ring.it += total;
+    tma_store_wait_all();
+    if (!ok) return fail();
+    if (per == 0) {  // nothing to move for this CTA: still one arrival per shard
+      for (int k = 1; k < f.n; ++k) atomicAdd(f.landed + (f.rank + k) % f.n, 1u);
+    }
   }
   __threadfence_system();
   if (atomicAdd(flag_ptr(my_ws, OFF_COUNTERS, 3), 1u) + 1u == f.t_pulled) {
@@ -191,7 +236,26 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
   // rotation that makes every rank start on data it already owns
   int m_rot = 0, n_rot = 0, k_rot = 0;
   if (FUSE == FUSE_GATHER_A && !A_MN) m_rot = (f.rank * f.rows_per_shard) / BM;
-  if (FUSE == FUSE_GATHER_B && !B_MN) n_rot = (f.rank * f.rows_per_shard) / BN;
+  // N-partitioned gather (B shards are blocks of output columns): visit the tiles shard by shard,
+  // local shard first, so that shard k is first touched after k/n of the GEMM (possible when a
+  // shard is a whole number of tile columns); otherwise only rotate the start.
+  int shard_n_tiles = 0;
+  if (FUSE == FUSE_GATHER_B && !B_MN) {
+    if (f.rows_per_shard % BN == 0 && p.num_n_tiles == (f.rows_per_shard / BN) * f.n) shard_n_tiles = f.rows_per_shard / BN;
+    else n_rot = (f.rank * f.rows_per_shard) / BN;
+  }
+  auto map_tile = [&](int t, int& tm, int& tn) {
+    if (shard_n_tiles > 0) {
+      const int per_shard = p.num_m_tiles * shard_n_tiles;
+      const int s = t / per_shard;
+      tile_coords(t - s * per_shard, p.num_m_tiles, shard_n_tiles, tm, tn);
+      tn += ((s + f.rank) % f.n) * shard_n_tiles;
+    } else {
+      tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
+      tm = (tm + m_rot) % p.num_m_tiles;
+      tn = (tn + n_rot) % p.num_n_tiles;
+    }
+  };
   if (FUSE == FUSE_GATHER_B && B_MN) k_rot = (f.rank * f.rows_per_shard) / BK;
   if (FUSE == FUSE_GATHER_A && A_MN) k_rot = (f.rank * f.rows_per_shard) / BK;
   if (FUSE == FUSE_REDUCE_SCATTER) m_rot = (((f.rank + 1) % f.n) * f.rows_per_rank) / BM;  // own rows last
@@ -237,9 +301,7 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
       };
       for (int t = cta; t < num_tiles && ok; t += num_ctas) {
         int tm, tn;
-        tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
-        tm = (tm + m_rot) % p.num_m_tiles;
-        tn = (tn + n_rot) % p.num_n_tiles;
+        map_tile(t, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
         if ((FUSE == FUSE_GATHER_A && !A_MN) || (FUSE == FUSE_GATHER_B && !B_MN)) {
           // the tile's rows of the gathered operand must have landed
@@ -353,9 +415,7 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
     uint32_t buf_phase = 0;
     for (int t = cta; t < num_tiles; t += num_ctas) {
       int tm, tn;
-      tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
-      tm = (tm + m_rot) % p.num_m_tiles;
-      tn = (tn + n_rot) % p.num_n_tiles;
+      map_tile(t, tm, tn);
       if (!mbar_wait(&tmem_full[buf], buf_phase, abort_flag)) {
         atomicCAS(p.status, 0u, (uint32_t)ST_TIMEOUT_TMEM_FULL);
         *abort_flag = 1;
@@ -380,7 +440,8 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
           *abort_flag = 1;
           break;
         }
-        // slot ``rank`` of the owner's staging area: [n][rows_per_rank][N] fp32
+        // slot ``rank`` of the owner's staging area: [n][rows_per_rank][N], fp32 or bf16; rs_base is kept
+        // in units of fp32 elements of an fp32 slot and halved below for bf16 slots
         rs_base = reinterpret_cast<float*>(f.peers.base[owner] + apbs::HEADER_BYTES) +
                   ((long long)f.rank * f.rows_per_rank + (row - (long long)owner * f.rows_per_rank)) * p.N;
       }
@@ -399,6 +460,33 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
           __syncwarp();
           const long long row0 = (long long)tm * BM + q * 32;  // first row of this warp's block
           float* blk = rs_base - (long long)lane * p.N;         // rs_base points at this lane's row
+          if (f.slot_bf16) {
+            // 8 bf16 (16 bytes) per lane, 4 lanes per 64-byte row segment, 8 rows per instruction
+            __nv_bfloat16* blk16 = reinterpret_cast<__nv_bfloat16*>(f.peers.base[(tm * BM) / f.rows_per_rank] + apbs::HEADER_BYTES) +
+                                   (blk - reinterpret_cast<float*>(f.peers.base[(tm * BM) / f.rows_per_rank] + apbs::HEADER_BYTES));
+            const int sub8 = lane >> 2, seg8 = (lane & 3) * 8;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int rr = sub8 + 8 * j;
+              if (row0 + rr < p.M) {
+                const float* sp = stg + rr * 33 + seg8;
+                __nv_bfloat16* dst = blk16 + (long long)rr * p.N + col + seg8;
+                if (col + seg8 + 8 <= p.N) {
+                  uint4 v;
+                  v.x = pack_bf16(sp[0], sp[1]);
+                  v.y = pack_bf16(sp[2], sp[3]);
+                  v.z = pack_bf16(sp[4], sp[5]);
+                  v.w = pack_bf16(sp[6], sp[7]);
+                  *reinterpret_cast<uint4*>(dst) = v;
+                } else {
+                  for (int e = 0; e < 8; ++e)
+                    if (col + seg8 + e < p.N) dst[e] = __float2bfloat16(sp[e]);
+                }
+              }
+            }
+            __syncwarp();
+            continue;
+          }
           const int sub = lane >> 3, seg = (lane & 7) * 4;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {

@@ -48,36 +48,73 @@ __device__ __forceinline__ void rs_final_reduce(const GemmParams& p, const FuseP
     if (!wait_ge<true>(flag_ptr(my_ws, OFF_CONTRIB, threadIdx.x), f.epoch, p.status)) ok_r = 0u;
   __syncthreads();
   if (!ok_r) return;
-  const long long nvec = c.acc_elems >> 2;
+  // One CTA per SM with 192 threads: 16 independent 16-byte loads per thread (48 KB per SM) are
+  // needed to keep HBM busy; fewer left this pass latency-bound.
+  constexpr int U = 16;
   const long long stride = (long long)ncta * blockDim.x;
-  for (long long i0 = (long long)cta * blockDim.x + threadIdx.x; i0 < nvec; i0 += 4 * stride) {
-    float4 acc[4];
+  if (f.slot_bf16) {
+    // bf16 slots, bf16 result: 8 elements per 16-byte vector, summed in fp32
+    const __nv_bfloat16* slots16 = reinterpret_cast<const __nv_bfloat16*>(my_ws + HEADER_BYTES);
+    const long long nvec8 = c.acc_elems >> 3;
+    for (long long i0 = (long long)cta * blockDim.x + threadIdx.x; i0 < nvec8; i0 += U * stride) {
+      float acc[U][8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+      for (int k = 0; k < f.n; ++k) {
+        const uint4* sl = reinterpret_cast<const uint4*>(slots16 + (long long)k * c.acc_elems);
+        uint4 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * stride < nvec8) x[u] = sl[i0 + u * stride];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (i0 + u * stride >= nvec8) continue;
+          const uint32_t w[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[u][2 * e] += __uint_as_float(w[e] << 16);
+            acc[u][2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= nvec8) continue;
+        uint4 o;
+        o.x = pack_bf16(acc[u][0] * c.scale, acc[u][1] * c.scale);
+        o.y = pack_bf16(acc[u][2] * c.scale, acc[u][3] * c.scale);
+        o.z = pack_bf16(acc[u][4] * c.scale, acc[u][5] * c.scale);
+        o.w = pack_bf16(acc[u][6] * c.scale, acc[u][7] * c.scale);
+        reinterpret_cast<uint4*>(c.out)[i] = o;
+      }
+    }
+    return;
+  }
+  const long long nvec = c.acc_elems >> 2;
+  for (long long i0 = (long long)cta * blockDim.x + threadIdx.x; i0 < nvec; i0 += U * stride) {
+    float4 acc[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < f.n; ++k) {
       const float4* sl = reinterpret_cast<const float4*>(slots + (long long)k * c.acc_elems);
-      float4 x[4];
+      float4 x[U];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < U; ++u)
         if (i0 + u * stride < nvec) x[u] = sl[i0 + u * stride];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < U; ++u)
         if (i0 + u * stride < nvec) { acc[u].x += x[u].x; acc[u].y += x[u].y; acc[u].z += x[u].z; acc[u].w += x[u].w; }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < U; ++u) {
       const long long i = i0 + u * stride;
       if (i >= nvec) continue;
       float4 v = acc[u];
       v.x *= c.scale; v.y *= c.scale; v.z *= c.scale; v.w *= c.scale;
-      if (c.out_fp32) {
-        reinterpret_cast<float4*>(c.out)[i] = v;
-      } else {
-        uint2 o;
-        o.x = pack_bf16(v.x, v.y);
-        o.y = pack_bf16(v.z, v.w);
-        reinterpret_cast<uint2*>(c.out)[i] = o;
-      }
+      reinterpret_cast<float4*>(c.out)[i] = v;
     }
   }
 }
@@ -158,9 +195,10 @@ extern "C" int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, i
   c.out = C; c.out_fp32 = out_fp32; c.scale = scale;
   c.t_phase0 = targets[0]; c.t_phase1 = targets[1]; c.t_gemm = targets[2];
   if (fuse == FUSE_REDUCE_SCATTER) {
-    if (rows_per_rank <= 0 || (rows_per_rank % BM) != 0 || (long long)rows_per_rank * n != M || (N & 3)) return 3;
+    if (rows_per_rank <= 0 || (rows_per_rank % BM) != 0 || (long long)rows_per_rank * n != M || (N & 7)) return 3;
     c.acc_elems = (long long)rows_per_rank * N;
-    if (c.acc_elems * 4 * n > stage_capacity) return 7;  // one fp32 slot per source rank
+    f.slot_bf16 = out_fp32 ? 0 : 1;  // partial sums travel in the precision of the result
+    if (c.acc_elems * (out_fp32 ? 4 : 2) * n > stage_capacity) return 7;  // one slot per source rank
   } else {
     if ((shard_bytes & 15) || shard_bytes > stage_capacity || rows_per_shard <= 0) return shard_bytes > stage_capacity ? 7 : 3;
     if ((reinterpret_cast<uintptr_t>(shard_src) & 15) || (reinterpret_cast<uintptr_t>(gbuf) & 15)) return 3;  // bulk copies

@@ -48,7 +48,11 @@ def _tangent_dependent(gm: fx.GraphModule, tangents) -> set:
     return T
 
 
-def fuse_collectives(gm: fx.GraphModule, tangents=(), reshard_after_forward: bool = True) -> dict:
+def fuse_collectives(gm: fx.GraphModule, tangents=(), reshard_after_forward: bool = True,
+                     fuse_contraction_gather: bool = False) -> dict:
+    """``fuse_contraction_gather``: also fuse a gather whose rows are the GEMM's contraction dim (the
+    FSDP dgrad).  Every output tile then needs every shard, so the kernel cannot start a tile on
+    local data while the rest arrives; measured slower than a prefetched gather, hence off by default."""
     g = gm.graph
     stats = {"ag_mm": 0, "mm_rs": 0}
     T = _tangent_dependent(gm, tangents)
@@ -93,6 +97,8 @@ def fuse_collectives(gm: fx.GraphModule, tangents=(), reshard_after_forward: boo
             a, b, trans_b, dt = u.args
             if b is ag and a is not ag and val.ndim == 2 and dim == 0:
                 mode = 0 if trans_b else 1
+                if mode == 1 and not fuse_contraction_gather:
+                    continue
                 args = (a, x, mode, 0, dt, group, n_ranks)
                 is_weight = True
             elif a is ag and b is not ag and _rows_leading(val.shape, dim):

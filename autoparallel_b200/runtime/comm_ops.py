@@ -33,6 +33,12 @@ lib.define("local_chunk(Tensor x, int dim, str group, int group_size) -> Tensor"
 
 #: group name -> symmetric-memory communicator (set by runtime.symm.enable_for_group)
 _symm_backends: dict[str, object] = {}
+#: False = stand-alone collectives stay on NCCL even where a communicator exists (fused nodes still use it)
+_symm_standalone = True
+
+
+def _standalone_backend(group):
+    return _symm_backends.get(group) if _symm_standalone else None
 
 
 def _wait(t):
@@ -45,7 +51,7 @@ def _rank_in_group(group: str) -> int:
 
 
 def _all_gather(x, dim, group, n):
-    be = _symm_backends.get(group)
+    be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_gather(x, dim)
     x = x.contiguous()
@@ -61,7 +67,7 @@ def _all_gather(x, dim, group, n):
 
 
 def _reduce_scatter(x, dim, group, n):
-    be = _symm_backends.get(group)
+    be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.reduce_scatter(x, dim)
     shape = list(x.shape)
@@ -74,7 +80,7 @@ def _reduce_scatter(x, dim, group, n):
 
 
 def _all_reduce(x, group, n):
-    be = _symm_backends.get(group)
+    be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_reduce(x)
     out = torch.ops._c10d_functional.all_reduce(x.contiguous(), "sum", group)
@@ -84,7 +90,7 @@ def _all_reduce(x, group, n):
 def _all_to_all(x, split_dim, concat_dim, group, n):
     """Each rank splits ``x`` into n chunks along ``split_dim``, sends chunk r to rank r, and
     concatenates what it receives along ``concat_dim`` (Shard(concat_dim) -> Shard(split_dim))."""
-    be = _symm_backends.get(group)
+    be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_to_all(x, split_dim, concat_dim)
     chunks = x.chunk(n, dim=split_dim)
@@ -188,7 +194,7 @@ lib.define("comm_wait(Tensor x) -> Tensor")
 
 
 def _ag_start(x, dim, group, n):
-    be = _symm_backends.get(group)
+    be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_gather_start(x, dim)
     if dim != 0:
@@ -197,7 +203,7 @@ def _ag_start(x, dim, group, n):
 
 
 def _rs_start(x, dim, group, n):
-    be = _symm_backends.get(group)
+    be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.reduce_scatter_start(x, dim)
     if dim != 0:
@@ -209,7 +215,7 @@ def _rs_start(x, dim, group, n):
 
 
 def _ar_start(x, group, n):
-    be = _symm_backends.get(group)
+    be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_reduce_start(x)
     return torch.ops._c10d_functional.all_reduce(x.contiguous(), "sum", group)

@@ -273,7 +273,23 @@ def enable_for_mesh(mesh, workspace_bytes: int = 1 << 30, num_ctas: int = 32) ->
     return [enable_for_group(mesh.get_group(i), workspace_bytes, num_ctas) for i in range(mesh.ndim) if mesh.shape[i] > 1]
 
 
+def enabled_for_mesh(mesh) -> bool:
+    """True if every mesh dim of extent > 1 has a communicator."""
+    try:
+        names = [mesh.get_group(i).group_name for i in range(mesh.ndim) if mesh.shape[i] > 1]
+    except Exception:
+        return False
+    return bool(names) and all(n in _groups for n in names)
+
+
+def route_standalone_collectives(on: bool) -> None:
+    """``False``: only the fused GEMM+collective nodes use the symmetric-memory kernels; stand-alone
+    collectives (and their split-phase forms) go to NCCL.  ``True`` (default) routes everything here."""
+    comm_ops._symm_standalone = bool(on)
+
+
 def disable_all() -> None:
     for name in list(_groups):
         comm_ops._symm_backends.pop(name, None)
         _groups.pop(name, None)
+    comm_ops._symm_standalone = True

@@ -41,7 +41,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="debugging only: override the layer count (invalidates the metric)")
     ap.add_argument("--ac", default="auto", choices=["auto", "none", "selective", "full"])
     ap.add_argument("--executor", default="streams", choices=["graph", "streams"])
-    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "symm"])
+    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "symm", "hybrid"],
+                    help="nccl: NCCL collectives under the overlap scheduler; symm: own NVLink kernels for everything, GEMMs fused "
+                         "with their collective; hybrid: fused GEMM+collective kernels, stand-alone collectives on NCCL")
     return ap.parse_args()
 
 
@@ -136,6 +138,15 @@ def run_ours(args):
     if ac == "auto":
         # one GPU holds fp32 params + grads + Adam moments (16 B/param): recompute cheap ops there
         ac = "selective" if world == 1 and cfg.num_params() > 4e9 else "none"
+    comm_mode = args.comm
+    if comm_mode == "auto":
+        comm_mode = os.environ.get("APB200_COMM", "nccl")
+    if world > 1 and comm_mode in ("symm", "hybrid"):
+        # communicators first: the planner fuses a GEMM with its collective only where they exist
+        from autoparallel_b200.runtime import symm
+
+        symm.enable_for_mesh(mesh)
+        symm.route_standalone_collectives(comm_mode == "symm")
     t0 = time.perf_counter()
     with AutoParallel(model, input_fn, mesh, MPPolicy(torch.bfloat16, torch.float32), activation_checkpointing=ac) as ap:
         ap.add_parameter_memory_constraint()
@@ -146,11 +157,8 @@ def run_ours(args):
         solver = ap.sharding_optimizer
         ilp_solve_s = solver.timings.get("solve")
         n_coll = dict(ap.lowered.num_collectives)
+        fused_nodes = dict(ap.fusion_stats)
     plan_s = time.perf_counter() - t0
-    if args.comm == "symm" or (args.comm == "auto" and world > 1 and os.environ.get("APB200_SYMM", "0") == "1"):
-        from autoparallel_b200.runtime import symm
-
-        symm.enable_for_mesh(mesh)
     pm.to_empty(device="cuda")
     pm.init_weights(seed=0)
     opt = AdamW(pm.parameters(), lr=3e-4, weight_decay=0.1)
@@ -235,6 +243,8 @@ def run_ours(args):
                 "optimizer": "AdamW (fp32 state, in the timed region)",
                 "activation_checkpointing": ac,
                 "executor": args.executor,
+                "comm": comm_mode if world > 1 else "none",
+                "fused_nodes": fused_nodes,
                 "collectives_in_graph": n_coll,
                 "l2": "no explicit flush: per-step working set (>=16 GB of weights + activations) >> 126 MB L2",
             },
