@@ -45,10 +45,14 @@ def main():
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--only", default=None, choices=["gemm_nt", "gemm_tn", "rms_norm_bwd", "xent_bwd"],
                     help="run a single small case (what a profiler capture is taken on)")
+    ap.add_argument("--pair", default=None, choices=["on", "off"], help="force the CTA-pair (cta_group::2) GEMM kernel on or off")
+    ap.add_argument("--gemm-only", action="store_true", help="stop after the GEMM rows")
     args = ap.parse_args()
     from autoparallel_b200.ops import cuda_impl, library as L
 
     cuda_impl.ensure_loaded()
+    if args.pair is not None:
+        cuda_impl.extension().gemm_set_pair_mode(args.pair == "on")
     hbm, tf_burst, tf_sus, src = _peaks()
     dev = "cuda"
     bf = torch.bfloat16
@@ -104,6 +108,8 @@ def main():
                 ms, best = time_fn(mk, lambda a, b: torch.matmul(a, b.t()), pool=3)
                 rec(f"  cublas_nt {m}x{n}x{k}", ms, best, flops=2.0 * m * n * k)
     cuda_impl.check_status()
+    if args.gemm_only:
+        return
     D = 4096
     mk = lambda: (torch.randn(M, D, device=dev, dtype=bf), torch.randn(D, device=dev, dtype=bf))
     ms, best = time_fn(mk, lambda x, w: L.ops.rms_norm(x, w, 1e-5), pool=8)

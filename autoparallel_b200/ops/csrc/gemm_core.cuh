@@ -78,6 +78,40 @@ __device__ __forceinline__ void red_add_v4_sys(float* addr, float a, float b, fl
 }
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
+// Epilogue store of one accumulator row chunk: 32 consecutive columns of ``row`` starting at ``col``.
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, long long row, int col, const uint32_t (&r)[32]) {
+  if (row >= p.M || col >= p.N) return;
+  if (p.out_fp32) {
+    float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
+    if (col + 32 <= p.N && (p.ldc & 3) == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<uint4*>(dst)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col + i < p.N) dst[i] = __uint_as_float(r[i]);
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
+    if (col + 32 <= p.N && (p.ldc & 7) == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 v;
+        v.x = pack_bf16(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+        v.y = pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+        v.z = pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+        v.w = pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+        reinterpret_cast<uint4*>(dst)[i] = v;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col + i < p.N) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------- gather warp
 // One lane per CTA drives the copy engine: it publishes this CTA's share of the local shard into the
 // rank's symmetric staging area (and into the local full-size operand), then pulls the same share of
@@ -505,39 +539,7 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
           __syncwarp();
           continue;
         }
-        if (row < p.M && col < p.N) {
-          if (FUSE == FUSE_REDUCE_SCATTER) {
-            // handled below (needs the whole warp)
-          } else if (p.out_fp32) {
-            float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
-            if (col + 32 <= p.N && (p.ldc & 3) == 0) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                reinterpret_cast<uint4*>(dst)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (col + i < p.N) dst[i] = __uint_as_float(r[i]);
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
-            if (col + 32 <= p.N && (p.ldc & 7) == 0) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                uint4 v;
-                v.x = pack_bf16(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
-                v.y = pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-                v.z = pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-                v.w = pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-                reinterpret_cast<uint4*>(dst)[i] = v;
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (col + i < p.N) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
-            }
-          }
-        }
+        store_row_chunk(p, row, col, r);
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty[buf]);
