@@ -11,6 +11,7 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
                   int a_mn_major, int b_mn_major, int out_fp32, uint32_t* status, int num_sms, cudaStream_t stream);
 void apb_gemm_set_pair_mode(int on);
 int apb_gemm_get_pair_mode();
+int apb_gemm_fused_ctas(int fuse, int M, int N, int comm_ctas, int num_sms);
 int apb_rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int D, float eps, int is_bf16,
                      cudaStream_t st);
 int apb_rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw, float* dw_acc,
@@ -207,4 +208,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_header_bytes", &symm_header_bytes);
   m.def("symm_collective", &symm_collective);
   m.def("gemm_fused", &gemm_fused);
+  m.def("gemm_fused_ctas", [](int64_t fuse, int64_t M, int64_t N, int64_t comm_ctas) {
+    return (int64_t)apb_gemm_fused_ctas((int)fuse, (int)M, (int)N, (int)comm_ctas, num_sms());
+  });
 }

@@ -1,7 +1,14 @@
 // Body of the persistent tcgen05 GEMM CTA, shared by the plain GEMM (gemm_tcgen05.cu) and the GEMM
 // kernels fused with a collective (gemm_fused.cu).
 //
-//   tile 128 x 256 x 64, 4 TMA stages, two 256-column TMEM accumulators
+//   PAIR = false: one CTA per tile of 128 x 256 x 64, 4 TMA stages, two 256-column TMEM accumulators
+//   PAIR = true:  a cluster of two CTAs per tile of 256 x 256 x 64 (tcgen05 cta_group::2): each CTA
+//                 owns 128 rows of A, 128 of the 256 B rows (output columns) and 128 accumulator rows
+//                 in its own TMEM; the MMA of the even CTA reads both halves of B, so every SM stages
+//                 32 KB per k-block instead of 48 KB and six stages fit.  TMA transaction bytes and
+//                 the epilogues' "accumulator free" arrivals go to the even CTA's barriers; "stage
+//                 free" and "accumulator full" are committed by the MMA thread to each CTA's barrier
+//                 separately (two plain commits; no multicast anywhere).
 //   warp 0: TMA producer | warp 1: TMEM owner + MMA issuer | warps 2..5: epilogue
 //   warp 6 (gather-fused kernels only): copy engine driver, see gather_comm_warp
 //
@@ -28,6 +35,7 @@ constexpr int B_STAGE_BYTES = BN * BK * 2;
 constexpr int CHUNK_BYTES = BK * 128;  // one [BK x 64-element] MN-major box
 constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int PAIR_STAGES = 6;  // 6 x (16 KB of A + 16 KB of B) = the same 192 KB as 4 x 48 KB
 constexpr int EPI_STAGE_FLOATS = 32 * 33;  // per epilogue warp: one 32x32 fp32 block, padded
 constexpr int GEMM_FUSED_RS_SMEM_BYTES = GEMM_SMEM_BYTES + 4 * EPI_STAGE_FLOATS * 4;
 constexpr int AG_NBUF = 4, AG_CHUNK = 8192;  // bounce ring of the gather warp: 3 bulk loads in flight per CTA
@@ -246,30 +254,40 @@ __device__ __forceinline__ void gather_comm_warp(const GemmParams& p, const Fuse
 }
 
 // cta / num_ctas: index of this CTA among the GEMM CTAs of the launch (fused kernels also run
-// communication CTAs that are not counted here).
-template <bool A_MN, bool B_MN, int FUSE>
+// communication CTAs that are not counted here).  With PAIR, CTAs 2i and 2i+1 form cluster i.
+template <bool A_MN, bool B_MN, int FUSE, bool PAIR = false>
 __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                          const FuseParams& f, int cta, int num_ctas, uint8_t* smem_raw) {
+  constexpr int ST = PAIR ? PAIR_STAGES : STAGES;
+  constexpr int A_BYTES = A_STAGE_BYTES;                          // 128 rows of A per CTA
+  constexpr int B_BYTES = PAIR ? B_STAGE_BYTES / 2 : B_STAGE_BYTES;  // PAIR: this CTA's 128 of the 256 B rows
+  constexpr int B_ROWS = PAIR ? BN / 2 : BN;
+  constexpr int TM = PAIR ? 2 * BM : BM;                          // tile rows
+  static_assert(ST * (A_BYTES + B_BYTES) == STAGES * (A_STAGE_BYTES + B_STAGE_BYTES), "both layouts fill the same shared memory");
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
-  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
-  uint64_t* full = bars;                         // [STAGES]
-  uint64_t* empty = bars + STAGES;               // [STAGES]
-  uint64_t* tmem_full = bars + 2 * STAGES;       // [2]
-  uint64_t* tmem_empty = bars + 2 * STAGES + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint8_t* sB = smem + ST * A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ST * (A_BYTES + B_BYTES));
+  uint64_t* full = bars;                     // [ST]  PAIR: the even CTA's are used
+  uint64_t* empty = bars + ST;               // [ST]
+  uint64_t* tmem_full = bars + 2 * ST;       // [2]
+  uint64_t* tmem_empty = bars + 2 * ST + 2;  // [2]   PAIR: the even CTA's are used (256 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * ST + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  uint64_t* ring_bars = bars + 2 * STAGES + 6;   // [AG_NBUF], gather-fused kernels only
+  uint64_t* ring_bars = bars + 2 * ST + 6;   // [AG_NBUF], gather-fused kernels only
   constexpr bool GATHER = FUSE == FUSE_GATHER_A || FUSE == FUSE_GATHER_B;
+  const uint32_t half = PAIR ? cluster_ctarank() : 0u;  // 0 = even CTA: issues the MMAs, owns the shared barriers
+  const int unit = PAIR ? (cta >> 1) : cta;             // tiles are dealt to CTAs or to CTA pairs
+  const int num_units = PAIR ? (num_ctas >> 1) : num_ctas;
+  const int num_m_units = (p.M + TM - 1) / TM;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int num_tiles = num_m_units * p.num_n_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
   // rotation that makes every rank start on data it already owns
   int m_rot = 0, n_rot = 0, k_rot = 0;
-  if (FUSE == FUSE_GATHER_A && !A_MN) m_rot = (f.rank * f.rows_per_shard) / BM;
+  if (FUSE == FUSE_GATHER_A && !A_MN) m_rot = (f.rank * f.rows_per_shard) / TM;
   // N-partitioned gather (B shards are blocks of output columns): visit the tiles shard by shard,
   // local shard first, so that shard k is first touched after k/n of the GEMM (possible when a
   // shard is a whole number of tile columns); otherwise only rotate the start.
@@ -280,28 +298,28 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
   }
   auto map_tile = [&](int t, int& tm, int& tn) {
     if (shard_n_tiles > 0) {
-      const int per_shard = p.num_m_tiles * shard_n_tiles;
+      const int per_shard = num_m_units * shard_n_tiles;
       const int s = t / per_shard;
-      tile_coords(t - s * per_shard, p.num_m_tiles, shard_n_tiles, tm, tn);
+      tile_coords(t - s * per_shard, num_m_units, shard_n_tiles, tm, tn);
       tn += ((s + f.rank) % f.n) * shard_n_tiles;
     } else {
-      tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
-      tm = (tm + m_rot) % p.num_m_tiles;
+      tile_coords(t, num_m_units, p.num_n_tiles, tm, tn);
+      tm = (tm + m_rot) % num_m_units;
       tn = (tn + n_rot) % p.num_n_tiles;
     }
   };
   if (FUSE == FUSE_GATHER_B && B_MN) k_rot = (f.rank * f.rows_per_shard) / BK;
   if (FUSE == FUSE_GATHER_A && A_MN) k_rot = (f.rank * f.rows_per_shard) / BK;
-  if (FUSE == FUSE_REDUCE_SCATTER) m_rot = (((f.rank + 1) % f.n) * f.rows_per_rank) / BM;  // own rows last
+  if (FUSE == FUSE_REDUCE_SCATTER) m_rot = (((f.rank + 1) % f.n) * f.rows_per_rank) / TM;  // own rows last
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < ST; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], 128);
+      mbar_init(&tmem_empty[b], PAIR ? 256 : 128);
     }
     if (GATHER)
       for (int b = 0; b < AG_NBUF; ++b) mbar_init(&ring_bars[b], 1);
@@ -311,11 +329,20 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) {
+    cluster_arrive();  // the other CTA's barriers are initialised before anything is signalled to them
+    cluster_wait();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -333,14 +360,15 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
         landed_mask |= 1u << s;
         return true;
       };
-      for (int t = cta; t < num_tiles && ok; t += num_ctas) {
+      for (int t = unit; t < num_tiles && ok; t += num_units) {
         int tm, tn;
         map_tile(t, tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
+        // rows of A and of B that THIS CTA stages
+        const int m0 = tm * TM + (int)half * BM, n0 = tn * BN + (int)half * B_ROWS;
         if ((FUSE == FUSE_GATHER_A && !A_MN) || (FUSE == FUSE_GATHER_B && !B_MN)) {
           // the tile's rows of the gathered operand must have landed
           const int r0 = (FUSE == FUSE_GATHER_A) ? m0 : n0;
-          const int extent = (FUSE == FUSE_GATHER_A) ? min(BM, p.M - m0) : min(BN, p.N - n0);
+          const int extent = max(1, (FUSE == FUSE_GATHER_A) ? min(BM, p.M - m0) : min(B_ROWS, p.N - n0));
           const int s0 = r0 / f.rows_per_shard, s1 = (r0 + extent - 1) / f.rows_per_shard;
           for (int s = s0; s <= s1 && ok; ++s) ok = shard_ready(s);
           if (!ok) {
@@ -365,22 +393,40 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
             *abort_flag = 1;
             break;
           }
-          mbar_expect_tx(&full[stage], A_STAGE_BYTES + B_STAGE_BYTES);
-          uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
-          uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
-          if (!A_MN) {
-            tma_load_2d(a_dst, &tmA, &full[stage], kb * BK, m0);
-          } else {
+          uint8_t* a_dst = sA + stage * A_BYTES;
+          uint8_t* b_dst = sB + stage * B_BYTES;
+          if (PAIR) {
+            // both CTAs' bytes are counted on the even CTA's barrier
+            const uint32_t full_addr = map_to_cta(&full[stage], 0);
+            if (half == 0) mbar_expect_tx(&full[stage], 2 * (A_BYTES + B_BYTES));
+            if (!A_MN) {
+              tma_load_2d_pair(a_dst, &tmA, full_addr, kb * BK, m0);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_2d(a_dst + c * CHUNK_BYTES, &tmA, &full[stage], m0 + c * 64, kb * BK);
-          }
-          if (!B_MN) {
-            tma_load_2d(b_dst, &tmB, &full[stage], kb * BK, n0);
-          } else {
+              for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(a_dst + c * CHUNK_BYTES, &tmA, full_addr, m0 + c * 64, kb * BK);
+            }
+            if (!B_MN) {
+              tma_load_2d_pair(b_dst, &tmB, full_addr, kb * BK, n0);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_2d(b_dst + c * CHUNK_BYTES, &tmB, &full[stage], n0 + c * 64, kb * BK);
+              for (int c = 0; c < B_ROWS / 64; ++c) tma_load_2d_pair(b_dst + c * CHUNK_BYTES, &tmB, full_addr, n0 + c * 64, kb * BK);
+            }
+          } else {
+            mbar_expect_tx(&full[stage], A_BYTES + B_BYTES);
+            if (!A_MN) {
+              tma_load_2d(a_dst, &tmA, &full[stage], kb * BK, m0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BM / 64; ++c) tma_load_2d(a_dst + c * CHUNK_BYTES, &tmA, &full[stage], m0 + c * 64, kb * BK);
+            }
+            if (!B_MN) {
+              tma_load_2d(b_dst, &tmB, &full[stage], kb * BK, n0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < B_ROWS / 64; ++c) tma_load_2d(b_dst + c * CHUNK_BYTES, &tmB, &full[stage], n0 + c * 64, kb * BK);
+            }
           }
-          if (++stage == STAGES) {
+          if (++stage == ST) {
             stage = 0;
             phase ^= 1;
           }
@@ -389,14 +435,14 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+    if (lane == 0 && half == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(TM, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
       uint32_t buf_phase = 0;
       bool ok = true;
-      for (int t = cta; t < num_tiles && ok; t += num_ctas) {
+      for (int t = unit; t < num_tiles && ok; t += num_units) {
         if (!mbar_wait(&tmem_empty[buf], buf_phase ^ 1, abort_flag)) {
           atomicCAS(p.status, 0u, (uint32_t)ST_TIMEOUT_TMEM_EMPTY);
           *abort_flag = 1;
@@ -412,24 +458,36 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
-          const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
+          const uint32_t a_addr = smem_u32(sA + stage * A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * B_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t a_desc = A_MN ? make_smem_desc(a_addr + k * (UMMA_K * 128), CHUNK_BYTES, 1024)
                                          : make_smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
             const uint64_t b_desc = B_MN ? make_smem_desc(b_addr + k * (UMMA_K * 128), CHUNK_BYTES, 1024)
                                          : make_smem_desc(b_addr + k * (UMMA_K * 2), 16, 1024);
-            umma_f16(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if (PAIR) umma_f16_pair(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else umma_f16(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&empty[stage]);  // stage reusable once these MMAs have read it
-          if (++stage == STAGES) {
+          // stage reusable once these MMAs have read it (PAIR: in both CTAs)
+          if (PAIR) {
+            umma_commit_pair(map_to_cta(&empty[stage], 0));
+            umma_commit_pair(map_to_cta(&empty[stage], 1));
+          } else {
+            umma_commit(&empty[stage]);
+          }
+          if (++stage == ST) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(&tmem_full[buf]);
+        if (PAIR) {
+          umma_commit_pair(map_to_cta(&tmem_full[buf], 0));
+          umma_commit_pair(map_to_cta(&tmem_full[buf], 1));
+        } else {
+          umma_commit(&tmem_full[buf]);
+        }
         if (++buf == 2) {
           buf = 0;
           buf_phase ^= 1;
@@ -439,7 +497,7 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
   } else if (GATHER && warp == 6) {
     // ------------------------------------------------------------------ gather warp
     if (lane == 0) {
-      BounceRing ring{smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256, ring_bars, 0u};
+      BounceRing ring{smem + ST * (A_BYTES + B_BYTES) + 256, ring_bars, 0u};
       gather_comm_warp(p, f, cta, num_ctas, ring, abort_flag);
     }
   } else {
@@ -447,21 +505,22 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int buf = 0;
     uint32_t buf_phase = 0;
-    for (int t = cta; t < num_tiles; t += num_ctas) {
+    for (int t = unit; t < num_tiles; t += num_units) {
       int tm, tn;
       map_tile(t, tm, tn);
+      const long long cta_row0 = (long long)tm * TM + (long long)half * BM;  // first of this CTA's 128 rows
       if (!mbar_wait(&tmem_full[buf], buf_phase, abort_flag)) {
         atomicCAS(p.status, 0u, (uint32_t)ST_TIMEOUT_TMEM_FULL);
         *abort_flag = 1;
         break;
       }
       tc_fence_after();
-      const long long row = (long long)tm * BM + q * 32 + lane;
+      const long long row = cta_row0 + q * 32 + lane;
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
       float* rs_base = nullptr;
       if (FUSE == FUSE_REDUCE_SCATTER) {
-        const int owner = (tm * BM) / f.rows_per_rank;
+        const int owner = (int)(cta_row0 / f.rows_per_rank);
         // the owner zeroes its accumulation buffer at the start of the step and then raises "ready"
         bool ok = true;
         if (owner != f.rank) {
@@ -488,16 +547,16 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
         if (FUSE == FUSE_REDUCE_SCATTER) {
           // Transpose the warp's 32x32 block through shared memory so that every store instruction
           // writes four 128-byte row segments: NVLink moves full segments instead of 16-byte crumbs.
-          float* stg = reinterpret_cast<float*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256) + (warp - 2) * EPI_STAGE_FLOATS;
+          float* stg = reinterpret_cast<float*>(smem + ST * (A_BYTES + B_BYTES) + 256) + (warp - 2) * EPI_STAGE_FLOATS;
 #pragma unroll
           for (int i = 0; i < 32; ++i) stg[lane * 33 + i] = __uint_as_float(r[i]);
           __syncwarp();
-          const long long row0 = (long long)tm * BM + q * 32;  // first row of this warp's block
+          const long long row0 = cta_row0 + q * 32;  // first row of this warp's block
           float* blk = rs_base - (long long)lane * p.N;         // rs_base points at this lane's row
           if (f.slot_bf16) {
             // 8 bf16 (16 bytes) per lane, 4 lanes per 64-byte row segment, 8 rows per instruction
-            __nv_bfloat16* blk16 = reinterpret_cast<__nv_bfloat16*>(f.peers.base[(tm * BM) / f.rows_per_rank] + apbs::HEADER_BYTES) +
-                                   (blk - reinterpret_cast<float*>(f.peers.base[(tm * BM) / f.rows_per_rank] + apbs::HEADER_BYTES));
+            __nv_bfloat16* blk16 = reinterpret_cast<__nv_bfloat16*>(f.peers.base[(int)(cta_row0 / f.rows_per_rank)] + apbs::HEADER_BYTES) +
+                                   (blk - reinterpret_cast<float*>(f.peers.base[(int)(cta_row0 / f.rows_per_rank)] + apbs::HEADER_BYTES));
             const int sub8 = lane >> 2, seg8 = (lane & 3) * 8;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -542,7 +601,8 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
         store_row_chunk(p, row, col, r);
       }
       tc_fence_before();
-      mbar_arrive(&tmem_empty[buf]);
+      if (PAIR) mbar_arrive_cluster(map_to_cta(&tmem_empty[buf], 0));
+      else mbar_arrive(&tmem_empty[buf]);
       if (++buf == 2) {
         buf = 0;
         buf_phase ^= 1;
@@ -552,9 +612,14 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) {
+    cluster_arrive();  // neither CTA frees TMEM (or exits) while the other may still read or signal
+    cluster_wait();
+  }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if (PAIR) tmem_dealloc_pair(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -590,13 +655,14 @@ inline int make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t ou
 }
 
 // Tensor maps of both operands for C[M,N] = opA * opB (see gemm_tcgen05.cu for the conventions).
+// ``pair``: the CTA-pair kernels load a K-major B in boxes of 128 rows (each CTA stages half of the tile columns).
 inline int make_operand_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, const void* B, int M, int N, int K,
-                             long long lda, long long ldb, int a_mn_major, int b_mn_major) {
+                             long long lda, long long ldb, int a_mn_major, int b_mn_major, bool pair = false) {
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return 3;
   int e = !a_mn_major ? make_map(tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM)
                       : make_map(tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BK);
   if (e) return e;
-  return !b_mn_major ? make_map(tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BN)
+  return !b_mn_major ? make_map(tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, pair ? BN / 2 : BN)
                      : make_map(tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BK);
 }
 

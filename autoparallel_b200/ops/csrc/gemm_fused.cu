@@ -137,16 +137,14 @@ __device__ __forceinline__ void comm_reduce_scatter(const GemmParams& p, const F
   // fits per SM and a communication CTA that lingered would keep a GEMM CTA off its SM.
 }
 
-template <bool A_MN, bool B_MN, int FUSE>
-__global__ void __launch_bounds__(FUSE == FUSE_REDUCE_SCATTER ? GEMM_THREADS : GEMM_AG_THREADS, 1)
-gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p,
-                  FuseParams f, CommParams c) {
-  extern __shared__ uint8_t smem_raw[];
+template <bool A_MN, bool B_MN, int FUSE, bool PAIR>
+__device__ __forceinline__ void fused_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const FuseParams& f,
+                                           const CommParams& c, uint8_t* smem_raw) {
   if (FUSE == FUSE_REDUCE_SCATTER && (int)blockIdx.x < c.comm_ctas) {
     comm_reduce_scatter(p, f, c, blockIdx.x);
     return;
   }
-  gemm_cta<A_MN, B_MN, FUSE>(tmA, tmB, p, f, blockIdx.x - c.comm_ctas, gridDim.x - c.comm_ctas, smem_raw);
+  gemm_cta<A_MN, B_MN, FUSE, PAIR>(tmA, tmB, p, f, blockIdx.x - c.comm_ctas, gridDim.x - c.comm_ctas, smem_raw);
   if (FUSE == FUSE_REDUCE_SCATTER) {
     using namespace apbs;
     uint8_t* my_ws = f.peers.base[f.rank];
@@ -160,9 +158,46 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
+template <bool A_MN, bool B_MN, int FUSE>
+__global__ void __launch_bounds__(FUSE == FUSE_REDUCE_SCATTER ? GEMM_THREADS : GEMM_AG_THREADS, 1)
+gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p,
+                  FuseParams f, CommParams c) {
+  extern __shared__ uint8_t smem_raw[];
+  fused_body<A_MN, B_MN, FUSE, false>(tmA, tmB, p, f, c, smem_raw);
+}
+
+// Same on CTA pairs (clusters of two, 256 x 256 tiles).  With a reduce-scatter the communication
+// CTAs come first in the grid and their number is even, so GEMM CTAs 2i and 2i+1 share a cluster.
+template <bool A_MN, bool B_MN, int FUSE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FUSE == FUSE_REDUCE_SCATTER ? GEMM_THREADS : GEMM_AG_THREADS, 1)
+gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p,
+                       FuseParams f, CommParams c) {
+  extern __shared__ uint8_t smem_raw[];
+  fused_body<A_MN, B_MN, FUSE, true>(tmA, tmB, p, f, c, smem_raw);
+}
+
 }  // namespace apb
 
 using namespace apb;
+
+extern "C" int apb_gemm_get_pair_mode();
+extern "C" int apb_gemm_resident_pairs(int num_sms);
+
+static bool fused_uses_pairs(int M, int N, int comm_ctas) {
+  return apb_gemm_get_pair_mode() && M >= 2 * BM && N >= BN && (comm_ctas & 1) == 0;
+}
+
+// Number of GEMM CTAs a fused launch of this shape runs (the host keeps running totals of their arrivals).
+extern "C" int apb_gemm_fused_ctas(int fuse, int M, int N, int comm_ctas, int num_sms) {
+  const int cc = fuse == FUSE_REDUCE_SCATTER ? comm_ctas : 0;
+  if (fused_uses_pairs(M, N, cc)) {
+    const int tiles2 = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    const int resident = apb_gemm_resident_pairs(num_sms) - cc / 2;
+    return 2 * (tiles2 < resident ? tiles2 : resident);
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return tiles < num_sms ? tiles : num_sms;
+}
 
 // fuse: 1 gather A, 2 gather B, 3 reduce-scatter.  ``targets``: {phase0, phase1, gemm} arrival totals
 // (gathers: one arrival per GEMM CTA in phases 0 and 1; reduce-scatter: comm_ctas in phase 0, GEMM CTAs in 'gemm').
@@ -176,8 +211,9 @@ extern "C" int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, i
                               const unsigned* targets, int comm_ctas, uint32_t* status, int num_sms, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (n > apbs::MAX_RANKS || n < 1 || comm_ctas < 1) return 3;
+  const bool pair = fused_uses_pairs(M, N, fuse == FUSE_REDUCE_SCATTER ? comm_ctas : 0);
   CUtensorMap tmA, tmB;
-  const int e = make_operand_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_mn_major, b_mn_major);
+  const int e = make_operand_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_mn_major, b_mn_major, pair);
   if (e) return e;
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
@@ -204,8 +240,7 @@ extern "C" int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, i
     if ((reinterpret_cast<uintptr_t>(shard_src) & 15) || (reinterpret_cast<uintptr_t>(gbuf) & 15)) return 3;  // bulk copies
     c.comm_ctas = 0;
   }
-  const int tiles = p.num_m_tiles * p.num_n_tiles;
-  const int gemm_ctas = tiles < num_sms ? tiles : num_sms;
+  const int gemm_ctas = apb_gemm_fused_ctas(fuse, M, N, comm_ctas, num_sms);
   const int grid = gemm_ctas + c.comm_ctas;
   const int smem_bytes = fuse == FUSE_REDUCE_SCATTER ? GEMM_FUSED_RS_SMEM_BYTES : GEMM_FUSED_AG_SMEM_BYTES;
   const int threads = fuse == FUSE_REDUCE_SCATTER ? GEMM_THREADS : GEMM_AG_THREADS;
@@ -213,12 +248,19 @@ extern "C" int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, i
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     kern<<<grid, threads, smem_bytes, stream>>>(tmA, tmB, p, f, c);
   };
-#define APB_LAUNCH_FUSED(FUSE)                                                        \
-  do {                                                                                \
-    if (!a_mn_major && !b_mn_major) launch(gemm_fused_kernel<false, false, FUSE>);    \
-    else if (!a_mn_major && b_mn_major) launch(gemm_fused_kernel<false, true, FUSE>); \
-    else if (a_mn_major && !b_mn_major) launch(gemm_fused_kernel<true, false, FUSE>); \
-    else launch(gemm_fused_kernel<true, true, FUSE>);                                 \
+#define APB_LAUNCH_FUSED(FUSE)                                                               \
+  do {                                                                                       \
+    if (pair) {                                                                              \
+      if (!a_mn_major && !b_mn_major) launch(gemm_fused_pair_kernel<false, false, FUSE>);    \
+      else if (!a_mn_major && b_mn_major) launch(gemm_fused_pair_kernel<false, true, FUSE>); \
+      else if (a_mn_major && !b_mn_major) launch(gemm_fused_pair_kernel<true, false, FUSE>); \
+      else launch(gemm_fused_pair_kernel<true, true, FUSE>);                                 \
+    } else {                                                                                 \
+      if (!a_mn_major && !b_mn_major) launch(gemm_fused_kernel<false, false, FUSE>);         \
+      else if (!a_mn_major && b_mn_major) launch(gemm_fused_kernel<false, true, FUSE>);      \
+      else if (a_mn_major && !b_mn_major) launch(gemm_fused_kernel<true, false, FUSE>);      \
+      else launch(gemm_fused_kernel<true, true, FUSE>);                                      \
+    }                                                                                        \
   } while (0)
   if (fuse == FUSE_GATHER_A) APB_LAUNCH_FUSED(FUSE_GATHER_A);
   else if (fuse == FUSE_GATHER_B) APB_LAUNCH_FUSED(FUSE_GATHER_B);

@@ -5,8 +5,8 @@
 //                            B: [N,K] (K-major) or [K,N] (MN-major), bf16
 //                            C: bf16 or fp32, row-major
 //
-// Two kernels: one CTA per SM on 128 x 256 tiles (gemm_core.cuh), and CTA pairs on 256 x 256 tiles
-// with tcgen05 cta_group::2 (gemm_pair.cuh), which halves the B traffic into each SM's shared
+// Two kernels from one body (gemm_core.cuh): one CTA per SM on 128 x 256 tiles, and CTA pairs on
+// 256 x 256 tiles with tcgen05 cta_group::2, which halves the B traffic into each SM's shared
 // memory; ``apb_gemm_set_pair_mode`` selects between them.  All four
 // operand-major combinations run on the tensor cores directly (MN-major operands use the MN-major
 // shared-memory descriptor), so dgrad / wgrad need no transposed copies.
@@ -14,7 +14,6 @@
 // This is the kernel behind aten.mm / apb200::mm_nd / mm_wgrad / gemm; the reference reaches
 // cuBLAS for the same nodes (autoparallel/graph_passes/graph_utils.py:320-412).
 #include "gemm_core.cuh"
-#include "gemm_pair.cuh"
 
 namespace apb {
 
@@ -30,18 +29,26 @@ template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
-  gemm_pair_cta<A_MN, B_MN>(tmA, tmB, p, blockIdx.x >> 1, gridDim.x >> 1, smem_raw);
+  FuseParams f{};
+  gemm_cta<A_MN, B_MN, FUSE_NONE, true>(tmA, tmB, p, f, blockIdx.x, gridDim.x, smem_raw);
 }
 
 static int g_pair_mode = 1;  // 0: one CTA per tile, 1: CTA pairs where the shape allows (default)
 
-// Number of CTA pairs that can be resident at once (an SM without a free partner in its GPC stays idle).
-template <typename Kern>
-static int resident_pairs(Kern kern, int num_sms) {
+}  // namespace apb
+
+// Number of CTA pairs that can be resident at once (an SM without a free partner in its GPC stays
+// idle); cached after the first query.
+extern "C" int apb_gemm_resident_pairs(int num_sms) {
+  static int cached = 0;
+  if (cached > 0) return cached;
+  auto kern = apb::gemm_bf16_pair_kernel<false, false>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, apb::GEMM_SMEM_BYTES);
+  using namespace apb;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(num_sms & ~1));
   cfg.blockDim = dim3(GEMM_THREADS);
-  cfg.dynamicSmemBytes = GEMM_PAIR_SMEM_BYTES;
+  cfg.dynamicSmemBytes = GEMM_SMEM_BYTES;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
   attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
@@ -52,10 +59,9 @@ static int resident_pairs(Kern kern, int num_sms) {
     cudaGetLastError();
     n = num_sms / 2;
   }
+  cached = n;
   return n;
 }
-
-}  // namespace apb
 
 using namespace apb;
 
@@ -82,17 +88,16 @@ extern "C" int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     if (!b_mn_major) e2 = make_map(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BN / 2);
     if (e2) return e2;
     const int tiles2 = ((M + 2 * BM - 1) / (2 * BM)) * p.num_n_tiles;
-    auto launch2 = [&](auto kern, int& cached_pairs) {
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_PAIR_SMEM_BYTES);
-      if (cached_pairs == 0) cached_pairs = resident_pairs(kern, num_sms);
-      const int pairs = tiles2 < cached_pairs ? tiles2 : cached_pairs;
-      kern<<<2 * pairs, GEMM_THREADS, GEMM_PAIR_SMEM_BYTES, stream>>>(tmA, tmB, p);
+    const int resident = apb_gemm_resident_pairs(num_sms);
+    const int pairs = tiles2 < resident ? tiles2 : resident;
+    auto launch2 = [&](auto kern) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+      kern<<<2 * pairs, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p);
     };
-    static int pairs_cache[4] = {0, 0, 0, 0};
-    if (!a_mn_major && !b_mn_major) launch2(gemm_bf16_pair_kernel<false, false>, pairs_cache[0]);
-    else if (!a_mn_major && b_mn_major) launch2(gemm_bf16_pair_kernel<false, true>, pairs_cache[1]);
-    else if (a_mn_major && !b_mn_major) launch2(gemm_bf16_pair_kernel<true, false>, pairs_cache[2]);
-    else launch2(gemm_bf16_pair_kernel<true, true>, pairs_cache[3]);
+    if (!a_mn_major && !b_mn_major) launch2(gemm_bf16_pair_kernel<false, false>);
+    else if (!a_mn_major && b_mn_major) launch2(gemm_bf16_pair_kernel<false, true>);
+    else if (a_mn_major && !b_mn_major) launch2(gemm_bf16_pair_kernel<true, false>);
+    else launch2(gemm_bf16_pair_kernel<true, true>);
     return cudaGetLastError() == cudaSuccess ? 0 : 4;
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;

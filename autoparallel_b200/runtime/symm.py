@@ -138,13 +138,14 @@ class SymmGroup:
         landed = self._landed()
         self.epoch += 1
         ctas = self.fused_comm_ctas
-        # the kernel runs min(#SMs, #tiles) GEMM CTAs over 128 x 256 output tiles
+        # the kernel reports how many GEMM CTAs (or CTA pairs) a launch of this shape runs
+        M_full = c.shape[0] * self.n if fuse == self.FUSE_REDUCE_SCATTER else c.shape[0]
+        gemm_ctas = int(self._C.gemm_fused_ctas(fuse, M_full, c.shape[1], ctas))
         if fuse == self.FUSE_REDUCE_SCATTER:
             self.arrivals[2] += ctas
-            self.arrivals[4] += min(self._num_sms, -(-c.shape[0] * self.n // 128) * -(-c.shape[1] // 256))
+            self.arrivals[4] += gemm_ctas
         else:
             # every GEMM CTA carries a gather warp that arrives once per phase and once per shard
-            gemm_ctas = min(self._num_sms, -(-c.shape[0] // 128) * -(-c.shape[1] // 256))
             self.arrivals[2] += gemm_ctas
             self.arrivals[3] += gemm_ctas
             self._landed_total += gemm_ctas
