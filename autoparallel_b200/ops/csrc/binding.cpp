@@ -11,6 +11,8 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
                   int a_mn_major, int b_mn_major, int out_fp32, uint32_t* status, int num_sms, cudaStream_t stream);
 void apb_gemm_set_pair_mode(int on);
 int apb_gemm_get_pair_mode();
+void apb_gemm_set_reserved_sms(int n);
+int apb_gemm_get_reserved_sms();
 int apb_gemm_fused_ctas(int fuse, int M, int N, int comm_ctas, int num_sms);
 int apb_rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int D, float eps, int is_bf16,
                      cudaStream_t st);
@@ -194,6 +196,8 @@ void gemm_fused(int64_t fuse, const at::Tensor& a, const at::Tensor& b, at::Tens
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_set_pair_mode", [](bool on) { apb_gemm_set_pair_mode(on ? 1 : 0); });
+  m.def("gemm_set_reserved_sms", [](int64_t n) { apb_gemm_set_reserved_sms((int)n); });
+  m.def("gemm_get_reserved_sms", []() { return (int64_t)apb_gemm_get_reserved_sms(); });
   m.def("gemm_get_pair_mode", []() { return apb_gemm_get_pair_mode() != 0; });
   m.def("rms_norm_fwd", &rms_norm_fwd);
   m.def("rms_norm_bwd", &rms_norm_bwd);

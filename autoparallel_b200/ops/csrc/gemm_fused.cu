@@ -182,6 +182,7 @@ using namespace apb;
 
 extern "C" int apb_gemm_get_pair_mode();
 extern "C" int apb_gemm_resident_pairs(int num_sms);
+extern "C" int apb_gemm_get_reserved_sms();
 
 static bool fused_uses_pairs(int M, int N, int comm_ctas) {
   return apb_gemm_get_pair_mode() && M >= 2 * BM && N >= BN && (comm_ctas & 1) == 0;
@@ -192,11 +193,13 @@ extern "C" int apb_gemm_fused_ctas(int fuse, int M, int N, int comm_ctas, int nu
   const int cc = fuse == FUSE_REDUCE_SCATTER ? comm_ctas : 0;
   if (fused_uses_pairs(M, N, cc)) {
     const int tiles2 = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
-    const int resident = apb_gemm_resident_pairs(num_sms) - cc / 2;
+    int resident = apb_gemm_resident_pairs(num_sms) - cc / 2 - apb_gemm_get_reserved_sms() / 2;
+    if (resident < 1) resident = 1;
     return 2 * (tiles2 < resident ? tiles2 : resident);
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  return tiles < num_sms ? tiles : num_sms;
+  const int usable = num_sms - apb_gemm_get_reserved_sms() > 0 ? num_sms - apb_gemm_get_reserved_sms() : 1;
+  return tiles < usable ? tiles : usable;
 }
 
 // fuse: 1 gather A, 2 gather B, 3 reduce-scatter.  ``targets``: {phase0, phase1, gemm} arrival totals

@@ -65,6 +65,11 @@ extern "C" int apb_gemm_resident_pairs(int num_sms) {
 
 using namespace apb;
 
+// SMs that the GEMM kernels leave idle so that communication kernels launched on other streams (NCCL)
+// find a free SM right away: a persistent GEMM CTA owns its SM's shared memory for the whole kernel.
+static int g_reserved_sms = 0;
+extern "C" void apb_gemm_set_reserved_sms(int n) { g_reserved_sms = n < 0 ? 0 : (n & ~1); }
+extern "C" int apb_gemm_get_reserved_sms() { return g_reserved_sms; }
 extern "C" void apb_gemm_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
 extern "C" int apb_gemm_get_pair_mode() { return g_pair_mode; }
 
@@ -88,7 +93,8 @@ extern "C" int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     if (!b_mn_major) e2 = make_map(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BN / 2);
     if (e2) return e2;
     const int tiles2 = ((M + 2 * BM - 1) / (2 * BM)) * p.num_n_tiles;
-    const int resident = apb_gemm_resident_pairs(num_sms);
+    int resident = apb_gemm_resident_pairs(num_sms) - g_reserved_sms / 2;
+    if (resident < 1) resident = 1;
     const int pairs = tiles2 < resident ? tiles2 : resident;
     auto launch2 = [&](auto kern) {
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
@@ -101,7 +107,8 @@ extern "C" int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     return cudaGetLastError() == cudaSuccess ? 0 : 4;
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
-  const int grid = tiles < num_sms ? tiles : num_sms;
+  const int usable = num_sms - g_reserved_sms > 0 ? num_sms - g_reserved_sms : 1;
+  const int grid = tiles < usable ? tiles : usable;
   auto launch = [&](auto kern) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
     kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p);

@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "symm", "hybrid"],
                     help="nccl: NCCL collectives under the overlap scheduler; symm: own NVLink kernels for everything, GEMMs fused "
                          "with their collective; hybrid: fused GEMM+collective kernels, stand-alone collectives on NCCL")
+    ap.add_argument("--reserve-sms", type=int, default=None,
+                    help="SMs the GEMM kernels leave idle for NCCL kernels on other streams, which are then capped to as many CTAs "
+                         "(default 0: measured slower at N=2, 492 ms with 16 and 523 ms with 8 against 468 ms with none)")
     return ap.parse_args()
 
 
@@ -117,8 +120,17 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29500")
+    reserve = args.reserve_sms
+    if reserve is None:
+        reserve = int(os.environ.get("APB200_RESERVE_SMS", "0")) if world > 1 else 0
+    if reserve > 0:
+        # NCCL kernels get as many CTAs as the GEMM kernels leave SMs free (a persistent GEMM CTA owns
+        # its SM's shared memory, so a collective launched beside it would otherwise wait for a GEMM to end)
+        os.environ.setdefault("NCCL_MAX_CTAS", str(reserve))
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
     mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    cuda_impl.ensure_loaded()
+    cuda_impl.extension().gemm_set_reserved_sms(reserve)
 
     cfg = {"llama3_8b": llama3.llama3_8b, "llama3_debug": llama3.llama3_debug,
            "llama3_1b": lambda **kw: llama3.llama3_8b(dim=2048, n_layers=16, n_heads=16, n_kv_heads=8, ffn_hidden=8192, **kw)}[args.model](
@@ -140,13 +152,21 @@ def run_ours(args):
         ac = "selective" if world == 1 and cfg.num_params() > 4e9 else "none"
     comm_mode = args.comm
     if comm_mode == "auto":
-        comm_mode = os.environ.get("APB200_COMM", "nccl")
+        # measured on this model: the fused kernels win at 8 GPUs (489.6 vs 496.1 ms), NCCL under the
+        # overlap scheduler at 2 and 4 (468 vs 472 ms, 491 vs 504 ms)
+        comm_mode = os.environ.get("APB200_COMM", "hybrid" if world >= 8 else "nccl")
     if world > 1 and comm_mode in ("symm", "hybrid"):
         # communicators first: the planner fuses a GEMM with its collective only where they exist
         from autoparallel_b200.runtime import symm
 
-        symm.enable_for_mesh(mesh)
-        symm.route_standalone_collectives(comm_mode == "symm")
+        try:
+            symm.enable_for_mesh(mesh)
+            symm.route_standalone_collectives(comm_mode == "symm")
+        except Exception as e:  # no peer access / symmetric memory on this machine: NCCL carries everything
+            if rank == 0:
+                print(f"symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr, flush=True)
+            symm.disable_all()
+            comm_mode = "nccl"
     t0 = time.perf_counter()
     with AutoParallel(model, input_fn, mesh, MPPolicy(torch.bfloat16, torch.float32), activation_checkpointing=ac) as ap:
         ap.add_parameter_memory_constraint()
@@ -244,6 +264,7 @@ def run_ours(args):
                 "activation_checkpointing": ac,
                 "executor": args.executor,
                 "comm": comm_mode if world > 1 else "none",
+                "reserved_sms_for_comm": reserve,
                 "fused_nodes": fused_nodes,
                 "collectives_in_graph": n_coll,
                 "l2": "no explicit flush: per-step working set (>=16 GB of weights + activations) >> 126 MB L2",
