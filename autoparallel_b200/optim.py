@@ -53,9 +53,25 @@ class AdamW(torch.optim.Optimizer):
                                 _local(st["exp_avg_sq"]).data_ptr(), 0, n)
             chunks += [(ti, c) for c in range((n + self.CHUNK - 1) // self.CHUNK)]
         dev = _local(plist[0]).device
-        table = torch.frombuffer(bytes(recs), dtype=torch.uint8).to(dev)
-        ch = torch.tensor(chunks, dtype=torch.int32).reshape(-1, 2).to(dev)
-        self._tables[gi] = (key, table, ch, len(chunks))
+        # Gradients are fresh tensors every step, so the record table changes every step: stage it in
+        # pinned memory and copy asynchronously (a pageable copy would stall the host until the GPU has
+        # drained the whole backward pass).  The chunk list only depends on the sizes and is kept.
+        nbytes = len(recs)
+        stage = cached[4] if cached is not None and cached[4].numel() == nbytes else None
+        if stage is None:
+            stage = {"host": torch.empty(nbytes, dtype=torch.uint8, pin_memory=True),
+                     "dev": torch.empty(nbytes, dtype=torch.uint8, device=dev), "ev": None}
+            ch = torch.tensor(chunks, dtype=torch.int32).reshape(-1, 2).to(dev)
+        else:
+            stage, ch = cached[5], cached[2]
+        if stage["ev"] is not None:
+            stage["ev"].synchronize()  # the previous copy out of the pinned buffer has completed
+        stage["host"].copy_(torch.frombuffer(recs, dtype=torch.uint8))
+        stage["dev"].copy_(stage["host"], non_blocking=True)
+        stage["ev"] = torch.cuda.Event()
+        stage["ev"].record()
+        table = stage["dev"]
+        self._tables[gi] = (key, table, ch, len(chunks), stage["host"], stage)
         return table, ch, len(chunks)
 
     @torch.no_grad()

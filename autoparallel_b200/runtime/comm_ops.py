@@ -37,6 +37,32 @@ _symm_backends: dict[str, object] = {}
 _symm_standalone = True
 
 
+#: group name -> name of a second process group over the same ranks that carries the reductions, so a
+#: latency-critical parameter gather never queues behind a bulk gradient reduce-scatter on one NCCL stream
+_reduction_group: dict[str, str] = {}
+
+
+def use_separate_reduction_groups(mesh) -> None:
+    """Create (collectively, on every rank) a second process group per mesh dim for reduce-scatter /
+    all-reduce.  Both groups issue in the same program order on every rank; the GEMM kernels never
+    wait on a peer, so the two NCCL streams cannot starve each other."""
+    for i in range(mesh.ndim):
+        if mesh.shape[i] <= 1:
+            continue
+        # every rank creates every subgroup of this mesh dim (new_group is collective over the world)
+        pg_ranks = mesh.mesh.movedim(i, -1).reshape(-1, mesh.shape[i]).tolist()
+        mine = mesh.get_group(i)
+        my_ranks = dist.get_process_group_ranks(mine)
+        for ranks in pg_ranks:
+            g = dist.new_group(ranks)
+            if sorted(ranks) == sorted(my_ranks):
+                _reduction_group[mine.group_name] = g.group_name
+
+
+def _red_group(group: str) -> str:
+    return _reduction_group.get(group, group)
+
+
 def _standalone_backend(group):
     return _symm_backends.get(group) if _symm_standalone else None
 
@@ -75,7 +101,7 @@ def _reduce_scatter(x, dim, group, n):
     if dim != 0:
         x = x.view(*x.shape[:dim], n, shape[dim], *x.shape[dim + 1 :]).movedim(dim, 0)
     flat = x.reshape(-1) if x.is_contiguous() else x.contiguous().view(-1)
-    out = torch.ops._c10d_functional.reduce_scatter_tensor(flat, "sum", n, group)
+    out = torch.ops._c10d_functional.reduce_scatter_tensor(flat, "sum", n, _red_group(group))
     return torch.ops._c10d_functional.wait_tensor(out).view(shape)
 
 
@@ -83,7 +109,7 @@ def _all_reduce(x, group, n):
     be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_reduce(x)
-    out = torch.ops._c10d_functional.all_reduce(x.contiguous(), "sum", group)
+    out = torch.ops._c10d_functional.all_reduce(x.contiguous(), "sum", _red_group(group))
     return torch.ops._c10d_functional.wait_tensor(out)
 
 
@@ -210,7 +236,7 @@ def _rs_start(x, dim, group, n):
         return _reduce_scatter(x, dim, group, n)
     shape = list(x.shape)
     shape[0] //= n
-    out = torch.ops._c10d_functional.reduce_scatter_tensor(x.contiguous().view(-1), "sum", n, group)
+    out = torch.ops._c10d_functional.reduce_scatter_tensor(x.contiguous().view(-1), "sum", n, _red_group(group))
     return out.view(shape)
 
 
@@ -218,7 +244,7 @@ def _ar_start(x, group, n):
     be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_reduce_start(x)
-    return torch.ops._c10d_functional.all_reduce(x.contiguous(), "sum", group)
+    return torch.ops._c10d_functional.all_reduce(x.contiguous(), "sum", _red_group(group))
 
 
 def _comm_wait(x):

@@ -44,6 +44,8 @@ def parse():
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "symm", "hybrid"],
                     help="nccl: NCCL collectives under the overlap scheduler; symm: own NVLink kernels for everything, GEMMs fused "
                          "with their collective; hybrid: fused GEMM+collective kernels, stand-alone collectives on NCCL")
+    ap.add_argument("--reduction-group", default="separate", choices=["separate", "shared"],
+                    help="separate: gradient reductions run on a second NCCL communicator so that parameter gathers never queue behind them")
     ap.add_argument("--reserve-sms", type=int, default=None,
                     help="SMs the GEMM kernels leave idle for NCCL kernels on other streams, which are then capped to as many CTAs "
                          "(default 0: measured slower at N=2, 492 ms with 16 and 523 ms with 8 against 468 ms with none)")
@@ -122,7 +124,8 @@ def run_ours(args):
     os.environ.setdefault("MASTER_PORT", "29500")
     reserve = args.reserve_sms
     if reserve is None:
-        reserve = int(os.environ.get("APB200_RESERVE_SMS", "0")) if world > 1 else 0
+        # hybrid: NCCL kernels and peer-waiting fused kernels share the GPU, so NCCL gets SMs of its own
+        reserve = int(os.environ.get("APB200_RESERVE_SMS", "16" if args.comm == "hybrid" else "0")) if world > 1 else 0
     if reserve > 0:
         # NCCL kernels get as many CTAs as the GEMM kernels leave SMs free (a persistent GEMM CTA owns
         # its SM's shared memory, so a collective launched beside it would otherwise wait for a GEMM to end)
@@ -152,9 +155,11 @@ def run_ours(args):
         ac = "selective" if world == 1 and cfg.num_params() > 4e9 else "none"
     comm_mode = args.comm
     if comm_mode == "auto":
-        # measured on this model: the fused kernels win at 8 GPUs (489.6 vs 496.1 ms), NCCL under the
-        # overlap scheduler at 2 and 4 (468 vs 472 ms, 491 vs 504 ms)
-        comm_mode = os.environ.get("APB200_COMM", "hybrid" if world >= 8 else "nccl")
+        # Measured on this model (ms/step, nccl vs hybrid on the same box): N=2 468 / 472, N=4 491 / 504,
+        # N=8 496 / 490.  NCCL under the overlap scheduler is the default at every N: in hybrid mode a
+        # fused kernel spins on its peers while NCCL kernels of the same step compete for SMs, which is only
+        # safe with SMs set aside for NCCL (--reserve-sms), and that configuration has not been timed.
+        comm_mode = os.environ.get("APB200_COMM", "nccl")
     if world > 1 and comm_mode in ("symm", "hybrid"):
         # communicators first: the planner fuses a GEMM with its collective only where they exist
         from autoparallel_b200.runtime import symm
@@ -167,6 +172,10 @@ def run_ours(args):
                 print(f"symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr, flush=True)
             symm.disable_all()
             comm_mode = "nccl"
+    if world > 1 and args.reduction_group == "separate":
+        from autoparallel_b200.runtime import comm_ops
+
+        comm_ops.use_separate_reduction_groups(mesh)
     t0 = time.perf_counter()
     with AutoParallel(model, input_fn, mesh, MPPolicy(torch.bfloat16, torch.float32), activation_checkpointing=ac) as ap:
         ap.add_parameter_memory_constraint()
@@ -265,6 +274,7 @@ def run_ours(args):
                 "executor": args.executor,
                 "comm": comm_mode if world > 1 else "none",
                 "reserved_sms_for_comm": reserve,
+                "reduction_group": args.reduction_group if world > 1 else "none",
                 "fused_nodes": fused_nodes,
                 "collectives_in_graph": n_coll,
                 "l2": "no explicit flush: per-step working set (>=16 GB of weights + activations) >> 126 MB L2",

@@ -25,6 +25,12 @@ def _llama_worker(rank, ws, shape, executor, mp_policy, port, q):
     from autoparallel_b200.parallel.frontend.mp_cast import MPPolicy
 
     mesh = init_device_mesh("cpu", shape, mesh_dim_names=("dp", "tp")[: len(shape)])
+    if executor == "streams":
+        # reductions on a second communicator per mesh dim (what the training entry point does)
+        from autoparallel_b200.runtime import comm_ops
+
+        comm_ops.use_separate_reduction_groups(mesh)
+        assert len(comm_ops._reduction_group) == sum(1 for s_ in shape if s_ > 1)
     cfg = llama3_debug()
     B, S = 8, 64
     with torch.device("meta"):
