@@ -1,4 +1,5 @@
-"""Mixture-of-experts decoder with expert parallelism through ``local_map``.
+"""Mixture-of-experts decoder with expert parallelism through ``local_map`` or through
+planner-visible MoE operators (``MoEConfig.expert_mode``).
 
 Config of record: 12 layers, d_model 2048, 16 query / 4 KV heads, RoPE, RMSNorm, vocab 102400;
 every FFN is MoE with 64 routed SwiGLU experts (hidden 1408), softmax top-8 router, plus one
@@ -48,6 +49,11 @@ class MoEConfig:
     init_std: float = 0.02
     ep_axis: str = "ep"
     router_bias_zipf: Optional[float] = None  # s of a Zipf(s) bias over experts (skewed-load runs)
+    #: "local_map": the routed block is one opaque region with hand-written all-to-alls on ``ep_axis``;
+    #: "planner": the block is built from the apb200 MoE operators (ops/moe_ops.py) and the solver
+    #: chooses where the token buffer moves to the experts (no mesh axis is named in the model)
+    expert_mode: str = "local_map"
+    dispatch_blocks: int = 8  # planner mode: token blocks with their own per-expert capacity (a multiple of the shard count)
 
     def attn_cfg(self) -> LlamaConfig:
         return LlamaConfig(dim=self.dim, n_layers=self.n_layers, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
@@ -89,9 +95,7 @@ def _expert_region(x, gate_w, gate_idx, w1, w3, w2, *, ep_axis: str, num_experts
     send = send.view(n, e_loc * capacity, d)
     recv = all_to_all(send.reshape(n * e_loc * capacity, d), ep_axis, 0, 0).view(n, e_loc, capacity, d)
     h = recv.permute(1, 0, 2, 3).reshape(e_loc, n * capacity, d)    # expert-major
-    a = torch.bmm(h, w1)
-    b = torch.bmm(h, w3)
-    y = torch.bmm(F.silu(a) * b, w2)                                # [E_loc, n*C, d]
+    y = K.grouped_mm(K.swiglu(K.grouped_mm(h, w1), K.grouped_mm(h, w3)), w2)   # [E_loc, n*C, d]: one grouped GEMM launch each
     back = y.view(e_loc, n, capacity, d).permute(1, 0, 2, 3).reshape(n * e_loc * capacity, d)
     got = all_to_all(back, ep_axis, 0, 0)                           # [E*C, d] in this rank's slot order
     got = torch.cat([got, got.new_zeros(1, d)], 0)
@@ -121,6 +125,9 @@ class MoEFFN(nn.Module):
         gate_w, gate_idx = torch.topk(scores, cfg.top_k, dim=-1)
         gate_w = gate_w / gate_w.sum(-1, keepdim=True)
         shared = self.shared_w2(K.swiglu(self.shared_w1(x), self.shared_w3(x)))
+        if cfg.expert_mode == "planner":
+            return shared + self._routed_planner(x.reshape(b * s, d), gate_w.to(x.dtype).reshape(b * s, -1),
+                                                 gate_idx.reshape(b * s, -1)).view(b, s, d)
         tokens_per_rank = (b * s) // axis_size(cfg.ep_axis)
         capacity = max(1, math.ceil(cfg.capacity_factor * tokens_per_rank * cfg.top_k / cfg.num_experts))
 
@@ -133,6 +140,17 @@ class MoEFFN(nn.Module):
         routed = local_map(region, out_placements=(tok_pl,), in_placements=(tok_pl,) * 6)(
             gate_idx.reshape(b * s, -1), x.reshape(b * s, d), self.w1, self.w3, self.w2, gate_w.to(x.dtype).reshape(b * s, -1))
         return shared + routed.view(b, s, d)
+
+    def _routed_planner(self, xf, gate_w, gate_idx):
+        """Routed experts as graph nodes the solver places: slots -> scatter -> 3 grouped GEMMs -> gather."""
+        cfg = self.cfg
+        T, d = xf.shape
+        E, nb = cfg.num_experts, cfg.dispatch_blocks
+        capacity = max(1, math.ceil(cfg.capacity_factor * (T // nb) * cfg.top_k / E))
+        slot = K.moe_slots(gate_idx, E, capacity, nb)
+        h = K.moe_dispatch(xf, slot, E, capacity, nb).view(E, nb * capacity, d)
+        y = K.grouped_mm(K.swiglu(K.grouped_mm(h, self.w1), K.grouped_mm(h, self.w3)), self.w2)
+        return K.moe_combine(y.view(E, nb, capacity, d), slot, gate_w)
 
     def init_weights(self, std: float):
         nn.init.normal_(self.router.weight, mean=0.0, std=std)

@@ -11,3 +11,5 @@ from .library import (  # noqa: F401
     rope,
     swiglu,
 )
+from . import moe_ops  # noqa: F401,E402  (registers the planner-visible MoE operators)
+from .moe_ops import grouped_mm, moe_combine, moe_dispatch, moe_slots  # noqa: F401,E402

@@ -9,6 +9,8 @@
 extern "C" {
 int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
                   int a_mn_major, int b_mn_major, int out_fp32, uint32_t* status, int num_sms, cudaStream_t stream);
+int apb_gemm_grouped_bf16(const void* A, const void* B, void* C, int G, int M, int N, int K, int a_mn_major, int b_mn_major,
+                          int out_fp32, uint32_t* status, int num_sms, cudaStream_t stream);
 void apb_gemm_set_pair_mode(int on);
 int apb_gemm_get_pair_mode();
 void apb_gemm_set_reserved_sms(int n);
@@ -74,6 +76,23 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_maj
   check(apb_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, a.stride(0), b.stride(0), c.stride(0), a_mn_major,
                       b_mn_major, out_fp32, reinterpret_cast<uint32_t*>(status.data_ptr()), num_sms(), stream()),
         "apb_gemm_bf16");
+}
+
+// c[g] = opA[g] * opB[g]; a: [G,M,K] (or [G,K,M] if a_mn_major); b: [G,N,K] (or [G,K,N]); c: [G,M,N]; all contiguous.
+void gemm_grouped(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, at::Tensor& status) {
+  c10::cuda::CUDAGuard g(a.device());
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm_grouped: bf16 operands required");
+  TORCH_CHECK(a.dim() == 3 && b.dim() == 3 && c.dim() == 3 && a.is_contiguous() && b.is_contiguous() && c.is_contiguous(),
+              "gemm_grouped: contiguous 3-d operands required");
+  const int G = c.size(0), M = c.size(1), N = c.size(2);
+  const int K = a_mn_major ? a.size(1) : a.size(2);
+  TORCH_CHECK(a.size(0) == G && b.size(0) == G && (a_mn_major ? a.size(2) : a.size(1)) == M, "gemm_grouped: A shape mismatch");
+  TORCH_CHECK((b_mn_major ? b.size(2) : b.size(1)) == N && (b_mn_major ? b.size(1) : b.size(2)) == K, "gemm_grouped: B shape mismatch");
+  const bool out_fp32 = c.scalar_type() == at::kFloat;
+  TORCH_CHECK(out_fp32 || c.scalar_type() == at::kBFloat16, "gemm_grouped: output must be bf16 or fp32");
+  check(apb_gemm_grouped_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), G, M, N, K, a_mn_major, b_mn_major, out_fp32,
+                              reinterpret_cast<uint32_t*>(status.data_ptr()), num_sms(), stream()),
+        "apb_gemm_grouped_bf16");
 }
 
 void rms_norm_fwd(const at::Tensor& x, const at::Tensor& w, at::Tensor& y, at::Tensor& rstd, double eps) {
@@ -195,6 +214,7 @@ void gemm_fused(int64_t fuse, const at::Tensor& a, const at::Tensor& b, at::Tens
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("gemm_grouped", &gemm_grouped);
   m.def("gemm_set_pair_mode", [](bool on) { apb_gemm_set_pair_mode(on ? 1 : 0); });
   m.def("gemm_set_reserved_sms", [](int64_t n) { apb_gemm_set_reserved_sms((int)n); });
   m.def("gemm_get_reserved_sms", []() { return (int64_t)apb_gemm_get_reserved_sms(); });

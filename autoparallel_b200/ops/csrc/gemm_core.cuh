@@ -51,6 +51,7 @@ struct GemmParams {
   int out_fp32;
   int num_m_tiles, num_n_tiles;
   uint32_t* status;
+  int groups = 1;  // grouped GEMM: G independent problems of the same M, N, K, stacked along a third tensor-map dim
 };
 
 struct FuseParams {
@@ -87,10 +88,11 @@ __device__ __forceinline__ void red_add_v4_sys(float* addr, float a, float b, fl
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 // Epilogue store of one accumulator row chunk: 32 consecutive columns of ``row`` starting at ``col``.
-__device__ __forceinline__ void store_row_chunk(const GemmParams& p, long long row, int col, const uint32_t (&r)[32]) {
+// ``c_off``: element offset of the output matrix inside C (grouped GEMM: group * M * ldc).
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, long long row, int col, const uint32_t (&r)[32], long long c_off = 0) {
   if (row >= p.M || col >= p.N) return;
   if (p.out_fp32) {
-    float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
+    float* dst = reinterpret_cast<float*>(p.C) + c_off + row * p.ldc + col;
     if (col + 32 <= p.N && (p.ldc & 3) == 0) {
 #pragma unroll
       for (int i = 0; i < 8; ++i)
@@ -101,7 +103,7 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, long long r
         if (col + i < p.N) dst[i] = __uint_as_float(r[i]);
     }
   } else {
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + row * p.ldc + col;
     if (col + 32 <= p.N && (p.ldc & 7) == 0) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -255,7 +257,8 @@ __device__ __forceinline__ void gather_comm_warp(const GemmParams& p, const Fuse
 
 // cta / num_ctas: index of this CTA among the GEMM CTAs of the launch (fused kernels also run
 // communication CTAs that are not counted here).  With PAIR, CTAs 2i and 2i+1 form cluster i.
-template <bool A_MN, bool B_MN, int FUSE, bool PAIR = false>
+// GROUPED: p.groups problems; operands are 3-D tensor maps [group][rows][inner] (FUSE_NONE only).
+template <bool A_MN, bool B_MN, int FUSE, bool PAIR = false, bool GROUPED = false>
 __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                          const FuseParams& f, int cta, int num_ctas, uint8_t* smem_raw) {
   constexpr int ST = PAIR ? PAIR_STAGES : STAGES;
@@ -283,7 +286,8 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = num_m_units * p.num_n_tiles;
+  const int tiles_per_group = num_m_units * p.num_n_tiles;
+  const int num_tiles = tiles_per_group * (GROUPED ? p.groups : 1);
   const int num_kb = (p.K + BK - 1) / BK;
   // rotation that makes every rank start on data it already owns
   int m_rot = 0, n_rot = 0, k_rot = 0;
@@ -297,6 +301,7 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
     else n_rot = (f.rank * f.rows_per_shard) / BN;
   }
   auto map_tile = [&](int t, int& tm, int& tn) {
+    if (GROUPED) t %= tiles_per_group;
     if (shard_n_tiles > 0) {
       const int per_shard = num_m_units * shard_n_tiles;
       const int s = t / per_shard;
@@ -365,6 +370,7 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
         map_tile(t, tm, tn);
         // rows of A and of B that THIS CTA stages
         const int m0 = tm * TM + (int)half * BM, n0 = tn * BN + (int)half * B_ROWS;
+        const int grp = GROUPED ? t / tiles_per_group : 0;
         if ((FUSE == FUSE_GATHER_A && !A_MN) || (FUSE == FUSE_GATHER_B && !B_MN)) {
           // the tile's rows of the gathered operand must have landed
           const int r0 = (FUSE == FUSE_GATHER_A) ? m0 : n0;
@@ -395,36 +401,33 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
           }
           uint8_t* a_dst = sA + stage * A_BYTES;
           uint8_t* b_dst = sB + stage * B_BYTES;
+          // one load helper for the four cases (pair or not, 2-D or grouped 3-D)
+          const uint32_t full_addr = PAIR ? map_to_cta(&full[stage], 0) : 0u;
+          auto load = [&](uint8_t* dst, const CUtensorMap* tm_, int x, int y) {
+            if (PAIR) {
+              if (GROUPED) tma_load_3d_pair(dst, tm_, full_addr, x, y, grp);
+              else tma_load_2d_pair(dst, tm_, full_addr, x, y);
+            } else {
+              if (GROUPED) tma_load_3d(dst, tm_, &full[stage], x, y, grp);
+              else tma_load_2d(dst, tm_, &full[stage], x, y);
+            }
+          };
           if (PAIR) {
-            // both CTAs' bytes are counted on the even CTA's barrier
-            const uint32_t full_addr = map_to_cta(&full[stage], 0);
-            if (half == 0) mbar_expect_tx(&full[stage], 2 * (A_BYTES + B_BYTES));
-            if (!A_MN) {
-              tma_load_2d_pair(a_dst, &tmA, full_addr, kb * BK, m0);
-            } else {
-#pragma unroll
-              for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(a_dst + c * CHUNK_BYTES, &tmA, full_addr, m0 + c * 64, kb * BK);
-            }
-            if (!B_MN) {
-              tma_load_2d_pair(b_dst, &tmB, full_addr, kb * BK, n0);
-            } else {
-#pragma unroll
-              for (int c = 0; c < B_ROWS / 64; ++c) tma_load_2d_pair(b_dst + c * CHUNK_BYTES, &tmB, full_addr, n0 + c * 64, kb * BK);
-            }
+            if (half == 0) mbar_expect_tx(&full[stage], 2 * (A_BYTES + B_BYTES));  // both CTAs' bytes land on the even CTA's barrier
           } else {
             mbar_expect_tx(&full[stage], A_BYTES + B_BYTES);
-            if (!A_MN) {
-              tma_load_2d(a_dst, &tmA, &full[stage], kb * BK, m0);
-            } else {
+          }
+          if (!A_MN) {
+            load(a_dst, &tmA, kb * BK, m0);
+          } else {
 #pragma unroll
-              for (int c = 0; c < BM / 64; ++c) tma_load_2d(a_dst + c * CHUNK_BYTES, &tmA, &full[stage], m0 + c * 64, kb * BK);
-            }
-            if (!B_MN) {
-              tma_load_2d(b_dst, &tmB, &full[stage], kb * BK, n0);
-            } else {
+            for (int c = 0; c < BM / 64; ++c) load(a_dst + c * CHUNK_BYTES, &tmA, m0 + c * 64, kb * BK);
+          }
+          if (!B_MN) {
+            load(b_dst, &tmB, kb * BK, n0);
+          } else {
 #pragma unroll
-              for (int c = 0; c < B_ROWS / 64; ++c) tma_load_2d(b_dst + c * CHUNK_BYTES, &tmB, &full[stage], n0 + c * 64, kb * BK);
-            }
+            for (int c = 0; c < B_ROWS / 64; ++c) load(b_dst + c * CHUNK_BYTES, &tmB, n0 + c * 64, kb * BK);
           }
           if (++stage == ST) {
             stage = 0;
@@ -598,7 +601,7 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
           __syncwarp();
           continue;
         }
-        store_row_chunk(p, row, col, r);
+        store_row_chunk(p, row, col, r, GROUPED ? (long long)(t / tiles_per_group) * p.M * p.ldc : 0);
       }
       tc_fence_before();
       if (PAIR) mbar_arrive_cluster(map_to_cta(&tmem_empty[buf], 0));
@@ -649,6 +652,21 @@ inline int make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t ou
   cuuint32_t box[2] = {64, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 2;
+}
+
+// 3-D bf16 tensor map [groups][outer][inner] (dense: group stride = outer * ld), box 64 x box_outer x 1.
+inline int make_map_3d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t groups, uint64_t ld_elems,
+                       uint32_t box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return 1;
+  cuuint64_t dims[3] = {inner, outer, groups};
+  cuuint64_t strides[2] = {ld_elems * 2, ld_elems * outer * 2};
+  cuuint32_t box[3] = {64, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 2;

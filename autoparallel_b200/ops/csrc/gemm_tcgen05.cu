@@ -33,6 +33,23 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   gemm_cta<A_MN, B_MN, FUSE_NONE, true>(tmA, tmB, p, f, blockIdx.x, gridDim.x, smem_raw);
 }
 
+// Grouped GEMM: G problems of one shape (the expert projections of a capacity-based MoE layer).
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  FuseParams f{};
+  gemm_cta<A_MN, B_MN, FUSE_NONE, false, true>(tmA, tmB, p, f, blockIdx.x, gridDim.x, smem_raw);
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_grouped_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  FuseParams f{};
+  gemm_cta<A_MN, B_MN, FUSE_NONE, true, true>(tmA, tmB, p, f, blockIdx.x, gridDim.x, smem_raw);
+}
+
 static int g_pair_mode = 1;  // 0: one CTA per tile, 1: CTA pairs where the shape allows (default)
 
 }  // namespace apb
@@ -117,5 +134,52 @@ extern "C" int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   else if (!a_mn_major && b_mn_major) launch(gemm_bf16_kernel<false, true>);
   else if (a_mn_major && !b_mn_major) launch(gemm_bf16_kernel<true, false>);
   else launch(gemm_bf16_kernel<true, true>);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// C[g] = opA[g] * opB[g] for g < G; every operand is a dense stack [G, rows, cols] of bf16 matrices
+// (K-major [rows=M or N, cols=K], or MN-major [rows=K, cols=M or N]); C is [G, M, N] bf16 or fp32.
+extern "C" int apb_gemm_grouped_bf16(const void* A, const void* B, void* C, int G, int M, int N, int K, int a_mn_major,
+                                     int b_mn_major, int out_fp32, uint32_t* status, int num_sms, cudaStream_t stream) {
+  if (G <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
+  const int a_inner = a_mn_major ? M : K, b_inner = b_mn_major ? N : K;
+  if ((a_inner & 7) || (b_inner & 7) || (N & 7)) return 3;  // 16-byte rows for TMA and for the vector stores
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15)) return 3;
+  const bool pair = g_pair_mode && M >= 2 * BM && N >= BN;
+  CUtensorMap tmA, tmB;
+  int e = !a_mn_major ? make_map_3d(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)G, (uint64_t)K, BM)
+                      : make_map_3d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)G, (uint64_t)M, BK);
+  if (e) return e;
+  e = !b_mn_major ? make_map_3d(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)G, (uint64_t)K, pair ? BN / 2 : BN)
+                  : make_map_3d(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)G, (uint64_t)N, BK);
+  if (e) return e;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = N; p.out_fp32 = out_fp32;
+  p.num_m_tiles = (M + BM - 1) / BM;
+  p.num_n_tiles = (N + BN - 1) / BN;
+  p.status = status;
+  p.groups = G;
+  auto launch = [&](auto kern, int grid) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+    kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p);
+  };
+  if (pair) {
+    const long long tiles2 = (long long)G * ((M + 2 * BM - 1) / (2 * BM)) * p.num_n_tiles;
+    int resident = apb_gemm_resident_pairs(num_sms) - g_reserved_sms / 2;
+    if (resident < 1) resident = 1;
+    const int grid = 2 * (int)(tiles2 < resident ? tiles2 : resident);
+    if (!a_mn_major && !b_mn_major) launch(gemm_grouped_pair_kernel<false, false>, grid);
+    else if (!a_mn_major && b_mn_major) launch(gemm_grouped_pair_kernel<false, true>, grid);
+    else if (a_mn_major && !b_mn_major) launch(gemm_grouped_pair_kernel<true, false>, grid);
+    else launch(gemm_grouped_pair_kernel<true, true>, grid);
+  } else {
+    const long long tiles = (long long)G * p.num_m_tiles * p.num_n_tiles;
+    const int usable = num_sms - g_reserved_sms > 0 ? num_sms - g_reserved_sms : 1;
+    const int grid = (int)(tiles < usable ? tiles : usable);
+    if (!a_mn_major && !b_mn_major) launch(gemm_grouped_kernel<false, false>, grid);
+    else if (!a_mn_major && b_mn_major) launch(gemm_grouped_kernel<false, true>, grid);
+    else if (a_mn_major && !b_mn_major) launch(gemm_grouped_kernel<true, false>, grid);
+    else launch(gemm_grouped_kernel<true, true>, grid);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }

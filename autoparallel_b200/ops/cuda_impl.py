@@ -134,6 +134,35 @@ def _mm_wgrad(a, b, out_dtype):
     return gemm_raw(_as2d(a), _as2d(b), True, True, out_dtype)
 
 
+def _grouped_ok(*ts):
+    return all(t.dtype == torch.bfloat16 and t.shape[-1] % 8 == 0 for t in ts)
+
+
+def _grouped_mm(a, b, trans_b, out_dtype):
+    """[E,M,K] x ([E,N,K] if trans_b else [E,K,N]) -> [E,M,N]: every expert in one launch of the grouped tcgen05 GEMM."""
+    n = b.shape[1] if trans_b else b.shape[2]
+    if not _grouped_ok(a, b) or n % 8 or out_dtype not in (torch.bfloat16, torch.float32):
+        from .moe_ops import _grouped_mm as ref
+
+        return ref(a, b, trans_b, out_dtype)
+    c = torch.empty((a.shape[0], a.shape[1], n), dtype=out_dtype, device=a.device)
+    _C.gemm_grouped(a.contiguous(), b.contiguous(), c, False, not trans_b, status_buffer(a.device))
+    _count()
+    return c
+
+
+def _grouped_mm_wgrad(a, b, out_dtype):
+    """sum over rows of a[E,M,Ka]^T b[E,M,Nb] -> [E,Ka,Nb] (both operands read as stored)."""
+    if not _grouped_ok(a, b) or out_dtype not in (torch.bfloat16, torch.float32):
+        from .moe_ops import _grouped_mm_wgrad as ref
+
+        return ref(a, b, out_dtype)
+    c = torch.empty((a.shape[0], a.shape[2], b.shape[2]), dtype=out_dtype, device=a.device)
+    _C.gemm_grouped(a.contiguous(), b.contiguous(), c, True, True, status_buffer(a.device))
+    _count()
+    return c
+
+
 # ----------------------------------------------------------------------------------- pointwise etc.
 def _dtype_cast(x, dtype):
     if x.dtype == dtype:
@@ -277,6 +306,8 @@ def _register() -> None:
     R("gemm", _gemm)
     R("mm_nd", _mm_nd)
     R("mm_wgrad", _mm_wgrad)
+    R("grouped_mm", _grouped_mm)
+    R("grouped_mm_wgrad", _grouped_mm_wgrad)
     R("dtype_cast", _dtype_cast)
     R("rms_norm", _rms_norm)
     R("rms_norm_bwd", _rms_norm_bwd)

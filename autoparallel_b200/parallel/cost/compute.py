@@ -66,6 +66,12 @@ def _flops(op, args, in_shapes: list[list[int]], out_shapes: list[list[int]]) ->
     if op is apb.mm_wgrad.default:
         a, b = in_shapes[0], in_shapes[1]
         return 2.0 * _numel(a) * b[-1]
+    if op is apb.grouped_mm.default:
+        a, b = in_shapes[0], in_shapes[1]
+        return 2.0 * _numel(a) * (b[1] if args[2] else b[2])
+    if op is apb.grouped_mm_wgrad.default:
+        a, b = in_shapes[0], in_shapes[1]
+        return 2.0 * _numel(a) * b[2]
     if op is apb.gemm.default or op is aten.mm.default:
         a = in_shapes[0]
         return 2.0 * _numel(a) * out_shapes[0][-1] if op is aten.mm.default else 2.0 * _numel(a) * out_shapes[0][-1]

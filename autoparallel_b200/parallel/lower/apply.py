@@ -50,6 +50,24 @@ _SIZE_ARG = {
 }
 
 
+def _localize_moe_slots(args, val, lval):
+    # block count follows the token shard: every rank keeps whole blocks
+    args[3] = args[3] * lval.shape[0] // val.shape[0]
+    return args
+
+
+def _localize_moe_scatter(args, val, lval):
+    args[5] = lval.shape[1]
+    return args
+
+
+# op -> rewrite of integer arguments that describe a global extent (args list, global value, local value)
+_INT_ARG_LOCALIZERS = {
+    torch.ops.apb200.moe_slots.default: _localize_moe_slots,
+    torch.ops.apb200.moe_scatter.default: _localize_moe_scatter,
+}
+
+
 @dataclasses.dataclass
 class LoweredGraph:
     gm: fx.GraphModule
@@ -222,6 +240,8 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
                 else:
                     new_args[pos] = list(lval.shape)
                 new_args = tuple(new_args)
+            if node.target in _INT_ARG_LOCALIZERS and isinstance(lval, torch.Tensor):
+                new_args = tuple(_INT_ARG_LOCALIZERS[node.target](list(new_args), val, lval))
             from ..strategies.local_map_rules import is_local_map_node, local_map_body
 
             if is_local_map_node(node):

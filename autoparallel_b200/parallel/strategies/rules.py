@@ -195,6 +195,48 @@ def _gemm(ctx):
     return expand_rows(ctx, [(S(0), S(am), R), (S(1), R, S(bn)), (P, S(ak), S(bk))])
 
 
+# ---- planner-visible mixture-of-experts ops (ops/moe_ops.py).  Tokens [T, ..] and the block dim of the
+# buffer [E, nb, C, d] shard together (every rank keeps whole token blocks); the feature dim d can be
+# split through scatter / gather with replicated routing.  The expert dim is never sharded INSIDE
+# these ops: expert parallelism is the redistribution Shard(1) -> Shard(0) of the buffer (one
+# all-to-all) between the scatter and the grouped GEMMs, which the solver prices like any other edge.
+@register_rule(apb.moe_slots.default)
+def _moe_slots(ctx):
+    return expand_rows(ctx, [(S(0), S(0))])
+
+
+@register_rule(apb.moe_scatter.default)
+def _moe_scatter(ctx):
+    # (buf, src, slot, w)
+    return expand_rows(ctx, [(S(1), S(0), S(0), S(0)), (S(3), S(1), R, R), (P, P, R, R)])
+
+
+@register_rule(apb.moe_gather.default)
+def _moe_gather(ctx):
+    # (out, buf, slot, w)
+    return expand_rows(ctx, [(S(0), S(1), S(0), S(0)), (S(1), S(3), R, R), (P, P, R, R)])
+
+
+@register_rule(apb.moe_gate_grad.default)
+def _moe_gate_grad(ctx):
+    # (dw, buf, slot, g): a feature-dim split leaves partial dot products
+    return expand_rows(ctx, [(S(0), S(1), S(0), S(0)), (P, S(3), R, S(1))])
+
+
+@register_rule(apb.grouped_mm.default)
+def _grouped_mm(ctx):
+    trans_b = ctx.args[2]
+    kdim, ndim = (2, 1) if trans_b else (1, 2)
+    # (out [E,M,N], a [E,M,K], b): experts, rows, columns, contraction
+    return expand_rows(ctx, [(S(0), S(0), S(0)), (S(1), S(1), R), (S(2), R, S(ndim)), (P, S(2), S(kdim))])
+
+
+@register_rule(apb.grouped_mm_wgrad.default)
+def _grouped_mm_wgrad(ctx):
+    # (out [E,Ka,Nb], a [E,M,Ka], b [E,M,Nb])
+    return expand_rows(ctx, [(S(0), S(0), S(0)), (P, S(1), S(1)), (S(1), S(2), R), (S(2), R, S(2))])
+
+
 @register_rule(apb.embedding_bwd.default)
 def _embedding_bwd(ctx):
     dy, ids = ctx.in_vals

@@ -78,6 +78,32 @@ def test_gemm_cta_pairs(K, M, N, K_, ta, tb):
     _close(c, A @ B, rtol=1e-3, atol=1e-3 * (K_ ** 0.5))
 
 
+@pytest.mark.parametrize("E,M,N,K_", [(4, 256, 256, 128), (8, 384, 704, 192), (3, 100, 136, 72), (16, 512, 1408, 2048)])
+@pytest.mark.parametrize("pair", [True, False])
+def test_grouped_gemm(K, E, M, N, K_, pair):
+    """Expert GEMMs of a capacity-based MoE layer: forward (B as stored [E,K,N]), dgrad (B^T) and wgrad."""
+    lib, impl = K
+    ext = impl.extension()
+    torch.manual_seed(3)
+    a = torch.randn(E, M, K_, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(E, K_, N, device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn(E, M, N, device="cuda", dtype=torch.bfloat16)
+    prev = ext.gemm_get_pair_mode()
+    ext.gemm_set_pair_mode(pair)
+    try:
+        y = lib.ops.grouped_mm(a, w, False, torch.float32)
+        da = lib.ops.grouped_mm(dy, w, True, torch.float32)
+        dw = lib.ops.grouped_mm_wgrad(a, dy, torch.float32)
+        torch.cuda.synchronize()
+        impl.check_status()
+    finally:
+        ext.gemm_set_pair_mode(prev)
+    A, W, DY = a.float().cpu(), w.float().cpu(), dy.float().cpu()
+    _close(y, torch.bmm(A, W), 1e-3, 1e-3 * K_ ** 0.5)
+    _close(da, torch.bmm(DY, W.transpose(1, 2)), 1e-3, 1e-3 * N ** 0.5)
+    _close(dw, torch.bmm(A.transpose(1, 2), DY), 1e-3, 1e-3 * M ** 0.5)
+
+
 def test_mm_nd_and_wgrad(K):
     lib, impl = K
     torch.manual_seed(1)
