@@ -83,6 +83,7 @@ class AutoParallel:
         plan_device: Optional[str] = None,
         fuse_collectives: Any = None,
         bucket_collectives: bool = False,
+        ordered_sharding: bool = True,
     ):
         if dynamic:
             raise NotImplementedError(
@@ -100,6 +101,7 @@ class AutoParallel:
         self.plan_device = plan_device
         self.fuse_collectives = fuse_collectives
         self.bucket_collectives = bucket_collectives
+        self.ordered_sharding = ordered_sharding
         self.bucket_stats = {}
         self.fusion_stats = {}
         model = clone_model_for_tracing(model)
@@ -215,7 +217,7 @@ class AutoParallel:
         self._assert_entered()
         sol = sharding_placement if sharding_placement is not None else self.sharding_placement
         t0 = time.perf_counter()
-        lowered = lower_to_local_graph(self.joint, sol, self.mesh)
+        lowered = lower_to_local_graph(self.joint, sol, self.mesh, ordered_sharding=self.ordered_sharding)
         from .parallel.passes.peephole import fuse_cast_into_gemm
 
         from .parallel.frontend.trace import index_joint_graph

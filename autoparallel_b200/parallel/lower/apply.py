@@ -72,7 +72,8 @@ _INT_ARG_LOCALIZERS = {
 class LoweredGraph:
     gm: fx.GraphModule
     joint: JointGraph  # re-indexed over ``gm``
-    #: placements of parameters / buffers / inputs / outputs in the solution
+    #: placements of parameters / buffers / inputs / outputs in the solution (a parameter whose shards
+    #: were re-nested by the ordered-sharding pass carries a ``_StridedShard``)
     param_placements: dict[str, tuple]
     buffer_placements: dict[str, tuple]
     input_placements: list[Optional[tuple]]
@@ -90,15 +91,28 @@ def _spec_for_input(producer_spec: OpSpec, consumer: fx.Node) -> Optional[DTenso
 
 
 class _Redistributor:
-    def __init__(self, graph: fx.Graph, mesh):
+    def __init__(self, graph: fx.Graph, mesh, fuse_flat: bool = True):
         self.g = graph
         self.mesh = mesh
+        self.fuse_flat = fuse_flat
         self.groups = []
         for i in range(mesh.ndim):
             pg = mesh.get_group(i)
             self.groups.append((pg.group_name, mesh.shape[i]))
+        self.flat_group = None  # (name, size) of the flattened mesh, created on first use
         self.cache: dict[tuple, fx.Node] = {}
         self.counts = {"all_gather": 0, "reduce_scatter": 0, "all_reduce": 0, "all_to_all": 0, "local_chunk": 0}
+
+    def _flat(self):
+        """Process group over every rank of the mesh in row-major order (None if it cannot be made)."""
+        if self.flat_group is None and self.mesh.ndim > 1:
+            try:
+                flat = self.mesh._flatten()
+                self.flat_group = (flat.get_group().group_name, flat.size())
+            except Exception as e:  # unnamed mesh dims, or a backend that cannot split: keep per-dim collectives
+                logger.info("flattened mesh unavailable (%s); nested shards use one collective per mesh dim", e)
+                self.flat_group = False
+        return self.flat_group or None
 
     def _emit(self, kind: str, args: tuple, like: fx.Node, shape) -> fx.Node:
         n = self.g.call_function(getattr(comm, kind).default, args)
@@ -110,20 +124,24 @@ class _Redistributor:
         self.counts[kind] += 1
         return n
 
-    def __call__(self, x: fx.Node, key_node: fx.Node, src: DTensorSpec, dst: DTensorSpec) -> fx.Node:
-        """Emit (or reuse) the collectives taking local tensor ``x`` from ``src`` to ``dst``."""
+    def __call__(self, x: fx.Node, key_node: fx.Node, src: DTensorSpec, dst: DTensorSpec, order=None) -> fx.Node:
+        """Emit (or reuse) the collectives taking local tensor ``x`` from ``src`` to ``dst``; ``order`` is
+        the nesting order of mesh dims for a tensor dim sharded over several of them."""
         if src.placements == dst.placements:
             return x
-        key = (key_node, tuple(dst.placements))
+        key = (key_node, tuple(dst.placements), order)
         hit = self.cache.get(key)
         if hit is not None:
             return hit
-        from .redistribute import plan_redistribution
+        from .redistribute import FLAT, fuse_over_flat_mesh, plan_redistribution
 
         cur = x
         shape = list(x.meta["val"].shape)
-        for st in plan_redistribution(src.placements, dst.placements, self.mesh.shape):
-            gname, n = self.groups[st.mesh_dim]
+        steps = plan_redistribution(src.placements, dst.placements, self.mesh.shape, order=order)
+        if self.fuse_flat and self._flat() is not None:
+            steps = fuse_over_flat_mesh(steps, self.mesh.ndim, order)
+        for st in steps:
+            gname, n = self.flat_group if st.mesh_dim == FLAT else self.groups[st.mesh_dim]
             if st.kind == "all_gather":
                 shape[st.dim] *= n
                 cur = self._emit("all_gather", (cur, st.dim, gname, n), x, shape)
@@ -173,13 +191,16 @@ def _local_val(val, spec: Optional[DTensorSpec], mesh):
     return val.new_empty(ls)
 
 
-def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mesh) -> LoweredGraph:
+def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mesh, ordered_sharding: bool = True) -> LoweredGraph:
     from ..frontend.trace import index_joint_graph
 
     old_g = joint.gm.graph
     new_g = fx.Graph()
     env: dict[fx.Node, fx.Node] = {}
-    redis = _Redistributor(new_g, mesh)
+    redis = _Redistributor(new_g, mesh, fuse_flat=ordered_sharding)
+    from .ordered import compute_shard_orders, dtensor_placements
+
+    orders = compute_shard_orders(joint, solution, mesh) if ordered_sharding else {}
 
     for node in old_g.nodes:
         if node.op == "placeholder":
@@ -220,7 +241,8 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
                 dst = spec.input_specs[s] if spec.input_specs else None
                 if src is None or dst is None:
                     return env[a]
-                return redis(env[a], a, src, dst)
+                # a re-nested layout applies to edges leaving the parameter chain and to the edge into its gradient
+                return redis(env[a], a, src, dst, orders.get(a) or orders.get(node))
 
             new_args, new_kwargs = fx.node.map_arg((node.args, node.kwargs), conv)
             out_spec = spec.output_specs
@@ -276,7 +298,8 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
     return LoweredGraph(
         gm=new_gm,
         joint=new_joint,
-        param_placements={k: pl(v) for k, v in joint.param_nodes.items()},
+        param_placements={k: (dtensor_placements(pl(v), orders.get(v), tuple(mesh.shape)) if pl(v) is not None else None)
+                          for k, v in joint.param_nodes.items()},
         buffer_placements={k: pl(v) for k, v in joint.buffer_nodes.items()},
         input_placements=[pl(n) for n in joint.input_nodes],
         output_placements=[pl(n) for n in joint.fwd_outputs],

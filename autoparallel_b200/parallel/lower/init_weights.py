@@ -32,6 +32,18 @@ logger = logging.getLogger(__name__)
 _BIG = 1 << 28  # elements; materialising more than this per tensor earns a warning
 
 
+def _distribute(full: torch.Tensor, mesh, placements) -> DTensor:
+    """``distribute_tensor`` that also understands a re-nested shard order (``_StridedShard``)."""
+    from .ordered import local_shard, order_of_dtensor_placements
+
+    order = order_of_dtensor_placements(placements, mesh.ndim)
+    if order is None:
+        return distribute_tensor(full, mesh, placements, src_data_rank=None)
+    coord = mesh.get_coordinate()
+    local = local_shard(full, placements, coord, tuple(mesh.shape), order)
+    return DTensor.from_local(local, mesh, placements, run_check=False, shape=full.shape, stride=full.contiguous().stride())
+
+
 def _shard_like(full: torch.Tensor, like: DTensor) -> DTensor:
     if full.numel() >= _BIG and any(p.is_shard() for p in like.placements):
         warnings.warn(
@@ -40,7 +52,7 @@ def _shard_like(full: torch.Tensor, like: DTensor) -> DTensor:
             stacklevel=3,
         )
     full = full.detach().to(device=like.device, dtype=like.dtype)
-    return distribute_tensor(full, like.device_mesh, like.placements, src_data_rank=None)
+    return _distribute(full, like.device_mesh, like.placements)
 
 
 class _CopyFromPlain(TorchDispatchMode):
@@ -121,7 +133,7 @@ def _run_materialized(module: nn.Module, user_init, args, kwargs):
                     src = cur.detach().to(dt.dtype)
                     if tuple(src.shape) != tuple(dt.shape):
                         raise RuntimeError(f"init_weights changed the shape of {name}: {tuple(src.shape)} vs {tuple(dt.shape)}")
-                    shard = distribute_tensor(src, dt.device_mesh, dt.placements, src_data_rank=None)
+                    shard = _distribute(src, dt.device_mesh, dt.placements)
                     dt._local_tensor.copy_(shard._local_tensor)
             store[name] = dt
     return out

@@ -32,7 +32,15 @@ class RedistributeError(RuntimeError):
     pass
 
 
-def plan_redistribution(src: Sequence[Placement], dst: Sequence[Placement], mesh_shape: Sequence[int]) -> list[Step]:
+def plan_redistribution(src: Sequence[Placement], dst: Sequence[Placement], mesh_shape: Sequence[int],
+                        order: Optional[Sequence[int]] = None) -> list[Step]:
+    """``order``: mesh dims from the outermost shard to the innermost for tensor dims sharded over
+    several mesh dims (default: mesh-dim order).  A different order is planned on the permuted mesh
+    and the steps are mapped back, so every rule below applies unchanged."""
+    if order is not None and tuple(order) != tuple(range(len(mesh_shape))):
+        perm = list(order)
+        steps = plan_redistribution([src[i] for i in perm], [dst[i] for i in perm], [mesh_shape[i] for i in perm])
+        return [s._replace(mesh_dim=perm[s.mesh_dim]) for s in steps]
     nd = len(mesh_shape)
     cur = list(src)
     steps: list[Step] = []
@@ -92,4 +100,28 @@ def plan_redistribution(src: Sequence[Placement], dst: Sequence[Placement], mesh
         else:
             raise RedistributeError(f"cannot redistribute {p} -> {q} on mesh dim {i}")
         cur[i] = q
+    return steps
+
+
+FLAT = -1  # Step.mesh_dim of a collective that runs on the flattened mesh (all mesh dims at once)
+
+
+def fuse_over_flat_mesh(steps: list[Step], nd: int, order: Optional[Sequence[int]] = None) -> list[Step]:
+    """``(S(d), .., S(d)) -> (R, .., R)`` planned as one all-gather per mesh dim, or ``(P, .., P) ->
+    (S(d), .., S(d))`` planned as one reduce-scatter per mesh dim, is the same data movement as ONE
+    collective over the flattened mesh, because ranks of the flattened mesh are numbered in the
+    default nesting order of the shards.  Only whole-mesh runs with the default order are fused.
+    Reference: autoparallel/shardings/ordered_sharding.py:33-67."""
+    if nd < 2 or len(steps) != nd or (order is not None and tuple(order) != tuple(range(nd))):
+        return steps
+    kinds = {s.kind for s in steps}
+    dims = {s.dim for s in steps}
+    if len(kinds) != 1 or len(dims) != 1:
+        return steps
+    kind = next(iter(kinds))
+    mesh_dims = [s.mesh_dim for s in steps]
+    if kind == "all_gather" and mesh_dims == list(range(nd - 1, -1, -1)):
+        return [Step("all_gather", FLAT, steps[0].dim)]
+    if kind == "reduce_scatter" and mesh_dims == list(range(nd)):
+        return [Step("reduce_scatter", FLAT, steps[0].dim)]
     return steps

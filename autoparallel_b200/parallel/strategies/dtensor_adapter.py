@@ -38,7 +38,7 @@ def local_shape(shape: Sequence[int], mesh_shape: Sequence[int], placements: Seq
     """Per-rank shape (ceil-div) or None when a shard would be smaller than the mesh dim."""
     out = list(shape)
     for n, p in zip(mesh_shape, placements):
-        if isinstance(p, Shard):
+        if isinstance(p, Shard) or type(p).__name__ == "_StridedShard":  # a re-nested shard halves the dim like any shard
             d = p.dim
             if d >= len(out) or out[d] < n:
                 return None

@@ -193,6 +193,75 @@ def test_moe_planner_visible_ops_match_one_rank():
     assert abs(g2 - g1) / g1 < 1e-3
 
 
+def _ordered_worker(rank, ws, ordered, port, q):
+    """2 x 2 mesh, MLP pinned to FSDP over "dp" + tensor parallelism over "tp": the column-parallel weight is
+    (Shard(0), Shard(0)) and is used as (Replicate(), Shard(0))."""
+    _init(rank, ws, port)
+    import torch.nn as nn
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Partial, Replicate, Shard, _StridedShard
+
+    from autoparallel_b200 import AutoParallel
+
+    apb = torch.ops.apb200
+
+    class MLP(nn.Module):
+        def __init__(self, d=64, h=128):
+            super().__init__()
+            self.w1 = nn.Linear(d, h, bias=False)
+            self.w2 = nn.Linear(h, d, bias=False)
+
+        def forward(self, x):
+            return self.w2(torch.relu(self.w1(x))).square().mean()
+
+    mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("dp", "tp"))
+    torch.manual_seed(0)
+    ref = MLP()
+    with torch.device("meta"):
+        m = MLP()
+    with AutoParallel(m, lambda: torch.randn(8, 16, 64), mesh, ordered_sharding=ordered) as ap:
+        ap.add_input_constraints([(Shard(0), Replicate())])
+        first_mm = next(n for n in ap.gm.graph.nodes if n.op == "call_function" and n.target is apb.mm_nd.default)
+        ap.sharding_optimizer.add_node_constraint(first_mm, (Shard(0), Shard(2)))
+        for k, p in ap.joint.param_nodes.items():
+            ap.sharding_optimizer.add_node_constraint(p, (Shard(0), Shard(0)) if "w1" in k else (Shard(1), Shard(1)))
+        # weight gradients leave the GEMM summed over "dp" only later: (Partial, Shard) -> reduce-scatter over "dp"
+        for k, gnode in ap.joint.param_grads.items():
+            wg = gnode.all_input_nodes[0]
+            assert wg.target is apb.mm_wgrad.default
+            ap.sharding_optimizer.add_node_constraint(wg, (Partial(), Shard(0)) if "w1" in k else (Partial(), Shard(1)))
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+        n_coll = sum(v for k, v in ap.lowered.num_collectives.items() if k != "local_chunk")
+        strided = any(isinstance(p, _StridedShard) for pl in ap.lowered.param_placements.values() for p in pl)
+    pm.to_empty(device="cpu")
+    with torch.no_grad():
+        for (n, p), (_, p_ref) in zip(pm.named_parameters(), ref.named_parameters()):
+            from autoparallel_b200.parallel.lower.init_weights import _distribute
+
+            p._local_tensor.copy_(_distribute(p_ref.detach(), mesh, p.placements)._local_tensor)
+            assert torch.equal(p.full_tensor(), p_ref), n  # the re-nested layout reassembles to the same tensor
+    torch.manual_seed(1)
+    x = torch.randn(8, 16, 64)
+    loss = pm(x.chunk(2, 0)[mesh.get_local_rank(0)])
+    loss.backward()
+    rl = ref(x)
+    rl.backward()
+    worst = max(((p.grad.full_tensor() - p_ref.grad).abs().max() / p_ref.grad.abs().max()).item()
+                for (_, p), (_, p_ref) in zip(pm.named_parameters(), ref.named_parameters()))
+    if rank == 0:
+        q.put((abs(loss.item() - rl.item()), worst, n_coll, strided))
+    dist.destroy_process_group()
+
+
+def test_ordered_sharding_renests_fsdp_tp_weights():
+    dl, dg, n_ordered, strided = _run(_ordered_worker, 4, True)
+    assert strided and dl < 1e-5 and dg < 1e-4
+    dl0, dg0, n_default, strided0 = _run(_ordered_worker, 4, False)
+    assert not strided0 and dl0 < 1e-5 and dg0 < 1e-4
+    assert n_ordered < n_default  # the dp-gather of the column-parallel weight is one collective, not two and a re-slice
+
+
 def _dcp_worker(rank, ws, tmp, port, q):
     _init(rank, ws, port)
     import torch.distributed.checkpoint as dcp
