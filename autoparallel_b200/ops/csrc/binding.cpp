@@ -13,6 +13,10 @@ int apb_gemm_grouped_bf16(const void* A, const void* B, void* C, int G, int M, i
                           int out_fp32, uint32_t* status, int num_sms, cudaStream_t stream);
 void apb_gemm_set_pair_mode(int on);
 int apb_gemm_get_pair_mode();
+void apb_gemm_set_dynamic_tiles(int on);
+int apb_gemm_get_dynamic_tiles();
+void apb_gemm_set_pair_stages(int n);
+int apb_gemm_get_pair_stages();
 void apb_gemm_set_reserved_sms(int n);
 int apb_gemm_get_reserved_sms();
 int apb_gemm_fused_ctas(int fuse, int M, int N, int comm_ctas, int num_sms);
@@ -216,6 +220,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_grouped", &gemm_grouped);
   m.def("gemm_set_pair_mode", [](bool on) { apb_gemm_set_pair_mode(on ? 1 : 0); });
+  m.def("gemm_set_dynamic_tiles", [](bool on) { apb_gemm_set_dynamic_tiles(on ? 1 : 0); });
+  m.def("gemm_get_dynamic_tiles", []() { return apb_gemm_get_dynamic_tiles() != 0; });
+  m.def("gemm_set_pair_stages", [](int64_t n) { apb_gemm_set_pair_stages((int)n); });
+  m.def("gemm_get_pair_stages", []() { return (int64_t)apb_gemm_get_pair_stages(); });
   m.def("gemm_set_reserved_sms", [](int64_t n) { apb_gemm_set_reserved_sms((int)n); });
   m.def("gemm_get_reserved_sms", []() { return (int64_t)apb_gemm_get_reserved_sms(); });
   m.def("gemm_get_pair_mode", []() { return apb_gemm_get_pair_mode() != 0; });

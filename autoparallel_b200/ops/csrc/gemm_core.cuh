@@ -52,6 +52,7 @@ struct GemmParams {
   int num_m_tiles, num_n_tiles;
   uint32_t* status;
   int groups = 1;  // grouped GEMM: G independent problems of the same M, N, K, stacked along a third tensor-map dim
+  int* tile_counter = nullptr;  // dynamic tile scheduling (DYN): {next tile, pairs that have drained}, both zero between launches
 };
 
 struct FuseParams {
@@ -258,15 +259,25 @@ __device__ __forceinline__ void gather_comm_warp(const GemmParams& p, const Fuse
 // cta / num_ctas: index of this CTA among the GEMM CTAs of the launch (fused kernels also run
 // communication CTAs that are not counted here).  With PAIR, CTAs 2i and 2i+1 form cluster i.
 // GROUPED: p.groups problems; operands are 3-D tensor maps [group][rows][inner] (FUSE_NONE only).
-template <bool A_MN, bool B_MN, int FUSE, bool PAIR = false, bool GROUPED = false>
+// ST_ARG: number of TMA stages (0 = as many as fit: 6 for pairs, 4 for single CTAs); fewer stages leave
+// shared memory for a communication kernel's CTA to share the SM.
+//
+// DYN (CTA pairs, FUSE_NONE): tiles are handed out at run time.  The even CTA's producer thread takes the
+// next tile index from a global counter and publishes it through a four-entry ring in BOTH CTAs'
+// shared memory (remote store + remote mbarrier arrive); the odd CTA's producer, the MMA thread and
+// the eight epilogue warps of the pair read it there and release the entry on the even CTA's
+// barrier.  A pair that starts late or shares its SMs with another kernel (a communication kernel on
+// another stream) simply takes fewer tiles, so nothing waits for the slowest pair's fixed share.
+constexpr int TILE_RING = 4;
+template <bool A_MN, bool B_MN, int FUSE, bool PAIR = false, bool GROUPED = false, int ST_ARG = 0, bool DYN = false>
 __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                          const FuseParams& f, int cta, int num_ctas, uint8_t* smem_raw) {
-  constexpr int ST = PAIR ? PAIR_STAGES : STAGES;
+  constexpr int ST = ST_ARG > 0 ? ST_ARG : (PAIR ? PAIR_STAGES : STAGES);
   constexpr int A_BYTES = A_STAGE_BYTES;                          // 128 rows of A per CTA
   constexpr int B_BYTES = PAIR ? B_STAGE_BYTES / 2 : B_STAGE_BYTES;  // PAIR: this CTA's 128 of the 256 B rows
   constexpr int B_ROWS = PAIR ? BN / 2 : BN;
   constexpr int TM = PAIR ? 2 * BM : BM;                          // tile rows
-  static_assert(ST * (A_BYTES + B_BYTES) == STAGES * (A_STAGE_BYTES + B_STAGE_BYTES), "both layouts fill the same shared memory");
+  static_assert(ST * (A_BYTES + B_BYTES) <= STAGES * (A_STAGE_BYTES + B_STAGE_BYTES), "stages must fit the launch's shared memory");
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + ST * A_BYTES;
@@ -278,6 +289,11 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * ST + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   uint64_t* ring_bars = bars + 2 * ST + 6;   // [AG_NBUF], gather-fused kernels only
+  static_assert(!DYN || (PAIR && FUSE == FUSE_NONE), "dynamic tiles: CTA pairs, plain GEMM");
+  uint64_t* tile_ready = bars + 2 * ST + 10;  // [TILE_RING] DYN: entry published (1 arrival, in each CTA)
+  uint64_t* tile_free = tile_ready + TILE_RING;  // [TILE_RING] DYN: entry read by all 10 readers of the pair (even CTA's)
+  volatile int* tile_ring = reinterpret_cast<volatile int*>(tile_free + TILE_RING);  // [TILE_RING]
+  static_assert((2 * PAIR_STAGES + 10 + 2 * TILE_RING) * 8 + TILE_RING * 4 <= 256, "barrier block");
   constexpr bool GATHER = FUSE == FUSE_GATHER_A || FUSE == FUSE_GATHER_B;
   const uint32_t half = PAIR ? cluster_ctarank() : 0u;  // 0 = even CTA: issues the MMAs, owns the shared barriers
   const int unit = PAIR ? (cta >> 1) : cta;             // tiles are dealt to CTAs or to CTA pairs
@@ -317,6 +333,49 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
   if (FUSE == FUSE_GATHER_A && A_MN) k_rot = (f.rank * f.rows_per_shard) / BK;
   if (FUSE == FUSE_REDUCE_SCATTER) m_rot = (((f.rank + 1) % f.n) * f.rows_per_rank) / TM;  // own rows last
 
+  // Tile sequence of one role (each role keeps its own position ``it``).  Static: unit, unit + num_units, ...
+  // Dynamic: entry ``it`` of the ring; -1 ends the sequence (also after a timed-out wait).
+  auto read_tile = [&](int& it) -> int {
+    if (!DYN) {
+      const long long t = (long long)unit + (long long)it * num_units;
+      ++it;
+      return t < num_tiles ? (int)t : -1;
+    }
+    const int slot = it % TILE_RING;
+    if (!mbar_wait_cluster(&tile_ready[slot], (it / TILE_RING) & 1, abort_flag)) {
+      atomicCAS(p.status, 0u, (uint32_t)ST_TIMEOUT_FULL);
+      *abort_flag = 1;
+      return -1;
+    }
+    const int t = tile_ring[slot];
+    mbar_arrive_cluster(map_to_cta(&tile_free[slot], 0));
+    ++it;
+    return t;
+  };
+  // Even CTA's producer thread (DYN): take the next tile and publish it to both CTAs.
+  auto fetch_tile = [&](int& it) -> int {
+    const int slot = it % TILE_RING;
+    if (!mbar_wait_cluster(&tile_free[slot], ((it / TILE_RING) & 1) ^ 1, abort_flag)) {
+      atomicCAS(p.status, 0u, (uint32_t)ST_TIMEOUT_EMPTY);
+      *abort_flag = 1;
+      return -1;
+    }
+    int t = atomicAdd(p.tile_counter, 1);
+    if (t >= num_tiles) t = -1;
+    tile_ring[slot] = t;
+    st_cluster_u32(map_to_cta(const_cast<int*>(&tile_ring[slot]), 1), (uint32_t)t);
+    mbar_arrive_cluster(map_to_cta(&tile_ready[slot], 0));
+    mbar_arrive_cluster(map_to_cta(&tile_ready[slot], 1));
+    ++it;
+    if (t < 0 && atomicAdd(p.tile_counter + 1, 1) == num_units - 1) {
+      // every pair has drained: leave the counters at zero for the next launch
+      p.tile_counter[0] = 0;
+      p.tile_counter[1] = 0;
+      __threadfence();
+    }
+    return t;
+  };
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < ST; ++s) {
       mbar_init(&full[s], 1);
@@ -326,6 +385,11 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
       mbar_init(&tmem_full[b], 1);
       mbar_init(&tmem_empty[b], PAIR ? 256 : 128);
     }
+    if (DYN)
+      for (int b = 0; b < TILE_RING; ++b) {
+        mbar_init(&tile_ready[b], 1);
+        mbar_init(&tile_free[b], 10);  // odd CTA: producer + 4 epilogue warps; even CTA: MMA thread + 4 epilogue warps
+      }
     if (GATHER)
       for (int b = 0; b < AG_NBUF; ++b) mbar_init(&ring_bars[b], 1);
     *abort_flag = 0;
@@ -365,7 +429,9 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
         landed_mask |= 1u << s;
         return true;
       };
-      for (int t = unit; t < num_tiles && ok; t += num_units) {
+      int tile_it = 0;
+      for (int t = (DYN && half == 0) ? fetch_tile(tile_it) : read_tile(tile_it); t >= 0 && ok;
+           t = (DYN && half == 0) ? fetch_tile(tile_it) : read_tile(tile_it)) {
         int tm, tn;
         map_tile(t, tm, tn);
         // rows of A and of B that THIS CTA stages
@@ -445,7 +511,8 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
       int buf = 0;
       uint32_t buf_phase = 0;
       bool ok = true;
-      for (int t = unit; t < num_tiles && ok; t += num_units) {
+      int tile_it = 0;
+      for (int t = read_tile(tile_it); t >= 0 && ok; t = read_tile(tile_it)) {
         if (!mbar_wait(&tmem_empty[buf], buf_phase ^ 1, abort_flag)) {
           atomicCAS(p.status, 0u, (uint32_t)ST_TIMEOUT_TMEM_EMPTY);
           *abort_flag = 1;
@@ -508,7 +575,13 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int buf = 0;
     uint32_t buf_phase = 0;
-    for (int t = unit; t < num_tiles; t += num_units) {
+    int tile_it = 0;
+    auto next_epi_tile = [&]() -> int {  // lane 0 reads the sequence, the warp follows
+      int t = 0;
+      if (lane == 0) t = read_tile(tile_it);
+      return __shfl_sync(0xffffffffu, t, 0);
+    };
+    for (int t = next_epi_tile(); t >= 0; t = next_epi_tile()) {
       int tm, tn;
       map_tile(t, tm, tn);
       const long long cta_row0 = (long long)tm * TM + (long long)half * BM;  // first of this CTA's 128 rows

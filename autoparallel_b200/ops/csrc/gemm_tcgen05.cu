@@ -25,12 +25,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   gemm_cta<A_MN, B_MN, FUSE_NONE>(tmA, tmB, p, f, blockIdx.x, gridDim.x, smem_raw);
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int ST = 0, bool DYN = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   FuseParams f{};
-  gemm_cta<A_MN, B_MN, FUSE_NONE, true>(tmA, tmB, p, f, blockIdx.x, gridDim.x, smem_raw);
+  gemm_cta<A_MN, B_MN, FUSE_NONE, true, false, ST, DYN>(tmA, tmB, p, f, blockIdx.x, gridDim.x, smem_raw);
 }
 
 // Grouped GEMM: G problems of one shape (the expert projections of a capacity-based MoE layer).
@@ -84,6 +84,33 @@ using namespace apb;
 
 // SMs that the GEMM kernels leave idle so that communication kernels launched on other streams (NCCL)
 // find a free SM right away: a persistent GEMM CTA owns its SM's shared memory for the whole kernel.
+// TMA stages of the CTA-pair GEMM: 6 fill the SM's shared memory; 5 or 4 leave 32 / 64 KB more for a
+// communication kernel's CTA to become resident beside a GEMM CTA.
+static int g_pair_stages = 6;
+extern "C" void apb_gemm_set_pair_stages(int n) { g_pair_stages = n <= 4 ? 4 : (n == 5 ? 5 : 6); }
+extern "C" int apb_gemm_get_pair_stages() { return g_pair_stages; }
+// Dynamic tile scheduling of the CTA-pair GEMM (see gemm_core.cuh): off = every pair owns a fixed share.
+static int g_dynamic_tiles = 0;
+extern "C" void apb_gemm_set_dynamic_tiles(int on) { g_dynamic_tiles = on ? 1 : 0; }
+extern "C" int apb_gemm_get_dynamic_tiles() { return g_dynamic_tiles; }
+
+// {next tile, drained pairs} per device, zero between launches (the last pair of a launch resets them).
+static int* tile_counters() {
+  static int* per_device[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (per_device[dev] == nullptr) {
+    int* ptr = nullptr;
+    if (cudaMalloc(&ptr, 2 * sizeof(int)) != cudaSuccess || cudaMemset(ptr, 0, 2 * sizeof(int)) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    per_device[dev] = ptr;
+  }
+  return per_device[dev];
+}
+
 static int g_reserved_sms = 0;
 extern "C" void apb_gemm_set_reserved_sms(int n) { g_reserved_sms = n < 0 ? 0 : (n & ~1); }
 extern "C" int apb_gemm_get_reserved_sms() { return g_reserved_sms; }
@@ -113,14 +140,28 @@ extern "C" int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     int resident = apb_gemm_resident_pairs(num_sms) - g_reserved_sms / 2;
     if (resident < 1) resident = 1;
     const int pairs = tiles2 < resident ? tiles2 : resident;
+    const int smem2 = g_pair_stages * (A_STAGE_BYTES + B_STAGE_BYTES / 2) + 1024 + 256;
     auto launch2 = [&](auto kern) {
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
-      kern<<<2 * pairs, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p);
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
+      kern<<<2 * pairs, GEMM_THREADS, smem2, stream>>>(tmA, tmB, p);
     };
-    if (!a_mn_major && !b_mn_major) launch2(gemm_bf16_pair_kernel<false, false>);
-    else if (!a_mn_major && b_mn_major) launch2(gemm_bf16_pair_kernel<false, true>);
-    else if (a_mn_major && !b_mn_major) launch2(gemm_bf16_pair_kernel<true, false>);
-    else launch2(gemm_bf16_pair_kernel<true, true>);
+#define APB_LAUNCH_PAIR(ST)                                                              \
+  do {                                                                                   \
+    if (!a_mn_major && !b_mn_major) launch2(gemm_bf16_pair_kernel<false, false, ST>);    \
+    else if (!a_mn_major && b_mn_major) launch2(gemm_bf16_pair_kernel<false, true, ST>); \
+    else if (a_mn_major && !b_mn_major) launch2(gemm_bf16_pair_kernel<true, false, ST>); \
+    else launch2(gemm_bf16_pair_kernel<true, true, ST>);                                 \
+  } while (0)
+    int* counters = (g_dynamic_tiles && g_pair_stages == 6) ? tile_counters() : nullptr;
+    if (counters != nullptr) {
+      p.tile_counter = counters;
+      if (!a_mn_major && !b_mn_major) launch2(gemm_bf16_pair_kernel<false, false, 0, true>);
+      else if (!a_mn_major && b_mn_major) launch2(gemm_bf16_pair_kernel<false, true, 0, true>);
+      else if (a_mn_major && !b_mn_major) launch2(gemm_bf16_pair_kernel<true, false, 0, true>);
+      else launch2(gemm_bf16_pair_kernel<true, true, 0, true>);
+    } else if (g_pair_stages == 4) APB_LAUNCH_PAIR(4);
+    else if (g_pair_stages == 5) APB_LAUNCH_PAIR(5);
+    else APB_LAUNCH_PAIR(0);
     return cudaGetLastError() == cudaSuccess ? 0 : 4;
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;

@@ -42,7 +42,7 @@ _symm_standalone = True
 _reduction_group: dict[str, str] = {}
 
 
-def use_separate_reduction_groups(mesh) -> None:
+def use_separate_reduction_groups(mesh, pg_options=None) -> None:
     """Create (collectively, on every rank) a second process group per mesh dim for reduce-scatter /
     all-reduce.  Both groups issue in the same program order on every rank; the GEMM kernels never
     wait on a peer, so the two NCCL streams cannot starve each other."""
@@ -54,7 +54,7 @@ def use_separate_reduction_groups(mesh) -> None:
         mine = mesh.get_group(i)
         my_ranks = dist.get_process_group_ranks(mine)
         for ranks in pg_ranks:
-            g = dist.new_group(ranks)
+            g = dist.new_group(ranks, pg_options=pg_options)
             if sorted(ranks) == sorted(my_ranks):
                 _reduction_group[mine.group_name] = g.group_name
 

@@ -46,6 +46,12 @@ def parse():
                          "with their collective; hybrid: fused GEMM+collective kernels, stand-alone collectives on NCCL")
     ap.add_argument("--reduction-group", default="separate", choices=["separate", "shared"],
                     help="separate: gradient reductions run on a second NCCL communicator so that parameter gathers never queue behind them")
+    ap.add_argument("--dynamic-tiles", default=None, choices=["on", "off"],
+                    help="hand GEMM tiles to the CTA pairs at run time (a pair that shares its SMs with a collective's kernel takes fewer)")
+    ap.add_argument("--nccl-priority", default="high", choices=["high", "normal"],
+                    help="priority of the NCCL streams: with 'high' a collective's CTAs are placed first whenever SMs free up")
+    ap.add_argument("--gemm-stages", type=int, default=None, choices=[4, 5, 6],
+                    help="TMA stages of the CTA-pair GEMM; fewer leave shared memory for an NCCL CTA beside each GEMM CTA")
     ap.add_argument("--reserve-sms", type=int, default=None,
                     help="SMs the GEMM kernels leave idle for NCCL kernels on other streams, which are then capped to as many CTAs "
                          "(default 0: measured slower at N=2, 492 ms with 16 and 523 ms with 8 against 468 ms with none)")
@@ -130,10 +136,18 @@ def run_ours(args):
         # NCCL kernels get as many CTAs as the GEMM kernels leave SMs free (a persistent GEMM CTA owns
         # its SM's shared memory, so a collective launched beside it would otherwise wait for a GEMM to end)
         os.environ.setdefault("NCCL_MAX_CTAS", str(reserve))
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+    pg_opts = None
+    if world > 1 and args.nccl_priority == "high":
+        pg_opts = dist.ProcessGroupNCCL.Options()
+        pg_opts.is_high_priority_stream = True
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank), pg_options=pg_opts)
     mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
     cuda_impl.ensure_loaded()
     cuda_impl.extension().gemm_set_reserved_sms(reserve)
+    if args.gemm_stages is not None:
+        cuda_impl.extension().gemm_set_pair_stages(args.gemm_stages)
+    dynamic_tiles = (args.dynamic_tiles == "on") if args.dynamic_tiles is not None else world > 1
+    cuda_impl.extension().gemm_set_dynamic_tiles(dynamic_tiles)
 
     cfg = {"llama3_8b": llama3.llama3_8b, "llama3_debug": llama3.llama3_debug,
            "llama3_1b": lambda **kw: llama3.llama3_8b(dim=2048, n_layers=16, n_heads=16, n_kv_heads=8, ffn_hidden=8192, **kw)}[args.model](
@@ -175,7 +189,7 @@ def run_ours(args):
     if world > 1 and args.reduction_group == "separate":
         from autoparallel_b200.runtime import comm_ops
 
-        comm_ops.use_separate_reduction_groups(mesh)
+        comm_ops.use_separate_reduction_groups(mesh, pg_options=pg_opts)
     t0 = time.perf_counter()
     with AutoParallel(model, input_fn, mesh, MPPolicy(torch.bfloat16, torch.float32), activation_checkpointing=ac) as ap:
         ap.add_parameter_memory_constraint()
@@ -274,6 +288,9 @@ def run_ours(args):
                 "executor": args.executor,
                 "comm": comm_mode if world > 1 else "none",
                 "reserved_sms_for_comm": reserve,
+                "gemm_stages": cuda_impl.extension().gemm_get_pair_stages(),
+                "gemm_dynamic_tiles": bool(cuda_impl.extension().gemm_get_dynamic_tiles()),
+                "nccl_stream_priority": args.nccl_priority if world > 1 else "none",
                 "reduction_group": args.reduction_group if world > 1 else "none",
                 "fused_nodes": fused_nodes,
                 "collectives_in_graph": n_coll,

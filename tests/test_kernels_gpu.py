@@ -58,24 +58,30 @@ def test_gemm(K, M, N, K_, ta, tb, out_dtype):
 
 @pytest.mark.parametrize("M,N,K_", [(256, 256, 64), (512, 768, 320), (1000, 520, 136), (4096, 4096, 1024), (384, 264, 72)])
 @pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
-def test_gemm_cta_pairs(K, M, N, K_, ta, tb):
-    """Same GEMM through the two-CTA (cta_group::2) kernel: 256 x 256 tiles split over a CTA pair."""
+@pytest.mark.parametrize("dynamic", [False, True])
+def test_gemm_cta_pairs(K, M, N, K_, ta, tb, dynamic):
+    """Same GEMM through the two-CTA (cta_group::2) kernel: 256 x 256 tiles split over a CTA pair, with tiles
+    dealt statically or handed out at run time; launched twice in a row (the tile counter must come back to zero)."""
     lib, impl = K
     ext = impl.extension()
     torch.manual_seed(2)
     a = torch.randn((K_, M) if ta else (M, K_), device="cuda", dtype=torch.bfloat16)
     b = torch.randn((N, K_) if tb else (K_, N), device="cuda", dtype=torch.bfloat16)
-    prev = ext.gemm_get_pair_mode()
+    prev, prev_dyn = ext.gemm_get_pair_mode(), ext.gemm_get_dynamic_tiles()
     ext.gemm_set_pair_mode(True)
+    ext.gemm_set_dynamic_tiles(dynamic)
     try:
+        c0 = lib.ops.gemm(a, b, ta, tb, torch.float32)
         c = lib.ops.gemm(a, b, ta, tb, torch.float32)
         torch.cuda.synchronize()
         impl.check_status()
     finally:
         ext.gemm_set_pair_mode(prev)
+        ext.gemm_set_dynamic_tiles(prev_dyn)
     A = a.float().cpu().t() if ta else a.float().cpu()
     B = b.float().cpu().t() if tb else b.float().cpu()
     _close(c, A @ B, rtol=1e-3, atol=1e-3 * (K_ ** 0.5))
+    assert torch.equal(c0, c)
 
 
 @pytest.mark.parametrize("E,M,N,K_", [(4, 256, 256, 128), (8, 384, 704, 192), (3, 100, 136, 72), (16, 512, 1408, 2048)])
