@@ -151,7 +151,11 @@ def upstream_strategy(op, schema: OpSchema, out_val=None):
     decomposition tracing → replicate-everything (warned once per op)."""
     fn = propagator.op_strategy_funcs.get(op)
     if fn is not None:
-        return fn(schema)
+        try:
+            return fn(schema)
+        except (AssertionError, IndexError, NotImplementedError, RuntimeError, TypeError, ValueError) as e:
+            # the registered function does not cover this call form (e.g. ``None`` entries in an index list)
+            logger.debug("registered strategy of %s failed: %s", op, e)
     for fb in (_single_dim_fallback, _decomp_fallback):
         try:
             res = fb(op, schema)

@@ -317,9 +317,51 @@ def _getitem(ctx):
     idx = ctx.args[1]
     specs = []
     for s in strat.strategies:
-        spec = s.output_specs[idx]
+        outs = s.output_specs
+        if not isinstance(outs, (tuple, list)) or idx >= len(outs):
+            raise RuntimeError(
+                f"getitem[{idx}] of a producer whose strategy describes {len(outs) if isinstance(outs, (tuple, list)) else 1} "
+                f"outputs (producer value has {len(ctx.in_vals[0]) if isinstance(ctx.in_vals[0], (tuple, list)) else 1})"
+            )
+        spec = outs[idx]
         specs.append(OpSpec(spec, input_specs=[spec]))
     return OpStrategy(specs)
+
+
+# ------------------------------------------------------------------------------ dropout / indexing
+@register_rule(aten.native_dropout.default)
+def _native_dropout(ctx):
+    """(out, mask) of one input: any dim may be sharded, every rank draws its own mask for its shard."""
+    (x,) = ctx.in_vals
+    return expand_rows(ctx, [(S(i), S(i), S(i)) for i in range(x.ndim)])
+
+
+@register_rule(aten.native_dropout_backward.default)
+def _native_dropout_bwd(ctx):
+    g = ctx.in_vals[0]
+    return expand_rows(ctx, [(S(i), S(i), S(i)) for i in range(g.ndim)])
+
+
+@register_rule(aten.index.Tensor)
+def _index_tensor(ctx):
+    """``x[..., idx, ...]`` with ONE index tensor (other entries ``None``): untouched dims of ``x`` shard
+    through (shifted by the index tensor's rank), or the index tensor is sharded and ``x`` is whole along
+    the indexed dim.  Other forms run replicated."""
+    x = ctx.in_vals[0]
+    index_list = ctx.args[1]
+    pos = [i for i, a in enumerate(index_list) if a is not None]
+    if len(pos) != 1 or len(ctx.in_vals) != 2:
+        return expand_rows(ctx, [])
+    k, idx = pos[0], ctx.in_vals[1]
+    shift = idx.ndim - 1
+    rows = []
+    for d in range(x.ndim):
+        if d == k:
+            continue
+        rows.append((S(d if d < k else d + shift), S(d), R))
+    for j in range(idx.ndim):
+        rows.append((S(k + j), R, S(j)))
+    return expand_rows(ctx, rows)
 
 
 # ------------------------------------------------------------------------------ view / reshape
@@ -446,18 +488,27 @@ def _layer_norm_bwd(ctx):
 
 
 # ------------------------------------------------------------------------------ misc ATen gaps
+def _mask_rows(ctx, first_extra: int, d: int) -> tuple:
+    """Placements of the tensor inputs after q/k/v(/...): an attention mask follows the batch / head shard
+    where it has that dim in full and stays whole where it broadcasts (extent 1)."""
+    q = ctx.in_vals[1] if first_extra == 6 else ctx.in_vals[0]
+    out = []
+    for v in ctx.in_vals[first_extra:]:
+        follows = isinstance(v, torch.Tensor) and v.ndim == q.ndim and v.shape[d] == q.shape[d] and v.shape[d] > 1
+        out.append(S(d) if follows else R)
+    return tuple(out)
+
+
 @register_rule(aten._scaled_dot_product_flash_attention_for_cpu.default)
 def _sdpa_cpu(ctx):
     # q,k,v [B,H,S,D] (+ optional mask) -> (out [B,H,S,D], lse [B,H,S]); batch- and head-parallel
-    extra = (R,) * (len(ctx.in_vals) - 3)
-    return expand_rows(ctx, [(S(0), S(0), S(0), S(0), S(0)) + extra, (S(1), S(1), S(1), S(1), S(1)) + extra])
+    return expand_rows(ctx, [(S(d),) * 5 + _mask_rows(ctx, 3, d) for d in (0, 1)])
 
 
 @register_rule(aten._scaled_dot_product_flash_attention_for_cpu_backward.default)
 def _sdpa_cpu_bwd(ctx):
     # (dout, q, k, v, out, lse, ...) -> (dq, dk, dv)
-    extra = (R,) * (len(ctx.in_vals) - 6)
-    return expand_rows(ctx, [(S(0),) * 9 + extra, (S(1),) * 9 + extra])
+    return expand_rows(ctx, [(S(d),) * 9 + _mask_rows(ctx, 6, d) for d in (0, 1)])
 
 
 @register_rule(aten.squeeze.dims, aten.squeeze.dim)
