@@ -129,7 +129,15 @@ class AutoParallel:
                 if self.plan_device is not None:
                     topo = comm_cost.Topology([comm_cost.NVLINK5] * self.mesh.ndim)
                 if isinstance(self.cost_model, str) and self.cost_model not in ("auto", "nccl"):
-                    topo.load_table(self.cost_model)
+                    # "measured" / "measured:symm": the table taken on this device type that ships with the package
+                    if self.cost_model.startswith("measured"):
+                        backend = self.cost_model.partition(":")[2] or "nccl"
+                        path = comm_cost.Topology.measured_table_path(self.plan_device or "B200", backend)
+                        if path is None:
+                            raise ValueError(f"no measured collective table for {self.plan_device or 'B200'} / {backend}")
+                        topo.load_table(path)
+                    else:
+                        topo.load_table(self.cost_model)
                 comm_cost.set_topology(topo)
             if self.plan_device is not None:
                 device_cost.set_device_limit(device_cost.DEVICE_LIMITS[self.plan_device])

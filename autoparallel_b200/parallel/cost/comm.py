@@ -76,6 +76,14 @@ class Topology:
             links.append(INFINIBAND if spans_nodes else NVLINK5)
         return cls(links)
 
+    @staticmethod
+    def measured_table_path(device: str = "B200", backend: str = "nccl") -> Optional[str]:
+        """Path of the collective table measured on ``device`` that ships with the package, if there is one."""
+        import os
+
+        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tables", f"{device.lower()}_nvswitch_{backend}.json")
+        return path if os.path.exists(path) else None
+
     def load_table(self, path: str) -> None:
         with open(path) as f:
             raw = json.load(f)

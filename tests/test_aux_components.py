@@ -149,3 +149,22 @@ def test_overlap_simulator_cli(fake_world, tmp_path, capsys):
     report = json.loads(out)
     assert report["plan"]["collectives"]["all_gather"] > 0 and "exposed_collectives_after" in json.dumps(report)
     assert (tmp_path / "trace_fw.json").exists() or any(p.name.startswith("trace_") for p in tmp_path.iterdir())
+
+
+def test_shipped_measured_table_changes_the_prices(mesh_1d):
+    from autoparallel_b200.parallel.cost import comm
+
+    path = comm.Topology.measured_table_path("B200", "nccl")
+    assert path is not None and comm.Topology.measured_table_path("B200", "symm") is not None
+    model = comm.Topology([comm.NVLINK5])
+    measured = comm.Topology([comm.NVLINK5])
+    measured.load_table(path)
+    for n in (2, 4, 8):
+        a, b = model.all_gather(0, n, 1 << 26), measured.all_gather(0, n, 1 << 26)
+        assert b > 0 and 0.2 < a / b < 5  # same order of magnitude as the link model, but not the same number
+        assert measured.reduce_scatter(0, n, 1 << 28) > measured.reduce_scatter(0, n, 1 << 24)
+    ap = _llama(mesh_1d, plan_device="B200", cost_model="measured")
+    try:
+        assert ap.sharding_optimizer.objective_value > 0
+    finally:
+        ap.__exit__(None, None, None)
