@@ -37,6 +37,7 @@ int apb_xent_bwd(const float* dloss, const void* logits, const long long* labels
 int apb_embedding_bwd(const void* dy, const long long* ids, float* out_f32, long long tokens, int D, int is_bf16,
                       cudaStream_t st);
 int apb_symm_header_bytes();
+int apb_symm_wait_probe(const uint32_t* flag, unsigned target, unsigned limit_ms, uint32_t* status, cudaStream_t st);
 int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank, int n, unsigned epoch, const void* src,
                         void* dst, long long outer, long long inner_bytes, int elem_kind, float scale, long long stage_capacity,
                         uint32_t* status, int num_ctas, unsigned target0, unsigned target1, cudaStream_t st);
@@ -174,6 +175,15 @@ void adamw(const at::Tensor& table, const at::Tensor& chunks, int64_t num_chunks
 
 int64_t symm_header_bytes() { return apb_symm_header_bytes(); }
 
+// Bounded wait on a device flag (int32 tensor, element 0) that the caller may or may not ever raise.
+void symm_wait_probe(const at::Tensor& flag, int64_t target, int64_t limit_ms, at::Tensor& status) {
+  c10::cuda::CUDAGuard g(flag.device());
+  TORCH_CHECK(flag.scalar_type() == at::kInt && flag.numel() >= 1, "symm_wait_probe: int32 flag tensor required");
+  check(apb_symm_wait_probe(reinterpret_cast<const uint32_t*>(flag.data_ptr()), (unsigned)target, (unsigned)limit_ms,
+                            reinterpret_cast<uint32_t*>(status.data_ptr()), stream()),
+        "apb_symm_wait_probe");
+}
+
 // One collective on a symmetric workspace (see symm_comm.cu).  src/dst are ordinary device tensors.
 void symm_collective(int64_t mode, const std::vector<int64_t>& peer_ptrs, int64_t rank, int64_t epoch, const at::Tensor& src,
                      at::Tensor& dst, int64_t outer, int64_t inner_bytes, int64_t elem_kind, double scale,
@@ -238,6 +248,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_bwd", &embedding_bwd);
   m.def("adamw", &adamw);
   m.def("symm_header_bytes", &symm_header_bytes);
+  m.def("symm_wait_probe", &symm_wait_probe);
   m.def("symm_collective", &symm_collective);
   m.def("gemm_fused", &gemm_fused);
   m.def("gemm_fused_ctas", [](int64_t fuse, int64_t M, int64_t N, int64_t comm_ctas) {

@@ -169,6 +169,19 @@ extern "C" {
 
 int apb_symm_header_bytes() { return HEADER_BYTES; }
 
+// One thread waits for ``*flag >= target`` with the kernels' bounded wait and a caller-chosen limit.
+// With a flag that nothing raises this is the error path of every collective in miniature: the wait
+// runs out, the status word is set, the kernel returns and the context stays usable.
+__global__ void wait_probe_kernel(const uint32_t* flag, uint32_t target, uint32_t* status, unsigned long long limit_ns) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) wait_ge<false>(flag, target, status, limit_ns);
+}
+
+int apb_symm_wait_probe(const uint32_t* flag, unsigned target, unsigned limit_ms, uint32_t* status, cudaStream_t st) {
+  if (limit_ms > 2000u) limit_ms = 2000u;
+  wait_probe_kernel<<<1, 32, 0, st>>>(flag, target, status, (unsigned long long)limit_ms * 1000000ull);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
 // peer_ptrs: host array of n workspace base pointers (this process's mappings of every rank's buffer).
 // mode: 0 all-gather, 1 reduce-scatter (sum), 2 all-to-all.  Returns 0 or an error code.
 int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank, int n, unsigned epoch, const void* src,

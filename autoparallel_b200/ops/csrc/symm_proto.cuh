@@ -45,8 +45,10 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 }
 
 // Bounded wait for *flag >= target (wrap-safe signed difference).  SYS: the flag is written by another GPU.
+// On expiry the status word gets ST_TIMEOUT_PEER (first error wins) and the caller returns.
 template <bool SYS>
-__device__ __forceinline__ bool wait_ge(const uint32_t* flag, uint32_t target, uint32_t* status) {
+__device__ __forceinline__ bool wait_ge(const uint32_t* flag, uint32_t target, uint32_t* status,
+                                        unsigned long long limit_ns = kPeerWaitLimitNs) {
   uint32_t v = SYS ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
   if ((int32_t)(v - target) >= 0) return true;
   const unsigned long long t0 = gtime();
@@ -54,7 +56,7 @@ __device__ __forceinline__ bool wait_ge(const uint32_t* flag, uint32_t target, u
     v = SYS ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
     if ((int32_t)(v - target) >= 0) return true;
     if ((i & 31u) == 0u) {
-      if (gtime() - t0 > kPeerWaitLimitNs) {
+      if (gtime() - t0 > limit_ns) {
         atomicCAS(status, 0u, ST_TIMEOUT_PEER);
         return false;
       }

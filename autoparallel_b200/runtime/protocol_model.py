@@ -1,0 +1,152 @@
+"""Host model of the flag protocol that the symmetric-memory kernels follow, for checking it without a GPU.
+
+Every rank owns a workspace ``[ flags | staging ]`` that all ranks can address.  Flags carry the epoch of
+the collective that wrote them and only grow:
+
+* ``ready[r]`` on rank p – rank r's staging content for this epoch is complete (p may pull from it),
+* ``done[r]``  on rank p – rank r will not touch p's staging for this epoch any more,
+* ``contrib[r]`` on rank p – rank r has stored all its partial results into p's staging (GEMM → reduce-scatter).
+
+The device code is in ``ops/csrc/symm_proto.cuh`` (waits, flag layout), ``symm_comm.cu`` (stand-alone
+collectives), ``gemm_core.cuh`` / ``gemm_fused.cu`` (fused kernels).  This module restates the same steps with
+one Python thread per rank and the same ordering rules, so that the protocol – not the CUDA – can be
+exercised under arbitrary interleavings, with ranks that are late, and with a rank that never raises a flag.
+A wait that runs out does what the kernels do: it records ``(rank, flag, peer, expected, observed)`` and the
+collective returns an error instead of blocking.
+"""
+from __future__ import annotations
+
+import dataclasses
+import random
+import threading
+import time
+from typing import Callable, Optional
+
+import numpy as np
+
+
+@dataclasses.dataclass
+class WaitTimeout:
+    rank: int
+    flag: str
+    peer: int
+    expected: int
+    observed: int
+
+
+class Workspace:
+    """One rank's symmetric buffer: three flag arrays and a staging area."""
+
+    def __init__(self, n: int, stage_elems: int):
+        self.ready = [0] * n
+        self.done = [0] * n
+        self.contrib = [0] * n
+        self.stage = np.zeros(stage_elems, dtype=np.float32)
+
+
+class Fabric:
+    """All workspaces plus the condition variable that stands in for memory becoming visible."""
+
+    def __init__(self, n: int, stage_elems: int, wait_limit_s: float = 0.5, jitter: float = 0.0, seed: int = 0):
+        self.n = n
+        self.ws = [Workspace(n, stage_elems) for _ in range(n)]
+        self.cv = threading.Condition()
+        self.wait_limit_s = wait_limit_s
+        self.jitter = jitter
+        self.rng = random.Random(seed)
+        self.errors: list[WaitTimeout] = []
+
+    # -- the two primitives of symm_proto.cuh
+    def raise_flag(self, owner: int, kind: str, idx: int, epoch: int) -> None:
+        """``st.release`` of ``epoch`` into ``kind[idx]`` of rank ``owner``'s workspace."""
+        self._pause()
+        with self.cv:
+            flags = getattr(self.ws[owner], kind)
+            flags[idx] = max(flags[idx], epoch)
+            self.cv.notify_all()
+
+    def wait_ge(self, rank: int, kind: str, idx: int, epoch: int) -> bool:
+        """Bounded ``ld.acquire`` spin on ``kind[idx] >= epoch`` of ``rank``'s own workspace."""
+        deadline = time.monotonic() + self.wait_limit_s
+        with self.cv:
+            flags = getattr(self.ws[rank], kind)
+            while flags[idx] < epoch:
+                left = deadline - time.monotonic()
+                if left <= 0:
+                    self.errors.append(WaitTimeout(rank, kind, idx, epoch, flags[idx]))
+                    return False
+                self.cv.wait(left)
+        return True
+
+    def _pause(self) -> None:
+        if self.jitter:
+            time.sleep(self.rng.random() * self.jitter)
+
+
+# ------------------------------------------------------------------------------------- collectives
+def all_gather(f: Fabric, rank: int, epoch: int, shard: np.ndarray, skip_ready: bool = False) -> Optional[np.ndarray]:
+    """Pull-based all-gather (symm_comm.cu; the gather warp of the fused kernel follows the same steps)."""
+    n, me = f.n, f.ws[rank]
+    m = shard.size
+    for peer in range(n):  # phase 0: my staging is free once every peer has finished the previous collective
+        if peer != rank and not f.wait_ge(rank, "done", peer, epoch - 1):
+            return None
+    me.stage[:m] = shard
+    if not skip_ready:  # (failure injection: a rank that never publishes)
+        for peer in range(n):
+            if peer != rank:
+                f.raise_flag(peer, "ready", rank, epoch)
+    out = np.empty(n * m, dtype=np.float32)
+    out[rank * m:(rank + 1) * m] = shard
+    for k in range(1, n):  # phase 1: pull every peer's shard, nearest rank first
+        peer = (rank + k) % n
+        if not f.wait_ge(rank, "ready", peer, epoch):
+            return None
+        f._pause()
+        out[peer * m:(peer + 1) * m] = f.ws[peer].stage[:m]
+    for peer in range(n):  # phase 2: I will not read anybody's staging again in this epoch
+        if peer != rank:
+            f.raise_flag(peer, "done", rank, epoch)
+    return out
+
+
+def gemm_reduce_scatter(f: Fabric, rank: int, epoch: int, partial: np.ndarray) -> Optional[np.ndarray]:
+    """Push-based reduce-scatter of the fused GEMM: ``partial`` is this rank's full-size product; block r
+    of it belongs to rank r and is stored into slot ``rank`` of r's staging area."""
+    n, me = f.n, f.ws[rank]
+    m = partial.size // n
+    for peer in range(n):  # communication CTAs: slots are free once every peer has left the previous collective
+        if peer != rank and not f.wait_ge(rank, "done", peer, epoch - 1):
+            return None
+    for peer in range(n):
+        f.raise_flag(peer, "ready", rank, epoch)  # ... including myself: my own epilogue waits on it too
+    for k in range(1, n + 1):  # epilogues: other ranks' blocks first, own block last
+        owner = (rank + k) % n
+        if not f.wait_ge(rank, "ready", owner, epoch):
+            return None
+        f._pause()
+        f.ws[owner].stage[rank * m:(rank + 1) * m] = partial[owner * m:(owner + 1) * m]
+    for peer in range(n):  # last GEMM CTA: all my stores are out
+        f.raise_flag(peer, "contrib", rank, epoch)
+        if peer != rank:
+            f.raise_flag(peer, "done", rank, epoch)
+    for peer in range(n):  # final sum once every rank's contribution has landed
+        if not f.wait_ge(rank, "contrib", peer, epoch):
+            return None
+    return me.stage[: n * m].reshape(n, m).sum(0)
+
+
+def run_ranks(n: int, body: Callable[[Fabric, int], object], stage_elems: int, **fabric_kw):
+    """Run ``body(fabric, rank)`` on one thread per rank; returns (fabric, results by rank)."""
+    f = Fabric(n, stage_elems, **fabric_kw)
+    results: list = [None] * n
+
+    def work(r):
+        results[r] = body(f, r)
+
+    threads = [threading.Thread(target=work, args=(r,)) for r in range(n)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    return f, results

@@ -212,3 +212,31 @@ def test_attention(K, causal):
     _close(dq, rdq, 5e-2, 5e-2)
     _close(dk, rdk, 5e-2, 5e-2)
     _close(dv, rdv, 5e-2, 5e-2)
+
+
+def test_wait_that_runs_out_reports_and_leaves_the_context_usable(K):
+    """The error path of every peer wait, without a peer: a flag that nothing raises, a short limit.  The kernel
+    returns by itself, the host turns the status word into an exception, and the next kernels run normally."""
+    import time
+
+    lib, impl = K
+    ext = impl.extension()
+    torch.cuda.synchronize()
+    impl.check_status()
+    flag = torch.zeros(4, dtype=torch.int32, device="cuda")
+    status = impl.status_buffer("cuda")
+    t0 = time.perf_counter()
+    ext.symm_wait_probe(flag, 1, 200, status)  # waits for flag >= 1 for at most 200 ms
+    torch.cuda.synchronize()
+    assert 0.15 < time.perf_counter() - t0 < 1.5
+    with pytest.raises(RuntimeError, match="peer flag"):
+        impl.check_status()
+    impl.check_status()  # reported once, then cleared
+    flag.fill_(3)
+    ext.symm_wait_probe(flag, 2, 200, status)  # a flag that IS raised: no wait, no error
+    a = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+    c = lib.ops.gemm(a, b, False, True, torch.float32)
+    torch.cuda.synchronize()
+    impl.check_status()
+    _close(c, a.float().cpu() @ b.float().cpu().t(), 1e-3, 1e-3 * 128 ** 0.5)

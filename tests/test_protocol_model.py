@@ -1,0 +1,78 @@
+"""The flag protocol of the symmetric-memory kernels, exercised on the host: random interleavings, a late
+rank, back-to-back collectives of different kinds on the same flags, and a rank that never raises its flag."""
+import time
+
+import numpy as np
+import pytest
+
+from autoparallel_b200.runtime import protocol_model as pm
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_all_gather_and_reduce_scatter_interleave_correctly(n):
+    m = 16
+    rng = np.random.default_rng(0)
+    shards = rng.standard_normal((3, n, m)).astype(np.float32)          # [epoch][rank]
+    partials = rng.standard_normal((3, n, n * m)).astype(np.float32)    # [epoch][rank] full-size products
+
+    def body(f, r):
+        outs, epoch = [], 0
+        for e in range(3):  # kernels of one rank run in stream order; epochs grow by one per collective
+            epoch += 1
+            outs.append(pm.all_gather(f, r, epoch, shards[e, r]))
+            epoch += 1
+            outs.append(pm.gemm_reduce_scatter(f, r, epoch, partials[e, r]))
+        return outs
+
+    f, res = pm.run_ranks(n, body, stage_elems=n * n * m, jitter=2e-4, seed=n)
+    assert f.errors == []
+    for r in range(n):
+        for e in range(3):
+            assert np.array_equal(res[r][2 * e], shards[e].reshape(-1))
+            want = partials[e].sum(0)[r * m:(r + 1) * m]
+            assert np.allclose(res[r][2 * e + 1], want, atol=1e-5)
+
+
+def test_a_late_rank_is_waited_for():
+    n, m = 4, 8
+    data = np.arange(n * m, dtype=np.float32).reshape(n, m)
+
+    def body(f, r):
+        if r == 3:
+            time.sleep(0.15)  # well inside the wait limit
+        return pm.all_gather(f, r, 1, data[r])
+
+    f, res = pm.run_ranks(n, body, stage_elems=m, wait_limit_s=1.0)
+    assert f.errors == [] and all(np.array_equal(x, data.reshape(-1)) for x in res)
+
+
+def test_a_flag_that_is_never_raised_ends_in_a_bounded_error():
+    n, m = 4, 8
+    data = np.ones((n, m), dtype=np.float32)
+
+    def body(f, r):
+        return pm.all_gather(f, r, 1, data[r], skip_ready=(r == 2))
+
+    t0 = time.monotonic()
+    f, res = pm.run_ranks(n, body, stage_elems=m, wait_limit_s=0.2)
+    assert time.monotonic() - t0 < 2.0  # nobody blocks: every wait gives up after its limit
+    assert res[2] is not None  # the silent rank itself could pull everything
+    assert all(res[r] is None for r in (0, 1, 3))
+    assert {(e.rank, e.flag, e.peer, e.expected, e.observed) for e in f.errors} == {(r, "ready", 2, 1, 0) for r in (0, 1, 3)}
+    # the next collective cannot start either: the ranks that gave up never said "done", and that is reported too
+    f2_errors_before = len(f.errors)
+    assert pm.all_gather(f, 2, 2, data[2]) is None and len(f.errors) == f2_errors_before + 1
+    assert f.errors[-1].flag == "done" and f.errors[-1].rank == 2
+
+
+def test_reduce_scatter_waits_for_every_contribution():
+    n, m = 2, 4
+    partial = np.ones((n, n * m), dtype=np.float32)
+
+    def body(f, r):
+        if r == 1:
+            return None  # rank 1 never launches its kernel
+        return pm.gemm_reduce_scatter(f, r, 1, partial[r])
+
+    f, res = pm.run_ranks(n, body, stage_elems=n * m, wait_limit_s=0.2)
+    assert res[0] is None and f.errors and f.errors[0].rank == 0 and f.errors[0].peer == 1
