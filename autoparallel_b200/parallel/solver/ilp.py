@@ -186,29 +186,45 @@ class ShardingOptimizer:
                 self._node_cost[n] = np.array([compute_cost.strategy_compute_cost(n, s) for s in st], dtype=np.float64)
             else:
                 self._node_cost[n] = np.zeros(len(st))
+        # Repeated layers produce the same (consumer options, producer options, tensor) triples over and
+        # over: the cost matrix of an edge is computed once per distinct triple and shared (read-only).
+        memo: dict[tuple, np.ndarray] = {}
+
+        def pl_of(spec):
+            return None if spec is None else tuple(spec.placements)
+
         for n, slot, p in self.edges:
             cs, ps = self.strats[n].strategies, self.strats[p].strategies
-            m = np.zeros((len(cs), len(ps)))
             if n.op == "call_function" and n.target is operator.getitem:
-                m[:] = INF_COST
+                m = np.full((len(cs), len(ps)), INF_COST)
                 np.fill_diagonal(m, 0.0)
                 self._edge_cost[(n, slot)] = m
                 continue
-            idx = n.args[1] if False else None
-            for j, psp in enumerate(ps):
+            srcs = []
+            for psp in ps:
                 src = psp.output_specs
                 if isinstance(src, (tuple, list)):
                     # tuple producers are only consumed through getitem (handled above) or by HOPs
                     src = next((x for x in src if x is not None), None)
-                for o, csp in enumerate(cs):
-                    dst = csp.input_specs[slot]
-                    if src is None or dst is None:
-                        continue
-                    c = comm_cost.redistribute_cost(src, dst)
-                    if c == math.inf:
-                        m[o, j] = INF_COST
-                    else:
-                        m[o, j] = c + (TRANSITION_EPS if src.placements != dst.placements else 0.0)
+                srcs.append(src)
+            dsts = [csp.input_specs[slot] for csp in cs]
+            ref = next((x for x in srcs if x is not None), None)
+            tm = None if ref is None or ref.tensor_meta is None else (tuple(ref.tensor_meta.shape), ref.tensor_meta.dtype)
+            key = (tuple(pl_of(d) for d in dsts), tuple(pl_of(x) for x in srcs), tm)
+            m = memo.get(key)
+            if m is None:
+                m = np.zeros((len(cs), len(ps)))
+                for j, src in enumerate(srcs):
+                    for o, dst in enumerate(dsts):
+                        if src is None or dst is None:
+                            continue
+                        c = comm_cost.redistribute_cost(src, dst)
+                        if c == math.inf:
+                            m[o, j] = INF_COST
+                        else:
+                            m[o, j] = c + (TRANSITION_EPS if src.placements != dst.placements else 0.0)
+                m.setflags(write=False)
+                memo[key] = m
             self._edge_cost[(n, slot)] = m
 
     # ------------------------------------------------------------------ structural constraints
