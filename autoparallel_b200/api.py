@@ -260,9 +260,10 @@ class AutoParallel:
         self.parallel_gm = lowered.gm
         return lowered
 
-    def apply_placement(self, sharding_placement=None, *, executor: Optional[str] = None) -> nn.Module:
+    def apply_placement(self, sharding_placement=None, *, executor: Optional[str] = None, overlap_config=None) -> nn.Module:
         """Build the parallel module.  ``executor``: ``None``/"graph" runs the generated FX code,
-        "streams" runs it through the multi-stream overlap executor."""
+        "streams" runs it through the multi-stream overlap executor (``overlap_config``: an
+        ``parallel.passes.overlap.OverlapConfig`` with the prefetch depth / bytes in flight / pending reductions)."""
         from .runtime.executor import build_runtime
 
         lowered = self.lower(sharding_placement)
@@ -270,7 +271,7 @@ class AutoParallel:
         parts = partition_joint(lowered.joint)
         fwd_only = extract_forward(lowered.joint)
         self.partitioned = parts
-        runtime = build_runtime(lowered, parts, fwd_only, self.mesh, executor=executor)
+        runtime = build_runtime(lowered, parts, fwd_only, self.mesh, executor=executor, overlap_config=overlap_config)
         sharded_params, sharded_buffers = _meta_state(self.model, lowered, self.mesh)
         expected = input_utils.expected_local_inputs(self.joint.traced_inputs, lowered.input_placements, self.mesh)
         traced = self.joint.traced_inputs

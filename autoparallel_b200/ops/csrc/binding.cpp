@@ -13,6 +13,8 @@ int apb_gemm_grouped_bf16(const void* A, const void* B, void* C, int G, int M, i
                           int out_fp32, uint32_t* status, int num_sms, cudaStream_t stream);
 void apb_gemm_set_pair_mode(int on);
 int apb_gemm_get_pair_mode();
+int apb_gemm_yield_request(int pairs, cudaStream_t stream);
+int apb_gemm_yield_outstanding();
 void apb_gemm_set_dynamic_tiles(int on);
 int apb_gemm_get_dynamic_tiles();
 void apb_gemm_set_pair_stages(int n);
@@ -230,6 +232,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_grouped", &gemm_grouped);
   m.def("gemm_set_pair_mode", [](bool on) { apb_gemm_set_pair_mode(on ? 1 : 0); });
+  m.def("gemm_yield_request", [](int64_t pairs) { check(apb_gemm_yield_request((int)pairs, stream()), "apb_gemm_yield_request"); });
+  m.def("gemm_yield_outstanding", []() { return (int64_t)apb_gemm_yield_outstanding(); });
   m.def("gemm_set_dynamic_tiles", [](bool on) { apb_gemm_set_dynamic_tiles(on ? 1 : 0); });
   m.def("gemm_get_dynamic_tiles", []() { return apb_gemm_get_dynamic_tiles() != 0; });
   m.def("gemm_set_pair_stages", [](int64_t n) { apb_gemm_set_pair_stages((int)n); });

@@ -52,7 +52,9 @@ struct GemmParams {
   int num_m_tiles, num_n_tiles;
   uint32_t* status;
   int groups = 1;  // grouped GEMM: G independent problems of the same M, N, K, stacked along a third tensor-map dim
-  int* tile_counter = nullptr;  // dynamic tile scheduling (DYN): {next tile, pairs that have drained}, both zero between launches
+  // dynamic tile scheduling (DYN): {next tile, pairs that have left, SM-pair requests, pairs that gave up their SMs};
+  // all but the requests are zero between launches
+  int* tile_counter = nullptr;
 };
 
 struct FuseParams {
@@ -268,6 +270,10 @@ __device__ __forceinline__ void gather_comm_warp(const GemmParams& p, const Fuse
 // the eight epilogue warps of the pair read it there and release the entry on the even CTA's
 // barrier.  A pair that starts late or shares its SMs with another kernel (a communication kernel on
 // another stream) simply takes fewer tiles, so nothing waits for the slowest pair's fixed share.
+// Before each fetch the producer also looks at a request counter: a collective that is about to launch on
+// another stream asks for some SM pairs (its kernel cannot become resident while every SM holds a
+// persistent GEMM CTA), and that many pairs - never more than half of the launch - leave early; the tiles
+// they would have taken go to the pairs that stay.
 constexpr int TILE_RING = 4;
 template <bool A_MN, bool B_MN, int FUSE, bool PAIR = false, bool GROUPED = false, int ST_ARG = 0, bool DYN = false>
 __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
@@ -360,17 +366,34 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap& tmA, const CUtensorM
       *abort_flag = 1;
       return -1;
     }
-    int t = atomicAdd(p.tile_counter, 1);
-    if (t >= num_tiles) t = -1;
+    int t = -1;
+    bool leave = false;
+    if (*reinterpret_cast<volatile int*>(p.tile_counter + 2) > 0) {
+      if (atomicSub(p.tile_counter + 2, 1) > 0) {
+        if (atomicAdd(p.tile_counter + 3, 1) < num_units / 2) {
+          leave = true;  // this pair hands its two SMs to the waiting kernel
+        } else {
+          atomicSub(p.tile_counter + 3, 1);
+          atomicAdd(p.tile_counter + 2, 1);
+        }
+      } else {
+        atomicAdd(p.tile_counter + 2, 1);  // somebody else took the last request
+      }
+    }
+    if (!leave) {
+      t = atomicAdd(p.tile_counter, 1);
+      if (t >= num_tiles) t = -1;
+    }
     tile_ring[slot] = t;
     st_cluster_u32(map_to_cta(const_cast<int*>(&tile_ring[slot]), 1), (uint32_t)t);
     mbar_arrive_cluster(map_to_cta(&tile_ready[slot], 0));
     mbar_arrive_cluster(map_to_cta(&tile_ready[slot], 1));
     ++it;
     if (t < 0 && atomicAdd(p.tile_counter + 1, 1) == num_units - 1) {
-      // every pair has drained: leave the counters at zero for the next launch
+      // every pair has left: zero the per-launch counters for the next launch (requests carry over)
       p.tile_counter[0] = 0;
       p.tile_counter[1] = 0;
+      p.tile_counter[3] = 0;
       __threadfence();
     }
     return t;

@@ -94,7 +94,8 @@ static int g_dynamic_tiles = 0;
 extern "C" void apb_gemm_set_dynamic_tiles(int on) { g_dynamic_tiles = on ? 1 : 0; }
 extern "C" int apb_gemm_get_dynamic_tiles() { return g_dynamic_tiles; }
 
-// {next tile, drained pairs} per device, zero between launches (the last pair of a launch resets them).
+// {next tile, pairs that left, SM-pair requests, pairs that gave up their SMs} per device; the last pair of a
+// launch zeroes all but the requests.
 static int* tile_counters() {
   static int* per_device[64] = {nullptr};
   int dev = 0;
@@ -102,13 +103,38 @@ static int* tile_counters() {
   if (dev < 0 || dev >= 64) return nullptr;
   if (per_device[dev] == nullptr) {
     int* ptr = nullptr;
-    if (cudaMalloc(&ptr, 2 * sizeof(int)) != cudaSuccess || cudaMemset(ptr, 0, 2 * sizeof(int)) != cudaSuccess) {
+    if (cudaMalloc(&ptr, 4 * sizeof(int)) != cudaSuccess || cudaMemset(ptr, 0, 4 * sizeof(int)) != cudaSuccess) {
       cudaGetLastError();
       return nullptr;
     }
     per_device[dev] = ptr;
   }
   return per_device[dev];
+}
+
+// Asks the GEMM kernels that follow on this device to give up ``pairs`` SM pairs (see gemm_core.cuh).  Runs as a
+// one-warp kernel in stream order, so the request appears exactly when the stream reaches this point; such
+// a kernel fits beside a resident GEMM CTA.  Outstanding requests are capped.
+__global__ void yield_request_kernel(int* counters, int pairs, int cap) {
+  if (threadIdx.x == 0) {
+    const int cur = *reinterpret_cast<volatile int*>(counters + 2);
+    if (cur < cap) atomicAdd(counters + 2, pairs < cap - cur ? pairs : cap - cur);
+  }
+}
+extern "C" int apb_gemm_yield_request(int pairs, cudaStream_t stream) {
+  int* counters = tile_counters();
+  if (counters == nullptr || pairs <= 0) return 0;
+  yield_request_kernel<<<1, 32, 0, stream>>>(counters, pairs, 32);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+// Outstanding requests (synchronises the device; for tests).
+extern "C" int apb_gemm_yield_outstanding() {
+  int* counters = tile_counters();
+  if (counters == nullptr) return -1;
+  int host[4] = {0, 0, 0, 0};
+  cudaDeviceSynchronize();
+  cudaMemcpy(host, counters, sizeof(host), cudaMemcpyDeviceToHost);
+  return host[0] != 0 || host[1] != 0 || host[3] != 0 ? -2 : host[2];
 }
 
 static int g_reserved_sms = 0;

@@ -219,12 +219,32 @@ lib.define("all_reduce_start(Tensor x, str group, int group_size) -> Tensor")
 lib.define("comm_wait(Tensor x) -> Tensor")
 
 
+#: SM pairs that the GEMM kernels are asked to give up whenever an NCCL collective is issued split-phase
+#: (0 = never).  A persistent GEMM holds every SM, so a collective launched beside it would otherwise
+#: start only when the compute stream runs dry; needs the GEMM's dynamic tile scheduling.
+_yield_pairs = 0
+
+
+def set_sm_yield(pairs: int) -> None:
+    global _yield_pairs
+    _yield_pairs = max(0, int(pairs))
+
+
+def _request_sms(x) -> None:
+    if _yield_pairs and x.is_cuda:
+        from ..ops import cuda_impl
+
+        cuda_impl.ensure_loaded()
+        cuda_impl.extension().gemm_yield_request(_yield_pairs)
+
+
 def _ag_start(x, dim, group, n):
     be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_gather_start(x, dim)
     if dim != 0:
         return _all_gather(x, dim, group, n)  # inner-dim gathers need a post-permute: keep synchronous
+    _request_sms(x)
     return torch.ops._c10d_functional.all_gather_into_tensor(x.contiguous(), n, group)
 
 
@@ -236,6 +256,7 @@ def _rs_start(x, dim, group, n):
         return _reduce_scatter(x, dim, group, n)
     shape = list(x.shape)
     shape[0] //= n
+    _request_sms(x)
     out = torch.ops._c10d_functional.reduce_scatter_tensor(x.contiguous().view(-1), "sum", n, _red_group(group))
     return out.view(shape)
 

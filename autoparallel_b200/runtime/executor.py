@@ -27,7 +27,8 @@ from ..parallel.lower.partition import PartitionedGraph
 
 
 class Runtime:
-    def __init__(self, lowered: LoweredGraph, parts: PartitionedGraph, fwd_only: fx.GraphModule, mesh, executor: Optional[str]):
+    def __init__(self, lowered: LoweredGraph, parts: PartitionedGraph, fwd_only: fx.GraphModule, mesh, executor: Optional[str],
+                 overlap_config=None):
         self.lowered = lowered
         self.parts = parts
         self.mesh = mesh
@@ -66,8 +67,8 @@ class Runtime:
         if self.executor == "streams":
             from ..parallel.passes.overlap import schedule_for_streams
 
-            self.fw = schedule_for_streams(self.fw, mesh)
-            self.bw = schedule_for_streams(self.bw, mesh)
+            self.fw = schedule_for_streams(self.fw, mesh, overlap_config)
+            self.bw = schedule_for_streams(self.bw, mesh, overlap_config)
 
     def gather_inputs(self, params, buffers, inputs):
         src = {"param": params, "buffer": buffers, "input": inputs}
@@ -116,5 +117,5 @@ def _make_function(rt: Runtime):
     return ParallelGraphFunction.apply
 
 
-def build_runtime(lowered, parts, fwd_only, mesh, executor=None) -> Runtime:
-    return Runtime(lowered, parts, fwd_only, mesh, executor)
+def build_runtime(lowered, parts, fwd_only, mesh, executor=None, overlap_config=None) -> Runtime:
+    return Runtime(lowered, parts, fwd_only, mesh, executor, overlap_config)

@@ -50,6 +50,11 @@ def parse():
                     help="hand GEMM tiles to the CTA pairs at run time (a pair that shares its SMs with a collective's kernel takes fewer)")
     ap.add_argument("--nccl-priority", default="high", choices=["high", "normal"],
                     help="priority of the NCCL streams: with 'high' a collective's CTAs are placed first whenever SMs free up")
+    ap.add_argument("--prefetch-depth", type=int, default=None, help="overlap scheduler: parameter gathers issued ahead of use")
+    ap.add_argument("--max-in-flight-gb", type=float, default=None, help="overlap scheduler: gathered-but-unused bytes allowed")
+    ap.add_argument("--pending-reductions", type=int, default=None, help="overlap scheduler: gradient reductions left pending before one is waited for")
+    ap.add_argument("--yield-pairs", type=int, default=None,
+                    help="SM pairs the GEMM kernels give up for each NCCL collective issued beside them (needs --dynamic-tiles on)")
     ap.add_argument("--gemm-stages", type=int, default=None, choices=[4, 5, 6],
                     help="TMA stages of the CTA-pair GEMM; fewer leave shared memory for an NCCL CTA beside each GEMM CTA")
     ap.add_argument("--reserve-sms", type=int, default=None,
@@ -149,6 +154,11 @@ def run_ours(args):
     # measured at N=2 on one box: 463.8 ms with dynamic tiles + high-priority NCCL streams, 468.2 ms without
     dynamic_tiles = (args.dynamic_tiles == "on") if args.dynamic_tiles is not None else world > 1
     cuda_impl.extension().gemm_set_dynamic_tiles(dynamic_tiles)
+    yield_pairs = args.yield_pairs if args.yield_pairs is not None else 0
+    if world > 1 and dynamic_tiles and yield_pairs > 0:
+        from autoparallel_b200.runtime import comm_ops as _co
+
+        _co.set_sm_yield(yield_pairs)
 
     cfg = {"llama3_8b": llama3.llama3_8b, "llama3_debug": llama3.llama3_debug,
            "llama3_1b": lambda **kw: llama3.llama3_8b(dim=2048, n_layers=16, n_heads=16, n_kv_heads=8, ffn_hidden=8192, **kw)}[args.model](
@@ -196,7 +206,16 @@ def run_ours(args):
         ap.add_parameter_memory_constraint()
         ap.add_input_constraints([(Shard(0),)] * 2)
         ap.optimize_placement()
-        pm = ap.apply_placement(executor=args.executor)
+        from autoparallel_b200.parallel.passes.overlap import OverlapConfig
+
+        ocfg = OverlapConfig()
+        if args.prefetch_depth is not None:
+            ocfg.prefetch_depth = args.prefetch_depth
+        if args.max_in_flight_gb is not None:
+            ocfg.max_in_flight_bytes = int(args.max_in_flight_gb * 2**30)
+        if args.pending_reductions is not None:
+            ocfg.max_pending_reductions = args.pending_reductions
+        pm = ap.apply_placement(executor=args.executor, overlap_config=ocfg)
         timings = dict(ap.timings)
         solver = ap.sharding_optimizer
         ilp_solve_s = solver.timings.get("solve")
@@ -289,6 +308,9 @@ def run_ours(args):
                 "executor": args.executor,
                 "comm": comm_mode if world > 1 else "none",
                 "reserved_sms_for_comm": reserve,
+                "overlap": {"prefetch_depth": ocfg.prefetch_depth, "max_in_flight_gib": round(ocfg.max_in_flight_bytes / 2**30, 2),
+                            "pending_reductions": ocfg.max_pending_reductions},
+                "sm_pairs_yielded_per_collective": yield_pairs if world > 1 and dynamic_tiles else 0,
                 "gemm_stages": cuda_impl.extension().gemm_get_pair_stages(),
                 "gemm_dynamic_tiles": bool(cuda_impl.extension().gemm_get_dynamic_tiles()),
                 "nccl_stream_priority": args.nccl_priority if world > 1 else "none",

@@ -240,3 +240,28 @@ def test_wait_that_runs_out_reports_and_leaves_the_context_usable(K):
     torch.cuda.synchronize()
     impl.check_status()
     _close(c, a.float().cpu() @ b.float().cpu().t(), 1e-3, 1e-3 * 128 ** 0.5)
+
+
+def test_gemm_gives_up_sm_pairs_on_request_and_still_finishes(K):
+    """A collective about to launch beside a persistent GEMM asks for SM pairs: that many pairs (at most half of the
+    launch) leave early, the rest take over their tiles, the result is unchanged and the requests are used up."""
+    lib, impl = K
+    ext = impl.extension()
+    torch.manual_seed(5)
+    a = torch.randn(4096, 1024, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(4096, 1024, device="cuda", dtype=torch.bfloat16)
+    ref = lib.ops.gemm(a, b, False, True, torch.float32)
+    prev = ext.gemm_get_dynamic_tiles()
+    ext.gemm_set_dynamic_tiles(True)
+    try:
+        for pairs in (8, 1000, 3):
+            ext.gemm_yield_request(pairs)
+            c = lib.ops.gemm(a, b, False, True, torch.float32)
+            left = ext.gemm_yield_outstanding()
+            assert left == 0, left  # every request found a pair (requests are capped at 32, below half the launch)
+            assert torch.equal(c, ref)
+        c = lib.ops.gemm(a, b, False, True, torch.float32)  # no request: nobody leaves
+        assert torch.equal(c, ref) and ext.gemm_yield_outstanding() == 0
+        impl.check_status()
+    finally:
+        ext.gemm_set_dynamic_tiles(prev)
