@@ -286,3 +286,41 @@ def test_gpt2_plans_and_lowers(mesh_1d):
         assert len(sharded) >= len(ap.joint.param_nodes) // 2
         low = ap.lower()
         assert low.num_collectives["all_gather"] > 0
+
+
+def test_less_common_ops_plan_and_execute(mesh_1d):
+    """split / stack / einsum (plain and batched, with parameters) / select / arange / rand_like / repeat / bit-cast views."""
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w = nn.Parameter(torch.empty(64, 64))
+            self.v = nn.Parameter(torch.empty(4, 64, 16))
+
+        def forward(self, x):  # [16, 32, 64]
+            a, b = torch.split(x, [16, 16], dim=1)
+            s = torch.stack([a, b], dim=0)
+            e = torch.einsum("kbsd,de->kbse", s, self.w)
+            h = torch.einsum("bsd,hdf->bhsf", x, self.v)
+            sel = e.select(0, 1) + e[0]
+            pos = torch.arange(16, device=x.device)
+            noise = torch.rand_like(sel) * 0.0
+            out = sel + pos.view(1, 16, 1) + noise + h.sum(1)[:, :16, :].repeat(1, 1, 4)
+            bits = out.view(torch.int32).bitwise_and(0).view(torch.float32)
+            return (out + bits).sum()
+
+    ap = _enter(mesh_1d, M, lambda: torch.randn(16, 32, 64))
+    try:
+        ap.add_parameter_memory_constraint()
+        ap.add_input_constraints([(Shard(0),)])
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    finally:
+        ap.__exit__(None, None, None)
+    pm.to_empty(device="cpu")
+    with torch.no_grad():
+        for p in pm.parameters():
+            p._local_tensor.normal_()
+    loss = pm(torch.randn(2, 32, 64))
+    loss.backward()
+    assert loss.ndim == 0 and all(p.grad is not None for p in pm.parameters())
