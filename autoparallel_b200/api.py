@@ -85,11 +85,10 @@ class AutoParallel:
         bucket_collectives: bool = False,
         ordered_sharding: bool = True,
     ):
-        if dynamic:
-            raise NotImplementedError(
-                "dynamic=True (symbolic batch) is not supported: graphs are specialised to static shapes so they can "
-                "be replayed as CUDA graphs"
-            )
+        # dynamic=True: graphs stay specialised to static shapes (every kernel launch has fixed extents), but the
+        # parallel module accepts inputs of other shapes by building - once per shape - a new specialisation
+        # that reuses the solved placements instead of solving again (see ``_specialize``).
+        self.dynamic = bool(dynamic)
         self.fake_mode = FakeTensorMode()
         self.mp_policy = mp_cast.canonicalize_mp(mp_policy)
         self.mesh = mesh
@@ -122,6 +121,34 @@ class AutoParallel:
         try:
             self._prev_topology = comm_cost._topology
             self._prev_limit = device_cost._override
+            self._install_cost_models()
+            self._stack.enter_context(self.mesh)
+            t0 = time.perf_counter()
+            self.joint = build_joint_graph(self.model, self.input_fn, self.fake_mode)
+            self.gm = self.joint.gm
+            self.timings["trace"] = time.perf_counter() - t0
+            t0 = time.perf_counter()
+            self.sharding_optimizer = self._new_optimizer(self.joint)
+            self.timings["build_optimizer"] = time.perf_counter() - t0
+            self.active = True
+        except BaseException:
+            self._restore()
+            self._stack.close()
+            raise
+        return self
+
+    def _new_optimizer(self, joint) -> ShardingOptimizer:
+        force_hp = (
+            self.mp_policy is not None
+            and self.mp_policy.reduce_dtype is not None
+            and self.mp_policy.param_dtype is not None
+            and self.mp_policy.reduce_dtype.itemsize > self.mp_policy.param_dtype.itemsize
+        )
+        return ShardingOptimizer(joint, self.mesh, force_grad_reduce_in_higher_precision=force_hp,
+                                 repeated_subgraphs=self.repeated_subgraphs)
+
+    def _install_cost_models(self) -> None:
+        if True:  # (kept as one block: topology first, then the device table)
             if isinstance(self.cost_model, comm_cost.Topology):
                 comm_cost.set_topology(self.cost_model)
             else:
@@ -141,31 +168,6 @@ class AutoParallel:
                 comm_cost.set_topology(topo)
             if self.plan_device is not None:
                 device_cost.set_device_limit(device_cost.DEVICE_LIMITS[self.plan_device])
-            self._stack.enter_context(self.mesh)
-            t0 = time.perf_counter()
-            self.joint = build_joint_graph(self.model, self.input_fn, self.fake_mode)
-            self.gm = self.joint.gm
-            self.timings["trace"] = time.perf_counter() - t0
-            force_hp = (
-                self.mp_policy is not None
-                and self.mp_policy.reduce_dtype is not None
-                and self.mp_policy.param_dtype is not None
-                and self.mp_policy.reduce_dtype.itemsize > self.mp_policy.param_dtype.itemsize
-            )
-            t0 = time.perf_counter()
-            self.sharding_optimizer = ShardingOptimizer(
-                self.joint,
-                self.mesh,
-                force_grad_reduce_in_higher_precision=force_hp,
-                repeated_subgraphs=self.repeated_subgraphs,
-            )
-            self.timings["build_optimizer"] = time.perf_counter() - t0
-            self.active = True
-        except BaseException:
-            self._restore()
-            self._stack.close()
-            raise
-        return self
 
     def _restore(self):
         comm_cost.set_topology(self._prev_topology)
@@ -225,11 +227,19 @@ class AutoParallel:
         self._assert_entered()
         sol = sharding_placement if sharding_placement is not None else self.sharding_placement
         t0 = time.perf_counter()
-        lowered = lower_to_local_graph(self.joint, sol, self.mesh, ordered_sharding=self.ordered_sharding)
-        from .parallel.passes.peephole import fuse_cast_into_gemm
+        lowered = self._lower(self.joint, sol)
+        self.timings["lower"] = time.perf_counter() - t0
+        self.lowered = lowered
+        self.parallel_gm = lowered.gm
+        return lowered
 
+    def _lower(self, joint: JointGraph, sol) -> LoweredGraph:
+        """Solution -> per-rank graph with the graph passes applied (no state of this object is changed
+        except the pass statistics)."""
+        lowered = lower_to_local_graph(joint, sol, self.mesh, ordered_sharding=self.ordered_sharding)
         from .parallel.frontend.trace import index_joint_graph
         from .parallel.passes.fuse_collectives import fuse_collectives
+        from .parallel.passes.peephole import fuse_cast_into_gemm
 
         changed = fuse_cast_into_gemm(lowered.gm)
         fuse = self.fuse_collectives
@@ -251,51 +261,147 @@ class AutoParallel:
             self.bucket_stats = bucket_collectives(lowered.gm)
             changed += self.bucket_stats["members"]
         if changed:
-            lowered.joint = index_joint_graph(lowered.gm, self.joint.traced_inputs, self.joint.out_spec)
+            lowered.joint = index_joint_graph(lowered.gm, joint.traced_inputs, joint.out_spec)
         mark_fsdp_recompute(lowered.joint, self.reshard_after_forward)
         if self.activation_checkpointing != "none":
             apply_activation_checkpointing(lowered.joint, self.activation_checkpointing)
-        self.timings["lower"] = time.perf_counter() - t0
-        self.lowered = lowered
-        self.parallel_gm = lowered.gm
         return lowered
+
+    def _build_runtime(self, joint: JointGraph, lowered: LoweredGraph, executor, overlap_config):
+        """(runtime, expected local inputs, traced inputs, pytree spec of the output) of one specialisation."""
+        from .runtime.executor import build_runtime
+
+        parts = partition_joint(lowered.joint)
+        fwd_only = extract_forward(lowered.joint)
+        runtime = build_runtime(lowered, parts, fwd_only, self.mesh, executor=executor, overlap_config=overlap_config)
+        expected = input_utils.expected_local_inputs(joint.traced_inputs, lowered.input_placements, self.mesh)
+        return runtime, expected, joint.traced_inputs, _user_out_spec(joint), parts
 
     def apply_placement(self, sharding_placement=None, *, executor: Optional[str] = None, overlap_config=None) -> nn.Module:
         """Build the parallel module.  ``executor``: ``None``/"graph" runs the generated FX code,
         "streams" runs it through the multi-stream overlap executor (``overlap_config``: an
         ``parallel.passes.overlap.OverlapConfig`` with the prefetch depth / bytes in flight / pending reductions)."""
-        from .runtime.executor import build_runtime
-
         lowered = self.lower(sharding_placement)
         t0 = time.perf_counter()
-        parts = partition_joint(lowered.joint)
-        fwd_only = extract_forward(lowered.joint)
+        runtime, expected, traced, out_spec, parts = self._build_runtime(self.joint, lowered, executor, overlap_config)
         self.partitioned = parts
-        runtime = build_runtime(lowered, parts, fwd_only, self.mesh, executor=executor, overlap_config=overlap_config)
         sharded_params, sharded_buffers = _meta_state(self.model, lowered, self.mesh)
-        expected = input_utils.expected_local_inputs(self.joint.traced_inputs, lowered.input_placements, self.mesh)
-        traced = self.joint.traced_inputs
         param_names = list(lowered.joint.param_nodes)
         buffer_names = list(lowered.joint.buffer_nodes)
-        out_spec = _user_out_spec(self.joint)
+        #: shape key -> specialisation; the planned shapes are the first entry
+        specializations = {self._shape_key(expected): (runtime, expected, traced, out_spec)}
+        solved = self.sharding_placement if sharding_placement is None else sharding_placement
+        planner = self
 
         def forward(module, *args, **kwargs):
             flat = input_utils.flatten_call(traced, args, kwargs)
-            input_utils.check_forward_args(flat, expected)
+            entry = (runtime, expected, traced, out_spec)
+            if planner.dynamic:
+                key = planner._shape_key_of_call(flat, expected)
+                entry = specializations.get(key)
+                if entry is None:
+                    entry = planner._specialize(flat, expected, lowered.input_placements, solved, executor, overlap_config)
+                    specializations[key] = entry
+            rt, exp, _, ospec = entry
+            input_utils.check_forward_args(flat, exp)
             params = [_local(module.get_parameter(n)) for n in param_names]
             buffers = [_local(module.get_buffer(n)) for n in buffer_names]
-            tensors = [a for a, e in zip(flat, expected) if e[0] == "tensor"]
-            outs = runtime(params, buffers, tensors, torch.is_grad_enabled())
-            if out_spec is not None:
-                return tree_unflatten(list(outs), out_spec)
+            tensors = [a for a, e in zip(flat, exp) if e[0] == "tensor"]
+            outs = rt(params, buffers, tensors, torch.is_grad_enabled())
+            if ospec is not None:
+                return tree_unflatten(list(outs), ospec)
             return outs[0] if len(outs) == 1 else tuple(outs)
 
         module = make_parallel_module(self.model, sharded_params, sharded_buffers, forward)
         module.__dict__["_apb200_runtime"] = runtime
         module.__dict__["_apb200_lowered"] = lowered
+        module.__dict__["_apb200_specializations"] = specializations
         wrap_init_weights(module)
         self.timings["apply"] = time.perf_counter() - t0
         return module
+
+    # ------------------------------------------------------------------ shape specialisation (dynamic=True)
+    @staticmethod
+    def _shape_key(expected) -> tuple:
+        return tuple(e[1] if e[0] == "tensor" else None for e in expected)
+
+    @staticmethod
+    def _shape_key_of_call(flat, expected) -> tuple:
+        return tuple(tuple(a.shape) if e[0] == "tensor" and isinstance(a, torch.Tensor) else None for a, e in zip(flat, expected))
+
+    def _specialize(self, flat, expected, input_placements, solved, executor, overlap_config):
+        """A second (third, ...) specialisation of the parallel module for inputs of another shape: the model
+        is traced again at the new global shapes and every node takes the placement it has in the solved
+        plan - matched by node name and placement, not solved again.  Raises if the two graphs differ in
+        structure (shape-dependent control flow) or a placement does not exist at the new shape (a dim that
+        no longer divides by the mesh)."""
+        from .parallel.strategies.dtensor_adapter import local_shape
+
+        flat_traced, spec = tree_flatten((self.joint.traced_inputs.args, self.joint.traced_inputs.kwargs))
+        new_flat = []
+        for a, e, pl, old in zip(flat, expected, list(input_placements) + [None] * len(flat), flat_traced):
+            if e[0] != "tensor":
+                new_flat.append(old)
+                continue
+            if not isinstance(a, torch.Tensor) or a.ndim != len(e[1]) or a.dtype != e[2]:
+                input_utils.check_forward_args(flat, expected)  # reports rank / dtype mismatches in the usual words
+            g = list(a.shape)
+            for n, p in zip(self.mesh.shape, pl or ()):
+                if isinstance(p, Shard):
+                    g[p.dim] *= n
+            new_flat.append(("global", tuple(g), a.dtype))
+
+        def input_fn():
+            vals = [torch.zeros(v[1], dtype=v[2]) if isinstance(v, tuple) and v and v[0] == "global" else v for v in new_flat]
+            args, kwargs = tree_unflatten(vals, spec)
+            return ForwardInputs(tuple(args), dict(kwargs))
+
+        prev_topo, prev_limit = comm_cost._topology, device_cost._override
+        try:
+            self._install_cost_models()
+            with self.mesh:
+                joint = build_joint_graph(self.model, input_fn, self.fake_mode)
+                opt = self._new_optimizer(joint)
+                sol = _transfer_solution(solved, opt)
+                lowered = self._lower(joint, sol)
+                runtime, exp, traced, out_spec, _ = self._build_runtime(joint, lowered, executor, overlap_config)
+        finally:
+            comm_cost.set_topology(prev_topo)
+            device_cost.set_device_limit(prev_limit)
+        for (k, v), (k2, v2) in zip(lowered.param_placements.items(), self.lowered.param_placements.items()):
+            if k != k2 or tuple(v or ()) != tuple(v2 or ()):
+                raise RuntimeError(f"specialisation for new input shapes changed the placement of parameter {k}")
+        got = self._shape_key_of_call(flat, exp)
+        if got != self._shape_key(exp):
+            raise ValueError(f"inputs of local shapes {got} do not correspond to whole shards of a global batch on this mesh")
+        return runtime, exp, traced, out_spec
+
+
+def _transfer_solution(solved: dict, opt) -> dict:
+    """Solution for ``opt``'s graph that gives every node the placements it has in ``solved`` (a solution of a graph
+    of the same structure traced at other shapes)."""
+    from .parallel.solver.ilp import _out_placements
+
+    def sig(spec):
+        ins = tuple(tuple(i.placements) if i is not None else None for i in (spec.input_specs or ()))
+        return (_out_placements(spec), ins)
+
+    by_name = {n.name: sig(s) for n, s in solved.items()}
+    sol, selected = {}, {}
+    for n in opt.nodes:
+        want = by_name.get(n.name)
+        if want is None:
+            raise RuntimeError(f"the graph traced at the new shapes has a node the plan does not know ({n.name}): "
+                               "the model's structure depends on the input shape")
+        idx = next((i for i, s in enumerate(opt.strats[n].strategies) if sig(s) == want), None)
+        if idx is None:
+            raise RuntimeError(f"placement {want[0]} of {n.name} is not available at the new input shape "
+                               "(a sharded dim no longer divides by the mesh?)")
+        selected[n] = idx
+        sol[n] = opt.strats[n].strategies[idx]
+    opt.selected, opt.solution = selected, sol
+    opt._validate()
+    return sol
 
 
 def _local(t):

@@ -262,6 +262,65 @@ def test_ordered_sharding_renests_fsdp_tp_weights():
     assert n_ordered < n_default  # the dp-gather of the column-parallel weight is one collective, not two and a re-slice
 
 
+def _dynamic_worker(rank, ws, port, q):
+    """dynamic=True: the module is planned at one batch / sequence size and then called with others."""
+    _init(rank, ws, port)
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Shard
+
+    from autoparallel_b200 import AutoParallel, ForwardInputs
+    from autoparallel_b200.models.llama3 import Transformer, llama3_debug
+
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("dp",))
+    cfg = llama3_debug(n_layers=2)
+    with torch.device("meta"):
+        m = Transformer(cfg)
+
+    def input_fn():
+        return ForwardInputs((torch.randint(0, cfg.vocab_size, (4, 32)),), {"labels": torch.randint(0, cfg.vocab_size, (4, 32))})
+
+    with AutoParallel(m, input_fn, mesh, dynamic=True) as ap:
+        ap.add_parameter_memory_constraint()
+        ap.add_input_constraints([(Shard(0),)] * 2)
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    pm.to_empty(device="cpu")
+    pm.init_weights(seed=0)
+    ref = Transformer(cfg)
+    ref.init_weights(seed=0)
+    worst = 0.0
+    for step, (B, S) in enumerate([(4, 32), (8, 32), (4, 64), (8, 32)]):
+        torch.manual_seed(10 + step)
+        tok = torch.randint(0, cfg.vocab_size, (B, S))
+        lab = torch.randint(0, cfg.vocab_size, (B, S))
+        loss = pm(tok.chunk(ws, 0)[rank], labels=lab.chunk(ws, 0)[rank])
+        loss.backward()
+        rl = ref(tok, lab)
+        rl.backward()
+        worst = max(worst, abs(loss.item() - rl.item()))
+        for (n, p), (_, p2) in zip(pm.named_parameters(), ref.named_parameters()):
+            g = p.grad.full_tensor().float()
+            worst = max(worst, ((g - p2.grad).abs().max() / (p2.grad.abs().max() + 1e-12)).item())
+            p.grad = None
+            p2.grad = None
+    n_spec = len(pm.__dict__["_apb200_specializations"])
+    err = None
+    try:
+        pm(tok[:3], labels=lab[:3])  # 3 rows per rank x 2 ranks = global batch 6: fine on 2 ranks
+    except Exception as e:  # noqa: BLE001
+        err = f"{type(e).__name__}: {e}"
+    if rank == 0:
+        q.put((worst, n_spec, err))
+    dist.destroy_process_group()
+
+
+def test_dynamic_shapes_are_served_by_respecialisation():
+    worst, n_spec, err = _run(_dynamic_worker, 2)
+    assert worst < 1e-4
+    assert n_spec == 3  # (4,32) as planned, then (8,32) and (4,64); the second (8,32) reuses its specialisation
+    assert err is None
+
+
 def _dcp_worker(rank, ws, tmp, port, q):
     _init(rank, ws, port)
     import torch.distributed.checkpoint as dcp
