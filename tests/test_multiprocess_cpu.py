@@ -386,6 +386,78 @@ def _dcp_worker(rank, ws, tmp, port, q):
     dist.destroy_process_group()
 
 
+def _dcp_ordered_worker(rank, ws, tmp, port, q):
+    """Checkpoint written from a plan whose column-parallel weight is stored re-nested (_StridedShard), read back
+    (a) into a plan with the default nesting and (b) as full tensors."""
+    _init(rank, ws, port)
+    import torch.distributed.checkpoint as dcp
+    import torch.nn as nn
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Partial, Replicate, Shard, _StridedShard
+
+    from autoparallel_b200 import AutoParallel
+    from autoparallel_b200.parallel.lower.init_weights import _distribute
+
+    apb = torch.ops.apb200
+
+    class MLP(nn.Module):
+        def __init__(self, d=64, h=128):
+            super().__init__()
+            self.w1 = nn.Linear(d, h, bias=False)
+            self.w2 = nn.Linear(h, d, bias=False)
+
+        def forward(self, x):
+            return self.w2(torch.relu(self.w1(x))).square().mean()
+
+    mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("dp", "tp"))
+
+    def build(ordered):
+        with torch.device("meta"):
+            m = MLP()
+        with AutoParallel(m, lambda: torch.randn(8, 16, 64), mesh, ordered_sharding=ordered) as ap:
+            ap.add_input_constraints([(Shard(0), Replicate())])
+            first_mm = next(n for n in ap.gm.graph.nodes if n.op == "call_function" and n.target is apb.mm_nd.default)
+            ap.sharding_optimizer.add_node_constraint(first_mm, (Shard(0), Shard(2)))
+            for k, p in ap.joint.param_nodes.items():
+                ap.sharding_optimizer.add_node_constraint(p, (Shard(0), Shard(0)) if "w1" in k else (Shard(1), Shard(1)))
+            for k, gnode in ap.joint.param_grads.items():
+                ap.sharding_optimizer.add_node_constraint(gnode.all_input_nodes[0], (Partial(), Shard(0)) if "w1" in k else (Partial(), Shard(1)))
+            ap.optimize_placement()
+            pm = ap.apply_placement()
+        pm.to_empty(device="cpu")
+        return pm
+
+    torch.manual_seed(0)
+    ref = MLP()
+    src = build(True)
+    assert any(isinstance(p, _StridedShard) for t in src.parameters() for p in t.placements)
+    with torch.no_grad():
+        for (n, t), (_, r) in zip(src.named_parameters(), ref.named_parameters()):
+            t._local_tensor.copy_(_distribute(r.detach(), mesh, t.placements)._local_tensor)
+    dcp.save({"model": src.state_dict()}, checkpoint_id=tmp)
+    dst = build(False)  # default nesting: a different physical layout of the same logical tensors
+    assert not any(isinstance(p, _StridedShard) for t in dst.parameters() for p in t.placements)
+    with torch.no_grad():
+        for t in dst.parameters():
+            t._local_tensor.zero_()
+    state = {"model": dst.state_dict()}
+    dcp.load(state, checkpoint_id=tmp)
+    dst.load_state_dict(state["model"])
+    worst = max((t.full_tensor() - r).abs().max().item() for (_, t), (_, r) in zip(dst.named_parameters(), ref.named_parameters()))
+    torch.manual_seed(1)
+    x = torch.randn(8, 16, 64)
+    a = src(x.chunk(2, 0)[mesh.get_local_rank(0)]).item()
+    b = dst(x.chunk(2, 0)[mesh.get_local_rank(0)]).item()
+    if rank == 0:
+        q.put((worst, abs(a - b)))
+    dist.destroy_process_group()
+
+
+def test_dcp_moves_a_checkpoint_between_shard_nestings(tmp_path):
+    worst, dloss = _run(_dcp_ordered_worker, 4, str(tmp_path / "ckpt_ordered"))
+    assert worst == 0.0 and dloss < 1e-6
+
+
 def test_dcp_round_trip_of_sharded_params_and_optimizer_state(tmp_path):
     want, got = _run(_dcp_worker, 2, str(tmp_path / "ckpt"))
     assert abs(want - got) < 1e-5
