@@ -42,6 +42,14 @@ def code_to_dtype(code: int) -> torch.dtype:
 # schemas
 # --------------------------------------------------------------------------------------
 lib.define("dtype_cast(Tensor x, ScalarType dtype) -> Tensor")
+
+
+def _cast_ref(x, dtype):
+    from . import shadow
+
+    hit = shadow.lookup(x, dtype) if x.dtype != dtype else None
+    return hit if hit is not None else x.to(dtype)
+
 lib.define("rms_norm(Tensor x, Tensor weight, float eps) -> (Tensor, Tensor)")
 lib.define("rms_norm_bwd(Tensor dy, Tensor x, Tensor weight, Tensor rstd) -> (Tensor, Tensor)")
 lib.define("rope(Tensor x, Tensor cos, Tensor sin, bool conj) -> Tensor")
@@ -183,7 +191,7 @@ def _embedding_bwd_ref(dy, ids, num_rows):
 
 
 _CPU_IMPLS = {
-    "dtype_cast": lambda x, dtype: x.to(dtype),
+    "dtype_cast": lambda x, dtype: _cast_ref(x, dtype),
     "rms_norm": _rms_norm_ref,
     "rms_norm_bwd": _rms_norm_bwd_ref,
     "rope": _rope_ref,

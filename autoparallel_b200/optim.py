@@ -24,11 +24,24 @@ def _local(t):
 class AdamW(torch.optim.Optimizer):
     CHUNK = 65536
 
-    def __init__(self, params: Iterable, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, grad_scale: float = 1.0):
+    def __init__(self, params: Iterable, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, grad_scale: float = 1.0,
+                 emit_bf16: bool = False):
+        """``emit_bf16``: also write every updated fp32 parameter as bf16 into a shadow buffer that
+        ``apb200::dtype_cast`` hands out in place of a cast (ops/shadow.py); costs 2 bytes per parameter."""
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self.grad_scale = grad_scale
+        self.emit_bf16 = emit_bf16
+        self._shadows: dict = {}
         self._tables: dict = {}
+
+    def _shadow_of(self, p):
+        lp = _local(p)
+        sh = self._shadows.get(id(p))
+        if sh is None or sh.shape != lp.shape or sh.device != lp.device:
+            sh = torch.empty_like(lp, dtype=torch.bfloat16)
+            self._shadows[id(p)] = sh
+        return sh
 
     def _init_state(self, p):
         st = self.state[p]
@@ -49,8 +62,9 @@ class AdamW(torch.optim.Optimizer):
             st = self.state[p]
             lp, lg = _local(p), _local(p.grad)
             n = lp.numel()
+            lp_ptr = self._shadow_of(p).data_ptr() if self.emit_bf16 and lp.dtype == torch.float32 else 0
             recs += struct.pack("<QQQQQq", lp.data_ptr(), lg.data_ptr(), _local(st["exp_avg"]).data_ptr(),
-                                _local(st["exp_avg_sq"]).data_ptr(), 0, n)
+                                _local(st["exp_avg_sq"]).data_ptr(), lp_ptr, n)
             chunks += [(ti, c) for c in range((n + self.CHUNK - 1) // self.CHUNK)]
         dev = _local(plist[0]).device
         # Gradients are fresh tensors every step, so the record table changes every step: stage it in
@@ -104,6 +118,11 @@ class AdamW(torch.optim.Optimizer):
                 cuda_impl.extension().adamw(table, ch, n, group["lr"], b1, b2, group["eps"], group["weight_decay"], bc1, bc2,
                                             self.grad_scale)
                 cuda_impl._count()
+                if self.emit_bf16:
+                    from .ops import shadow
+
+                    for p in plist:
+                        shadow.publish(_local(p), self._shadow_of(p))
             else:
                 for p in plist:
                     st = self.state[p]
@@ -113,4 +132,10 @@ class AdamW(torch.optim.Optimizer):
                     v.mul_(b2).addcmul_(g, g, value=1 - b2)
                     upd = (m / bc1) / ((v / bc2).sqrt() + group["eps"])
                     lp.mul_(1 - group["lr"] * group["weight_decay"]).add_(upd.to(lp.dtype), alpha=-group["lr"])
+                    if self.emit_bf16 and lp.dtype == torch.float32:
+                        from .ops import shadow
+
+                        sh = self._shadow_of(p)
+                        sh.copy_(lp)
+                        shadow.publish(lp, sh)
         return loss

@@ -55,6 +55,9 @@ def parse():
     ap.add_argument("--pending-reductions", type=int, default=None, help="overlap scheduler: gradient reductions left pending before one is waited for")
     ap.add_argument("--yield-pairs", type=int, default=None,
                     help="SM pairs the GEMM kernels give up for each NCCL collective issued beside them (needs --dynamic-tiles on)")
+    ap.add_argument("--emit-bf16", default="on", choices=["on", "off"],
+                    help="AdamW also writes each updated parameter as bf16 (2 bytes/param more memory); the forward and "
+                         "backward casts of the parameters then cost no kernel")
     ap.add_argument("--gemm-stages", type=int, default=None, choices=[4, 5, 6],
                     help="TMA stages of the CTA-pair GEMM; fewer leave shared memory for an NCCL CTA beside each GEMM CTA")
     ap.add_argument("--reserve-sms", type=int, default=None,
@@ -224,7 +227,7 @@ def run_ours(args):
     plan_s = time.perf_counter() - t0
     pm.to_empty(device="cuda")
     pm.init_weights(seed=0)
-    opt = AdamW(pm.parameters(), lr=3e-4, weight_decay=0.1)
+    opt = AdamW(pm.parameters(), lr=3e-4, weight_decay=0.1, emit_bf16=(args.emit_bf16 == "on"))
 
     g = torch.Generator(device="cpu").manual_seed(1234 + rank)
     n_sets = 4
@@ -311,6 +314,7 @@ def run_ours(args):
                 "overlap": {"prefetch_depth": ocfg.prefetch_depth, "max_in_flight_gib": round(ocfg.max_in_flight_bytes / 2**30, 2),
                             "pending_reductions": ocfg.max_pending_reductions},
                 "sm_pairs_yielded_per_collective": yield_pairs if world > 1 and dynamic_tiles else 0,
+                "optimizer_emits_bf16_params": args.emit_bf16 == "on",
                 "gemm_stages": cuda_impl.extension().gemm_get_pair_stages(),
                 "gemm_dynamic_tiles": bool(cuda_impl.extension().gemm_get_dynamic_tiles()),
                 "nccl_stream_priority": args.nccl_priority if world > 1 else "none",

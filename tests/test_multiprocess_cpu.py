@@ -262,6 +262,56 @@ def test_ordered_sharding_renests_fsdp_tp_weights():
     assert n_ordered < n_default  # the dp-gather of the column-parallel weight is one collective, not two and a re-slice
 
 
+def _shadow_worker(rank, ws, emit, port, q):
+    """Three optimizer steps under bf16 compute; with ``emit`` the optimizer writes the bf16 parameter copies."""
+    _init(rank, ws, port)
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Shard
+
+    from autoparallel_b200 import AutoParallel, ForwardInputs
+    from autoparallel_b200.models.llama3 import Transformer, llama3_debug
+    from autoparallel_b200.ops import shadow
+    from autoparallel_b200.optim import AdamW
+    from autoparallel_b200.parallel.frontend.mp_cast import MPPolicy
+
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("dp",))
+    cfg = llama3_debug(n_layers=2)
+    with torch.device("meta"):
+        m = Transformer(cfg)
+
+    def input_fn():
+        return ForwardInputs((torch.randint(0, cfg.vocab_size, (4, 32)),), {"labels": torch.randint(0, cfg.vocab_size, (4, 32))})
+
+    with AutoParallel(m, input_fn, mesh, MPPolicy(torch.bfloat16, torch.float32)) as ap:
+        ap.add_parameter_memory_constraint()
+        ap.add_input_constraints([(Shard(0),)] * 2)
+        ap.optimize_placement()
+        pm = ap.apply_placement(executor="streams")
+    pm.to_empty(device="cpu")
+    pm.init_weights(seed=0)
+    opt = AdamW(pm.parameters(), lr=1e-2, emit_bf16=emit)
+    torch.manual_seed(5)
+    tok = torch.randint(0, cfg.vocab_size, (4, 32)).chunk(ws, 0)[rank]
+    losses = []
+    for _ in range(3):
+        loss = pm(tok, labels=tok)
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        losses.append(loss.item())
+    if rank == 0:
+        q.put((losses, shadow.hits))
+    dist.destroy_process_group()
+
+
+def test_bf16_shadows_from_the_optimizer_change_nothing_but_the_casts():
+    with_shadow, hits = _run(_shadow_worker, 2, True)
+    without, no_hits = _run(_shadow_worker, 2, False)
+    assert with_shadow == without  # the shadow holds exactly what the cast would produce
+    assert no_hits == 0 and hits >= 2 * 20  # from the second step on every parameter cast is answered by its shadow
+    assert with_shadow[2] < with_shadow[0]
+
+
 def _dynamic_worker(rank, ws, port, q):
     """dynamic=True: the module is planned at one batch / sequence size and then called with others."""
     _init(rank, ws, port)

@@ -141,3 +141,38 @@ def test_moe_ops_match_dense_reference_and_are_shard_invariant():
         assert torch.equal(buf_b[:, 0], buf[:, b])
         parts.append(K.moe_combine(y[:, b:b + 1], s_b, gw[sl]))
     assert torch.allclose(torch.cat(parts), out, atol=1e-6)
+
+
+def test_adamw_bf16_shadow_replaces_the_cast_until_the_parameter_changes():
+    from autoparallel_b200.ops import shadow
+    from autoparallel_b200.optim import AdamW
+
+    shadow.clear()
+    torch.manual_seed(0)
+    p = torch.nn.Parameter(torch.randn(64, 32))
+    opt = AdamW([p], lr=1e-2, emit_bf16=True)
+    cast = torch.ops.apb200.dtype_cast
+    assert cast(p.detach(), torch.bfloat16).data_ptr() != p.data_ptr()  # nothing published yet: a real cast
+    # (the runtime hands the cast a view of the parameter shard: same storage, same version counter)
+    p.grad = torch.randn_like(p)
+    opt.step()
+    before = shadow.hits
+    lp = cast(p.detach(), torch.bfloat16)
+    assert shadow.hits == before + 1 and torch.equal(lp, p.data.to(torch.bfloat16))
+    assert cast(p.detach(), torch.bfloat16).data_ptr() == lp.data_ptr()  # the same buffer every time, no new tensor
+    assert cast(p.detach(), torch.float16).dtype == torch.float16 and shadow.hits == before + 2  # other dtypes: ordinary cast
+    with torch.no_grad():
+        p.mul_(2.0)  # changed outside the optimizer: the shadow is stale and must not be used
+    fresh = cast(p.detach(), torch.bfloat16)
+    assert shadow.hits == before + 2 and torch.equal(fresh, p.data.to(torch.bfloat16)) and fresh.data_ptr() != lp.data_ptr()
+    p.grad = torch.randn_like(p)
+    opt.step()  # valid again after the next optimizer step
+    assert torch.equal(cast(p.detach(), torch.bfloat16), p.data.to(torch.bfloat16)) and shadow.hits == before + 3
+    ref = torch.nn.Parameter(p.data.clone())
+    plain = AdamW([ref], lr=1e-2)
+    g = torch.randn_like(p)
+    p.grad, ref.grad = g.clone(), g.clone()
+    opt.state[p]["step"].zero_(); opt.state[p]["exp_avg"].zero_(); opt.state[p]["exp_avg_sq"].zero_()
+    opt.step(); plain.step()
+    assert torch.allclose(p.data, ref.data)  # emitting the shadow does not change the update
+    shadow.clear()
