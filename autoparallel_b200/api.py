@@ -20,13 +20,11 @@ partitioning is tag-driven, and the per-rank graph is executed by this framework
 from __future__ import annotations
 
 import contextlib
-import copy
 import logging
 import time
 from typing import Any, Callable, Optional, Sequence
 
 import torch
-import torch.fx as fx
 import torch.nn as nn
 from torch._subclasses import FakeTensorMode
 from torch.distributed.tensor import DTensor

@@ -14,7 +14,7 @@ pins an intermediate tensor's placement.  Reference: autoparallel/collectives.py
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Sequence
 
 import torch
 from torch.distributed.tensor.placement_types import Placement

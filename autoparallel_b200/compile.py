@@ -13,7 +13,6 @@ from __future__ import annotations
 
 from typing import Callable, Optional
 
-import torch
 import torch.fx as fx
 
 

@@ -23,8 +23,7 @@ from typing import Optional
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
-from torch.distributed.tensor.placement_types import Replicate, Shard
+from torch.distributed.tensor.placement_types import Shard
 
 from .. import ops as K
 from ..collectives import all_to_all, axis_size, local_map

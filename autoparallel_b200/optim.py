@@ -9,7 +9,6 @@ pointers that is built once; on CPU the same math runs in PyTorch.
 """
 from __future__ import annotations
 
-import math
 import struct
 from typing import Iterable
 

@@ -15,7 +15,6 @@ from __future__ import annotations
 
 import dataclasses
 import logging
-import math
 import operator
 from typing import Any, Optional
 

@@ -19,7 +19,6 @@ from __future__ import annotations
 import contextlib
 import functools
 import logging
-import types
 import warnings
 
 import torch

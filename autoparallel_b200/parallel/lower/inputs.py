@@ -8,11 +8,10 @@ autoparallel/input_validation.py:27-324.
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Optional, Sequence
+from typing import Any, Optional, Sequence
 
 import torch
 from torch.distributed.tensor import DTensor
-from torch.distributed.tensor.placement_types import Replicate
 from torch.utils._pytree import tree_flatten, tree_unflatten
 
 from ..frontend.trace import ForwardInputs

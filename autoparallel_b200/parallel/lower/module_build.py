@@ -11,7 +11,6 @@ function.  Reference: autoparallel/module_construction.py:17-246.
 from __future__ import annotations
 
 import copy
-from collections import OrderedDict
 from typing import Callable
 
 import torch

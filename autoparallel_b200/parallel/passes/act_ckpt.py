@@ -13,7 +13,7 @@ normalisation results are recomputed, GEMM and attention outputs are kept, and p
 from __future__ import annotations
 
 import math
-from typing import Iterable, Optional
+from typing import Optional
 
 import torch
 import torch.fx as fx

@@ -12,7 +12,7 @@ import logging
 import operator
 import time
 from collections import defaultdict
-from typing import Any, Optional
+from typing import Any
 
 import torch
 import torch.fx as fx

@@ -18,7 +18,6 @@ from typing import Optional
 
 import numpy as np
 import torch
-import torch.fx as fx
 
 FORMAT_VERSION = 1
 
