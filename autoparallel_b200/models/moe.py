@@ -23,6 +23,7 @@ from typing import Optional
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 from torch.distributed.tensor.placement_types import Shard
 
 from .. import ops as K
@@ -51,8 +52,20 @@ class MoEConfig:
     #: "local_map": the routed block is one opaque region with hand-written all-to-alls on ``ep_axis``;
     #: "planner": the block is built from the apb200 MoE operators (ops/moe_ops.py) and the solver
     #: chooses where the token buffer moves to the experts (no mesh axis is named in the model)
+    #: "gqa": grouped-query attention as in the Llama model; "mla": multi-head latent attention (low-rank
+    #: compressed keys / values with a rotary part shared by all heads, optional low-rank queries)
+    attention: str = "gqa"
+    q_lora_rank: int = 0
+    kv_lora_rank: int = 64
+    qk_nope_head_dim: int = 32
+    qk_rope_head_dim: int = 16
+    v_head_dim: int = 32
     expert_mode: str = "local_map"
     dispatch_blocks: int = 8  # planner mode: token blocks with their own per-expert capacity (a multiple of the shard count)
+
+    def rope_dim(self) -> int:
+        """Width of the rotated part of a query / key head."""
+        return self.qk_rope_head_dim if self.attention == "mla" else self.dim // self.n_heads
 
     def attn_cfg(self) -> LlamaConfig:
         return LlamaConfig(dim=self.dim, n_layers=self.n_layers, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
@@ -101,6 +114,59 @@ def _expert_region(x, gate_w, gate_idx, w1, w3, w2, *, ep_axis: str, num_experts
     per_assign = got[slot] * (gate_w.reshape(-1, 1) * keep.unsqueeze(1)).to(got.dtype)
     out = torch.zeros_like(x).index_add(0, tok, per_assign)
     return out
+
+
+class MLAttention(nn.Module):
+    """Multi-head latent attention (the attention of the reference's DeepSeek-V3 test model,
+    autoparallel/_testing/models/dsv3.py:1382-1530): keys and values are projected down to ``kv_lora_rank``
+    (+ one rotary key of ``qk_rope_head_dim`` shared by all heads), normalised, and projected up per head;
+    queries optionally take the same detour.  Query / key heads are ``qk_nope + qk_rope`` wide, value heads
+    ``v_head_dim``; values are zero-padded to the query width for the attention operator and the padding is
+    dropped from its output."""
+
+    def __init__(self, cfg: MoEConfig):
+        super().__init__()
+        self.h = cfg.n_heads
+        self.nope, self.rope, self.vd = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        self.qk = self.nope + self.rope
+        self.kv_rank, self.q_rank = cfg.kv_lora_rank, cfg.q_lora_rank
+        if self.q_rank == 0:
+            self.wq = nn.Linear(cfg.dim, self.h * self.qk, bias=False)
+        else:
+            self.wq_a = nn.Linear(cfg.dim, self.q_rank, bias=False)
+            self.q_norm = RMSNorm(self.q_rank, cfg.norm_eps)
+            self.wq_b = nn.Linear(self.q_rank, self.h * self.qk, bias=False)
+        self.wkv_a = nn.Linear(cfg.dim, self.kv_rank + self.rope, bias=False)
+        self.kv_norm = RMSNorm(self.kv_rank, cfg.norm_eps)
+        self.wkv_b = nn.Linear(self.kv_rank, self.h * (self.nope + self.vd), bias=False)
+        self.wo = nn.Linear(self.h * self.vd, cfg.dim, bias=False)
+
+    def forward(self, x, cos, sin):
+        b, s, _ = x.shape
+        q = self.wq(x) if self.q_rank == 0 else self.wq_b(self.q_norm(self.wq_a(x)))
+        q = q.view(b, s, self.h, self.qk)
+        q_nope, q_pe = q[..., : self.nope], q[..., self.nope:]
+        kv = self.wkv_a(x)
+        kv_c, k_pe = kv[..., : self.kv_rank], kv[..., self.kv_rank:]
+        k_pe = K.rope(k_pe.reshape(b, s, 1, self.rope), cos, sin)            # one rotary key for all heads
+        q_pe = K.rope(q_pe.contiguous(), cos, sin)
+        kvu = self.wkv_b(self.kv_norm(kv_c)).view(b, s, self.h, self.nope + self.vd)
+        k_nope, v = kvu[..., : self.nope], kvu[..., self.nope:]
+        q = torch.cat([q_nope, q_pe], dim=-1)
+        k = torch.cat([k_nope, k_pe.expand(b, s, self.h, self.rope)], dim=-1)
+        v = F.pad(v, (0, self.qk - self.vd)) if self.qk > self.vd else v
+        o = K.attention(q, k, v, causal=True, scale=self.qk ** -0.5)[..., : self.vd]
+        return self.wo(o.reshape(b, s, self.h * self.vd))
+
+    def init_weights(self, std: float, out_std: float):
+        for name in ("wq", "wq_a", "wq_b", "wkv_a", "wkv_b"):
+            lin = getattr(self, name, None)
+            if lin is not None:
+                nn.init.normal_(lin.weight, mean=0.0, std=std)
+        nn.init.normal_(self.wo.weight, mean=0.0, std=out_std)
+        self.kv_norm.init_weights()
+        if self.q_rank:
+            self.q_norm.init_weights()
 
 
 class MoEFFN(nn.Module):
@@ -168,7 +234,7 @@ class MoEFFN(nn.Module):
 class MoEBlock(nn.Module):
     def __init__(self, cfg: MoEConfig):
         super().__init__()
-        self.attention = Attention(cfg.attn_cfg())
+        self.attention = MLAttention(cfg) if cfg.attention == "mla" else Attention(cfg.attn_cfg())
         self.moe = MoEFFN(cfg)
         self.attention_norm = RMSNorm(cfg.dim, cfg.norm_eps)
         self.ffn_norm = RMSNorm(cfg.dim, cfg.norm_eps)
@@ -193,7 +259,7 @@ class MoETransformer(nn.Module):
         self.layers = nn.ModuleDict({str(i): MoEBlock(cfg) for i in range(cfg.n_layers)})
         self.norm = RMSNorm(cfg.dim, cfg.norm_eps)
         self.output = nn.Linear(cfg.dim, cfg.vocab_size, bias=False)
-        cos, sin = rope_tables(cfg.dim // cfg.n_heads, cfg.max_seq_len, cfg.rope_theta)
+        cos, sin = rope_tables(cfg.rope_dim(), cfg.max_seq_len, cfg.rope_theta)
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
 
@@ -212,7 +278,7 @@ class MoETransformer(nn.Module):
         if seed is not None:
             torch.manual_seed(seed)
         cfg = self.cfg
-        cos, sin = rope_tables(cfg.dim // cfg.n_heads, cfg.max_seq_len, cfg.rope_theta, device=self.rope_cos.device)
+        cos, sin = rope_tables(cfg.rope_dim(), cfg.max_seq_len, cfg.rope_theta, device=self.rope_cos.device)
         self.rope_cos, self.rope_sin = cos, sin
         nn.init.normal_(self.tok_embeddings.weight, mean=0.0, std=cfg.init_std)
         for layer in self.layers.values():

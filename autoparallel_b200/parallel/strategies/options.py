@@ -124,7 +124,7 @@ def _attach_meta(strat: OpStrategy, out_val, in_vals, mesh) -> None:
             s.input_specs = [s.output_spec]
         ins = list(s.input_specs)
         if len(ins) != len(in_vals):
-            raise RuntimeError(f"strategy has {len(ins)} input specs for {len(in_vals)} tensor inputs")
+            raise RuntimeError(f"strategy has {len(ins)} input specs for {len(in_vals)} tensor inputs (op {getattr(strat, '_apb200_op', '?')})")
         s.input_specs = [
             DTensorSpec(mesh, spec.placements, tensor_meta=tensor_meta_of(v)) for spec, v in zip(ins, in_vals)
         ]

@@ -342,6 +342,15 @@ def _native_dropout_bwd(ctx):
     return expand_rows(ctx, [(S(i), S(i), S(i)) for i in range(g.ndim)])
 
 
+@register_rule(aten.constant_pad_nd.default)
+def _constant_pad(ctx):
+    """Padding (or cropping, with negative amounts) leaves every other dim free to shard."""
+    x = ctx.in_vals[0]
+    pads = list(ctx.args[1])
+    touched = {x.ndim - 1 - i for i in range(len(pads) // 2) if pads[2 * i] != 0 or pads[2 * i + 1] != 0}
+    return expand_rows(ctx, [(S(d), S(d)) for d in range(x.ndim) if d not in touched])
+
+
 @register_rule(aten.index.Tensor)
 def _index_tensor(ctx):
     """``x[..., idx, ...]`` with ONE index tensor (other entries ``None``): untouched dims of ``x`` shard

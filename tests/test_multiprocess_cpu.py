@@ -262,6 +262,55 @@ def test_ordered_sharding_renests_fsdp_tp_weights():
     assert n_ordered < n_default  # the dp-gather of the column-parallel weight is one collective, not two and a re-slice
 
 
+def _mla_worker(rank, ws, port, q):
+    """MoE decoder with multi-head latent attention (low-rank queries too) and planner-visible experts."""
+    _init(rank, ws, port)
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Shard
+
+    from autoparallel_b200 import AutoParallel, ForwardInputs
+    from autoparallel_b200.models.moe import MoETransformer, moe_debug
+
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("dp",))
+    cfg = moe_debug(attention="mla", q_lora_rank=48, expert_mode="planner", dispatch_blocks=4, capacity_factor=8.0)
+    B, S = 4, 32
+    with torch.device("meta"):
+        m = MoETransformer(cfg)
+
+    def input_fn():
+        return ForwardInputs((torch.randint(0, cfg.vocab_size, (B, S)),), {"labels": torch.randint(0, cfg.vocab_size, (B, S))})
+
+    with AutoParallel(m, input_fn, mesh) as ap:
+        ap.add_parameter_memory_constraint()
+        ap.add_input_constraints([(Shard(0),)] * 2)
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    pm.to_empty(device="cpu")
+    pm.init_weights(seed=0)
+    ref = MoETransformer(cfg)
+    ref.init_weights(seed=0)
+    torch.manual_seed(1)
+    tok = torch.randint(0, cfg.vocab_size, (B, S))
+    lab = torch.randint(0, cfg.vocab_size, (B, S))
+    loss = pm(tok.chunk(ws, 0)[rank], labels=lab.chunk(ws, 0)[rank])
+    loss.backward()
+    rl = ref(tok, lab)
+    rl.backward()
+    worst = 0.0
+    for (n, p), (_, p2) in zip(pm.named_parameters(), ref.named_parameters()):
+        g = p.grad.full_tensor().float()
+        worst = max(worst, ((g - p2.grad).abs().max() / (p2.grad.abs().max() + 1e-12)).item())
+    if rank == 0:
+        q.put((abs(loss.item() - rl.item()), worst, sorted(n for n, _ in pm.named_parameters() if "wkv" in n or "wq_" in n)[:4]))
+    dist.destroy_process_group()
+
+
+def test_latent_attention_moe_matches_single_device():
+    dl, dg, names = _run(_mla_worker, 2)
+    assert dl < 1e-5 and dg < 1e-3
+    assert any("wkv_a" in n for n in names) and any("wq_a" in n for n in names)
+
+
 def _shadow_worker(rank, ws, emit, port, q):
     """Three optimizer steps under bf16 compute; with ``emit`` the optimizer writes the bf16 parameter copies."""
     _init(rank, ws, port)
