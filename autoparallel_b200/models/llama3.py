@@ -13,6 +13,7 @@ depth-scaled init.  Differences that are deliberate:
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 from typing import Optional
 
@@ -85,10 +86,31 @@ def llama3_debug(**kw) -> LlamaConfig:
     return LlamaConfig(**base)
 
 
-def rope_tables(head_dim: int, max_seq_len: int, theta: float, device=None):
-    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+def rope_tables(head_dim: int, max_seq_len: int, theta: float, device=None, yarn: Optional[dict] = None):
+    """cos / sin tables ``[max_seq_len, head_dim / 2]``.  ``yarn``: context extension of a model trained at
+    ``original_max_seq_len`` by ``factor``: rotary pairs that turn more than ``beta_fast`` times over the
+    original context keep their frequency, pairs that turn fewer than ``beta_slow`` times are slowed down by
+    ``factor`` (position interpolation), the ones in between blend linearly; both tables are scaled by the
+    attention temperature ``0.1 * mscale * ln(factor) + 1`` (the reference's DeepSeek-V3 model precomputes its
+    rotary frequencies this way, autoparallel/_testing/models/dsv3.py:62-135)."""
+    half = torch.arange(0, head_dim, 2, device=device, dtype=torch.float32)
+    inv = 1.0 / (theta ** (half / head_dim))
+    scale = 1.0
+    if yarn is not None and yarn.get("factor", 1.0) > 1.0:
+        factor = float(yarn["factor"])
+        orig = int(yarn.get("original_max_seq_len", max_seq_len))
+        beta_fast, beta_slow = float(yarn.get("beta_fast", 32.0)), float(yarn.get("beta_slow", 1.0))
+
+        def pair_with_rotations(r):  # index of the rotary pair that completes ``r`` turns over the original context
+            return head_dim * math.log(orig / (r * 2 * math.pi)) / (2 * math.log(theta))
+
+        lo = max(math.floor(pair_with_rotations(beta_fast)), 0)
+        hi = min(math.ceil(pair_with_rotations(beta_slow)), head_dim // 2 - 1)
+        ramp = ((torch.arange(head_dim // 2, device=device, dtype=torch.float32) - lo) / max(hi - lo, 1e-3)).clamp(0.0, 1.0)
+        inv = inv * (1.0 - ramp) + (inv / factor) * ramp
+        scale = 0.1 * float(yarn.get("mscale", 1.0)) * math.log(factor) + 1.0
     ang = torch.outer(torch.arange(max_seq_len, device=device, dtype=torch.float32), inv)
-    return ang.cos(), ang.sin()
+    return ang.cos() * scale, ang.sin() * scale
 
 
 class RMSNorm(nn.Module):

@@ -60,6 +60,8 @@ class MoEConfig:
     qk_nope_head_dim: int = 32
     qk_rope_head_dim: int = 16
     v_head_dim: int = 32
+    #: YaRN context extension of the rotary tables, e.g. {"factor": 4.0, "original_max_seq_len": 1024}
+    rope_yarn: Optional[dict] = None
     expert_mode: str = "local_map"
     dispatch_blocks: int = 8  # planner mode: token blocks with their own per-expert capacity (a multiple of the shard count)
 
@@ -259,7 +261,7 @@ class MoETransformer(nn.Module):
         self.layers = nn.ModuleDict({str(i): MoEBlock(cfg) for i in range(cfg.n_layers)})
         self.norm = RMSNorm(cfg.dim, cfg.norm_eps)
         self.output = nn.Linear(cfg.dim, cfg.vocab_size, bias=False)
-        cos, sin = rope_tables(cfg.rope_dim(), cfg.max_seq_len, cfg.rope_theta)
+        cos, sin = rope_tables(cfg.rope_dim(), cfg.max_seq_len, cfg.rope_theta, yarn=cfg.rope_yarn)
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
 
@@ -278,7 +280,7 @@ class MoETransformer(nn.Module):
         if seed is not None:
             torch.manual_seed(seed)
         cfg = self.cfg
-        cos, sin = rope_tables(cfg.rope_dim(), cfg.max_seq_len, cfg.rope_theta, device=self.rope_cos.device)
+        cos, sin = rope_tables(cfg.rope_dim(), cfg.max_seq_len, cfg.rope_theta, device=self.rope_cos.device, yarn=cfg.rope_yarn)
         self.rope_cos, self.rope_sin = cos, sin
         nn.init.normal_(self.tok_embeddings.weight, mean=0.0, std=cfg.init_std)
         for layer in self.layers.values():

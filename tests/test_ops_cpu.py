@@ -1,4 +1,5 @@
 """CPU reference implementations of the operator library against PyTorch's own autograd."""
+import math
 import torch
 import torch.nn.functional as F
 
@@ -176,3 +177,21 @@ def test_adamw_bf16_shadow_replaces_the_cast_until_the_parameter_changes():
     opt.step(); plain.step()
     assert torch.allclose(p.data, ref.data)  # emitting the shadow does not change the update
     shadow.clear()
+
+
+def test_yarn_rope_tables_keep_fast_pairs_and_stretch_slow_ones():
+    from autoparallel_b200.models.llama3 import rope_tables
+
+    d, n, theta = 64, 4096, 10000.0
+    cos0, sin0 = rope_tables(d, n, theta)
+    cos1, sin1 = rope_tables(d, n, theta, yarn={"factor": 4.0, "original_max_seq_len": 1024, "mscale": 1.0})
+    scale = 0.1 * math.log(4.0) + 1.0
+    assert cos1.shape == cos0.shape == (n, d // 2)
+    # the fastest pair keeps its frequency (only the temperature differs) ...
+    assert torch.allclose(cos1[:, 0] / scale, cos0[:, 0], atol=1e-5) and torch.allclose(sin1[:, 0] / scale, sin0[:, 0], atol=1e-5)
+    # ... the slowest pair is interpolated: position p of the extended context lands where p / 4 used to
+    p = torch.arange(0, n, 4)
+    assert torch.allclose(sin1[p, -1] / scale, sin0[p // 4, -1], atol=1e-4)
+    # factor 1 (or no yarn) is the plain table
+    c, s_ = rope_tables(d, n, theta, yarn={"factor": 1.0})
+    assert torch.equal(c, cos0) and torch.equal(s_, sin0)
