@@ -10,7 +10,7 @@ import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import torch
-from torch.distributed.tensor.placement_types import Replicate, Shard
+from torch.distributed.tensor.placement_types import Partial, Replicate, Shard
 
 from autoparallel_b200 import AutoParallel, ForwardInputs
 from autoparallel_b200.models import llama3
@@ -20,6 +20,30 @@ from autoparallel_b200.utils.visualizer import generate_visualization_html
 from examples._fake import fake_mesh
 
 
+def force_tp_constraints(autop) -> int:
+    """Megatron-style tensor parallelism by hand: in every block wq / wk / wv / w1 / w3 are column-parallel
+    (output features split over "tp"), wo / w2 row-parallel (partial sums over "tp").  Forward projections are
+    found through the module path recorded on their nodes.  (Reference counterpart: the helper of the same
+    purpose in examples/example_llama3.py.)"""
+    apb = torch.ops.apb200
+    col, row = ("wq", "wk", "wv", "w1", "w3"), ("wo", "w2")
+    pinned = 0
+    for node in autop.gm.graph.nodes:
+        if node.op != "call_function" or node.target is not apb.mm_nd.default:
+            continue
+        stack = node.meta.get("nn_module_stack")
+        if not stack:
+            continue  # backward nodes carry the forward stack under another key
+        leaf = str(list(stack.values())[-1][0]).split(".")[-1] if isinstance(stack, dict) else ""
+        if leaf in col:
+            autop.sharding_optimizer.add_node_constraint(node, (Shard(0), Shard(2)))
+            pinned += 1
+        elif leaf in row:
+            autop.sharding_optimizer.add_node_constraint(node, (Shard(0), Partial()))
+            pinned += 1
+    return pinned
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama3_8b")
@@ -27,6 +51,7 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--vocab-parallel", action="store_true")
+    ap.add_argument("--manual-tp", action="store_true", help="pin the Megatron pattern on every block (2-D mesh)")
     ap.add_argument("--html", default=None)
     a = ap.parse_args()
     shape = tuple(int(x) for x in a.mesh.split(","))
@@ -46,6 +71,9 @@ def main():
         autop.add_input_constraints([x_pl])
         out_pl = (Shard(0), Shard(2)) if (a.vocab_parallel and mesh.ndim == 2) else x_pl
         autop.add_output_constraints([out_pl])
+        if a.manual_tp and mesh.ndim == 2:
+            n = force_tp_constraints(autop)
+            print("pinned", n, "projections")
         autop.optimize_placement()
         opt = autop.sharding_optimizer
         print("ILP:", opt.problem_size, {k: round(v, 2) for k, v in opt.timings.items()})
