@@ -150,3 +150,99 @@ def run_ranks(n: int, body: Callable[[Fabric, int], object], stage_elems: int, *
     for t in threads:
         t.join()
     return f, results
+
+
+# ------------------------------------------------------------------------------------- dynamic GEMM tiles
+class TileCounters:
+    """The four device integers of the dynamic tile scheduler (gemm_core.cuh, ``DYN``): next tile, pairs that
+    have left, SM-pair requests of collectives, pairs that gave up their SMs in this launch."""
+
+    def __init__(self):
+        self.lock = threading.Lock()
+        self.next_tile = 0
+        self.left = 0
+        self.requests = 0
+        self.yielded = 0
+
+    def request(self, pairs: int, cap: int = 32) -> None:
+        with self.lock:
+            self.requests += max(0, min(pairs, cap - self.requests))
+
+
+def run_dynamic_gemm(counters: TileCounters, num_tiles: int, num_pairs: int, readers: int = 10, ring: int = 4,
+                     jitter: float = 0.0, seed: int = 0) -> dict:
+    """One launch: per CTA pair a fetching thread (the even CTA's producer) publishes tile indices through a
+    ``ring``-entry ring that ``readers`` consumer threads (odd CTA's producer, MMA thread, eight epilogue
+    warps) read and release.  Returns, per pair, the tiles each reader saw; the caller checks that every
+    tile was handled exactly once and by all readers of one pair alike."""
+    rng = random.Random(seed)
+    seen = {p: [[] for _ in range(readers)] for p in range(num_pairs)}
+
+    def pair_body(p):
+        cv = threading.Condition()
+        slots = [None] * ring
+        ready = [0] * ring   # phase counters: entry published (it // ring + 1)
+        freed = [0] * ring   # readers that released the entry, cumulative
+
+        def fetch():
+            it = 0
+            while True:
+                s = it % ring
+                with cv:
+                    cv.wait_for(lambda: freed[s] >= readers * (it // ring))  # everybody has read the previous use
+                t, leave = -1, False
+                with counters.lock:  # the atomics of the kernel, in the same order
+                    if counters.requests > 0:
+                        counters.requests -= 1
+                        if counters.yielded < num_pairs // 2:
+                            counters.yielded += 1
+                            leave = True
+                        else:
+                            counters.requests += 1
+                    if not leave:
+                        t = counters.next_tile
+                        counters.next_tile += 1
+                        if t >= num_tiles:
+                            t = -1
+                if jitter:
+                    time.sleep(rng.random() * jitter)
+                with cv:
+                    slots[s] = t
+                    ready[s] = it // ring + 1
+                    cv.notify_all()
+                it += 1
+                if t < 0:
+                    with counters.lock:
+                        counters.left += 1
+                        if counters.left == num_pairs:  # last pair out zeroes the per-launch counters
+                            counters.next_tile = counters.left = counters.yielded = 0
+                    return
+
+        def read(r):
+            it = 0
+            while True:
+                s = it % ring
+                with cv:
+                    cv.wait_for(lambda: ready[s] >= it // ring + 1)
+                    t = slots[s]
+                    freed[s] += 1
+                    cv.notify_all()
+                it += 1
+                if t < 0:
+                    return
+                seen[p][r].append(t)
+                if jitter:
+                    time.sleep(rng.random() * jitter)
+
+        ths = [threading.Thread(target=fetch)] + [threading.Thread(target=read, args=(r,)) for r in range(readers)]
+        for t in ths:
+            t.start()
+        for t in ths:
+            t.join()
+
+    pairs = [threading.Thread(target=pair_body, args=(p,)) for p in range(num_pairs)]
+    for t in pairs:
+        t.start()
+    for t in pairs:
+        t.join()
+    return seen

@@ -76,3 +76,25 @@ def test_reduce_scatter_waits_for_every_contribution():
 
     f, res = pm.run_ranks(n, body, stage_elems=n * m, wait_limit_s=0.2)
     assert res[0] is None and f.errors and f.errors[0].rank == 0 and f.errors[0].peer == 1
+
+
+@pytest.mark.parametrize("requests", [0, 3, 100])
+def test_dynamic_tiles_are_each_handled_once_even_when_pairs_leave(requests):
+    """Tile ring of the CTA-pair GEMM: every tile goes to exactly one pair, all readers of a pair see the same
+    sequence, pairs that leave on request never exceed half of the launch, and the counters are back at zero
+    for the next launch (which is run right away)."""
+    c = pm.TileCounters()
+    num_tiles, num_pairs = 97, 8
+    for launch in range(2):
+        c.request(requests)
+        asked = c.requests
+        seen = pm.run_dynamic_gemm(c, num_tiles, num_pairs, readers=10, jitter=1e-4, seed=launch)
+        tiles = []
+        for p in range(num_pairs):
+            assert all(s == seen[p][0] for s in seen[p])  # producer, MMA and epilogue roles agree
+            tiles += seen[p][0]
+        assert sorted(tiles) == list(range(num_tiles))
+        idle = sum(1 for p in range(num_pairs) if not seen[p][0])
+        assert idle <= max(num_pairs // 2, 0) + 0 or requests == 0
+        assert (c.next_tile, c.left, c.yielded) == (0, 0, 0)
+        assert c.requests == max(0, asked - num_pairs // 2)  # granted requests are used up, the rest carry over
