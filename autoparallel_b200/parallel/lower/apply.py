@@ -268,7 +268,12 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
             if is_local_map_node(node):
                 nn_ = _inline_region(new_g, local_map_body(node), new_args)
             else:
-                nn_ = new_g.call_function(node.target, new_args, new_kwargs)
+                target = node.target
+                if target in (aten.view.default, aten._unsafe_view.default):
+                    # strides of a kernel's output may differ from the ones tracing assumed (attention outputs
+                    # above all); reshape is the same view when one exists and a copy otherwise
+                    target = aten.reshape.default
+                nn_ = new_g.call_function(target, new_args, new_kwargs)
             nn_.meta = dict(node.meta)
             nn_.meta["val"] = lval
             nn_.meta["apb200_placements"] = (

@@ -94,7 +94,8 @@ def make_runtime_estimator(mesh, plan_device: Optional[str] = None) -> Callable[
         if t is C.comm_wait.default or not isinstance(t, torch._ops.OpOverload):
             return 0.0
         if t in (torch.ops.aten.view.default, torch.ops.aten.permute.default, torch.ops.aten.t.default, torch.ops.aten.alias.default,
-                 torch.ops.aten.slice.Tensor, torch.ops.aten.expand.default, torch.ops.aten.unsqueeze.default, torch.ops.aten._unsafe_view.default):
+                 torch.ops.aten.slice.Tensor, torch.ops.aten.expand.default, torch.ops.aten.unsqueeze.default, torch.ops.aten._unsafe_view.default,
+                 torch.ops.aten.reshape.default):
             return 0.0
         nb = _nbytes(val) + sum(_nbytes(a.meta.get("val")) for a in node.all_input_nodes)
         dt = torch.bfloat16

@@ -55,7 +55,7 @@ ZOO = {
 }
 
 
-def plan_one(name, mesh, batch, seq, execute):
+def plan_one(name, mesh, batch, seq, execute, bf16=False):
     import transformers as T
 
     task, make = ZOO[name]
@@ -81,7 +81,12 @@ def plan_one(name, mesh, batch, seq, execute):
 
     n_in = 2 if task == "seq2seq" else 1
     t0 = time.perf_counter()
-    with AutoParallel(model, input_fn, mesh) as autop:
+    policy = None
+    if bf16:
+        from autoparallel_b200.parallel.frontend.mp_cast import MPPolicy
+
+        policy = MPPolicy(torch.bfloat16, torch.float32)
+    with AutoParallel(model, input_fn, mesh, policy) as autop:
         autop.add_parameter_memory_constraint()
         autop.add_input_constraints([(Shard(0),) + (Replicate(),) * (mesh.ndim - 1)] * n_in)
         autop.optimize_placement()
@@ -112,6 +117,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=128)
     ap.add_argument("--execute", action="store_true")
+    ap.add_argument("--bf16", action="store_true", help="bf16 compute with fp32 gradient reduction")
     a = ap.parse_args()
     shape = tuple(int(x) for x in a.mesh.split(","))
     mesh = fake_mesh(shape, ("dp", "tp")[: len(shape)])
@@ -119,7 +125,7 @@ def main():
     failed = []
     for name in names:
         try:
-            secs, cost, coll = plan_one(name, mesh, a.batch, a.seq_len, a.execute)
+            secs, cost, coll = plan_one(name, mesh, a.batch, a.seq_len, a.execute, a.bf16)
             print(f"PASS {name:12s} {secs:6.1f}s  total {cost['total_us']:10.1f} us  collectives {coll}", flush=True)
         except Exception as e:  # keep going: the point is the list of families that plan
             failed.append(name)
