@@ -90,6 +90,10 @@ def _flops(op, args, in_shapes: list[list[int]], out_shapes: list[list[int]]) ->
         sk = in_shapes[2][1]
         causal = 0.5 if args[6] else 1.0
         return 10.0 * b * h * s * sk * d * causal
+    if isinstance(op, torch._ops.HigherOrderOperator):  # flex attention: the block mask's sparsity is not known here
+        b, h, s, d = in_shapes[0]
+        sk = in_shapes[1][2]
+        return (10.0 if "backward" in op.name() else 4.0) * b * h * s * sk * d
     name = str(op)
     if "scaled_dot_product" in name or "_attention" in name:
         q = in_shapes[1] if "backward" in name else in_shapes[0]
@@ -103,7 +107,8 @@ def _flops(op, args, in_shapes: list[list[int]], out_shapes: list[list[int]]) ->
 def strategy_compute_cost(node, spec: OpSpec, limit: Optional[DeviceLimit] = None) -> float:
     """Microseconds for ``node`` when run with ``spec``'s local shapes."""
     op = node.target
-    if op in _ZERO_COST or not isinstance(op, torch._ops.OpOverload):
+    flex = isinstance(op, torch._ops.HigherOrderOperator) and op.name() in ("flex_attention", "flex_attention_backward")
+    if op in _ZERO_COST or not (isinstance(op, torch._ops.OpOverload) or flex):
         return 0.0
     limit = limit or get_device_limit(spec.mesh.device_type)
     outs = spec.output_specs if isinstance(spec.output_specs, (tuple, list)) else [spec.output_specs]

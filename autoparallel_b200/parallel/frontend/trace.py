@@ -150,6 +150,27 @@ def _local_map_capture():
         yield
 
 
+@contextlib.contextmanager
+def _flex_attention_on_fake_cpu():
+    """Planning runs on fake CPU tensors, and flex attention's Python front end refuses inputs on the CPU
+    that require gradients (its eager CPU kernel has no backward).  Nothing is computed while tracing, and
+    the captured higher-order operators are device independent, so the check is lifted for the capture."""
+    try:
+        import torch.nn.attention.flex_attention as fa
+    except ImportError:  # pragma: no cover
+        yield
+        return
+    saved = getattr(fa, "_validate_device", None)
+    if saved is None:
+        yield
+        return
+    fa._validate_device = lambda query, key, value: None
+    try:
+        yield
+    finally:
+        fa._validate_device = saved
+
+
 def _add_unused_state(model: nn.Module, gm: fx.GraphModule) -> None:
     """Dynamo drops parameters ``forward`` never reads; re-attach them so they are sharded,
     initialised and checkpointed like the others (reference: tracing.py:99-137)."""
@@ -182,7 +203,8 @@ def build_joint_graph(
         traced_inputs = normalize_inputs(input_fn())
 
     with contextlib.ExitStack() as stack:
-        with cast_reads(True), _local_map_capture(), torch._dynamo.utils._disable_saved_tensors_hooks_during_tracing():
+        with cast_reads(True), _local_map_capture(), _flex_attention_on_fake_cpu(), \
+                torch._dynamo.utils._disable_saved_tensors_hooks_during_tracing():
             captured = _dynamo_graph_capture_for_export(model)(*traced_inputs.args, **traced_inputs.kwargs)
             _restore_state_dict(model, captured)
             _add_unused_state(model, captured)

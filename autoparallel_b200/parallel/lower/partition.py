@@ -104,8 +104,8 @@ def partition_joint(joint: JointGraph) -> PartitionedGraph:
         if n not in bw_side:
             continue
         for i in n.all_input_nodes:
-            if i in bw_side or i in seen or i in tangents:
-                continue
+            if i in bw_side or i in seen or i in tangents or i.op == "get_attr":
+                continue  # attributes (constants, sub-graphs of higher-order operators) are re-read, not saved
             seen.add(i)
             if i.op == "placeholder":
                 used_primals.append(i)

@@ -177,12 +177,16 @@ class ShardingOptimizer:
 
         if is_local_map_node(node):
             return local_map_options(self.mesh, node, strats)
+        from ..strategies.flex_rules import flex_attention_options, is_flex_attention_node
+
+        if is_flex_attention_node(node):
+            return flex_attention_options(self.mesh, node, strats)
         return opt.options_for_node(self.mesh, node, strats, self.even_only)
 
     def _build_costs(self) -> None:
         for n in self.nodes:
             st = self.strats[n].strategies
-            if n.op == "call_function" and isinstance(n.target, torch._ops.OpOverload):
+            if n.op == "call_function" and isinstance(n.target, (torch._ops.OpOverload, torch._ops.HigherOrderOperator)):
                 self._node_cost[n] = np.array([compute_cost.strategy_compute_cost(n, s) for s in st], dtype=np.float64)
             else:
                 self._node_cost[n] = np.zeros(len(st))
