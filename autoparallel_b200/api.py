@@ -65,6 +65,7 @@ class AutoParallel:
             ``comm.Topology``, or a path to a calibration table (JSON).
         repeated_subgraphs: share ILP variables between structurally identical layers.
         activation_checkpointing: ``"none" | "selective" | "full"``.
+        uneven_sharding: allow shards of unequal size (extents that the mesh dim does not divide).
     """
 
     def __init__(
@@ -82,7 +83,12 @@ class AutoParallel:
         fuse_collectives: Any = None,
         bucket_collectives: bool = False,
         ordered_sharding: bool = True,
+        uneven_sharding: bool = False,
     ):
+        # uneven_sharding=True: a tensor dim may be sharded although the mesh dim does not divide it.  Shards are
+        # ceil-sized chunks (the last non-empty one shorter, later ones empty); every rank lowers the graph with
+        # its own shard shapes and collectives on such dims pad to the chunk size and cut the result.
+        self.uneven_sharding = bool(uneven_sharding)
         # dynamic=True: graphs stay specialised to static shapes (every kernel launch has fixed extents), but the
         # parallel module accepts inputs of other shapes by building - once per shape - a new specialisation
         # that reuses the solved placements instead of solving again (see ``_specialize``).
@@ -143,7 +149,7 @@ class AutoParallel:
             and self.mp_policy.reduce_dtype.itemsize > self.mp_policy.param_dtype.itemsize
         )
         return ShardingOptimizer(joint, self.mesh, force_grad_reduce_in_higher_precision=force_hp,
-                                 repeated_subgraphs=self.repeated_subgraphs)
+                                 repeated_subgraphs=self.repeated_subgraphs, even_only=not self.uneven_sharding)
 
     def _install_cost_models(self) -> None:
         if True:  # (kept as one block: topology first, then the device table)
@@ -420,9 +426,9 @@ def _meta_state(model: nn.Module, lowered: LoweredGraph, mesh):
 
     def make(t: torch.Tensor, placements, requires_grad):
         placements = placements or (Replicate(),) * mesh.ndim
-        from .parallel.strategies.dtensor_adapter import local_shape
+        from .parallel.strategies.dtensor_adapter import my_local_shape
 
-        ls = local_shape(t.shape, mesh.shape, placements)
+        ls = my_local_shape(t.shape, mesh, placements)
         local = torch.empty(ls, dtype=t.dtype, device="meta")
         return DTensor.from_local(local, mesh, placements, run_check=False, shape=t.shape, stride=_contig_stride(t.shape))
 

@@ -24,7 +24,7 @@ import torch.fx as fx
 from ...runtime import comm_ops
 from ..frontend.graph_canon import all_input_nodes
 from ..frontend.trace import JointGraph
-from ..strategies.dtensor_adapter import DTensorSpec, OpSpec, Partial, Replicate, Shard, local_shape
+from ..strategies.dtensor_adapter import DTensorSpec, OpSpec, Partial, Replicate, Shard, is_even, local_shape_at, my_local_shape, shard_extent
 
 logger = logging.getLogger(__name__)
 aten = torch.ops.aten
@@ -123,6 +123,90 @@ class _Redistributor:
         self.counts[kind] += 1
         return n
 
+    def _local(self, target, args: tuple, like: fx.Node, shape) -> fx.Node:
+        n = self.g.call_function(target, args)
+        n.meta["val"] = like.meta["val"].new_empty(shape)
+        for k in ("stack_trace", "nn_module_stack", "seq_nr", "autograd_backward", "apb200_phase"):
+            if k in like.meta:
+                n.meta[k] = like.meta[k]
+        return n
+
+    def _uneven_steps(self, cur: fx.Node, like: fx.Node, steps, full: list[int], shape: list[int], placements) -> fx.Node:
+        """Collectives between shards of unequal size.  Ceil-sized chunks put all full chunks first, so a
+        gather of shards padded to the chunk size has the valid rows in front: pad, gather, cut the tail.
+        A scatter pads the whole extent to ``parts x chunk`` and every rank cuts its chunk down to what it
+        owns (possibly nothing).  Reference: autoparallel/apply_sharding.py:372-386 (pad / slice nodes)."""
+        coord = self.mesh.get_coordinate() or [0] * self.mesh.ndim
+        mshape = tuple(self.mesh.shape)
+        pl = list(placements)
+        nd = len(shape)
+
+        def seen_extent(m: int, d: int) -> int:
+            others = [Replicate() if i == m else p for i, p in enumerate(pl)]
+            return local_shape_at(full, mshape, others, coord)[d]
+
+        def pad_to(node, d, size):
+            if shape[d] == size:
+                return node
+            grow = size - shape[d]
+            shape[d] = size
+            return self._local(aten.constant_pad_nd.default, (node, _pad_spec(nd, d, grow), 0.0), like, shape)
+
+        def cut(node, d, start, end):
+            if start == 0 and end == shape[d]:
+                return node
+            shape[d] = max(0, end - start)
+            return self._local(aten.slice.Tensor, (node, d, start, end), like, shape)
+
+        for st in steps:
+            gname, n = self.groups[st.mesh_dim]
+            m, me = st.mesh_dim, coord[st.mesh_dim]
+            if st.kind == "all_reduce":
+                cur = self._emit("all_reduce", (cur, gname, n), like, shape)
+                pl[m] = Replicate()
+            elif st.kind == "all_gather":
+                d = st.dim
+                extent = seen_extent(m, d)
+                cur = pad_to(cur, d, -(-extent // n))
+                shape[d] *= n
+                cur = self._emit("all_gather", (cur, d, gname, n), like, shape)
+                cur = cut(cur, d, 0, extent)
+                pl[m] = Replicate()
+            elif st.kind == "reduce_scatter":
+                d = st.dim
+                extent = shape[d]
+                chunk = -(-extent // n)
+                cur = pad_to(cur, d, chunk * n)
+                shape[d] = chunk
+                cur = self._emit("reduce_scatter", (cur, d, gname, n), like, shape)
+                cur = cut(cur, d, 0, shard_extent(extent, n, me))
+                pl[m] = Shard(d)
+            elif st.kind == "all_to_all":
+                new, old = st.dim, st.dim2
+                old_extent, new_extent = seen_extent(m, old), shape[new]
+                chunk = -(-new_extent // n)
+                cur = pad_to(cur, old, -(-old_extent // n))
+                cur = pad_to(cur, new, chunk * n)
+                shape[old] *= n
+                shape[new] = chunk
+                cur = self._emit("all_to_all", (cur, new, old, gname, n), like, shape)
+                cur = cut(cur, old, 0, old_extent)
+                cur = cut(cur, new, 0, shard_extent(new_extent, n, me))
+                pl[m] = Shard(new)
+            elif st.kind == "local_chunk":
+                d = st.dim
+                extent = shape[d]
+                if extent % n == 0:
+                    shape[d] //= n
+                    cur = self._emit("local_chunk", (cur, d, gname, n), like, shape)
+                else:
+                    chunk = -(-extent // n)
+                    start = min(me * chunk, extent)
+                    cur = cut(cur, d, start, min(start + chunk, extent))
+                    self.counts["local_chunk"] += 1
+                pl[m] = Shard(d)
+        return cur
+
     def __call__(self, x: fx.Node, key_node: fx.Node, src: DTensorSpec, dst: DTensorSpec, order=None) -> fx.Node:
         """Emit (or reuse) the collectives taking local tensor ``x`` from ``src`` to ``dst``; ``order`` is
         the nesting order of mesh dims for a tensor dim sharded over several of them."""
@@ -137,6 +221,14 @@ class _Redistributor:
         cur = x
         shape = list(x.meta["val"].shape)
         steps = plan_redistribution(src.placements, dst.placements, self.mesh.shape, order=order)
+        full = list(src.tensor_meta.shape) if src.tensor_meta is not None else None
+        uneven = full is not None and not (
+            is_even(full, self.mesh.shape, src.placements) and is_even(full, self.mesh.shape, dst.placements)
+        )
+        if uneven:
+            cur = self._uneven_steps(cur, x, steps, full, shape, src.placements)
+            self.cache[key] = cur
+            return cur
         if self.fuse_flat and self._flat() is not None:
             steps = fuse_over_flat_mesh(steps, self.mesh.ndim, order)
         for st in steps:
@@ -158,6 +250,11 @@ class _Redistributor:
                 cur = self._emit("local_chunk", (cur, st.dim, gname, n), x, shape)
         self.cache[key] = cur
         return cur
+
+
+def _pad_spec(ndim: int, dim: int, amount: int) -> list[int]:
+    """``constant_pad_nd`` argument that appends ``amount`` entries at the end of ``dim``."""
+    return [0, 0] * (ndim - 1 - dim) + [0, amount]
 
 
 def _inline_region(g: fx.Graph, body: fx.GraphModule, args) -> fx.Node:
@@ -186,8 +283,8 @@ def _make_tuple(*xs):
 def _local_val(val, spec: Optional[DTensorSpec], mesh):
     if not isinstance(val, torch.Tensor) or spec is None:
         return val
-    ls = local_shape(val.shape, mesh.shape, spec.placements)
-    return val.new_empty(ls)
+    # this rank's own shard: smaller than rank 0's (or empty) where an extent does not divide
+    return val.new_empty(my_local_shape(val.shape, mesh, spec.placements))
 
 
 def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mesh, ordered_sharding: bool = True) -> LoweredGraph:

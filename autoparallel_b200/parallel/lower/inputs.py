@@ -15,7 +15,7 @@ from torch.distributed.tensor import DTensor
 from torch.utils._pytree import tree_flatten, tree_unflatten
 
 from ..frontend.trace import ForwardInputs
-from ..strategies.dtensor_adapter import local_shape
+from ..strategies.dtensor_adapter import my_local_shape
 
 
 def expected_local_inputs(traced: ForwardInputs, placements: Sequence[Optional[tuple]], mesh) -> list:
@@ -26,7 +26,7 @@ def expected_local_inputs(traced: ForwardInputs, placements: Sequence[Optional[t
         if isinstance(v, torch.Tensor):
             shape = list(v.shape)
             if pl is not None:
-                shape = local_shape(shape, mesh.shape, pl)
+                shape = my_local_shape(shape, mesh, pl)
             out.append(("tensor", tuple(shape), v.dtype))
         else:
             out.append(("value", v))

@@ -46,6 +46,41 @@ def local_shape(shape: Sequence[int], mesh_shape: Sequence[int], placements: Seq
     return out
 
 
+def shard_extent(extent: int, parts: int, index: int) -> int:
+    """Rows that part ``index`` of ``parts`` holds when ``extent`` rows are cut into ceil-sized chunks
+    (``torch.chunk`` / DTensor ``Shard`` semantics: full chunks first, then a shorter one, then empty ones)."""
+    c = -(-extent // parts)
+    return max(0, min(c, extent - index * c))
+
+
+def local_shape_at(shape: Sequence[int], mesh_shape: Sequence[int], placements: Sequence[Placement], coord: Sequence[int]) -> list[int]:
+    """Shape of the shard held by the rank at mesh coordinate ``coord`` (differs between ranks when a
+    sharded extent does not divide; equals ``local_shape`` when everything divides)."""
+    out = list(shape)
+    for n, p, c in zip(mesh_shape, placements, coord):
+        if isinstance(p, Shard) or type(p).__name__ == "_StridedShard":
+            out[p.dim] = shard_extent(out[p.dim], n, c)
+    return out
+
+
+def my_local_shape(shape: Sequence[int], mesh, placements: Sequence[Placement]) -> list[int]:
+    """Shape of the calling rank's own shard (rank 0's when the caller is not part of ``mesh``)."""
+    coord = mesh.get_coordinate()
+    if coord is None:
+        coord = [0] * mesh.ndim
+    return local_shape_at(shape, tuple(mesh.shape), placements, coord)
+
+
+def is_even(shape: Sequence[int], mesh_shape: Sequence[int], placements: Sequence[Placement]) -> bool:
+    out = list(shape)
+    for n, p in zip(mesh_shape, placements):
+        if isinstance(p, Shard) or type(p).__name__ == "_StridedShard":
+            if out[p.dim] % n:
+                return False
+            out[p.dim] //= n
+    return True
+
+
 def is_valid_spec(spec: Optional[DTensorSpec], mesh, even_only: bool) -> bool:
     if spec is None or spec.tensor_meta is None:
         return True
@@ -58,6 +93,18 @@ def is_valid_spec(spec: Optional[DTensorSpec], mesh, even_only: bool) -> bool:
             if even_only and shape[d] % n != 0:
                 return False
             shape[d] = -(-shape[d] // n)
+    if not even_only:
+        # an uneven tensor dim may be split by one mesh dim only: the shard sizes of a second split would
+        # depend on the first coordinate, which the lowered collectives do not handle
+        splits: dict[int, int] = {}
+        nested = set()
+        for n, p in zip(mesh.shape, spec.placements):
+            if isinstance(p, Shard):
+                if p.dim in splits:
+                    nested.add(p.dim)
+                splits[p.dim] = splits.get(p.dim, 1) * n
+        if any(spec.tensor_meta.shape[d] % splits[d] for d in nested):
+            return False
     return True
 
 

@@ -131,12 +131,42 @@ def _attach_meta(strat: OpStrategy, out_val, in_vals, mesh) -> None:
         s.redistribute_cost = None
 
 
-def _filter(strat: OpStrategy, mesh, even_only: bool) -> OpStrategy:
+def _view_keeps_counts(s, mesh) -> bool:
+    """A reshape is local only if every rank's input shard has as many elements as its output shard."""
+    import itertools as _it
+
+    from .dtensor_adapter import is_even, local_shape_at
+
+    i, o = s.input_specs[0], s.output_specs
+    if i is None or o is None or isinstance(o, (tuple, list)) or i.tensor_meta is None or o.tensor_meta is None:
+        return True
+    if is_even(i.tensor_meta.shape, mesh.shape, i.placements) and is_even(o.tensor_meta.shape, mesh.shape, o.placements):
+        return True
+    for coord in _it.product(*(range(n) for n in mesh.shape)):
+        a = local_shape_at(i.tensor_meta.shape, mesh.shape, i.placements, coord)
+        b = local_shape_at(o.tensor_meta.shape, mesh.shape, o.placements, coord)
+        na = nb = 1
+        for x in a:
+            na *= x
+        for x in b:
+            nb *= x
+        if na != nb:
+            return False
+    return True
+
+
+_RESHAPES = (torch.ops.aten.view.default, torch.ops.aten._unsafe_view.default, torch.ops.aten.reshape.default)
+
+
+def _filter(strat: OpStrategy, mesh, even_only: bool, op=None) -> OpStrategy:
     kept, seen = [], set()
     for s in strat.strategies:
         outs = s.output_specs if isinstance(s.output_specs, (tuple, list)) else [s.output_specs]
         if not all(is_valid_spec(x, mesh, even_only) for x in list(outs) + list(s.input_specs)):
             continue
+        if not even_only:
+            if op in _RESHAPES and s.input_specs and not _view_keeps_counts(s, mesh):
+                continue
         if not all(_plain_placements(x) for x in list(outs) + list(s.input_specs)):
             continue  # masked / avg / max partials need op-specific local math; not lowered
         key = (_fp_spec(s.output_specs), _fp_spec(s.input_specs))
@@ -198,7 +228,7 @@ def options_for_node(mesh, node: fx.Node, strats: dict[fx.Node, Any], even_only:
         flat_in_vals = [v for v in in_vals if isinstance(v, torch.Tensor)]
         _attach_meta(strat, out_val, flat_in_vals, mesh)
     if op is not operator.getitem:
-        strat = _filter(strat, mesh, even_only)
+        strat = _filter(strat, mesh, even_only, op)
     if len(strat.strategies) == 0:
         raise RuntimeError(f"no valid sharding strategy for node {node.name} ({op})")
     if key is not None:
