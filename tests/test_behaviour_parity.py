@@ -1,0 +1,216 @@
+"""Behaviours that the reference pins with small dedicated tests, checked here against this package on fake
+ranks: parameters that do not divide, a parameter smaller than the mesh, the parameter / gradient pairing when
+a gradient lacks an option, user methods on the parallel module, dict inputs and input validation, in-graph
+constructors and fresh mutations, log rendering, alias-preserving fake conversion, node constraints against
+the memory budget with removal and re-solve.
+(Reference: tests/test_optimize_placement.py:519-700, tests/test_paired_output_constraint.py,
+tests/test_api.py, tests/test_input_validation.py, tests/test_propagation_rules.py, tests/test_log_formatting.py,
+tests/test_tracing.py.)"""
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.distributed.tensor.placement_types import Replicate, Shard
+
+from autoparallel_b200 import AutoParallel, ForwardInputs
+
+
+def test_parameter_that_does_not_divide_keeps_the_memory_constraint_feasible(mesh_2d):
+    class M(nn.Module):
+        def __init__(s):
+            super().__init__()
+            s.l1 = nn.Linear(64, 21, bias=True)
+            s.l2 = nn.Linear(21, 64, bias=True)
+        def forward(s, x):
+            return s.l2(F.relu(s.l1(x)))
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.rand(16, 64), mesh_2d) as ap:
+        ap.add_input_constraints([(Shard(0), Replicate())])
+        ap.add_output_constraints([(Shard(0), Replicate())])
+        ap.add_parameter_memory_constraint(low=None, high=None)
+        sol = ap.optimize_placement()
+        assert all(p in sol for p in ap.joint.param_nodes.values())
+
+
+def test_parameter_smaller_than_the_mesh(mesh_1d):
+    class M(nn.Module):
+        def __init__(s):
+            super().__init__()
+            s.l1 = nn.Linear(64, 4, bias=True)
+            s.scale = nn.Parameter(torch.ones(1))
+        def forward(s, x):
+            return s.l1(x) * s.scale
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.rand(16, 64), mesh_1d) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.add_output_constraints([(Shard(0),)])
+        ap.add_parameter_memory_constraint(low=None, high=None)
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+
+
+def test_parameter_cannot_take_a_placement_its_gradient_lacks(mesh_2d):
+    with torch.device("meta"):
+        m = nn.Linear(64, 128, bias=False)
+    ap = AutoParallel(m, lambda: torch.rand(32, 64), mesh_2d)
+    ap.__enter__()
+    try:
+        opt = ap.sharding_optimizer
+        p = next(iter(ap.joint.param_nodes.values()))
+        g = next(iter(ap.joint.param_grads.values()))
+        removed = (Shard(0), Shard(0))
+        opt.strats[g].strategies = [s for s in opt.strats[g].strategies if tuple(s.output_spec.placements) != removed]
+        opt._node_cost.clear()
+        opt._edge_cost.clear()
+        opt._build_costs()
+        ap.add_input_constraints([(Shard(0), Replicate())])
+        ap.add_output_constraints([(Shard(0), Replicate())])
+        ap.add_parameter_memory_constraint(low=None, high=None)
+        sol = ap.optimize_placement()
+        chosen = tuple(sol[p].output_spec.placements)
+        assert chosen != removed, chosen
+        assert chosen in {tuple(s.output_spec.placements) for s in opt.strats[g].strategies}
+    finally:
+        ap.__exit__(None, None, None)
+
+
+def test_user_methods_properties_and_buffer_updates_on_the_parallel_module(mesh_1d):
+    class Base(nn.Module):
+        def helper(s):
+            return "base"
+    class M(Base):
+        tag = "x"
+        def __init__(s):
+            super().__init__()
+            s.l = nn.Linear(16, 16)
+            s.register_buffer("ema", torch.zeros(16))
+            s.decay = 0.9
+        def forward(s, x):
+            return s.l(x) + s.ema
+        @torch.no_grad()
+        def update_ema(s):
+            s.ema.mul_(s.decay).add_(1.0)
+        @classmethod
+        def make(cls):
+            return cls.tag
+        @property
+        def width(s):
+            return s.l.in_features
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.rand(8, 16), mesh_1d) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    pm.to_empty(device="cpu")
+    assert isinstance(pm, M) and isinstance(pm, Base) and pm.helper() == "base" and pm.make() == "x" and pm.width == 16 and pm.decay == 0.9
+    with torch.no_grad():
+        pm.ema.zero_()
+    pm.update_ema()
+    assert torch.allclose(pm.ema.to_local(), torch.ones_like(pm.ema.to_local()))
+
+
+def test_dict_inputs_outputs_and_shape_validation(mesh_1d):
+    class M(nn.Module):
+        def __init__(s):
+            super().__init__()
+            s.l = nn.Linear(16, 16)
+        def forward(s, batch):
+            return {"y": s.l(batch["x"]) + batch["bias"], "aux": batch["x"].mean()}
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: ForwardInputs(({"x": torch.rand(16, 16), "bias": torch.rand(16)},), {}), mesh_1d) as ap:
+        ap.add_input_constraints([(Shard(0),), (Replicate(),)])
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    pm.to_empty(device="cpu")
+    out = pm({"x": torch.rand(2, 16), "bias": torch.rand(16)})
+    assert set(out) == {"y", "aux"} and out["y"].shape[1] == 16
+    try:
+        pm({"x": torch.rand(3, 16), "bias": torch.rand(16)})
+        raise AssertionError("wrong shape accepted")
+    except ValueError:
+        pass
+
+
+def test_in_graph_constructors_index_put_and_fresh_mutation(mesh_1d):
+    class M(nn.Module):
+        def __init__(s):
+            super().__init__()
+            s.l = nn.Linear(16, 16)
+        def forward(s, x):
+            idx = torch.arange(x.shape[0], device=x.device)
+            buf = torch.zeros(x.shape[0], 16, device=x.device)
+            buf = buf.index_put((idx,), s.l(x))
+            buf[0] = 1.0
+            return buf * (idx.unsqueeze(1) + 1)
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.rand(16, 16), mesh_1d) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    pm.to_empty(device="cpu")
+    pm(torch.rand(2, 16)).sum().backward()
+
+
+def test_log_plain_verbose_and_colored(mesh_1d):
+    with torch.device("meta"):
+        m = nn.Linear(16, 16)
+    with AutoParallel(m, lambda: torch.rand(16, 16), mesh_1d) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.optimize_placement()
+        opt = ap.sharding_optimizer
+        a = opt.get_log(verbose=False)
+        b = opt.get_log(verbose=True)
+        c = opt.get_log(colored=True)
+        assert "placement" in a.lower() or "Shard" in a or "S(0)" in a, a[:200]
+        assert len(b) >= len(a) and "\x1b[" in c
+
+
+def test_fake_conversion_keeps_aliases():
+    from autoparallel_b200.parallel.frontend.trace import move_to_fake
+    from torch._subclasses import FakeTensorMode
+    class M(nn.Module):
+        def __init__(s):
+            super().__init__()
+            s.a = nn.Linear(4, 4)
+            s.b = nn.Linear(4, 4)
+            s.b.weight = s.a.weight
+            s.register_buffer("u", torch.zeros(4))
+            s.register_buffer("v", s.u)
+            s.c = s.a
+    with torch.device("meta"):
+        m = M()
+    f = move_to_fake(m, FakeTensorMode(), "cpu")
+    assert f.a.weight is f.b.weight and f.u is f.v and f.c is f.a and f.a.bias is not f.b.bias
+
+
+def test_node_constraint_against_memory_budget_then_removal_and_resolve(mesh_1d):
+    class M(nn.Module):
+        def __init__(s):
+            super().__init__()
+            s.l1 = nn.Linear(64, 64)
+            s.l2 = nn.Linear(64, 64)
+        def forward(s, x):
+            return s.l2(F.relu(s.l1(x)))
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.rand(16, 64), mesh_1d) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        name = ap.add_parameter_memory_constraint(low=None, high=None)
+        opt = ap.sharding_optimizer
+        w1 = ap.joint.param_nodes["l1.weight"]
+        c = opt.add_node_constraint(w1, (Replicate(),))
+        sol = ap.optimize_placement()
+        assert tuple(sol[w1].output_spec.placements) == (Replicate(),)
+        assert any(isinstance(p, Shard) for p in sol[ap.joint.param_nodes["l2.weight"]].output_spec.placements)
+        opt.remove_constraints([c])
+        sol = opt.resolve() if hasattr(opt, "resolve") else opt.get_solution()
+        assert any(isinstance(p, Shard) for p in sol[w1].output_spec.placements)
+        opt.remove_constraints([name])
+        sol = opt.resolve() if hasattr(opt, "resolve") else opt.get_solution()
+        assert tuple(sol[w1].output_spec.placements) == (Replicate(),)
+
