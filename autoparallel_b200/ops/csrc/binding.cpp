@@ -48,6 +48,8 @@ int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, int M, int N
                    int n, unsigned epoch, int rows_per_shard, const void* shard_src, void* gbuf, long long shard_bytes,
                    uint32_t* landed, unsigned landed_target, int rows_per_rank, float scale, long long stage_capacity,
                    const unsigned* targets, int comm_ctas, uint32_t* status, int num_sms, cudaStream_t stream);
+int apb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Sk, int H, int Hkv,
+                      int D, int causal, float scale, uint32_t* status, cudaStream_t stream);
 int apb_adamw(const void* tensors_dev, const void* chunks_dev, int num_chunks, float lr, float beta1, float beta2, float eps,
               float wd, float bc1, float bc2, float grad_scale, cudaStream_t st);
 }
@@ -100,6 +102,28 @@ void gemm_grouped(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool 
   check(apb_gemm_grouped_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), G, M, N, K, a_mn_major, b_mn_major, out_fp32,
                               reinterpret_cast<uint32_t*>(status.data_ptr()), num_sms(), stream()),
         "apb_gemm_grouped_bf16");
+}
+
+// q [B,S,H,D], k / v [B,Sk,Hkv,D] -> out [B,S,H,D] bf16, lse [B,H,S] fp32.  Returns false (nothing launched) for
+// shapes the kernel does not cover.
+bool attention_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& out, at::Tensor& lse, bool causal,
+                   double scale, at::Tensor& status) {
+  c10::cuda::CUDAGuard g(q.device());
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16 &&
+                  out.scalar_type() == at::kBFloat16 && lse.scalar_type() == at::kFloat,
+              "attention_fwd: bf16 q / k / v / out and fp32 lse required");
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4 && q.is_contiguous() && k.is_contiguous() && v.is_contiguous() &&
+                  out.is_contiguous() && lse.is_contiguous(),
+              "attention_fwd: contiguous [B, S, H, D] tensors required");
+  TORCH_CHECK(k.sizes() == v.sizes() && k.size(0) == q.size(0) && k.size(3) == q.size(3) && out.sizes() == q.sizes() &&
+                  lse.numel() == q.size(0) * q.size(1) * q.size(2),
+              "attention_fwd: shape mismatch");
+  const int err = apb_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), q.size(0),
+                                    q.size(1), k.size(1), q.size(2), k.size(2), q.size(3), causal, (float)scale,
+                                    reinterpret_cast<uint32_t*>(status.data_ptr()), stream());
+  if (err == 3) return false;
+  check(err, "apb_attention_fwd");
+  return true;
 }
 
 void rms_norm_fwd(const at::Tensor& x, const at::Tensor& w, at::Tensor& y, at::Tensor& rstd, double eps) {
@@ -241,6 +265,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_set_reserved_sms", [](int64_t n) { apb_gemm_set_reserved_sms((int)n); });
   m.def("gemm_get_reserved_sms", []() { return (int64_t)apb_gemm_get_reserved_sms(); });
   m.def("gemm_get_pair_mode", []() { return apb_gemm_get_pair_mode() != 0; });
+  m.def("attention_fwd", &attention_fwd);
   m.def("rms_norm_fwd", &rms_norm_fwd);
   m.def("rms_norm_bwd", &rms_norm_bwd);
   m.def("cast", &cast);

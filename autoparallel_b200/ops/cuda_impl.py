@@ -31,6 +31,10 @@ STATUS_NAMES = {
     4: "MMA issuer timed out waiting for a free accumulator",
     5: "timed out waiting for a peer flag",
     6: "bad argument",
+    7: "attention: MMA issuer timed out waiting for a K / V tile",
+    8: "attention: loader timed out waiting for a free K / V slot",
+    9: "attention: softmax timed out waiting for a score or product accumulator",
+    10: "attention: MMA issuer timed out waiting for a probability tile",
 }
 
 
@@ -251,7 +255,10 @@ def _embedding_bwd(dy, ids, num_rows):
 
 # ----------------------------------------------------------------------------------- attention (library)
 ATTENTION_BACKEND = os.environ.get("APB200_ATTENTION", "cudnn")  # "cudnn" | "flash"
-_cudnn_lse_ndim = [3]
+# forward kernel: "library" (the backend above) or "own" (ops/csrc/attention_fwd.cu where its shapes apply: bf16,
+# head dim 128, query length a multiple of 256, key length a multiple of 128; other shapes use the library)
+ATTENTION_FORWARD = os.environ.get("APB200_ATTENTION_FWD", "library")
+_cudnn_lse_ndim = [0]  # rank of the log-sum-exp tensor the cuDNN calls exchange (0 = not seen yet)
 
 
 def _expand_kv(t, rep):
@@ -261,7 +268,24 @@ def _expand_kv(t, rep):
     return t.unsqueeze(3).expand(b, s, h, rep, d).reshape(b, s, h * rep, d)
 
 
+def attention_forward_own(q, k, v, causal, scale):
+    """(out [B,S,H,D] bf16, lse [B,H,S] fp32) from this package's tcgen05 kernel, or None if it does not cover the shape."""
+    if q.dtype != torch.bfloat16 or q.shape[-1] != 128:
+        return None
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    out = torch.empty_like(q)
+    lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
+    if not _C.attention_fwd(q, k, v, out, lse, bool(causal), float(scale), status_buffer(q.device)):
+        return None
+    _count()
+    return out, lse
+
+
 def _attention(q, k, v, causal, scale):
+    if ATTENTION_FORWARD == "own":
+        res = attention_forward_own(q, k, v, causal, scale)
+        if res is not None:
+            return res
     rep = q.shape[2] // k.shape[2]
     if ATTENTION_BACKEND == "cudnn":
         rep = 1  # cuDNN takes grouped-query heads natively
@@ -288,6 +312,9 @@ def _attention_bwd(dout, q, k, v, out, lse, causal, scale):
     vt = _expand_kv(v, rep).transpose(1, 2)
     seed = torch.zeros((), dtype=torch.long, device=q.device)
     if ATTENTION_BACKEND == "cudnn":
+        if _cudnn_lse_ndim[0] == 0:  # forward ran elsewhere: ask a tiny cuDNN forward which rank it uses
+            tq = torch.zeros(1, 1, 128, d, dtype=q.dtype, device=q.device)
+            _cudnn_lse_ndim[0] = torch.ops.aten._scaled_dot_product_cudnn_attention(tq, tq, tq, None, True, 0.0, causal, False, scale=scale)[1].ndim
         lse_c = lse.unsqueeze(-1) if _cudnn_lse_ndim[0] == 4 else lse
         dq, dk, dv = torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
             dout.transpose(1, 2), qt, kt, vt, out.transpose(1, 2), lse_c, seed, seed, None, None, None, s, sk, 0.0, causal,

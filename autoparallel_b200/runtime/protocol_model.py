@@ -246,3 +246,192 @@ def run_dynamic_gemm(counters: TileCounters, num_tiles: int, num_pairs: int, rea
     for t in pairs:
         t.join()
     return seen
+
+
+# ------------------------------------------------------------------------------------- attention pipeline
+class PhaseBarrier:
+    """An mbarrier: ``count`` arrivals complete the current phase; ``wait(parity)`` returns once the phase of
+    that parity has completed, i.e. as soon as the barrier's current phase has the other parity."""
+
+    def __init__(self, count: int, cv: threading.Condition, limit_s: float):
+        self.count, self.pending, self.phase, self.cv, self.limit_s = count, count, 0, cv, limit_s
+
+    def arrive(self, n: int = 1) -> None:
+        with self.cv:
+            self.pending -= n
+            assert self.pending >= 0, "more arrivals than the barrier expects in one phase"
+            if self.pending == 0:
+                self.pending = self.count
+                self.phase += 1
+                self.cv.notify_all()
+
+    def wait(self, parity: int) -> bool:
+        with self.cv:
+            return self.cv.wait_for(lambda: (self.phase & 1) != parity, self.limit_s)
+
+
+def run_attention_pipeline(q: np.ndarray, k: np.ndarray, v: np.ndarray, causal: bool, scale: float,
+                           jitter: float = 0.0, seed: int = 0, ring: int = 3, tile: int = 128):
+    """Host model of one CTA of the attention forward kernel (ops/csrc/attention_fwd.cu): a loader, the MMA
+    issuer and one softmax thread per query tile exchange the same barriers, ring slots and accumulators in
+    the same order, with tensor-core work completing asynchronously.  ``q`` is [2 * tile, d] (the CTA's two
+    query tiles, assumed to be the LAST rows of the sequence when ``causal``), ``k`` / ``v`` are [Sk, d].
+    Returns (out, lse, errors)."""
+    rng = random.Random(seed)
+    cv = threading.Condition()
+    lim = 5.0
+    nq = 2
+    sk = k.shape[0]
+    first_row = sk - nq * tile if causal else 0  # absolute position of the CTA's first query row
+    qi = first_row // (nq * tile)
+    n_it = [(nq * qi + 1 + t) if causal else sk // tile for t in range(nq)]
+    n_max = n_it[-1]
+    kv_full = [PhaseBarrier(1, cv, lim) for _ in range(ring)]
+    kv_empty = [PhaseBarrier(1, cv, lim) for _ in range(ring)]
+    s_full = [PhaseBarrier(1, cv, lim) for _ in range(nq)]
+    p_full = [PhaseBarrier(1, cv, lim) for _ in range(nq)]  # (128 thread arrivals in the kernel; one thread here)
+    pv_full = [PhaseBarrier(1, cv, lim) for _ in range(nq)]
+    slots: list = [None] * ring
+    S: list = [None] * nq
+    P: list = [None] * nq
+    PV: list = [None] * nq
+    errors: list[str] = []
+    out = np.zeros((nq * tile, q.shape[1]), dtype=np.float64)
+    lse = np.zeros(nq * tile, dtype=np.float64)
+    async_work: list[threading.Thread] = []
+
+    def pause():
+        if jitter:
+            time.sleep(rng.random() * jitter)
+
+    def tensor_core(fn, *bars):
+        """MMAs complete some time after they are issued; the commit barriers fire afterwards."""
+        def work():
+            pause()
+            fn()
+            for b in bars:
+                b.arrive()
+        th = threading.Thread(target=work)
+        async_work.append(th)
+        th.start()
+        return th
+
+    def loader():
+        for i in range(2 * n_max):
+            s = i % ring
+            if not kv_empty[s].wait(((i // ring) & 1) ^ 1):
+                errors.append(f"loader: slot {s} never freed (item {i})")
+                return
+            pause()
+            j = i >> 1
+            src = v if (i & 1) else k
+            slots[s] = ("V" if (i & 1) else "K", j, src[j * tile:(j + 1) * tile].copy())
+            kv_full[s].arrive()
+
+    def mma():
+        pending: list[threading.Thread] = []
+
+        def wait_kv(i):
+            if not kv_full[i % ring].wait((i // ring) & 1):
+                errors.append(f"mma: item {i} never arrived")
+                return False
+            return True
+
+        def issue(fn, *bars):
+            # MMAs of one thread complete in order: each waits for the one before it
+            prev = pending[-1] if pending else None
+
+            def chained():
+                if prev is not None:
+                    prev.join()
+                fn()
+            pending.append(tensor_core(chained, *bars))
+
+        def qk(t, slot, j):
+            def fn():
+                kind, jj, data = slots[slot]
+                if (kind, jj) != ("K", j):
+                    errors.append(f"QK tile {t} iteration {j} read {kind}{jj}")
+                S[t] = q[t * tile:(t + 1) * tile] @ data.T
+            issue(fn, s_full[t])
+
+        def pv(t, slot, j):
+            def fn():
+                kind, jj, data = slots[slot]
+                if (kind, jj) != ("V", j):
+                    errors.append(f"PV tile {t} iteration {j} read {kind}{jj}")
+                PV[t] = P[t] @ data
+            issue(fn, pv_full[t])
+
+        if not wait_kv(0):
+            return
+        for t in range(nq):
+            qk(t, 0, 0)
+        issue(lambda: None, kv_empty[0])
+        for j in range(n_max):
+            iv, ik = 2 * j + 1, 2 * j + 2
+            more = j + 1 < n_max
+            if not wait_kv(iv) or (more and not wait_kv(ik)):
+                return
+            for t in range(nq):
+                if j >= n_it[t]:
+                    continue
+                if not p_full[t].wait(j & 1):
+                    errors.append(f"mma: P of tile {t} iteration {j} never arrived")
+                    return
+                pv(t, iv % ring, j)
+                if j + 1 < n_it[t]:
+                    qk(t, ik % ring, j + 1)
+            issue(lambda: None, kv_empty[iv % ring])
+            if more:
+                issue(lambda: None, kv_empty[ik % ring])
+
+    def softmax(t):
+        o = np.zeros((tile, q.shape[1]))
+        m_run = np.full(tile, -np.inf)
+        l_run = np.zeros(tile)
+        sl2 = scale * 1.4426950408889634
+        rows = np.arange(tile)[:, None]
+        cols = np.arange(tile)[None, :]
+        for j in range(n_it[t]):
+            if not s_full[t].wait(j & 1):
+                errors.append(f"softmax {t}: S of iteration {j} never arrived")
+                return
+            pause()
+            s = S[t].copy()
+            mask = (cols <= rows) if (causal and j == n_it[t] - 1) else np.ones((tile, tile), bool)
+            mx = np.where(mask, s, -np.inf).max(1)
+            m_new = np.maximum(m_run, mx * sl2)
+            alpha = np.exp2(m_run - m_new)
+            if j > 0:
+                if not pv_full[t].wait((j - 1) & 1):
+                    errors.append(f"softmax {t}: PV of iteration {j - 1} never arrived")
+                    return
+                o = (o + PV[t]) * alpha[:, None]
+            l_run = l_run * alpha
+            m_run = m_new
+            e = np.where(mask, np.exp2(s * sl2 - m_new[:, None]), 0.0)
+            l_run = l_run + e.sum(1)
+            pause()
+            P[t] = e
+            p_full[t].arrive()
+        if not pv_full[t].wait((n_it[t] - 1) & 1):
+            errors.append(f"softmax {t}: last PV never arrived")
+            return
+        out[t * tile:(t + 1) * tile] = (o + PV[t]) / l_run[:, None]
+        lse[t * tile:(t + 1) * tile] = (m_run + np.log2(l_run)) * 0.6931471805599453
+
+    ths = [threading.Thread(target=loader), threading.Thread(target=mma)] + [threading.Thread(target=softmax, args=(t,)) for t in range(nq)]
+    for th in ths:
+        th.start()
+    for th in ths:
+        th.join()
+    for th in async_work:
+        th.join()
+    return out, lse, errors
+
+
+def swizzle128_offset(row: int, chunk16: int) -> int:
+    """Byte offset of 16-byte unit ``chunk16`` (0..7) of ``row`` inside a 128-byte-swizzled [rows x 128 B] tile:
+    the unit index is XORed with the row index modulo 8 (what TMA writes and the MMA descriptors expect)."""
+    return row * 128 + ((chunk16 ^ (row & 7)) << 4)

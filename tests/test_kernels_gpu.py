@@ -214,6 +214,29 @@ def test_attention(K, causal):
     _close(dv, rdv, 5e-2, 5e-2)
 
 
+@pytest.mark.skipif(
+    __import__("os").environ.get("APB200_TEST_OWN_ATTENTION") != "1",
+    reason="own attention forward: opt-in (APB200_TEST_OWN_ATTENTION=1) until it has been validated on hardware",
+)
+@pytest.mark.parametrize("causal,S,Sk,H,Hkv", [(True, 256, 256, 2, 1), (True, 1024, 1024, 4, 2), (False, 256, 384, 2, 2)])
+def test_own_attention_forward(K, causal, S, Sk, H, Hkv):
+    lib, impl = K
+    torch.manual_seed(0)
+    q = torch.randn(2, S, H, 128, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(2, Sk, Hkv, 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(2, Sk, Hkv, 128, device="cuda", dtype=torch.bfloat16)
+    scale = 128 ** -0.5
+    res = impl.attention_forward_own(q, k, v, causal, scale)
+    assert res is not None, "shape is inside the kernel's coverage"
+    torch.cuda.synchronize()
+    impl.check_status()
+    o, lse = res
+    ro, rlse = _ref("attention", q, k, v, causal, scale)
+    _close(o, ro, 2e-2, 2e-2)
+    _close(lse, rlse, 1e-2, 1e-2)
+    assert impl.attention_forward_own(q[:, :128], k, v, False, scale) is None  # 128 query rows: not covered
+
+
 def test_wait_that_runs_out_reports_and_leaves_the_context_usable(K):
     """The error path of every peer wait, without a peer: a flag that nothing raises, a short limit.  The kernel
     returns by itself, the host turns the status word into an exception, and the next kernels run normally."""

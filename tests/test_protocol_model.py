@@ -98,3 +98,59 @@ def test_dynamic_tiles_are_each_handled_once_even_when_pairs_leave(requests):
         assert idle <= max(num_pairs // 2, 0) + 0 or requests == 0
         assert (c.next_tile, c.left, c.yielded) == (0, 0, 0)
         assert c.requests == max(0, asked - num_pairs // 2)  # granted requests are used up, the rest carry over
+
+
+# ------------------------------------------------------------------------------------- attention pipeline
+def _attention_reference(q, k, v, causal, scale):
+    import numpy as np
+
+    s = (q @ k.T) * scale
+    if causal:
+        first = k.shape[0] - q.shape[0]
+        s = np.where(np.arange(k.shape[0])[None, :] <= (first + np.arange(q.shape[0]))[:, None], s, -np.inf)
+    mx = s.max(1, keepdims=True)
+    e = np.exp(s - mx)
+    return (e / e.sum(1, keepdims=True)) @ v, np.log(e.sum(1)) + mx[:, 0]
+
+
+@pytest.mark.parametrize("causal,keys", [(True, 64), (True, 192), (True, 256), (False, 96), (False, 32)])
+def test_attention_pipeline_schedule_is_complete_and_exact(causal, keys):
+    """Loader, MMA issuer and the two softmax groups of the attention kernel, as host threads with the kernel's
+    barriers, three-slot K/V ring and deferred accumulation: every interleaving must give plain attention."""
+    import numpy as np
+
+    from autoparallel_b200.runtime.protocol_model import run_attention_pipeline
+
+    rng = np.random.default_rng(keys)
+    tile, d = 32, 8
+    q = rng.standard_normal((2 * tile, d))
+    k = rng.standard_normal((keys, d))
+    v = rng.standard_normal((keys, d))
+    want, want_lse = _attention_reference(q, k, v, causal, 0.3)
+    for seed in range(3):
+        out, lse, errors = run_attention_pipeline(q, k, v, causal, 0.3, jitter=0.002, seed=seed, tile=tile)
+        assert errors == []
+        assert np.abs(out - want).max() < 1e-12 and np.abs(lse - want_lse).max() < 1e-12
+
+
+@pytest.mark.parametrize("ring", [2, 3, 4])
+def test_attention_pipeline_ring_depth_only_changes_prefetch(ring):
+    """Two slots are the minimum (V_j and K_{j+1} are live together); more only let the loader run ahead."""
+    import numpy as np
+
+    from autoparallel_b200.runtime import protocol_model as pm
+
+    rng = np.random.default_rng(0)
+    q, k, v = rng.standard_normal((64, 8)), rng.standard_normal((128, 8)), rng.standard_normal((128, 8))
+    out, lse, errors = pm.run_attention_pipeline(q, k, v, True, 1.0, ring=ring, tile=32, jitter=0.001)
+    want, _ = _attention_reference(q, k, v, True, 1.0)
+    assert errors == [] and np.abs(out - want).max() < 1e-12
+
+
+def test_swizzle_offsets_are_a_permutation_of_each_atom():
+    from autoparallel_b200.runtime.protocol_model import swizzle128_offset
+
+    for atom in range(4):  # an atom is 8 rows x 128 bytes
+        seen = {swizzle128_offset(atom * 8 + r, c) for r in range(8) for c in range(8)}
+        assert seen == {atom * 1024 + 16 * i for i in range(64)}
+    assert swizzle128_offset(0, 3) == 48 and swizzle128_offset(1, 0) == 128 + 16 and swizzle128_offset(9, 1) == 9 * 128
