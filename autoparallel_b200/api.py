@@ -61,7 +61,8 @@ class AutoParallel:
         mesh: ``DeviceMesh`` whose dims are the axes placements refer to.
         mp_policy: object with ``param_dtype / reduce_dtype / output_dtype / cast_forward_inputs``.
         reshard_after_forward: re-gather FSDP parameters in backward instead of keeping them.
-        cost_model: ``"auto"`` (NVLink-5 α–β model or CPU loopback by mesh device), a
+        cost_model: ``"auto"`` (NVLink-5 α–β model or CPU loopback by mesh device), ``"nccl"`` (NCCL's algorithm /
+            protocol model, multi-node aware), ``"measured"`` / ``"measured:symm"`` (tables taken on B200), a
             ``comm.Topology``, or a path to a calibration table (JSON).
         repeated_subgraphs: share ILP variables between structurally identical layers.
         activation_checkpointing: ``"none" | "selective" | "full"``.
@@ -159,6 +160,13 @@ class AutoParallel:
                 topo = comm_cost.Topology.for_mesh(self.mesh)
                 if self.plan_device is not None:
                     topo = comm_cost.Topology([comm_cost.NVLINK5] * self.mesh.ndim)
+                if self.cost_model == "nccl":
+                    # NCCL's own algorithm / protocol choice per collective; nodes of 8 GPUs unless the mesh is smaller
+                    from .parallel.cost import nccl_model
+
+                    name = self.plan_device or (torch.cuda.get_device_name(0) if torch.cuda.is_available() else "B200")
+                    cfg = nccl_model.detect_topology(self.mesh.size(), ranks_per_host=min(self.mesh.size(), 8), device_name=name)
+                    topo = comm_cost.NcclTopology(cfg, tuple(self.mesh.shape))
                 if isinstance(self.cost_model, str) and self.cost_model not in ("auto", "nccl"):
                     # "measured" / "measured:symm": the table taken on this device type that ships with the package
                     if self.cost_model.startswith("measured"):

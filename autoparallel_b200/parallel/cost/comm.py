@@ -136,6 +136,38 @@ class Topology:
         return l.alpha(n) + nbytes_local * (n - 1) / n / (l.a2a_bw_gbs * 1e3)
 
 
+class NcclTopology(Topology):
+    """Prices every collective with the NCCL model (``cost/nccl_model.py``, ``cost/nccl_tuning.py``): measured tables
+    inside one NVSwitch node, the per-algorithm / per-protocol tuning model across nodes.  Tables loaded with
+    ``load_table`` still take precedence.  Selected by ``AutoParallel(..., cost_model="nccl")``."""
+
+    def __init__(self, config, mesh_shape: Sequence[int], tables: Optional[dict] = None):
+        from . import nccl_model, nccl_tuning
+
+        super().__init__(nccl_model.topology_link_models(config, mesh_shape), tables)
+        self.config = config
+        self._m = nccl_model
+        self.dims = [nccl_tuning.derive_mesh_dim_topo(config, tuple(mesh_shape), i) for i in range(len(mesh_shape))]
+
+    def _price(self, kind: str, coll, dim: int, n: int, nbytes: float) -> float:
+        t = self._table(kind, n, nbytes)
+        if t is not None:
+            return t
+        return self._m.dim_collective_time_us(coll, nbytes, self.dims[dim], self.config)
+
+    def all_gather(self, dim: int, n: int, nbytes: float) -> float:
+        return self._price("all_gather", self._m.Coll.ALL_GATHER, dim, n, nbytes)
+
+    def reduce_scatter(self, dim: int, n: int, nbytes: float) -> float:
+        return self._price("reduce_scatter", self._m.Coll.REDUCE_SCATTER, dim, n, nbytes)
+
+    def all_reduce(self, dim: int, n: int, nbytes: float) -> float:
+        return self._price("all_reduce", self._m.Coll.ALL_REDUCE, dim, n, nbytes)
+
+    def all_to_all(self, dim: int, n: int, nbytes_local: float) -> float:
+        return self._price("all_to_all", self._m.Coll.ALL_TO_ALL, dim, n, nbytes_local)
+
+
 _topology: Optional[Topology] = None
 _cache: dict = {}
 

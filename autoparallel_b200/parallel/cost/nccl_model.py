@@ -2,9 +2,10 @@
 
 This is the fallback pricing for mesh dims whose collectives still run through NCCL (the
 NCCL-only baseline plan, inter-node dims) and the reference point the measured NVLink-5 table is
-compared against.  It follows the structure of NCCL's tuning model – per-algorithm bus bandwidth
-capped per channel, per-protocol efficiency, base + per-hop latencies – with an empirical layer for
-NVSwitch nodes where a ring never pays per-hop link latency.  Numbers for H100 come from
+compared against.  Two layers: groups inside one NVSwitch node are priced from measured bandwidth / latency
+tables (a ring through a switch never pays per-hop link latency, so the per-step model overestimates it);
+everything else goes through ``nccl_tuning`` – per-algorithm bandwidth capped per channel, per-protocol
+efficiency, base + per-step latencies, Tree / Ring corrections.  Numbers for H100 come from
 nccl-tests fits; B200 numbers are measured on an 8-GPU NVSwitch node (peer copy 770 GB/s per
 direction, 8-rank all-reduce bus bandwidth 725 GB/s at 1 GiB).  Reference:
 autoparallel/cost_models/nccl_cost_model.py:40-1473 (whose "B200 ⇒ 72 GPUs per node" rule disables
@@ -29,6 +30,8 @@ class Algo(enum.Enum):
     TREE = "tree"
     NVLS = "nvls"
     NVLS_TREE = "nvls_tree"
+    COLLNET_DIRECT = "collnet_direct"
+    COLLNET_CHAIN = "collnet_chain"
 
 
 class Proto(enum.Enum):
@@ -55,13 +58,10 @@ class TopoConfig:
     nvswitch: bool = True
     nvls: bool = True
     max_channels: int = 32
+    n_channels: int = 0  # channels a collective uses (0: the architecture's default)
+    collnet: bool = False  # in-network reduction offered by the fabric (SHARP)
 
 
-#: protocol efficiency (fraction of the link a protocol's framing leaves) and per-step latency, us
-_PROTO_EFF = {Proto.LL: 0.5, Proto.LL128: 0.92, Proto.SIMPLE: 1.0}
-_PROTO_LAT = {Proto.LL: 0.6, Proto.LL128: 1.0, Proto.SIMPLE: 2.4}
-_BASE_LAT = {Algo.RING: 6.6, Algo.TREE: 8.4, Algo.NVLS: 5.0, Algo.NVLS_TREE: 7.0}
-_NET_LAT = {Proto.LL: 5.0, Proto.LL128: 8.5, Proto.SIMPLE: 14.0}
 _NVLS_EFF = {Arch.AMPERE: 0.0, Arch.HOPPER: 0.85, Arch.BLACKWELL: 0.74}
 
 #: measured intra-node algorithm bandwidth at 1 GiB (GB/s) and small-message latency (us) on NVSwitch
@@ -117,42 +117,9 @@ def eligible(algo: Algo, coll: Coll, topo: TopoConfig, n_ranks: int) -> bool:
         return topo.nvls and _NVLS_EFF[topo.arch] > 0 and topo.n_nodes == 1 and n_ranks > 2
     if algo is Algo.NVLS_TREE:
         return topo.nvls and _NVLS_EFF[topo.arch] > 0 and topo.n_nodes > 1
+    if algo in (Algo.COLLNET_DIRECT, Algo.COLLNET_CHAIN):
+        return topo.collnet and topo.n_nodes > 1 and coll is Coll.ALL_REDUCE
     return False
-
-
-def algo_time_us(coll: Coll, algo: Algo, proto: Proto, nbytes: float, n_ranks: int, topo: TopoConfig) -> float:
-    """Time of one collective under a fixed (algorithm, protocol).  ``nbytes``: all-gather – gathered
-    size; reduce-scatter – input size; all-reduce – tensor size."""
-    if n_ranks <= 1 or nbytes <= 0:
-        return 0.0
-    spans_nodes = n_ranks > topo.gpus_per_node
-    link = topo.inter_bw_gbs if spans_nodes else topo.intra_bw_gbs
-    bw = link * _PROTO_EFF[proto]
-    steps_lat = _PROTO_LAT[proto] + (_NET_LAT[proto] if spans_nodes else 0.0)
-    n = n_ranks
-    if algo is Algo.RING:
-        if coll is Coll.ALL_REDUCE:
-            traffic, steps = 2.0 * (n - 1) / n * nbytes, 2 * (n - 1)
-        else:
-            traffic, steps = (n - 1) / n * nbytes, n - 1
-        if topo.nvswitch and not spans_nodes:
-            steps = 1 + math.log2(n)  # through a switch a "ring" step costs no extra link hop
-        return _BASE_LAT[algo] + steps * steps_lat + traffic / (bw * 1e3)
-    if algo is Algo.TREE:
-        depth = 2 * math.ceil(math.log2(n))
-        return _BASE_LAT[algo] + depth * steps_lat + 2.0 * nbytes / (bw * 1e3)
-    if algo is Algo.NVLS:
-        # the switch reduces / multicasts: every GPU pushes its data once and receives the result once
-        eff = _NVLS_EFF[topo.arch]
-        traffic = nbytes if coll is Coll.ALL_REDUCE else (n - 1) / n * nbytes
-        return _BASE_LAT[algo] + 2 * steps_lat + traffic / (link * eff * 1e3)
-    if algo is Algo.NVLS_TREE:
-        eff = _NVLS_EFF[topo.arch]
-        nodes = max(1, n // topo.gpus_per_node)
-        intra = nbytes / (topo.intra_bw_gbs * eff * 1e3)
-        inter = 2.0 * nbytes / (topo.inter_bw_gbs * 1e3) * (nodes - 1) / nodes
-        return _BASE_LAT[algo] + 2 * math.ceil(math.log2(max(nodes, 2))) * (steps_lat + _NET_LAT[proto]) + intra + inter
-    raise ValueError(algo)
 
 
 def collective_time_us(coll: Coll, nbytes: float, n_ranks: int, topo: TopoConfig) -> float:
@@ -166,26 +133,36 @@ def collective_time_us(coll: Coll, nbytes: float, n_ranks: int, topo: TopoConfig
         if coll is Coll.ALL_REDUCE:
             return _interp(m["ar_lat"], n_ranks) + nbytes / (_interp(m["ar_bw"], n_ranks) * 1e3)
         return _interp(m["ag_rs_lat"], n_ranks) + nbytes / (_interp(m["ag_rs_bw"], n_ranks) * 1e3)
-    best = math.inf
-    for algo in Algo:
-        if not eligible(algo, coll, topo, n_ranks):
-            continue
-        for proto in Proto:
-            if proto is Proto.LL128 and algo in (Algo.NVLS, Algo.NVLS_TREE):
-                continue
-            best = min(best, algo_time_us(coll, algo, proto, nbytes, n_ranks, topo))
-    return best
+    # everything else (several nodes, or no NVSwitch): the per-algorithm, per-protocol tuning model
+    from . import nccl_tuning as T
+
+    ppn = max(1, min(topo.gpus_per_node, n_ranks))
+    ch = topo.n_channels or T.DEFAULT_CHANNELS[topo.arch]
+    d = T.DimTopo(n_ranks, ppn, max(1, n_ranks // ppn), ch, topo.intra_bw_gbs / ch, topo.inter_bw_gbs / ch)
+    return T.best_time_us(coll, nbytes, d, topo)[0]
+
+
+def dim_collective_time_us(coll: Coll, nbytes: float, d, topo: TopoConfig) -> float:
+    """Like ``collective_time_us`` for the group of one mesh dim (``d``: ``nccl_tuning.DimTopo``), whose members
+    may be spread over nodes with fewer than ``gpus_per_node`` of them in each."""
+    from . import nccl_tuning as T
+
+    if d.n_ranks <= 1 or nbytes <= 0:
+        return 0.0
+    if coll is Coll.ALL_TO_ALL:
+        return T.all_to_all_us(nbytes, d, topo)
+    if topo.nvswitch and d.n_nodes == 1:
+        return collective_time_us(coll, nbytes, d.n_ranks, topo)
+    return T.best_time_us(coll, nbytes, d, topo)[0]
 
 
 def all_to_all_time_us(nbytes_local: float, n_ranks: int, topo: TopoConfig) -> float:
-    m = _MEASURED_INTRA[topo.arch]
-    if n_ranks <= topo.gpus_per_node:
-        return m["a2a_lat"] + nbytes_local * (n_ranks - 1) / n_ranks / (m["a2a_bw"] * 1e3)
-    nodes = n_ranks // topo.gpus_per_node
-    off_node = nbytes_local * (n_ranks - topo.gpus_per_node) / n_ranks
-    on_node = nbytes_local * (topo.gpus_per_node - 1) / n_ranks
-    lat = {2: 37.0, 4: 42.0, 8: 60.0, 16: 98.0, 32: 290.0}
-    return _interp(lat, nodes) + max(off_node / (topo.inter_bw_gbs * 1e3), on_node / (m["a2a_bw"] * 1e3))
+    from . import nccl_tuning as T
+
+    ppn = max(1, min(topo.gpus_per_node, n_ranks))
+    ch = topo.n_channels or T.DEFAULT_CHANNELS[topo.arch]
+    d = T.DimTopo(n_ranks, ppn, max(1, n_ranks // ppn), ch, topo.intra_bw_gbs / ch, topo.inter_bw_gbs / ch)
+    return T.all_to_all_us(nbytes_local, d, topo)
 
 
 def a100_topo(n_nodes: int = 1) -> TopoConfig:
@@ -207,8 +184,9 @@ def gb200_nvl72_topo(n_racks: int = 1) -> TopoConfig:
 def detect_topology(world_size: int, ranks_per_host: Optional[int] = None, device_name: str = "") -> TopoConfig:
     """Topology from what is observable: ranks per host (default: all on one host up to 8) and, only
     for the architecture generation, the device name."""
-    name = device_name.upper()
-    arch = Arch.BLACKWELL if ("B200" in name or "B100" in name or "GB200" in name) else Arch.HOPPER if ("H100" in name or "H200" in name) else Arch.AMPERE if "A100" in name else Arch.BLACKWELL
+    from .nccl_tuning import arch_from_device_name
+
+    arch = arch_from_device_name(device_name) or Arch.BLACKWELL  # this package targets B200: unknown names plan as such
     rph = ranks_per_host or min(world_size, 8)
     n_nodes = max(1, world_size // rph)
     base = {Arch.BLACKWELL: b200_topo, Arch.HOPPER: h100_topo, Arch.AMPERE: a100_topo}[arch](n_nodes)
