@@ -110,8 +110,12 @@ def strategy_compute_cost(node, spec: OpSpec, limit: Optional[DeviceLimit] = Non
     flex = isinstance(op, torch._ops.HigherOrderOperator) and op.name() in ("flex_attention", "flex_attention_backward")
     if op in _ZERO_COST or not (isinstance(op, torch._ops.OpOverload) or flex):
         return 0.0
-    limit = limit or get_device_limit(spec.mesh.device_type)
     outs = spec.output_specs if isinstance(spec.output_specs, (tuple, list)) else [spec.output_specs]
+    # (``spec.mesh`` looks at the first output only, which is None when that output is not needed)
+    mesh = next((x.mesh for x in list(outs) + list(spec.input_specs or []) if x is not None), None)
+    if mesh is None:
+        return 0.0
+    limit = limit or get_device_limit(mesh.device_type)
     in_shapes, out_shapes = [], []
     nbytes = 0.0
     dtype = None

@@ -214,3 +214,25 @@ def test_node_constraint_against_memory_budget_then_removal_and_resolve(mesh_1d)
         sol = opt.resolve() if hasattr(opt, "resolve") else opt.get_solution()
         assert tuple(sol[w1].output_spec.placements) == (Replicate(),)
 
+
+
+def test_norm_as_first_op_on_an_input_without_gradient(mesh_1d):
+    # native_layer_norm_backward then has no input gradient: its first output spec is None
+    class M(nn.Module):
+        def __init__(s):
+            super().__init__()
+            s.n = nn.LayerNorm(32)
+            s.l = nn.Linear(32, 32)
+
+        def forward(s, x):
+            return s.l(s.n(x))
+
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.rand(16, 32), mesh_1d) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    pm.to_empty(device="cpu")
+    pm(torch.rand(2, 32)).sum().backward()
+    assert all(p.grad is not None for p in pm.parameters())
