@@ -300,6 +300,7 @@ class AutoParallel:
         sharded_params, sharded_buffers = _meta_state(self.model, lowered, self.mesh)
         param_names = list(lowered.joint.param_nodes)
         buffer_names = list(lowered.joint.buffer_nodes)
+        updated_buffers = list(lowered.joint.buffer_updates)
         #: shape key -> specialisation; the planned shapes are the first entry
         specializations = {self._shape_key(expected): (runtime, expected, traced, out_spec)}
         solved = self.sharding_placement if sharding_placement is None else sharding_placement
@@ -320,6 +321,11 @@ class AutoParallel:
             buffers = [_local(module.get_buffer(n)) for n in buffer_names]
             tensors = [a for a, e in zip(flat, exp) if e[0] == "tensor"]
             outs = rt(params, buffers, tensors, torch.is_grad_enabled())
+            if updated_buffers:  # new values of the buffers the forward mutates ride behind the user's outputs
+                outs, new_vals = outs[: len(outs) - len(updated_buffers)], outs[len(outs) - len(updated_buffers):]
+                with torch.no_grad():
+                    for name, val in zip(updated_buffers, new_vals):
+                        _local(module.get_buffer(name)).copy_(val.detach())
             if ospec is not None:
                 return tree_unflatten(list(outs), ospec)
             return outs[0] if len(outs) == 1 else tuple(outs)
@@ -485,7 +491,7 @@ def auto_parallel(
             ap.add_parameter_memory_constraint(*parameter_memory)
         if out_shardings is not None:
             ap.add_output_constraints(
-                input_utils.flatten_out_shardings(out_shardings, len(ap.joint.fwd_outputs), mesh)
+                input_utils.flatten_out_shardings(out_shardings, ap.joint.num_user_outputs or len(ap.joint.fwd_outputs), mesh)
             )
         ap.optimize_placement()
         return ap.apply_placement()

@@ -56,6 +56,10 @@ class JointGraph:
     traced_inputs: ForwardInputs
     #: number of forward outputs at the head of the output tuple
     num_fwd_outputs: int = 0
+    #: buffers the forward mutates in place (batch-norm statistics, counters): fqn -> node of the new value.  The new
+    #: values ride at the END of ``fwd_outputs`` (after the ``num_user_outputs`` values the caller sees).
+    buffer_updates: dict = dataclasses.field(default_factory=dict)
+    num_user_outputs: int = 0
 
     def tangent_of(self, out_idx: int) -> Optional[fx.Node]:
         for n in self.tangent_nodes:
@@ -265,9 +269,12 @@ def index_joint_graph(gm: fx.GraphModule, traced_inputs: ForwardInputs, out_spec
     fwd_outputs: list[Any] = []
     param_grads: dict[str, Optional[fx.Node]] = {k: None for k in params}
     input_grads: list[Optional[fx.Node]] = [None] * len(inputs)
+    buffer_updates: dict[str, fx.Node] = {}
     for v, d in zip(out_vals, out_descs):
         if isinstance(d, D.PlainAOTOutput):
             fwd_outputs.append(v)
+        elif isinstance(d, D.InputMutationAOTOutput) and isinstance(d.mutated_input, D.BufferAOTInput) and isinstance(v, fx.Node):
+            buffer_updates[d.mutated_input.target] = v
         elif isinstance(d, D.GradAOTOutput):
             src = d.grad_of
             if isinstance(src, D.ParamAOTInput):
@@ -278,8 +285,12 @@ def index_joint_graph(gm: fx.GraphModule, traced_inputs: ForwardInputs, out_spec
             continue  # gradient slot of an input that does not require grad
         else:
             raise NotImplementedError(f"unsupported joint-graph output descriptor {d!r}")
+    num_user = len(fwd_outputs)
+    fwd_outputs = fwd_outputs + list(buffer_updates.values())
     return JointGraph(
         gm=gm,
+        buffer_updates=buffer_updates,
+        num_user_outputs=num_user,
         param_nodes=params,
         buffer_nodes=buffers,
         input_nodes=inputs,

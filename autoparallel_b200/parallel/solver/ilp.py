@@ -243,7 +243,11 @@ class ShardingOptimizer:
             g = j.input_grads[i] if i < len(j.input_grads) else None
             if isinstance(n, fx.Node) and isinstance(g, fx.Node) and g in self.strats:
                 pairs.append((n, g))
-        for idx, o in enumerate(j.fwd_outputs):
+        for fqn, new in j.buffer_updates.items():  # a mutated buffer keeps its placement
+            b = j.buffer_nodes.get(fqn)
+            if isinstance(b, fx.Node) and isinstance(new, fx.Node) and b in self.strats and new in self.strats:
+                pairs.append((b, new))
+        for idx, o in enumerate(j.fwd_outputs[: j.num_user_outputs or len(j.fwd_outputs)]):
             t = j.tangent_of(idx)
             if isinstance(o, fx.Node) and t is not None and o in self.strats:
                 pairs.append((o, t))
@@ -340,7 +344,7 @@ class ShardingOptimizer:
         return names
 
     def add_sharded_output_constraint(self, placements: Sequence[Optional[Sequence[Placement]]]) -> list[str]:
-        outs = self.joint.fwd_outputs
+        outs = self.joint.fwd_outputs[: self.joint.num_user_outputs or len(self.joint.fwd_outputs)]
         if len(placements) != len(outs):
             raise ValueError(f"{len(placements)} output constraints given for {len(outs)} flat outputs")
         names = []

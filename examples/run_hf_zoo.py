@@ -50,9 +50,53 @@ ZOO = {
                                                  vocab_size=V, max_position_embeddings=512)),
     "roberta": ("masked-lm", lambda T: T.RobertaConfig(hidden_size=D, num_hidden_layers=L, num_attention_heads=H, intermediate_size=4 * D,
                                                        vocab_size=V, max_position_embeddings=514)),
+    "opt": _dec("OPTConfig", hidden_size=D, ffn_dim=4 * D, num_hidden_layers=L, num_attention_heads=H, vocab_size=V, word_embed_proj_dim=D,
+                max_position_embeddings=512),
+    "gpt_bigcode": _dec("GPTBigCodeConfig", n_embd=D, n_layer=L, n_head=H, vocab_size=V, n_positions=512),
+    "gemma": _dec("GemmaConfig", hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=4,
+                  head_dim=32, vocab_size=V, max_position_embeddings=512),
+    "gemma2": _dec("Gemma2Config", hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=4,
+                   head_dim=32, vocab_size=V, max_position_embeddings=512, sliding_window=128),
+    "phi3": _dec("Phi3Config", hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=4,
+                 vocab_size=V, max_position_embeddings=512, original_max_position_embeddings=512, pad_token_id=0),
+    "qwen3": _dec("Qwen3Config", hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=4,
+                  head_dim=32, vocab_size=V, max_position_embeddings=512),
+    "olmo": _dec("OlmoConfig", hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H, vocab_size=V,
+                 max_position_embeddings=512),
+    "olmo2": _dec("Olmo2Config", hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=4,
+                  vocab_size=V, max_position_embeddings=512),
+    "starcoder2": _dec("Starcoder2Config", hidden_size=D, intermediate_size=4 * D, num_hidden_layers=L, num_attention_heads=H,
+                       num_key_value_heads=4, vocab_size=V, max_position_embeddings=512, sliding_window=128),
+    "granite": _dec("GraniteConfig", hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=4,
+                    vocab_size=V, max_position_embeddings=512),
+    "cohere": _dec("CohereConfig", hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=4,
+                   vocab_size=V, max_position_embeddings=512),
+    "mpt": _dec("MptConfig", d_model=D, n_layers=L, n_heads=H, vocab_size=V, max_seq_len=512),
+    "codegen": _dec("CodeGenConfig", n_embd=D, n_layer=L, n_head=H, vocab_size=V, rotary_dim=16, n_positions=512),
+    "bart": ("seq2seq", lambda T: T.BartConfig(d_model=D, encoder_layers=L, decoder_layers=L, encoder_attention_heads=H, decoder_attention_heads=H,
+                                               encoder_ffn_dim=4 * D, decoder_ffn_dim=4 * D, vocab_size=V, max_position_embeddings=512)),
+    "electra": ("masked-lm", lambda T: T.ElectraConfig(hidden_size=D, embedding_size=D, num_hidden_layers=L, num_attention_heads=H,
+                                                       intermediate_size=4 * D, vocab_size=V, max_position_embeddings=512)),
+    "albert": ("masked-lm", lambda T: T.AlbertConfig(hidden_size=D, embedding_size=128, num_hidden_layers=L, num_attention_heads=H,
+                                                     intermediate_size=4 * D, vocab_size=V, max_position_embeddings=512)),
+    "vit": ("image-cls", lambda T: T.ViTConfig(hidden_size=D, num_hidden_layers=L, num_attention_heads=H, intermediate_size=4 * D,
+                                               image_size=64, patch_size=8, num_labels=16)),
+    "deit": ("image-cls", lambda T: T.DeiTConfig(hidden_size=D, num_hidden_layers=L, num_attention_heads=H, intermediate_size=4 * D,
+                                                 image_size=64, patch_size=8, num_labels=16)),
+    "resnet": ("image-cls", lambda T: T.ResNetConfig(embedding_size=32, hidden_sizes=[32, 64], depths=[1, 1], layer_type="basic", num_labels=16)),
+    "convnext": ("image-cls", lambda T: T.ConvNextConfig(num_stages=2, hidden_sizes=[32, 64], depths=[1, 1], num_labels=16)),
+    "whisper": ("speech", lambda T: T.WhisperConfig(d_model=D, encoder_layers=L, decoder_layers=L, encoder_attention_heads=H,
+                                                    decoder_attention_heads=H, encoder_ffn_dim=4 * D, decoder_ffn_dim=4 * D,
+                                                    vocab_size=V, num_mel_bins=16, max_source_positions=64, max_target_positions=512,
+                                                    pad_token_id=0, bos_token_id=1, eos_token_id=2, decoder_start_token_id=1)),
     "distilbert": ("masked-lm", lambda T: T.DistilBertConfig(dim=D, n_layers=L, n_heads=H, hidden_dim=4 * D, vocab_size=V,
                                                              max_position_embeddings=512)),
 }
+
+
+# LayerDrop draws a random number per layer and branches on it in Python while training: not capturable as one
+# graph.  These families are planned in eval mode (the branch is skipped; dropout is off).
+EVAL_MODE = {"opt", "bart", "whisper"}
 
 
 def plan_one(name, mesh, batch, seq, execute, bf16=False):
@@ -61,7 +105,10 @@ def plan_one(name, mesh, batch, seq, execute, bf16=False):
     task, make = ZOO[name]
     cfg = make(T)
     cfg.use_cache = False
-    auto = {"causal-lm": T.AutoModelForCausalLM, "seq2seq": T.AutoModelForSeq2SeqLM, "masked-lm": T.AutoModelForMaskedLM}[task]
+    if name == "deit":
+        cfg.architectures = ["DeiTForImageClassification"]  # the auto class maps this config to two heads
+    auto = {"causal-lm": T.AutoModelForCausalLM, "seq2seq": T.AutoModelForSeq2SeqLM, "masked-lm": T.AutoModelForMaskedLM,
+            "image-cls": T.AutoModelForImageClassification, "speech": T.AutoModelForSpeechSeq2Seq}[task]
     with torch.device("meta"):
         try:
             cfg._attn_implementation = "sdpa"
@@ -69,17 +116,23 @@ def plan_one(name, mesh, batch, seq, execute, bf16=False):
         except ValueError:  # architectures without a fused-attention path: explicit softmax(QK^T)V
             cfg._attn_implementation = "eager"
             model = auto.from_config(cfg)
+    if name in EVAL_MODE:
+        model.eval()
 
     def ids():
         return torch.randint(0, cfg.vocab_size, (batch, seq))
 
     def input_fn():
+        if task == "image-cls":
+            return ForwardInputs((), {"pixel_values": torch.randn(batch, 3, 64, 64)})
+        if task == "speech":  # log-mel frames in (two per encoder position), decoder tokens
+            return ForwardInputs((), {"input_features": torch.randn(batch, 16, 128), "decoder_input_ids": ids()})
         kw = {"input_ids": ids()}
         if task == "seq2seq":
             kw["decoder_input_ids"] = ids()
         return ForwardInputs((), kw)
 
-    n_in = 2 if task == "seq2seq" else 1
+    n_in = 2 if task in ("seq2seq", "speech") else 1
     t0 = time.perf_counter()
     policy = None
     if bf16:

@@ -12,7 +12,7 @@ pytest.importorskip("transformers")
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-@pytest.mark.parametrize("name", ["gpt2", "gptj", "falcon", "t5", "bert"])
+@pytest.mark.parametrize("name", ["gpt2", "gptj", "falcon", "t5", "bert", "gemma2", "opt", "vit", "resnet"])
 def test_family_plans_lowers_and_executes(mesh_1d, name):
     from examples.run_hf_zoo import plan_one
 
