@@ -520,6 +520,74 @@ def _sdpa_cpu_bwd(ctx):
     return expand_rows(ctx, [(S(d),) * 9 + _mask_rows(ctx, 6, d) for d in (0, 1)])
 
 
+# ------------------------------------------------------------------------------ convolution
+# convolution(input [N,C,...], weight [O,C/groups,...], bias [O]?, stride, padding, dilation, transposed, output_padding, groups)
+# Per mesh dim: split the batch; or (plain convolutions: one group, not transposed) split the output channels with
+# the weight's rows, or the input channels with the weight's columns (partial sums out; only without a bias, which
+# every rank would otherwise add once).  Spatial dims are never split (that would need halo exchanges).
+@register_rule(aten.convolution.default)
+def _convolution(ctx):
+    has_bias = len(ctx.in_vals) == 3
+    transposed, groups = bool(ctx.args[6]), int(ctx.args[8])
+    rows = [(S(0), S(0), R) + ((R,) if has_bias else ())]
+    if groups == 1 and not transposed:
+        rows.append((S(1), R, S(0)) + ((S(0),) if has_bias else ()))
+        if not has_bias:
+            rows.append((P, S(1), S(1)))
+    return expand_rows(ctx, rows)
+
+
+# convolution_backward(grad_out, input, weight, bias_sizes, ..., transposed, output_padding, groups, output_mask)
+#   -> (grad_input, grad_weight, grad_bias), each None where the mask says so
+@register_rule(aten.convolution_backward.default)
+def _convolution_bwd(ctx):
+    transposed, groups = bool(ctx.args[7]), int(ctx.args[9])
+    rows = [(S(0), P, P, S(0), S(0), R)]
+    if groups == 1 and not transposed:
+        rows.append((P, S(0), S(0), S(1), R, S(0)))    # output channels split: every rank holds a partial input gradient
+        rows.append((S(1), S(1), R, R, S(1), S(1)))    # input channels split
+    return expand_rows(ctx, rows)
+
+
+def _channel_row(ctx):
+    """Channel split of a batch-norm style op: [N, C, ...] tensors on dim 1, per-channel vectors on dim 0."""
+    def pl(v):
+        if not isinstance(v, torch.Tensor):
+            return None
+        return S(1) if v.ndim >= 2 else S(0) if v.ndim == 1 else R
+
+    return tuple(pl(v) for v in ctx.out_vals) + tuple(pl(v) for v in ctx.in_vals)
+
+
+# Batch statistics need every sample of a channel, so a training-mode batch norm is split over channels only (a batch
+# split would have to combine means and variances across ranks inside the op); with fixed statistics the batch may
+# be split as well.
+@register_rule(aten._native_batch_norm_legit_functional.default, aten._native_batch_norm_legit.default,
+               aten.native_batch_norm.default, aten.native_batch_norm_backward.default)
+def _batch_norm_training(ctx):
+    training = next((a for a in ctx.args if isinstance(a, bool)), True)
+    rows = [_channel_row(ctx)]
+    if not training and ctx.op is not aten.native_batch_norm_backward.default:
+        rows.append(tuple(S(0) if isinstance(v, torch.Tensor) and v.ndim >= 2 else (R if isinstance(v, torch.Tensor) else None) for v in ctx.out_vals)
+                    + tuple(S(0) if v.ndim >= 2 else R for v in ctx.in_vals))
+    return expand_rows(ctx, rows)
+
+
+@register_rule(aten._native_batch_norm_legit_no_training.default)
+def _batch_norm_eval(ctx):
+    batch = tuple(S(0) if isinstance(v, torch.Tensor) and v.ndim >= 2 else (R if isinstance(v, torch.Tensor) else None) for v in ctx.out_vals) \
+        + tuple(S(0) if v.ndim >= 2 else R for v in ctx.in_vals)
+    return expand_rows(ctx, [_channel_row(ctx), batch])
+
+
+@register_rule(aten.max_pool2d_with_indices.default, aten.max_pool2d_with_indices_backward.default)
+def _max_pool(ctx):
+    if ctx.in_vals[0].ndim != 4:
+        return expand_rows(ctx, [])
+    n = len(ctx.out_vals) + len(ctx.in_vals)
+    return expand_rows(ctx, [(S(0),) * n, (S(1),) * n])  # windows never cross samples or channels
+
+
 @register_rule(aten.squeeze.dims, aten.squeeze.dim)
 def _squeeze(ctx):
     x = ctx.in_vals[0]
