@@ -46,7 +46,21 @@ _SIZE_ARG = {
     aten.new_ones.default: 1,
     aten.new_empty.default: 1,
     aten.new_full.default: 1,
+    aten.new_empty_strided.default: 1,
+    aten.empty_strided.default: 0,
 }
+# factories whose argument after the size is a stride list
+_STRIDED_FACTORIES = (aten.new_empty_strided.default, aten.empty_strided.default)
+
+
+def _strides_like(old_strides, new_shape) -> list[int]:
+    """Dense strides for ``new_shape`` that keep the dim order of ``old_strides`` (outermost = largest stride)."""
+    order = sorted(range(len(new_shape)), key=lambda d: (-old_strides[d], d))
+    out, acc = [0] * len(new_shape), 1
+    for d in reversed(order):
+        out[d] = acc
+        acc *= max(int(new_shape[d]), 1)
+    return out
 
 
 def _localize_moe_slots(args, val, lval):
@@ -357,6 +371,8 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
                     new_args[pos] = [-1 if o == -1 else l for o, l in zip(old, lval.shape)]
                 else:
                     new_args[pos] = list(lval.shape)
+                    if node.target in _STRIDED_FACTORIES:
+                        new_args[pos + 1] = _strides_like(list(node.args[pos + 1]), list(lval.shape))
                 new_args = tuple(new_args)
             if node.target in _INT_ARG_LOCALIZERS and isinstance(lval, torch.Tensor):
                 new_args = tuple(_INT_ARG_LOCALIZERS[node.target](list(new_args), val, lval))

@@ -588,6 +588,17 @@ def _max_pool(ctx):
     return expand_rows(ctx, [(S(0),) * n, (S(1),) * n])  # windows never cross samples or channels
 
 
+@register_rule(aten.copy.default)
+def _copy(ctx):
+    # copy(dst, src) -> src broadcast into dst's shape: split any dim of dst; src follows where it has that dim in full
+    dst, src = ctx.in_vals[0], ctx.in_vals[1]
+    rows = []
+    for i in range(dst.ndim):
+        j = i - (dst.ndim - src.ndim)
+        rows.append((S(i), S(i), S(j) if j >= 0 and src.shape[j] == dst.shape[i] else R))
+    return expand_rows(ctx, rows)
+
+
 @register_rule(aten.squeeze.dims, aten.squeeze.dim)
 def _squeeze(ctx):
     x = ctx.in_vals[0]
