@@ -153,33 +153,33 @@ class AutoParallel:
                                  repeated_subgraphs=self.repeated_subgraphs, even_only=not self.uneven_sharding)
 
     def _install_cost_models(self) -> None:
-        if True:  # (kept as one block: topology first, then the device table)
-            if isinstance(self.cost_model, comm_cost.Topology):
-                comm_cost.set_topology(self.cost_model)
-            else:
-                topo = comm_cost.Topology.for_mesh(self.mesh)
-                if self.plan_device is not None:
-                    topo = comm_cost.Topology([comm_cost.NVLINK5] * self.mesh.ndim)
-                if self.cost_model == "nccl":
-                    # NCCL's own algorithm / protocol choice per collective; nodes of 8 GPUs unless the mesh is smaller
-                    from .parallel.cost import nccl_model
-
-                    name = self.plan_device or (torch.cuda.get_device_name(0) if torch.cuda.is_available() else "B200")
-                    cfg = nccl_model.detect_topology(self.mesh.size(), ranks_per_host=min(self.mesh.size(), 8), device_name=name)
-                    topo = comm_cost.NcclTopology(cfg, tuple(self.mesh.shape))
-                if isinstance(self.cost_model, str) and self.cost_model not in ("auto", "nccl"):
-                    # "measured" / "measured:symm": the table taken on this device type that ships with the package
-                    if self.cost_model.startswith("measured"):
-                        backend = self.cost_model.partition(":")[2] or "nccl"
-                        path = comm_cost.Topology.measured_table_path(self.plan_device or "B200", backend)
-                        if path is None:
-                            raise ValueError(f"no measured collective table for {self.plan_device or 'B200'} / {backend}")
-                        topo.load_table(path)
-                    else:
-                        topo.load_table(self.cost_model)
-                comm_cost.set_topology(topo)
+        # topology first, then the device table
+        if isinstance(self.cost_model, comm_cost.Topology):
+            comm_cost.set_topology(self.cost_model)
+        else:
+            topo = comm_cost.Topology.for_mesh(self.mesh)
             if self.plan_device is not None:
-                device_cost.set_device_limit(device_cost.DEVICE_LIMITS[self.plan_device])
+                topo = comm_cost.Topology([comm_cost.NVLINK5] * self.mesh.ndim)
+            if self.cost_model == "nccl":
+                # NCCL's own algorithm / protocol choice per collective; nodes of 8 GPUs unless the mesh is smaller
+                from .parallel.cost import nccl_model
+
+                name = self.plan_device or (torch.cuda.get_device_name(0) if torch.cuda.is_available() else "B200")
+                cfg = nccl_model.detect_topology(self.mesh.size(), ranks_per_host=min(self.mesh.size(), 8), device_name=name)
+                topo = comm_cost.NcclTopology(cfg, tuple(self.mesh.shape))
+            if isinstance(self.cost_model, str) and self.cost_model not in ("auto", "nccl"):
+                # "measured" / "measured:symm": the table taken on this device type that ships with the package
+                if self.cost_model.startswith("measured"):
+                    backend = self.cost_model.partition(":")[2] or "nccl"
+                    path = comm_cost.Topology.measured_table_path(self.plan_device or "B200", backend)
+                    if path is None:
+                        raise ValueError(f"no measured collective table for {self.plan_device or 'B200'} / {backend}")
+                    topo.load_table(path)
+                else:
+                    topo.load_table(self.cost_model)
+            comm_cost.set_topology(topo)
+        if self.plan_device is not None:
+            device_cost.set_device_limit(device_cost.DEVICE_LIMITS[self.plan_device])
 
     def _restore(self):
         comm_cost.set_topology(self._prev_topology)
