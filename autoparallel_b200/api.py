@@ -353,8 +353,6 @@ class AutoParallel:
         plan - matched by node name and placement, not solved again.  Raises if the two graphs differ in
         structure (shape-dependent control flow) or a placement does not exist at the new shape (a dim that
         no longer divides by the mesh)."""
-        from .parallel.strategies.dtensor_adapter import local_shape
-
         flat_traced, spec = tree_flatten((self.joint.traced_inputs.args, self.joint.traced_inputs.kwargs))
         new_flat = []
         for a, e, pl, old in zip(flat, expected, list(input_placements) + [None] * len(flat), flat_traced):
@@ -434,7 +432,6 @@ def _user_out_spec(joint: JointGraph):
 def _meta_state(model: nn.Module, lowered: LoweredGraph, mesh):
     """Meta-device DTensor parameters / buffers with the solved placements (the caller
     materialises them with ``to_empty`` + ``init_weights``)."""
-    from torch.distributed.tensor._dtensor_spec import DTensorSpec, TensorMeta
 
     params, buffers = {}, {}
 

@@ -21,7 +21,7 @@ import json
 import math
 from typing import Optional, Sequence
 
-from ..strategies.dtensor_adapter import DTensorSpec, Partial, Replicate, Shard
+from ..strategies.dtensor_adapter import DTensorSpec, Shard
 
 INF = float("inf")
 

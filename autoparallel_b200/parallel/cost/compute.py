@@ -14,7 +14,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from ..strategies.dtensor_adapter import DTensorSpec, OpSpec, Partial, Shard, local_shape
+from ..strategies.dtensor_adapter import DTensorSpec, OpSpec, local_shape
 from .device import DeviceLimit, get_device_limit
 
 aten = torch.ops.aten

@@ -24,7 +24,7 @@ import torch.fx as fx
 from ...runtime import comm_ops
 from ..frontend.graph_canon import all_input_nodes
 from ..frontend.trace import JointGraph
-from ..strategies.dtensor_adapter import DTensorSpec, OpSpec, Partial, Replicate, Shard, is_even, local_shape_at, my_local_shape, shard_extent
+from ..strategies.dtensor_adapter import DTensorSpec, OpSpec, Replicate, Shard, is_even, local_shape_at, my_local_shape, shard_extent
 
 logger = logging.getLogger(__name__)
 aten = torch.ops.aten

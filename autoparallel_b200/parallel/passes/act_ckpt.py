@@ -19,7 +19,7 @@ import torch
 import torch.fx as fx
 
 from ...runtime import comm_ops
-from ..frontend.graph_canon import all_input_nodes, param_derived_set
+from ..frontend.graph_canon import param_derived_set
 from ..frontend.trace import JointGraph
 from ..lower.partition import MUST_SAVE, RECOMPUTE
 

@@ -16,7 +16,7 @@ from typing import Any
 
 import torch
 import torch.fx as fx
-from torch.utils._pytree import tree_flatten, tree_map_only
+from torch.utils._pytree import tree_map_only
 
 from . import rules as _rules
 from .dtensor_adapter import (

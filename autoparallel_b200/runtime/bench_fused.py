@@ -12,7 +12,7 @@ rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
 dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
 from autoparallel_b200.runtime import symm, comm_ops
-from autoparallel_b200.ops import cuda_impl, library as L
+from autoparallel_b200.ops import cuda_impl
 g = symm.enable_for_group(dist.group.WORLD)
 name = dist.group.WORLD.group_name
 C = comm_ops.ops
