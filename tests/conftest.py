@@ -9,6 +9,16 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+def free_port() -> int:
+    """A TCP port that is free right now (multi-process tests rendezvous on 127.0.0.1; fixed ports collide when test
+    workers run side by side)."""
+    import socket
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
 

@@ -5,6 +5,7 @@ examples/../dsv3.py:1006-1008.)"""
 import os
 
 import torch
+from conftest import free_port
 import torch.distributed as dist
 import torch.multiprocessing as mp
 import torch.nn as nn
@@ -91,7 +92,7 @@ def _worker(rank, ws, port, q):
 def test_statistics_and_counters_follow_the_single_device_run_on_two_ranks():
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
-    mp.spawn(_worker, args=(2, 29590 + (os.getpid() % 100), q), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, free_port(), q), nprocs=2, join=True)
     res = q.get()
     assert res["out"] < 1e-5 and res["mean"] < 1e-6 and res["var"] < 1e-6 and res["grad"] < 1e-4, res
     assert res["steps"] == 3.0 and res["tracked"] == 3

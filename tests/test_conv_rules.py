@@ -3,6 +3,7 @@ and with the convolutions pinned to output-channel / input-channel sharding."""
 import os
 
 import pytest
+from conftest import free_port
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -98,7 +99,7 @@ def _worker(rank, ws, how, port, q):
 def test_cnn_matches_single_device_on_two_ranks(how):
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
-    mp.spawn(_worker, args=(2, how, 29490 + (os.getpid() % 100), q), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, how, free_port(), q), nprocs=2, join=True)
     res = q.get()
     assert res["out"] < 1e-5 and res["grad"] < 1e-5 and res["mean"] < 1e-6, res
     if how == "channels":

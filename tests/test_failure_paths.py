@@ -4,6 +4,7 @@ import json
 import os
 
 import pytest
+from conftest import free_port
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -86,7 +87,7 @@ def _leaving_worker(rank, ws, port, q):
 def test_a_rank_that_leaves_is_reported_by_the_next_collective():
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
-    port = 29800 + (os.getpid() % 100)
+    port = free_port()
     procs = [ctx.Process(target=_leaving_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()

@@ -4,6 +4,7 @@ shape-level execution on fake ranks, numerics on gloo ranks against plain causal
 import os
 
 import pytest
+from conftest import free_port
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -180,6 +181,6 @@ def _numerics_worker(rank, ws, how, port, q):
 def test_matches_plain_causal_attention_on_two_ranks(how):
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
-    mp.spawn(_numerics_worker, args=(2, how, 29870 + (os.getpid() % 100), q), nprocs=2, join=True)
+    mp.spawn(_numerics_worker, args=(2, how, free_port(), q), nprocs=2, join=True)
     err, worst = q.get()
     assert err < 1e-4 and worst < 1e-3

@@ -4,6 +4,7 @@ import os
 import sys
 
 import pytest
+from conftest import free_port
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -94,6 +95,6 @@ def _hf_worker(rank, ws, name, port, q):
 def test_hf_model_matches_single_device_on_two_ranks(name):
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
-    mp.spawn(_hf_worker, args=(2, name, 29650 + (os.getpid() % 200), q), nprocs=2, join=True)
+    mp.spawn(_hf_worker, args=(2, name, free_port(), q), nprocs=2, join=True)
     err, worst = q.get()
     assert err < 1e-4 and worst < 1e-3

@@ -5,6 +5,7 @@ import os
 import sys
 
 import pytest
+from conftest import free_port
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -73,7 +74,7 @@ def _llama_worker(rank, ws, shape, executor, mp_policy, port, q):
 def _run(fn, ws, *args):
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
-    port = 29600 + (os.getpid() % 300)
+    port = free_port()
     mp.spawn(fn, args=(ws, *args, port, q), nprocs=ws, join=True)
     return q.get()
 

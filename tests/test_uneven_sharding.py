@@ -5,6 +5,7 @@ tests/test_dynamic_shapes.py.)"""
 import os
 
 import pytest
+from conftest import free_port
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -119,7 +120,7 @@ def test_uneven_shards_match_single_device(mesh_shape, batch):
         ws *= m
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
-    mp.spawn(_worker, args=(ws, mesh_shape, batch, 29780 + (os.getpid() % 100), q), nprocs=ws, join=True)
+    mp.spawn(_worker, args=(ws, mesh_shape, batch, free_port(), q), nprocs=ws, join=True)
     per_rank = q.get()
     assert all(e < 1e-5 and w < 1e-4 for e, w, _, _ in per_rank), per_rank
     assert sum(shape[0] for _, _, _, shape in per_rank) == batch * (ws // mesh_shape[0])
@@ -176,5 +177,5 @@ def _redistribute_worker(rank, ws, port, q):
 def test_every_transition_between_uneven_shards_on_three_ranks():
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
-    mp.spawn(_redistribute_worker, args=(3, 29690 + (os.getpid() % 100), q), nprocs=3, join=True)
+    mp.spawn(_redistribute_worker, args=(3, free_port(), q), nprocs=3, join=True)
     assert q.get() == [[], [], []]
