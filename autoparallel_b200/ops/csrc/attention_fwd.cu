@@ -6,7 +6,8 @@
 //   warp 0      TMA producer: Q once, then K_0 V_0 K_1 V_1 ... through a ring of three 32-KB slots
 //   warp 1      MMA issuer:   S_t = Q_t K_j^T   (M 128, N 128, K 128; both operands K-major)
 //                             PV_t = P_t V_j    (A = P_t K-major from shared memory, B = V_j MN-major)
-//   warps 2-5   softmax of tile 0, one query row per thread;  warps 6-9: tile 1
+//   warps 2-3   idle (they complete the first warpgroup, which gives most of its registers away)
+//   warps 4-7   softmax of tile 0, one query row per thread;  warps 8-11: tile 1 (224 registers per thread)
 // TMEM (512 columns): S_0 | S_1 | PV_0 | PV_1, 128 fp32 columns each.  The output row lives in registers:
 // every PV_t product is a fresh accumulator that the row's thread adds to its running sum, rescaled when the
 // row maximum moves.  While one tile's threads are in the softmax, the tensor core works for the other tile.
@@ -43,7 +44,7 @@ constexpr int OFF_P = OFF_Q + NQ * TILE_BYTES;
 constexpr int OFF_RING = OFF_P + NQ * TILE_BYTES;
 constexpr int OFF_BARS = OFF_RING + RING * TILE_BYTES;
 constexpr int ATTN_SMEM_BYTES = OFF_BARS + 256 + 1024;  // + barriers + slack for the 1024-byte alignment
-constexpr int ATTN_THREADS = 32 * (2 + 4 * NQ);
+constexpr int ATTN_THREADS = 128 * (1 + NQ);  // one warpgroup of producer / MMA / idle warps, one per query tile
 static_assert(ATTN_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 
 enum : uint32_t { ST_ATTN_KV_FULL = 7, ST_ATTN_KV_EMPTY = 8, ST_ATTN_ACC_FULL = 9, ST_ATTN_ACC_EMPTY = 10 };
@@ -56,6 +57,11 @@ struct AttnParams {
   float scale_log2;    // softmax scale * log2(e)
   uint32_t* status;
 };
+
+// Register reallocation between warpgroups (all four warps of a group execute the same instruction): the first
+// group keeps 56 registers per thread, the softmax groups grow to 224: 4 x 32 x 56 + 8 x 32 x 224 = 64512 <= 65536.
+__device__ __forceinline__ void regs_shrink() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
+__device__ __forceinline__ void regs_grow() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;"); }
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -123,6 +129,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     *abort_flag = 1;
   };
 
+  if (warp < 4) {
+  regs_shrink();  // (each role's code sits behind its own register setting, so the compiler knows its budget)
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -217,9 +225,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (more) umma_commit(&kv_empty[ik % RING]);
       }
     }
+  }
   } else {
-    // ------------------------------------------------------------------ softmax + output (warps 2..9)
-    const int t = (warp - 2) >> 2;        // query tile of this warp
+    regs_grow();
+    // ------------------------------------------------------------------ softmax + output (warps 4..11)
+    const int t = (warp - 4) >> 2;        // query tile of this warp
     const int quarter = warp & 3;         // TMEM lane quarter this warp may read
     const int r = quarter * 32 + lane;    // row of the tile owned by this thread
     const uint32_t lane_base = tmem_base + (uint32_t(quarter * 32) << 16);
