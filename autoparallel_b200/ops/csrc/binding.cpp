@@ -40,6 +40,7 @@ int apb_embedding_bwd(const void* dy, const long long* ids, float* out_f32, long
                       cudaStream_t st);
 int apb_symm_header_bytes();
 int apb_symm_wait_probe(const uint32_t* flag, unsigned target, unsigned limit_ms, uint32_t* status, cudaStream_t st);
+void apb_symm_use_multicast_once(unsigned long long workspace_multicast_ptr);
 int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank, int n, unsigned epoch, const void* src,
                         void* dst, long long outer, long long inner_bytes, int elem_kind, float scale, long long stage_capacity,
                         uint32_t* status, int num_ctas, unsigned target0, unsigned target1, cudaStream_t st);
@@ -279,6 +280,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_header_bytes", &symm_header_bytes);
   m.def("symm_wait_probe", &symm_wait_probe);
   m.def("symm_collective", &symm_collective);
+  m.def("symm_use_multicast_once", [](int64_t ptr) { apb_symm_use_multicast_once((unsigned long long)ptr); });
   m.def("gemm_fused", &gemm_fused);
   m.def("gemm_fused_ctas", [](int64_t fuse, int64_t M, int64_t N, int64_t comm_ctas) {
     return (int64_t)apb_gemm_fused_ctas((int)fuse, (int)M, (int)N, (int)comm_ctas, num_sms());

@@ -9,6 +9,8 @@
 //            its staging area with 16-byte loads over NVLink - all-gather copies, reduce-scatter
 //            sums in fp32, all-to-all copies the chunk addressed to me;
 //   phase 2  the last CTA to finish raises my "done" flag on every peer.
+// Reduce-scatter has a second form (opt-in) that sums through NVSwitch: one ``multimem.ld_reduce`` on the
+// workspace's multicast address per 16 bytes instead of one load per peer.
 // Flags carry a monotonically increasing epoch, so nothing is ever reset.  Every wait is bounded
 // (~2 s): on expiry the kernel records ST_TIMEOUT_PEER_FLAG in the status word and returns.
 //
@@ -38,7 +40,30 @@ struct CollParams {
   float scale;         // reduce-scatter: result multiplied by this
   uint32_t* status;
   uint32_t target0, target1;  // arrival-counter values that mark the last CTA of phases 0 and 1
+  // reduce-scatter through the switch (NVLS): multicast address of the staging area (bound to every rank's
+  // workspace), or null.  One ``multimem.ld_reduce`` then returns the sum over all ranks, added inside NVSwitch,
+  // instead of n peer loads; this rank's own contribution is read through the same address, so its staging copy
+  // must be complete too (the rank raises its "ready" flag on itself as well).
+  const uint8_t* mc_stage;
 };
+
+__device__ __forceinline__ float4 multimem_sum_f32x4(const void* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+// eight bf16 values, accumulated in fp32 inside the switch, returned as four packed pairs
+__device__ __forceinline__ uint4 multimem_sum_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
 
 template <int MODE>
 __global__ void __launch_bounds__(512) symm_collective_kernel(CollParams p) {
@@ -47,6 +72,7 @@ __global__ void __launch_bounds__(512) symm_collective_kernel(CollParams p) {
   const int n = p.n;
   // bytes of this rank's input
   const long long in_bytes = (MODE == ALL_GATHER) ? p.outer * p.inner_bytes : p.outer * p.inner_bytes * n;
+  const bool nvls = MODE == REDUCE_SCATTER && p.mc_stage != nullptr;
   __shared__ uint32_t ok_s;
   if (threadIdx.x == 0) ok_s = 1u;
   __syncthreads();
@@ -59,7 +85,7 @@ __global__ void __launch_bounds__(512) symm_collective_kernel(CollParams p) {
   if (!ok_s) return;
   coop_copy16(my_stage, p.src, in_bytes, blockIdx.x, gridDim.x);
   if (arrive_is_last(flag_ptr(my_ws, OFF_COUNTERS, 0), p.target0)) {
-    if (threadIdx.x < n && threadIdx.x != p.rank)
+    if (threadIdx.x < n && (threadIdx.x != p.rank || nvls))
       st_release_sys(reinterpret_cast<uint32_t*>(p.peers.base[threadIdx.x] + OFF_READY + p.rank * FLAG_STRIDE), p.epoch);
   }
 
@@ -93,7 +119,7 @@ __global__ void __launch_bounds__(512) symm_collective_kernel(CollParams p) {
     }
   } else {
     // wait for everybody, then read chunk ``rank`` of every peer
-    if (threadIdx.x < n && threadIdx.x != p.rank) {
+    if (threadIdx.x < n && (threadIdx.x != p.rank || nvls)) {
       if (!wait_ge<true>(reinterpret_cast<uint32_t*>(my_ws + OFF_READY + threadIdx.x * FLAG_STRIDE), p.epoch, p.status)) ok_s = 0u;
     }
     __syncthreads();
@@ -107,7 +133,24 @@ __global__ void __launch_bounds__(512) symm_collective_kernel(CollParams p) {
         v = i - o * vec_per;
       }
       const long long src_off = (o * n + p.rank) * p.inner_bytes + (v << 4);
-      if (MODE == REDUCE_SCATTER) {
+      if (MODE == REDUCE_SCATTER && nvls) {
+        if (p.elem_kind == 0) {
+          float4 acc = multimem_sum_f32x4(p.mc_stage + src_off);
+          acc.x *= p.scale; acc.y *= p.scale; acc.z *= p.scale; acc.w *= p.scale;
+          reinterpret_cast<float4*>(p.dst + o * p.inner_bytes)[v] = acc;
+        } else {
+          uint4 raw = multimem_sum_bf16x8(p.mc_stage + src_off);
+          if (p.scale != 1.f) {
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __bfloat1622float2(h[j]);
+              h[j] = __floats2bfloat162_rn(f.x * p.scale, f.y * p.scale);
+            }
+          }
+          reinterpret_cast<uint4*>(p.dst + o * p.inner_bytes)[v] = raw;
+        }
+      } else if (MODE == REDUCE_SCATTER) {
         if (p.elem_kind == 0) {
           float4 xs[MAX_RANKS];
 #pragma unroll
@@ -182,6 +225,10 @@ int apb_symm_wait_probe(const uint32_t* flag, unsigned target, unsigned limit_ms
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
+// Multicast address of the workspace that the NEXT reduce-scatter call should sum through (0 = plain peer loads).
+static unsigned long long g_multicast_base = 0ull;
+void apb_symm_use_multicast_once(unsigned long long workspace_multicast_ptr) { g_multicast_base = workspace_multicast_ptr; }
+
 // peer_ptrs: host array of n workspace base pointers (this process's mappings of every rank's buffer).
 // mode: 0 all-gather, 1 reduce-scatter (sum), 2 all-to-all.  Returns 0 or an error code.
 int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank, int n, unsigned epoch, const void* src,
@@ -196,6 +243,9 @@ int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank,
   p.rank = rank; p.n = n; p.epoch = epoch;
   p.src = static_cast<const uint8_t*>(src); p.dst = static_cast<uint8_t*>(dst);
   p.outer = outer; p.inner_bytes = inner_bytes; p.elem_kind = elem_kind; p.scale = scale; p.status = status; p.target0 = target0; p.target1 = target1;
+  p.mc_stage = (mode == REDUCE_SCATTER && g_multicast_base != 0ull)
+                   ? reinterpret_cast<const uint8_t*>(g_multicast_base) + HEADER_BYTES : nullptr;
+  g_multicast_base = 0ull;  // one call only: the caller names the workspace's multicast address per collective
   if (mode == ALL_GATHER) symm_collective_kernel<ALL_GATHER><<<num_ctas, 512, 0, st>>>(p);
   else if (mode == REDUCE_SCATTER) symm_collective_kernel<REDUCE_SCATTER><<<num_ctas, 512, 0, st>>>(p);
   else if (mode == ALL_TO_ALL) symm_collective_kernel<ALL_TO_ALL><<<num_ctas, 512, 0, st>>>(p);

@@ -46,6 +46,12 @@ class SymmGroup:
         self.ws[: self.header].zero_()
         self.hdl = symm_mem.rendezvous(self.ws, self.group_name)
         self.peer_ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        # NVLS (opt-in, APB200_SYMM_NVLS=1): reduce-scatter sums through the workspace's multicast address with
+        # ``multimem.ld_reduce`` (added inside NVSwitch) instead of n peer loads.  Off by default: not yet timed on
+        # hardware, and a rank that dies while its memory is bound to a multicast object can fault its peers.
+        import os
+
+        self.multicast_ptr = int(getattr(self.hdl, "multicast_ptr", 0) or 0) if os.environ.get("APB200_SYMM_NVLS") == "1" else 0
         torch.cuda.synchronize()
         dist.barrier(self.pg)
         self.epoch = 0
@@ -64,6 +70,8 @@ class SymmGroup:
         self.epoch += 1
         self.arrivals[0] += self.num_ctas
         self.arrivals[1] += self.num_ctas
+        if mode == MODE_RS and self.multicast_ptr:
+            self._C.symm_use_multicast_once(self.multicast_ptr)
         self._C.symm_collective(mode, self.peer_ptrs, self.rank, self.epoch, src, dst, outer, inner_bytes, elem_kind, scale,
                                 self.capacity, self.status, self.num_ctas, self.arrivals[0] & 0xFFFFFFFF,
                                 self.arrivals[1] & 0xFFFFFFFF)
