@@ -99,7 +99,7 @@ ZOO = {
 EVAL_MODE = {"opt", "bart", "whisper"}
 
 
-def plan_one(name, mesh, batch, seq, execute, bf16=False):
+def plan_one(name, mesh, batch, seq, execute, bf16=False, uneven=False):
     import transformers as T
 
     task, make = ZOO[name]
@@ -139,7 +139,7 @@ def plan_one(name, mesh, batch, seq, execute, bf16=False):
         from autoparallel_b200.parallel.frontend.mp_cast import MPPolicy
 
         policy = MPPolicy(torch.bfloat16, torch.float32)
-    with AutoParallel(model, input_fn, mesh, policy) as autop:
+    with AutoParallel(model, input_fn, mesh, policy, uneven_sharding=uneven) as autop:
         autop.add_parameter_memory_constraint()
         autop.add_input_constraints([(Shard(0),) + (Replicate(),) * (mesh.ndim - 1)] * n_in)
         autop.optimize_placement()
@@ -171,6 +171,7 @@ def main():
     ap.add_argument("--seq-len", type=int, default=128)
     ap.add_argument("--execute", action="store_true")
     ap.add_argument("--bf16", action="store_true", help="bf16 compute with fp32 gradient reduction")
+    ap.add_argument("--uneven", action="store_true", help="allow shards of unequal size (try --seq-len 100)")
     a = ap.parse_args()
     shape = tuple(int(x) for x in a.mesh.split(","))
     mesh = fake_mesh(shape, ("dp", "tp")[: len(shape)])
@@ -178,7 +179,7 @@ def main():
     failed = []
     for name in names:
         try:
-            secs, cost, coll = plan_one(name, mesh, a.batch, a.seq_len, a.execute, a.bf16)
+            secs, cost, coll = plan_one(name, mesh, a.batch, a.seq_len, a.execute, a.bf16, a.uneven)
             print(f"PASS {name:12s} {secs:6.1f}s  total {cost['total_us']:10.1f} us  collectives {coll}", flush=True)
         except Exception as e:  # keep going: the point is the list of families that plan
             failed.append(name)
