@@ -588,6 +588,24 @@ def _max_pool(ctx):
     return expand_rows(ctx, [(S(0),) * n, (S(1),) * n])  # windows never cross samples or channels
 
 
+@register_rule(aten.index_put.default)
+def _index_put(ctx):
+    # index_put(self, indices, values, accumulate): rows addressed by the index tensors must be whole on every rank,
+    # so only dims behind a leading block of indexed dims are split; ``values`` follows where it has that dim in full.
+    self_v, values = ctx.in_vals[0], ctx.in_vals[-1]
+    indices = list(ctx.args[1])
+    m = len(indices)
+    if any(i is None for i in indices):
+        return expand_rows(ctx, [])
+    n_idx = len(ctx.in_vals) - 2
+    rows = []
+    for d in range(m, self_v.ndim):
+        vd = values.ndim - (self_v.ndim - d)
+        vpl = S(vd) if vd >= 0 and values.shape[vd] == self_v.shape[d] else R
+        rows.append((S(d), S(d)) + (R,) * n_idx + (vpl,))
+    return expand_rows(ctx, rows)
+
+
 @register_rule(aten.copy.default)
 def _copy(ctx):
     # copy(dst, src) -> src broadcast into dst's shape: split any dim of dst; src follows where it has that dim in full
