@@ -556,13 +556,19 @@ class ShardingOptimizer:
         A = coo_matrix((vals, (rows, cols)), shape=(r, nvar)).tocsr()
         self.timings["build"] = time.perf_counter() - t0
         t1 = time.perf_counter()
+        # Only the node choices are integer variables.  An edge variable z[o, j] is pinned by its row sums (= the
+        # consumer's choice) and column sums (= the producer's choice): with one-hot node choices exactly one entry
+        # is 1, so declaring the edge variables continuous is exact and leaves the branch-and-bound far fewer integers.
+        integrality = np.zeros(nvar)
+        n_node_vars = min(z_off.values()) if z_off else nvar
+        integrality[:n_node_vars] = 1
         options = {"disp": bool(verbose), "presolve": True}
         if self.time_limit is not None:
             options["time_limit"] = float(self.time_limit)
         res = milp(
             c=cost,
             constraints=LinearConstraint(A, np.array(lo), np.array(hi)),
-            integrality=np.ones(nvar),
+            integrality=integrality,
             bounds=Bounds(np.zeros(nvar), ub),
             options=options,
         )
