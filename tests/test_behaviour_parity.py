@@ -236,3 +236,34 @@ def test_norm_as_first_op_on_an_input_without_gradient(mesh_1d):
     pm.to_empty(device="cpu")
     pm(torch.rand(2, 32)).sum().backward()
     assert all(p.grad is not None for p in pm.parameters())
+
+
+def test_strided_factories_get_local_sizes_and_strides(mesh_1d):
+    from autoparallel_b200.parallel.lower.apply import _strides_like
+
+    assert _strides_like([64, 1, 8], [2, 8, 8]) == [64, 1, 8]  # dim order of the original strides is kept
+    assert _strides_like([1, 4], [4, 2]) == [1, 4]
+    assert _strides_like([12, 4, 1], [2, 3, 0]) == [3, 1, 1]   # empty extents count as 1 when accumulating
+
+    class M(nn.Module):
+        def __init__(s):
+            super().__init__()
+            s.l = nn.Linear(16, 16)
+
+        def forward(s, x):
+            y = s.l(x)
+            buf = y.new_empty_strided((x.shape[0], 16), (16, 1))
+            buf.copy_(y)
+            return buf * 2.0
+
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.rand(16, 16), mesh_1d) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.add_output_constraints([(Shard(0),)])
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    pm.to_empty(device="cpu")
+    out = pm(torch.rand(2, 16))
+    assert out.shape == (2, 16)
+    out.sum().backward()
