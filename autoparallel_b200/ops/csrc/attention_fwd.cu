@@ -244,7 +244,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     bool ok = true;
 
     for (int j = 0; j < n_mine; ++j) {
-      if (!mbar_wait(&s_full[t], j & 1, abort_flag)) {
+      // (the TMEM loads below are warp-wide instructions: the warp leaves together or not at all)
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, abort_flag))) {
         fail(ST_ATTN_ACC_FULL);
         ok = false;
         break;
@@ -267,7 +268,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float alpha = fast_exp2(m_run - m_new);  // 0 on the first tile (m_run = -inf)
       // the product of the previous iteration joins the running sum before the frame moves to m_new
       if (j > 0) {
-        if (!mbar_wait(&pv_full[t], (j - 1) & 1, abort_flag)) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&pv_full[t], (j - 1) & 1, abort_flag))) {
           fail(ST_ATTN_ACC_FULL);
           ok = false;
           break;
@@ -314,8 +315,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive(&p_full[t]);
     }
 
-    if (ok && n_mine > 0) {
-      if (!mbar_wait(&pv_full[t], (n_mine - 1) & 1, abort_flag)) {
+    if (ok) {  // (``ok`` is uniform across the warp: every exit above is taken by the whole warp)
+      if (!__all_sync(0xffffffffu, mbar_wait(&pv_full[t], (n_mine - 1) & 1, abort_flag))) {
         fail(ST_ATTN_ACC_FULL);
         ok = false;
       }
