@@ -49,6 +49,17 @@ int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, int M, int N
                    int n, unsigned epoch, int rows_per_shard, const void* shard_src, void* gbuf, long long shard_bytes,
                    uint32_t* landed, unsigned landed_target, int rows_per_rank, float scale, long long stage_capacity,
                    const unsigned* targets, int comm_ctas, uint32_t* status, int num_sms, cudaStream_t stream);
+int apb_dma_flag_bytes();
+int apb_dma_ring_max();
+int apb_dma_barrier(const unsigned long long* flags, int rank, int n, unsigned epoch, uint32_t* status, cudaStream_t st);
+int apb_dma_all_gather(void* dst, const unsigned long long* bases, long long offset, long long outer, long long inner_bytes,
+                       int rank, int n, cudaStream_t st);
+int apb_dma_rs_push(const void* src, const unsigned long long* bases, const unsigned long long* flags, long long stage_offset,
+                    long long slot_bytes, long long chunk_bytes, int entry, int ring, unsigned seq, int rank, int n,
+                    uint32_t* status, cudaStream_t st);
+int apb_dma_rs_sum(const void* src, void* dst, const unsigned long long* bases, const unsigned long long* flags,
+                   long long stage_offset, long long slot_bytes, long long chunk_bytes, int entry, unsigned seq, float scale,
+                   int rank, int n, int num_ctas, uint32_t* status, cudaStream_t st);
 int apb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Sk, int H, int Hkv,
                       int D, int causal, float scale, uint32_t* status, cudaStream_t stream);
 int apb_adamw(const void* tensors_dev, const void* chunks_dev, int num_chunks, float lr, float beta1, float beta2, float eps,
@@ -251,9 +262,58 @@ void gemm_fused(int64_t fuse, const at::Tensor& a, const at::Tensor& b, at::Tens
         "apb_gemm_fused");
 }
 
+// ------------------------------------------------------------------ copy-engine collectives (dma_comm.cu)
+std::vector<unsigned long long> u64(const std::vector<int64_t>& v) { return std::vector<unsigned long long>(v.begin(), v.end()); }
+
+void dma_barrier(const std::vector<int64_t>& flags, int64_t rank, int64_t epoch, at::Tensor& status) {
+  c10::cuda::CUDAGuard g(status.device());
+  auto f = u64(flags);
+  check(apb_dma_barrier(f.data(), (int)rank, (int)f.size(), (unsigned)epoch, reinterpret_cast<uint32_t*>(status.data_ptr()), stream()),
+        "apb_dma_barrier");
+}
+
+void dma_all_gather(at::Tensor& dst, const std::vector<int64_t>& bases, int64_t offset, int64_t outer, int64_t inner_bytes,
+                    int64_t rank) {
+  c10::cuda::CUDAGuard g(dst.device());
+  auto b = u64(bases);
+  TORCH_CHECK(dst.is_contiguous() && (int64_t)dst.nbytes() == outer * inner_bytes * (int64_t)b.size(), "dma_all_gather: output size");
+  check(apb_dma_all_gather(dst.data_ptr(), b.data(), offset, outer, inner_bytes, (int)rank, (int)b.size(), stream()),
+        "apb_dma_all_gather");
+}
+
+void dma_rs_push(const at::Tensor& src, const std::vector<int64_t>& bases, const std::vector<int64_t>& flags, int64_t stage_offset,
+                 int64_t slot_bytes, int64_t entry, int64_t ring, int64_t seq, int64_t rank, at::Tensor& status) {
+  c10::cuda::CUDAGuard g(src.device());
+  auto b = u64(bases), f = u64(flags);
+  TORCH_CHECK(src.is_contiguous() && src.nbytes() % b.size() == 0, "dma_rs_push: contiguous input of n equal chunks");
+  check(apb_dma_rs_push(src.data_ptr(), b.data(), f.data(), stage_offset, slot_bytes, (long long)(src.nbytes() / b.size()), (int)entry,
+                        (int)ring, (unsigned)seq, (int)rank, (int)b.size(), reinterpret_cast<uint32_t*>(status.data_ptr()), stream()),
+        "apb_dma_rs_push");
+}
+
+void dma_rs_sum(const at::Tensor& src, at::Tensor& dst, const std::vector<int64_t>& bases, const std::vector<int64_t>& flags,
+                int64_t stage_offset, int64_t slot_bytes, int64_t entry, int64_t seq, double scale, int64_t rank, int64_t num_ctas,
+                at::Tensor& status) {
+  c10::cuda::CUDAGuard g(src.device());
+  auto b = u64(bases), f = u64(flags);
+  TORCH_CHECK(src.scalar_type() == at::kFloat && dst.scalar_type() == at::kFloat && src.is_contiguous() && dst.is_contiguous(),
+              "dma_rs_sum: contiguous fp32 tensors");
+  TORCH_CHECK(dst.nbytes() * b.size() == src.nbytes(), "dma_rs_sum: output is one of n equal chunks");
+  check(apb_dma_rs_sum(src.data_ptr(), dst.data_ptr(), b.data(), f.data(), stage_offset, slot_bytes, (long long)dst.nbytes(), (int)entry,
+                       (unsigned)seq, (float)scale, (int)rank, (int)b.size(), (int)num_ctas,
+                       reinterpret_cast<uint32_t*>(status.data_ptr()), stream()),
+        "apb_dma_rs_sum");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("dma_flag_bytes", []() { return (int64_t)apb_dma_flag_bytes(); });
+  m.def("dma_ring_max", []() { return (int64_t)apb_dma_ring_max(); });
+  m.def("dma_barrier", &dma_barrier);
+  m.def("dma_all_gather", &dma_all_gather);
+  m.def("dma_rs_push", &dma_rs_push);
+  m.def("dma_rs_sum", &dma_rs_sum);
   m.def("gemm", &gemm);
   m.def("gemm_grouped", &gemm_grouped);
   m.def("gemm_set_pair_mode", [](bool on) { apb_gemm_set_pair_mode(on ? 1 : 0); });

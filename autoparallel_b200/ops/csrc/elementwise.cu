@@ -501,6 +501,7 @@ int apb_adamw(const void* tensors_dev, const void* chunks_dev, int num_chunks, f
 // ------------------------------------------------------------------------------------------------
 // Allocation-free RMSNorm backward (see apb_noalloc.h for the contract).
 // ------------------------------------------------------------------------------------------------
+#include <atomic>
 #include <mutex>
 
 #include "apb_noalloc.h"
@@ -512,14 +513,16 @@ static __device__ __align__(256) float g_noalloc_dw_acc[APB_NOALLOC_MAX_D];
 
 namespace {
 constexpr int kMaxDevices = 64;
-float* g_noalloc_ptr[kMaxDevices] = {};
+// The pointer is published with a release store after the SM count has been written, and read with
+// an acquire load: a thread that sees the pointer also sees the count, without taking the mutex.
+std::atomic<float*> g_noalloc_ptr[kMaxDevices] = {};
 int g_noalloc_sms[kMaxDevices] = {};
 std::mutex g_noalloc_mutex;
 
 // One-time per-device set-up; the caller's current device is the one being set up.
 int noalloc_setup(int dev) {
   std::lock_guard<std::mutex> lock(g_noalloc_mutex);
-  if (g_noalloc_ptr[dev] != nullptr) return APB_NOALLOC_OK;
+  if (g_noalloc_ptr[dev].load(std::memory_order_acquire) != nullptr) return APB_NOALLOC_OK;
   float* p = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dw_acc) != cudaSuccess || p == nullptr) {
     (void)cudaGetLastError();
@@ -531,7 +534,7 @@ int noalloc_setup(int dev) {
     return APB_NOALLOC_ERR_SETUP;
   }
   g_noalloc_sms[dev] = sms;
-  g_noalloc_ptr[dev] = p;
+  g_noalloc_ptr[dev].store(p, std::memory_order_release);
   return APB_NOALLOC_OK;
 }
 }  // namespace
@@ -542,11 +545,12 @@ extern "C" int apb_rms_norm_bwd_noalloc(const void* dy, const void* x, const voi
   if (D > APB_NOALLOC_MAX_D) return APB_NOALLOC_ERR_TOO_LARGE;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return APB_NOALLOC_ERR_SETUP;
-  if (g_noalloc_ptr[dev] == nullptr) {
+  float* acc = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (acc == nullptr) {
     const int e = noalloc_setup(dev);
     if (e != APB_NOALLOC_OK) return e;
+    acc = g_noalloc_ptr[dev].load(std::memory_order_acquire);
   }
-  float* acc = g_noalloc_ptr[dev];
   const int num_sms = g_noalloc_sms[dev];
   // the array keeps the previous call's sums: start from zero
   if (cudaMemsetAsync(acc, 0, sizeof(float) * D, st) != cudaSuccess) return APB_NOALLOC_ERR_LAUNCH;

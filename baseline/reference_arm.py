@@ -5,8 +5,17 @@ Nothing of this framework is on that path: the model is the reference's own Llam
 (``autoparallel._testing.models.llama3.Transformer``), compute is ATen / cuBLAS / cuDNN, collectives
 are c10d functional collectives on NCCL, the optimizer is ``torch.optim.AdamW``.  The only foreign
 piece is ``baseline/shims/pulp.py``: the reference needs PuLP + the CBC binary for its ILP, neither
-exists in this offline image, so a PuLP-compatible layer over HiGHS stands in for the *solver*.
-If anything in the reference fails to import or run here, one ``unavailable`` line is printed.
+exists in this offline image, so a PuLP-compatible layer over HiGHS stands in for the *solver*;
+and ``baseline/shims/torch_compat.py``, which adds to torch 2.11 the few private DTensor symbols of
+the newer nightly the reference was written against (listed in the printed line).  The reference's
+source is never edited.
+
+Execution follows the reference's own driver (``examples/example_llama3.py``): the parallel module
+is wrapped in ``torch.compile(..., backend=autoparallel_backend(enable_ac=False))``.  If that
+configuration cannot run here the arm falls back, in order, to the same backend with the
+reference's activation-checkpointing pass on (what one GPU needs to hold an 8B model with fp32
+optimizer state) and to the eager module that ``apply_placement`` returns; the mode that ran is
+printed.  If anything in the reference fails to import or run, one ``unavailable`` line is printed.
 """
 from __future__ import annotations
 
@@ -19,6 +28,16 @@ import traceback
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def _free_port() -> int:
+    """A TCP port that is free right now (single-process rendezvous on 127.0.0.1; a fixed port collides
+    when two jobs share a host).  Under torchrun MASTER_PORT is already set and this is not used."""
+    import socket
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def _unavailable(why: str) -> None:
     if int(os.environ.get("RANK", 0)) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why[:300]}), flush=True)
@@ -29,12 +48,12 @@ def run(args) -> None:
     if not os.path.isdir(os.path.join(ref, "autoparallel")):
         return _unavailable("reference is not installed under baseline/_ref")
     sys.path.insert(0, ref)
+    sys.path.append(os.path.join(HERE, "shims"))  # last: a real PuLP, if ever installed, wins over the shim
     try:
-        import pulp  # noqa: F401
-    except ImportError:
-        sys.path.insert(0, os.path.join(HERE, "shims"))
-    try:
-        _run(args)
+        import torch_compat
+
+        shimmed = list(torch_compat.install())
+        _run(args, shimmed)
     except Exception as e:  # the reference could not run in this image
         tb = traceback.format_exc().strip().splitlines()
         where = next((l.strip() for l in reversed(tb) if "autoparallel" in l and "File" in l), "")
@@ -48,7 +67,21 @@ def run(args) -> None:
             pass
 
 
-def _run(args) -> None:
+def _attempts(mode: str):
+    """(label, compiled?, enable_ac) in the order tried."""
+    table = {
+        "compile": [("torch.compile + autoparallel_backend(enable_ac=False)", True, False)],
+        "compile_ac": [("torch.compile + autoparallel_backend(enable_ac=True)", True, True)],
+        "eager": [("eager module from apply_placement", False, False)],
+    }
+    if mode in table:
+        return table[mode]
+    return table["compile"] + table["compile_ac"] + table["eager"]
+
+
+def _run(args, shimmed) -> None:
+    import gc
+
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F
@@ -66,7 +99,7 @@ def _run(args) -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local_rank)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29500")
+    os.environ.setdefault("MASTER_PORT", str(_free_port()))
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
     mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
     S = args.seq_len
@@ -81,7 +114,7 @@ def _run(args) -> None:
 
     mp_policy = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
     t0 = time.perf_counter()
-    with AutoParallel(model, input_fn, mesh, mp_policy) as autop:
+    with AutoParallel(model, input_fn, mesh, mp_policy, repeated_subgraphs=True) as autop:
         autop.add_parameter_memory_constraint(low=None, high=None)
         autop.add_input_constraints([(Shard(0),)])
         autop.add_output_constraints([(Shard(0),)])
@@ -92,19 +125,57 @@ def _run(args) -> None:
     plan_s = time.perf_counter() - t0
     parallel_mod.to_empty(device="cuda")
     parallel_mod.init_weights()
-    opt = torch.optim.AdamW(parallel_mod.parameters(), lr=3e-4, weight_decay=0.1)
+    try:
+        opt = torch.optim.AdamW(parallel_mod.parameters(), lr=3e-4, weight_decay=0.1, fused=True)
+        opt_name = "torch.optim.AdamW(fused=True)"
+    except Exception:
+        opt = torch.optim.AdamW(parallel_mod.parameters(), lr=3e-4, weight_decay=0.1)
+        opt_name = "torch.optim.AdamW"
     g = torch.Generator(device="cpu").manual_seed(1234 + rank)
     host = [(torch.randint(0, margs.vocab_size, (1, S), generator=g).pin_memory(),
              torch.randint(0, margs.vocab_size, (1, S), generator=g).pin_memory()) for _ in range(4)]
     devs = [(t.cuda(), l.cuda()) for t, l in host]
 
+    state = {"mod": parallel_mod}
+
     def step(tok, lab):
-        logits = parallel_mod(tok)
+        logits = state["mod"](tok)
         loss = F.cross_entropy(logits.flatten(0, 1).float(), lab.flatten())
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)
         return loss
+
+    # choose the first execution mode that completes one optimizer step on every rank
+    mode_ran, errors = None, []
+    for label, compiled, enable_ac in _attempts(os.environ.get("APB_REF_MODE", args.ref_mode if hasattr(args, "ref_mode") else "auto")):
+        ok = 1
+        try:
+            if compiled:
+                from autoparallel import autoparallel_backend
+
+                torch._dynamo.reset()
+                state["mod"] = torch.compile(parallel_mod, backend=autoparallel_backend(enable_ac=enable_ac))
+            else:
+                state["mod"] = parallel_mod
+            step(*devs[0])
+            torch.cuda.synchronize()
+        except Exception as e:  # out of memory, or a part of Inductor this torch does not have
+            ok = 0
+            errors.append(f"{label}: {type(e).__name__}: {str(e)[:120]}")
+            opt.zero_grad(set_to_none=True)
+            del e
+        flag = torch.tensor([ok], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 1:
+            mode_ran = label
+            break
+        state["mod"] = None
+        gc.collect()
+        torch.cuda.empty_cache()
+    if mode_ran is None:
+        raise RuntimeError("no execution mode of the reference ran: " + " | ".join(errors))
+    torch.cuda.reset_peak_memory_stats()
 
     def step_device(i):
         return step(*devs[i % 4])
@@ -146,11 +217,16 @@ def _run(args) -> None:
             "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "impl": "reference",
             "config": {"model": "llama3_8b" if not args.layers else f"llama3_8b[{args.layers} layers]", "global_batch": B_global, "seq_len": S,
-                       "parallelism": f"dp{world} (reference ILP; eager apply_placement; NCCL + cuBLAS/cuDNN)",
-                       "optimizer": "torch.optim.AdamW", "ilp_backend": "HiGHS behind a PuLP-compatible shim (CBC/PuLP absent offline)"},
+                       "parallelism": f"dp{world} (reference ILP; NCCL + cuBLAS/cuDNN)",
+                       "execution": mode_ran, "modes_that_failed": errors,
+                       "optimizer": opt_name, "ilp_backend": "HiGHS behind a PuLP-compatible shim (CBC/PuLP absent offline)",
+                       "torch_compat_shims": shimmed,
+                       "l2": "no explicit flush: per-step working set >> 126 MB L2"},
             "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": 2 * S * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": 0, "clocks": clocks, "ilp_solve_s": ilp_s, "plan_total_s": round(plan_s, 2),
             "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 1), "final_loss": float(last),
         }), flush=True)
+    if getattr(args, "kernel_table", None):
+        bench.write_kernel_table(args.kernel_table, step_device, rank)
     dist.destroy_process_group()

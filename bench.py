@@ -30,12 +30,28 @@ if ROOT not in sys.path:
 BASELINE_TOKENS_PER_S = None  # the reference publishes no throughput number
 
 
+def _free_port() -> int:
+    """A TCP port that is free right now (single-process rendezvous on 127.0.0.1; a fixed port collides
+    when two jobs share a host).  Under torchrun MASTER_PORT is already set and this is not used."""
+    import socket
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ref-mode", default="auto", choices=["auto", "compile", "compile_ac", "eager"],
+                    help="reference arm only: auto tries the reference driver's torch.compile backend, then the same with its "
+                         "activation-checkpointing pass, then the eager module")
+    ap.add_argument("--kernel-table", default=None, metavar="PATH",
+                    help="after the timed regions, run ONE more step under torch.profiler and write the device time per "
+                         "kernel name (JSON) to PATH; never part of a reported number")
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "llama3_debug", "llama3_1b"])
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=None, help="debugging only: override the layer count (invalidates the metric)")
@@ -117,6 +133,34 @@ class ClockSampler:
         }
 
 
+def write_kernel_table(path, step_fn, rank):
+    """One step under torch.profiler (after all timing); device time aggregated per kernel name."""
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step_fn(0)
+        torch.cuda.synchronize()
+    if rank != 0:
+        return
+    agg = collections.defaultdict(lambda: [0, 0.0])
+    t_min, t_max = None, None
+    for ev in prof.events():
+        if ev.device_type.name != "CUDA" and "cuda" not in str(ev.device_type).lower():
+            continue
+        dur = float(getattr(ev, "device_time_total", 0.0) or getattr(ev, "cuda_time_total", 0.0) or 0.0)
+        if dur <= 0:
+            continue
+        agg[ev.name][0] += 1
+        agg[ev.name][1] += dur
+    rows = sorted(({"kernel": k, "launches": n, "total_us": round(t, 1)} for k, (n, t) in agg.items()), key=lambda r: -r["total_us"])
+    with open(path, "w") as f:
+        json.dump({"sum_of_kernel_us": round(sum(r["total_us"] for r in rows), 1), "kernels": rows}, f, indent=1)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -135,7 +179,7 @@ def run_ours(args):
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}"
     torch.cuda.set_device(local_rank)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29500")
+    os.environ.setdefault("MASTER_PORT", str(_free_port()))
     reserve = args.reserve_sms
     if reserve is None:
         # hybrid: NCCL kernels and peer-waiting fused kernels share the GPU, so NCCL gets SMs of its own
@@ -335,6 +379,8 @@ def run_ours(args):
             "final_loss": float(last_e2e),
         }
         print(json.dumps(out), flush=True)
+    if args.kernel_table:
+        write_kernel_table(args.kernel_table, step_device, rank)
     dist.destroy_process_group()
 
 

@@ -10,6 +10,8 @@ import sys
 import pytest
 import torch
 
+from conftest import free_port
+
 pytestmark = pytest.mark.gpu
 
 WORKER = r'''
@@ -64,7 +66,7 @@ def test_symm_collectives_match_nccl(tmp_path):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     r = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-         "--master-port", "29571", str(script)],
+         "--master-port", str(free_port()), str(script)],
         env=env, capture_output=True, text=True, timeout=300,
     )
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
@@ -130,7 +132,7 @@ def test_fused_gemm_collectives(tmp_path):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     r = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-         "--master-port", "29572", str(script)],
+         "--master-port", str(free_port()), str(script)],
         env=env, capture_output=True, text=True, timeout=300,
     )
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

@@ -73,3 +73,58 @@ def test_rejects_width_beyond_builtin_array(lib):
     )
     assert rc == 7
     assert b"16384" in lib.apb_noalloc_strerror(rc)
+
+
+def _reference(dy, x, w, rstd):
+    from autoparallel_b200.ops import library as L
+
+    return L.ops.rms_norm_bwd(dy, x, w, rstd)
+
+
+def test_no_rows_gives_zero_weight_gradient(lib):
+    """An empty batch must still clear what an earlier call left in the built-in array."""
+    from autoparallel_b200.ops import library as L
+
+    D = 1024
+    x = torch.randn(64, D, device="cuda")
+    w = torch.randn(D, device="cuda")
+    _, rstd = L.ops.rms_norm(x, w, 1e-5)
+    _call(lib, torch.randn_like(x), x, w, rstd)  # leaves non-zero sums behind
+    empty = torch.empty(0, D, device="cuda")
+    _, dw = _call(lib, empty, empty, w, torch.empty(0, device="cuda"))
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(dw).item() == 0
+
+
+def test_width_changes_between_calls(lib):
+    """4096 -> 1024 -> 4096 on one stream: every call only trusts the part of the array it cleared."""
+    from autoparallel_b200.ops import library as L
+
+    torch.manual_seed(1)
+    for D in (4096, 1024, 4096):
+        x = torch.randn(257, D, device="cuda")
+        w = torch.randn(D, device="cuda")
+        dy = torch.randn(257, D, device="cuda")
+        _, rstd = L.ops.rms_norm(x, w, 1e-5)
+        ref_dx, ref_dw = _reference(dy, x, w, rstd)
+        dx, dw = _call(lib, dy, x, w, rstd)
+        torch.cuda.synchronize()
+        assert torch.allclose(dx, ref_dx, rtol=1e-5, atol=1e-5)
+        assert torch.allclose(dw, ref_dw, rtol=1e-3, atol=1e-3)
+
+
+def test_widest_supported_row_in_bf16(lib):
+    """D = 16384 is the last width the built-in array covers; bf16 takes the cast path on the way out."""
+    from autoparallel_b200.ops import library as L
+
+    torch.manual_seed(2)
+    rows, D = 33, 16384
+    x = torch.randn(rows, D, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(D, device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn(rows, D, device="cuda", dtype=torch.bfloat16)
+    _, rstd = L.ops.rms_norm(x, w, 1e-5)
+    ref_dx, ref_dw = _reference(dy, x, w, rstd)
+    dx, dw = _call(lib, dy, x, w, rstd)
+    torch.cuda.synchronize()
+    assert torch.allclose(dx.float(), ref_dx.float(), rtol=2e-2, atol=2e-2)
+    assert torch.allclose(dw.float(), ref_dw.float(), rtol=2e-2, atol=0.16)
