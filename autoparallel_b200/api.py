@@ -40,7 +40,7 @@ from .parallel.lower.apply import LoweredGraph, lower_to_local_graph
 from .parallel.lower.init_weights import wrap_init_weights
 from .parallel.lower.module_build import make_parallel_module
 from .parallel.lower.partition import extract_forward, partition_joint
-from .parallel.passes.act_ckpt import apply_activation_checkpointing, mark_fsdp_recompute
+from .parallel.passes.act_ckpt import apply_activation_checkpointing, apply_user_checkpoint_tags, mark_fsdp_recompute
 from .parallel.solver.ilp import InfeasibleError, ShardingOptimizer
 
 logger = logging.getLogger(__name__)
@@ -102,6 +102,10 @@ class AutoParallel:
         self.repeated_subgraphs = repeated_subgraphs
         self.cost_model = cost_model
         self.activation_checkpointing = activation_checkpointing
+        #: "full" checkpointing: bytes of activations per recomputation stage (None = square-root rule)
+        self.ac_stage_bytes: Optional[int] = None
+        self.user_ac_stats: dict = {}
+        self.ac_stats: dict = {}
         self.plan_device = plan_device
         self.fuse_collectives = fuse_collectives
         self.bucket_collectives = bucket_collectives
@@ -197,8 +201,23 @@ class AutoParallel:
             raise RuntimeError("this AutoParallel context has exited; it is not re-entrant")
 
     # ------------------------------------------------------------------ constraints
-    def add_parameter_memory_constraint(self, low: Optional[float] = None, high: Optional[float] = None):
+    def add_parameter_memory_constraint(self, low: Optional[float] = None, high: Optional[float] = None, *,
+                                        budget_bytes: Optional[float] = None, bytes_per_element: float = 16.0):
+        """Bound how much of the parameters every rank holds.
+
+        ``(low, high)`` is the reference's form (autoparallel/api.py: bounds on the mean per-parameter shard
+        ratio; ``high`` defaults to ``1 / mesh.size()``, i.e. fully sharded).  ``budget_bytes`` states the bound in
+        bytes instead: the per-rank bytes of parameter state, ``sum over parameters of (elements held locally x
+        bytes_per_element)``, must not exceed it.  ``bytes_per_element`` is the state kept per parameter element -
+        16 for an fp32 master copy, an fp32 gradient and two fp32 Adam moments, 18 with a bf16 copy on top - so
+        "fit the optimizer state of a 70B model into 180 GB per GPU" is ``budget_bytes=180e9 - activations``."""
         self._assert_entered()
+        if budget_bytes is not None:
+            if low is not None or high is not None:
+                raise ValueError("give either (low, high) or budget_bytes, not both")
+            if budget_bytes <= 0 or bytes_per_element <= 0:
+                raise ValueError("budget_bytes and bytes_per_element must be positive")
+            return self.sharding_optimizer.add_parameter_bytes_constraint(float(budget_bytes), float(bytes_per_element))
         low = 0.0 if low is None else low
         high = 1.0 / self.mesh.size() if high is None else high
         if low > high:
@@ -264,8 +283,10 @@ class AutoParallel:
             fuse = symm.enabled_for_mesh(self.mesh)
         if fuse:
             # "all" also fuses gathers along the contraction dim (kept apart by default: they cannot overlap tile by tile)
+            # "reductions" rewrites GEMM -> reduce-scatter only (parameter gathers stay separate nodes)
             self.fusion_stats = fuse_collectives(lowered.gm, lowered.joint.tangent_nodes, self.reshard_after_forward,
-                                                 fuse_contraction_gather=(fuse == "all"))
+                                                 fuse_contraction_gather=(fuse == "all"),
+                                                 patterns=("mm_rs",) if fuse == "reductions" else ("ag_mm", "mm_rs"))
             changed += sum(self.fusion_stats.values())
         if self.bucket_collectives:
             from .parallel.passes.bucketing import bucket_collectives
@@ -275,8 +296,12 @@ class AutoParallel:
         if changed:
             lowered.joint = index_joint_graph(lowered.gm, joint.traced_inputs, joint.out_spec)
         mark_fsdp_recompute(lowered.joint, self.reshard_after_forward)
+        # regions the user wrapped in torch.utils.checkpoint (with or without a selective policy) come first;
+        # the framework's own policy below never touches a node the user has tagged
+        self.user_ac_stats = apply_user_checkpoint_tags(lowered.joint)
         if self.activation_checkpointing != "none":
-            apply_activation_checkpointing(lowered.joint, self.activation_checkpointing)
+            self.ac_stats = apply_activation_checkpointing(lowered.joint, self.activation_checkpointing,
+                                                           stage_bytes=self.ac_stage_bytes)
         return lowered
 
     def _build_runtime(self, joint: JointGraph, lowered: LoweredGraph, executor, overlap_config):
@@ -306,9 +331,12 @@ class AutoParallel:
         solved = self.sharding_placement if sharding_placement is None else sharding_placement
         planner = self
 
+        #: the specialisation of the planned shapes; replaced when activation checkpointing is reconfigured
+        current = {"entry": (runtime, expected, traced, out_spec)}
+
         def forward(module, *args, **kwargs):
             flat = input_utils.flatten_call(traced, args, kwargs)
-            entry = (runtime, expected, traced, out_spec)
+            entry = current["entry"]
             if planner.dynamic:
                 key = planner._shape_key_of_call(flat, expected)
                 entry = specializations.get(key)
@@ -330,7 +358,29 @@ class AutoParallel:
                 return tree_unflatten(list(outs), ospec)
             return outs[0] if len(outs) == 1 else tuple(outs)
 
+        def set_activation_checkpointing(mode: str, stage_size_in_GiB: Optional[float] = None) -> dict:
+            """Re-partition the lowered graph under another activation-checkpointing policy (same placements, same
+            parameters): ``mode`` as in the constructor, ``stage_size_in_GiB`` the stage length of the "full" mode."""
+            planner.activation_checkpointing = mode
+            planner.ac_stage_bytes = None if stage_size_in_GiB is None else max(1, int(stage_size_in_GiB * 2**30))
+            with planner.mesh:
+                new_lowered = planner._lower(planner.joint, solved)
+                rt, exp, tr, ospec, new_parts = planner._build_runtime(planner.joint, new_lowered, executor, overlap_config)
+            planner.partitioned = new_parts
+            current["entry"] = (rt, exp, tr, ospec)
+            specializations.clear()
+            specializations[planner._shape_key(exp)] = current["entry"]
+            module.__dict__["_apb200_runtime"] = rt
+            module.__dict__["_apb200_lowered"] = new_lowered
+            module.__dict__["_apb200_ac_mode"] = mode
+            return {"mode": mode, "saved_bytes": new_parts.saved_bytes, "num_saved": new_parts.num_saved}
+
         module = make_parallel_module(self.model, sharded_params, sharded_buffers, forward)
+        module.__dict__["set_activation_checkpointing"] = set_activation_checkpointing
+        module.__dict__["_apb200_ac_mode"] = self.activation_checkpointing
+        from . import compile as _compile
+
+        _compile.register_parallel_module(module)
         module.__dict__["_apb200_runtime"] = runtime
         module.__dict__["_apb200_lowered"] = lowered
         module.__dict__["_apb200_specializations"] = specializations

@@ -1,11 +1,18 @@
 """CUDA implementations of the ``apb200`` operators on the in-tree sm_100a extension.
 
-Loaded on first use of an op with a CUDA tensor.  There is no silent fallback: if the extension
-is missing on a machine with a GPU the op raises, and fp32 GEMMs – which the tcgen05 kernel does
-not take – are the only case routed to a library call (``torch.matmul``), stated here.
+Loaded on first use of an op with a CUDA tensor.  If the extension is missing on a machine with a
+GPU the op raises.  A few inputs are outside what the kernels take and are answered by a library
+call instead; each such call is counted in ``library_fallbacks`` (printed by ``bench.py``) and the
+first of each kind is logged once, so a run never uses a library path without saying so:
 
-Attention currently runs through PyTorch's fused SDPA kernels (library call) behind the
-``apb200::attention`` schema; every other operator below is this framework's own kernel.
+* ``gemm``          operands that are not bf16 (fp32 / fp16 models), or row strides that are not a
+                    multiple of 16 bytes (TMA cannot address them) -> ``torch.matmul``
+* ``grouped_gemm``  the same conditions for the expert GEMMs -> the PyTorch composition
+* ``cast``          dtype pairs other than fp32 <-> bf16, or unaligned / strided inputs -> ``Tensor.to``
+* ``attention``     the fused-attention library kernel (cuDNN) when the own kernel is not selected
+
+``APB200_DIAG_LIBRARY_GEMM=1`` sends every GEMM to the library (a diagnostic for comparing power and
+time of a whole step; counted like any other fallback).
 """
 from __future__ import annotations
 
@@ -22,6 +29,18 @@ _lock = threading.Lock()
 _status: dict[int, torch.Tensor] = {}
 _scratch: dict[tuple, torch.Tensor] = {}
 launch_count = 0  # kernels of this extension launched since import (bench bookkeeping)
+#: calls answered by a library kernel instead of this extension's, by kind
+library_fallbacks: dict[str, int] = {}
+_DIAG_LIBRARY_GEMM = os.environ.get("APB200_DIAG_LIBRARY_GEMM") == "1"
+
+
+def _fallback(kind: str, why: str) -> None:
+    n = library_fallbacks.get(kind, 0)
+    library_fallbacks[kind] = n + 1
+    if n == 0:
+        import logging
+
+        logging.getLogger("autoparallel_b200").warning("library fallback for %s: %s (counted in cuda_impl.library_fallbacks)", kind, why)
 
 STATUS_NAMES = {
     0: "ok",
@@ -108,9 +127,12 @@ def gemm_raw(a2: torch.Tensor, b2: torch.Tensor, a_mn: bool, b_mn: bool, out_dty
     """C[M,N] = opA @ opB on the tcgen05 kernel.  a2: [M,K] or [K,M] if a_mn; b2: [N,K] or [K,N] if b_mn."""
     M = a2.shape[1] if a_mn else a2.shape[0]
     N = b2.shape[1] if b_mn else b2.shape[0]
-    if a2.dtype != torch.bfloat16 or b2.dtype != torch.bfloat16 or (a2.shape[1] % 8) or (b2.shape[1] % 8) or (N % 8):
+    if (_DIAG_LIBRARY_GEMM or a2.dtype != torch.bfloat16 or b2.dtype != torch.bfloat16 or (a2.shape[1] % 8) or (b2.shape[1] % 8)
+            or (N % 8)):
         # fp32 / fp16 operands, or row strides TMA cannot address (not multiples of 16 bytes):
         # library GEMM (not a tensor-core path of this framework)
+        _fallback("gemm", f"dtypes {a2.dtype}/{b2.dtype}, shapes {tuple(a2.shape)} {tuple(b2.shape)}"
+                  + (" [APB200_DIAG_LIBRARY_GEMM]" if _DIAG_LIBRARY_GEMM else ""))
         A = a2.t() if a_mn else a2
         B = b2 if b_mn else b2.t()
         if out_dtype == torch.float32 and A.dtype != torch.float32:
@@ -148,6 +170,7 @@ def _grouped_mm(a, b, trans_b, out_dtype):
     if not _grouped_ok(a, b) or n % 8 or out_dtype not in (torch.bfloat16, torch.float32):
         from .moe_ops import _grouped_mm as ref
 
+        _fallback("grouped_gemm", f"dtypes {a.dtype}/{b.dtype}, shapes {tuple(a.shape)} {tuple(b.shape)}")
         return ref(a, b, trans_b, out_dtype)
     c = torch.empty((a.shape[0], a.shape[1], n), dtype=out_dtype, device=a.device)
     _C.gemm_grouped(a.contiguous(), b.contiguous(), c, False, not trans_b, status_buffer(a.device))
@@ -160,6 +183,7 @@ def _grouped_mm_wgrad(a, b, out_dtype):
     if not _grouped_ok(a, b) or out_dtype not in (torch.bfloat16, torch.float32):
         from .moe_ops import _grouped_mm_wgrad as ref
 
+        _fallback("grouped_gemm", f"wgrad dtypes {a.dtype}/{b.dtype}, shapes {tuple(a.shape)} {tuple(b.shape)}")
         return ref(a, b, out_dtype)
     c = torch.empty((a.shape[0], a.shape[2], b.shape[2]), dtype=out_dtype, device=a.device)
     _C.gemm_grouped(a.contiguous(), b.contiguous(), c, True, True, status_buffer(a.device))
@@ -182,6 +206,7 @@ def _dtype_cast(x, dtype):
         _C.cast(x, out)
         _count()
         return out
+    _fallback("cast", f"{x.dtype} -> {dtype}, contiguous={x.is_contiguous()}")
     return x.to(dtype)
 
 
@@ -286,6 +311,7 @@ def _attention(q, k, v, causal, scale):
         res = attention_forward_own(q, k, v, causal, scale)
         if res is not None:
             return res
+    _fallback("attention", f"forward on the {ATTENTION_BACKEND} library kernel")
     rep = q.shape[2] // k.shape[2]
     if ATTENTION_BACKEND == "cudnn":
         rep = 1  # cuDNN takes grouped-query heads natively
@@ -302,6 +328,7 @@ def _attention(q, k, v, causal, scale):
 
 
 def _attention_bwd(dout, q, k, v, out, lse, causal, scale):
+    _fallback("attention_bwd", f"backward on the {ATTENTION_BACKEND} library kernel")
     rep = q.shape[2] // k.shape[2]
     if ATTENTION_BACKEND == "cudnn":
         rep = 1

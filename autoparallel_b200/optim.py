@@ -24,13 +24,17 @@ class AdamW(torch.optim.Optimizer):
     CHUNK = 65536
 
     def __init__(self, params: Iterable, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, grad_scale: float = 1.0,
-                 emit_bf16: bool = False):
+                 emit_bf16: bool = False, shadow_arena=None):
         """``emit_bf16``: also write every updated fp32 parameter as bf16 into a shadow buffer that
-        ``apb200::dtype_cast`` hands out in place of a cast (ops/shadow.py); costs 2 bytes per parameter."""
+        ``apb200::dtype_cast`` hands out in place of a cast (ops/shadow.py); costs 2 bytes per parameter.
+        ``shadow_arena`` (``runtime.dma.PeerArena``): the shadows are allocated inside the peer-addressable arena, so
+        that parameter all-gathers can be served by the copy engines; ``step()`` then brackets the update with two
+        arena barriers (no peer may still be reading the old shards, none may read the new ones too early)."""
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self.grad_scale = grad_scale
         self.emit_bf16 = emit_bf16
+        self.shadow_arena = shadow_arena if emit_bf16 else None
         self._shadows: dict = {}
         self._tables: dict = {}
 
@@ -38,7 +42,14 @@ class AdamW(torch.optim.Optimizer):
         lp = _local(p)
         sh = self._shadows.get(id(p))
         if sh is None or sh.shape != lp.shape or sh.device != lp.device:
-            sh = torch.empty_like(lp, dtype=torch.bfloat16)
+            sh = None
+            if self.shadow_arena is not None and lp.is_cuda:
+                try:
+                    sh = self.shadow_arena.alloc(tuple(lp.shape), torch.bfloat16)
+                except MemoryError:
+                    sh = None  # arena full: this shard's gathers fall back to the ordinary collectives
+            if sh is None:
+                sh = torch.empty_like(lp, dtype=torch.bfloat16)
             self._shadows[id(p)] = sh
         return sh
 
@@ -114,9 +125,13 @@ class AdamW(torch.optim.Optimizer):
 
                 cuda_impl.ensure_loaded()
                 table, ch, n = self._table(gi, plist)
+                if self.shadow_arena is not None:
+                    self.shadow_arena.barrier()  # every rank has finished reading the old shards
                 cuda_impl.extension().adamw(table, ch, n, group["lr"], b1, b2, group["eps"], group["weight_decay"], bc1, bc2,
                                             self.grad_scale)
                 cuda_impl._count()
+                if self.shadow_arena is not None:
+                    self.shadow_arena.barrier()  # the new shards are complete on every rank before anyone pulls
                 if self.emit_bf16:
                     from .ops import shadow
 

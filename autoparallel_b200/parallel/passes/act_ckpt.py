@@ -6,9 +6,19 @@ then clones that chain into the backward graph instead of saving the gathered we
 "reshard after forward"; without it the last node of each chain is pinned as saved.
 Reference: autoparallel/graph_passes/activation_checkpointing.py:182-271, 518-533.
 
+``apply_user_checkpoint_tags`` honours what the user wrote with ``torch.utils.checkpoint``: nodes
+traced inside a checkpointed region carry ``meta["recompute"]`` (a ``CheckpointPolicy`` from the
+region's selective-checkpoint policy, or "prefer recompute" for a plain region) and
+``meta["ac_graph_id"]``; save policies become ``must_save`` tags and recompute policies
+``recompute`` tags of the partitioner.  User tags are applied first and the framework's own policy
+never overrides them; parameter-gather chains stay "recompute" whatever the user region says
+(reference: :34, 224-235, 356, 410).
+
 ``apply_activation_checkpointing`` implements the memory-budget policy: cheap pointwise /
-normalisation results are recomputed, GEMM and attention outputs are kept, and per "stage" of
-``stage_bytes`` of live activations the cheapest cut is pinned (reference: :365-552).
+normalisation results are recomputed, GEMM and attention outputs are kept ("selective"), or
+everything is recomputed from stage boundaries ("full"): the forward is cut into stages of
+``stage_bytes`` of produced activations and in every stage the set of tensors alive at the point of
+least live memory is saved (reference: :365-494).
 """
 from __future__ import annotations
 
@@ -65,12 +75,115 @@ def mark_fsdp_recompute(joint: JointGraph, reshard_after_forward: bool = True) -
         for n in derived:
             if n.op == "call_function":
                 n.meta[RECOMPUTE] = True
+                n.meta["apb200_param_chain"] = True
                 count += 1
     else:
         for chain in fsdp_all_gather_chains(joint):
             chain[-1].meta[MUST_SAVE] = True
             count += 1
     return count
+
+
+def _forward_nodes(joint: JointGraph):
+    """(forward call_function nodes in order, set of tangent-dependent nodes)."""
+    T = set(joint.tangent_nodes)
+    for n in joint.gm.graph.nodes:
+        if n.op == "call_function" and any(i in T for i in n.all_input_nodes):
+            T.add(n)
+    # forward = what the forward outputs need; value-only nodes that only the backward reads (the cosine
+    # of a saved input, say) run on the backward side and must not count as forward activations
+    F, stack = set(), [o for o in joint.fwd_outputs if isinstance(o, fx.Node)]
+    while stack:
+        n = stack.pop()
+        if n in F:
+            continue
+        F.add(n)
+        stack.extend(n.all_input_nodes)
+    import operator as _op
+
+    for n in joint.gm.graph.nodes:
+        if n.op == "call_function" and n.target is _op.getitem and n.args[0] in F and n not in T:
+            F.add(n)
+    return [n for n in joint.gm.graph.nodes if n.op == "call_function" and n in F and n not in T], T
+
+
+def apply_user_checkpoint_tags(joint: JointGraph) -> dict:
+    """Translate ``CheckpointPolicy`` tags left by ``torch.utils.checkpoint`` regions into partitioner tags."""
+    from torch.utils.checkpoint import CheckpointPolicy
+
+    save = {CheckpointPolicy.MUST_SAVE, CheckpointPolicy.PREFER_SAVE}
+    recompute = {CheckpointPolicy.MUST_RECOMPUTE, CheckpointPolicy.PREFER_RECOMPUTE}
+    fwd, _ = _forward_nodes(joint)
+    stats = {"user_saved": 0, "user_recompute": 0, "regions": set()}
+    for n in fwd:
+        pol = n.meta.get("recompute")
+        if pol is None or n.meta.get("ac_graph_id") is None:
+            continue
+        stats["regions"].add(n.meta["ac_graph_id"])
+        if n.meta.get(RECOMPUTE) and not n.meta.get(MUST_SAVE):
+            continue  # parameter-gather chain: re-gathered in the backward whatever the region's policy says
+        if pol in save:
+            n.meta[MUST_SAVE] = True
+            n.meta.pop(RECOMPUTE, None)
+            stats["user_saved"] += 1
+        elif pol in recompute:
+            n.meta[RECOMPUTE] = True
+            stats["user_recompute"] += 1
+        n.meta["apb200_user_ac"] = True
+    stats["regions"] = len(stats["regions"])
+    return stats
+
+
+def min_live_memory_cuts(fwd: list, stage_bytes: int) -> list:
+    """Nodes to save so that no recomputation chain is longer than one stage.
+
+    The forward nodes are walked in order while tracking which results are alive (produced and still
+    needed by a later forward node; results that are always recomputed, such as gathered parameters, are
+    looked through).  A new stage starts whenever ``stage_bytes`` of results have been produced; in each
+    stage the position with the least live memory is the cut, and everything alive there is saved."""
+    in_fwd = set(fwd)
+    always_recomputed = {n for n in fwd if n.meta.get(RECOMPUTE) and not n.meta.get(MUST_SAVE) and not n.meta.get("apb200_user_ac")
+                         and n.meta.get("apb200_param_chain")}
+    preds: dict = {}
+    for n in fwd:
+        ps = []
+        for i in n.all_input_nodes:
+            if i in always_recomputed:
+                ps.extend(preds.get(i, ()))
+            elif i in in_fwd:
+                ps.append(i)
+        preds[n] = ps
+    last_user: dict = {}
+    for n in fwd:
+        last_user[n] = n
+        for p_ in preds[n]:
+            last_user[p_] = n
+    dies_at: dict = {}
+    for prod, cons in last_user.items():
+        dies_at.setdefault(cons, []).append(prod)
+    alive: dict = {}
+    live_bytes = 0
+    stages, cur, produced = [], [], 0
+    for n in fwd:
+        if n not in always_recomputed:
+            alive[n] = None
+            live_bytes += _nbytes(n)
+            for d in dies_at.get(n, ()):
+                if d in alive and d is not n:
+                    del alive[d]
+                    live_bytes -= _nbytes(d)
+            produced += _nbytes(n)
+        cur.append((live_bytes, n, list(alive)))
+        if produced >= stage_bytes:
+            stages.append(cur)
+            cur, produced = [], 0
+    if cur:
+        stages.append(cur)
+    cuts = []
+    for st in stages[:-1] if len(stages) > 1 else []:  # nothing follows the last stage: its results are consumed by the backward at once
+        _, _, live = min(st, key=lambda e: e[0])
+        cuts.extend(live)
+    return list(dict.fromkeys(cuts))
 
 
 def _nbytes(n: fx.Node) -> int:
@@ -92,13 +205,7 @@ def apply_activation_checkpointing(
     """
     if mode == "none":
         return {"recompute": 0, "saved": 0}
-    tangents = set(joint.tangent_nodes)
-    g = joint.gm.graph
-    T = set(tangents)
-    for n in g.nodes:
-        if n.op == "call_function" and any(i in T for i in n.all_input_nodes):
-            T.add(n)
-    fwd = [n for n in g.nodes if n.op == "call_function" and n not in T]
+    fwd, T = _forward_nodes(joint)
     n_rec = n_save = 0
     mm_seen = 0
     import operator
@@ -129,22 +236,16 @@ def apply_activation_checkpointing(
             n.meta[RECOMPUTE] = True
             n_rec += 1
     if mode == "full":
-        # pin stage boundaries: walk the forward in order, accumulate output bytes, and when a
-        # stage is full pin the narrowest single-tensor cut seen in it (a residual-stream tensor)
-        if stage_bytes is None:
+        if stage_bytes is None:  # "auto": the square root of the recomputable memory, in GiB
             total = sum(_nbytes(n) for n in fwd)
             stage_bytes = max(1, int(math.sqrt(max(total, 1) / 2**30) * 2**30)) if total > 2**30 else max(total // 8, 1)
-        acc = 0
-        best = None
-        for n in fwd:
-            acc += _nbytes(n)
-            users_fwd = [u for u in n.users if u not in T]
-            if isinstance(n.meta.get("val"), torch.Tensor) and len(users_fwd) >= 2 and n.target is aten.add.Tensor:
-                if best is None or _nbytes(n) <= _nbytes(best):
-                    best = n
-            if acc >= stage_bytes and best is not None:
-                best.meta[MUST_SAVE] = True
-                best.meta.pop(RECOMPUTE, None)
+        for cut in min_live_memory_cuts(fwd, stage_bytes):
+            if cut.meta.get("apb200_user_ac") or cut.target is operator.getitem:
+                continue  # user annotations take precedence; tuple elements follow their producer
+            if cut.meta.get(RECOMPUTE):
+                cut.meta.pop(RECOMPUTE, None)
+                n_rec -= 1
+            if not cut.meta.get(MUST_SAVE):
+                cut.meta[MUST_SAVE] = True
                 n_save += 1
-                acc, best = 0, None
     return {"recompute": n_rec, "saved": n_save}

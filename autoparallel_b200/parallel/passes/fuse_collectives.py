@@ -49,10 +49,12 @@ def _tangent_dependent(gm: fx.GraphModule, tangents) -> set:
 
 
 def fuse_collectives(gm: fx.GraphModule, tangents=(), reshard_after_forward: bool = True,
-                     fuse_contraction_gather: bool = False) -> dict:
+                     fuse_contraction_gather: bool = False, patterns=("ag_mm", "mm_rs")) -> dict:
     """``fuse_contraction_gather``: also fuse a gather whose rows are the GEMM's contraction dim (the
     FSDP dgrad).  Every output tile then needs every shard, so the kernel cannot start a tile on
-    local data while the rest arrives; measured slower than a prefetched gather, hence off by default."""
+    local data while the rest arrives; measured slower than a prefetched gather, hence off by default.
+    ``patterns``: which of the two families to rewrite (``("mm_rs",)`` keeps every gather a separate node,
+    e.g. when parameter gathers are served by the copy engines and only the reductions need a kernel)."""
     g = gm.graph
     stats = {"ag_mm": 0, "mm_rs": 0}
     T = _tangent_dependent(gm, tangents)
@@ -65,7 +67,7 @@ def fuse_collectives(gm: fx.GraphModule, tangents=(), reshard_after_forward: boo
         return gi
 
     # ---- GEMM -> reduce-scatter
-    for rs in [n for n in g.nodes if n.op == "call_function" and n.target is comm.reduce_scatter.default]:
+    for rs in [n for n in g.nodes if "mm_rs" in patterns and n.op == "call_function" and n.target is comm.reduce_scatter.default]:
         src, dim, group, n_ranks = rs.args
         if not (isinstance(src, fx.Node) and src.op == "call_function" and len(src.users) == 1):
             continue
@@ -86,7 +88,7 @@ def fuse_collectives(gm: fx.GraphModule, tangents=(), reshard_after_forward: boo
         stats["mm_rs"] += 1
 
     # ---- all-gather -> GEMM
-    for ag in [n for n in g.nodes if n.op == "call_function" and n.target is comm.all_gather.default]:
+    for ag in [n for n in g.nodes if "ag_mm" in patterns and n.op == "call_function" and n.target is comm.all_gather.default]:
         x, dim, group, n_ranks = ag.args
         users = sorted(ag.users, key=lambda u: order.get(u, 1 << 30))
         val = ag.meta["val"]

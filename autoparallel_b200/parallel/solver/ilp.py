@@ -359,6 +359,15 @@ class ShardingOptimizer:
         self.constraints[name] = Constraint(name, "memory", low=low, high=high, description=f"[{low}, {high}]")
         return name
 
+    def add_parameter_bytes_constraint(self, budget_bytes: float, bytes_per_element: float = 16.0) -> str:
+        """Per-rank bytes of parameter state (locally held elements x ``bytes_per_element``, summed over all
+        parameters) must not exceed ``budget_bytes``.  Unlike the ratio form every parameter weighs in with its
+        size, so a budget in GB can be stated directly."""
+        name = self._new_name("memory_bytes")
+        self.constraints[name] = Constraint(name, "memory_bytes", low=bytes_per_element, high=budget_bytes,
+                                            description=f"<= {budget_bytes:.4g} B at {bytes_per_element:g} B/element")
+        return name
+
     def remove_constraints(self, names: Sequence[str]) -> None:
         for n in names:
             self.constraints.pop(n, None)
@@ -409,7 +418,58 @@ class ShardingOptimizer:
         # forward / backward and first-gradient-use distinctions come from graph structure itself
         return refine_colors(self.nodes, self._inputs, self._initial_color(salts), self.cluster_rounds)
 
-    def get_solution(self, verbose: bool = False) -> dict[fx.Node, OpSpec]:
+    def conflicting_constraints(self, max_solves: int = 24) -> dict:
+        """Which user constraints clash, found by a deletion filter: starting from all constraints in force, each
+        one is left out in turn; if the problem stays infeasible without it, it is not part of the conflict and is
+        dropped for good.  What remains is an irreducible set: removing any single member makes the problem
+        feasible.  (The reference prints the constraint rows its solver reports as violated,
+        autoparallel/optimize_sharding.py:1115-1124; HiGHS returns no such list, so the set is computed.)"""
+        saved = dict(self.constraints)
+        saved_state = (self.solution, getattr(self, "selected", None), getattr(self, "objective_value", None))
+
+        def feasible(names) -> bool:
+            self.constraints = {k: saved[k] for k in names}
+            try:
+                self.get_solution(diagnose=False)
+                return True
+            except InfeasibleError:
+                return False
+
+        report = {"structural": False, "conflict": [], "exhaustive": True}
+        try:
+            if not feasible([]):
+                report["structural"] = True
+                report["text"] = ("infeasible even without user constraints: some node has no admissible strategy under the "
+                                  "mesh (for example extents that no mesh dim divides while uneven_sharding is off)")
+                return report
+            keep = list(saved)
+            solves = 0
+            for name in list(keep):
+                if solves >= max_solves:
+                    report["exhaustive"] = False
+                    break
+                trial = [k for k in keep if k != name]
+                solves += 1
+                if not feasible(trial):
+                    keep = trial  # still infeasible without it: not needed for the conflict
+            report["conflict"] = [{"name": k, "kind": saved[k].kind, "node": getattr(saved[k].node, "name", None),
+                                   "requires": saved[k].description} for k in keep]
+            lines = [f"conflicting constraints ({len(keep)} of {len(saved)}; removing any one of them makes the problem feasible"
+                     + ("" if report["exhaustive"] else "; search stopped early") + "):"]
+            for c in report["conflict"]:
+                where = f" on node {c['node']}" if c["node"] else ""
+                lines.append(f"  - {c['name']} [{c['kind']}]{where}: requires {c['requires']}")
+            report["text"] = "\n".join(lines)
+            return report
+        finally:
+            self.constraints = saved
+            self.solution, sel, obj = saved_state
+            if sel is not None:
+                self.selected = sel
+            if obj is not None:
+                self.objective_value = obj
+
+    def get_solution(self, verbose: bool = False, diagnose: bool = True) -> dict[fx.Node, OpSpec]:
         from scipy.optimize import Bounds, LinearConstraint, milp
         from scipy.sparse import coo_matrix
 
@@ -553,6 +613,24 @@ class ShardingOptimizer:
                     merged[i] += cf
                 add_row(list(merged), list(merged.values()), lo_sum - 1e-6, hi_sum + 1e-6)
 
+        for cst in self.constraints.values():
+            if cst.kind != "memory_bytes":
+                continue
+            merged = defaultdict(float)
+            fixed = 0.0  # parameters pinned by a node constraint still occupy memory: count their cheapest allowed option
+            for fqn, p in self.joint.param_nodes.items():
+                if p not in self.strats:
+                    continue
+                shape = list(p.meta["val"].shape)
+                y0 = y_off[cls[p]]
+                for i, s_ in enumerate(self.strats[p].strategies):
+                    ls = local_shape(shape, self.mesh.shape, s_.output_spec.placements)
+                    local_elems = math.prod(ls) if ls is not None else math.prod(shape)
+                    # scaled to GB so the row's coefficients stay well conditioned next to the 0/1 rows
+                    merged[y0 + i] += local_elems * cst.low / 1e9
+            if merged:
+                add_row(list(merged), list(merged.values()), -np.inf, cst.high / 1e9 - fixed)
+
         A = coo_matrix((vals, (rows, cols)), shape=(r, nvar)).tocsr()
         self.timings["build"] = time.perf_counter() - t0
         t1 = time.perf_counter()
@@ -581,11 +659,13 @@ class ShardingOptimizer:
         )
         if res.x is None or res.status not in (0, 1):
             self.solution = None
-            raise InfeasibleError(
-                "the sharding optimizer found no feasible placement: "
-                f"{res.message}. User constraints in force: "
-                + "; ".join(f"{c.name}={c.description}" for c in self.constraints.values())
-            )
+            msg = ("the sharding optimizer found no feasible placement: "
+                   f"{res.message}. User constraints in force: "
+                   + "; ".join(f"{c.name}={c.description}" for c in self.constraints.values()))
+            if diagnose and self.constraints:
+                self.infeasibility_report = self.conflicting_constraints()
+                msg += "\n" + self.infeasibility_report["text"]
+            raise InfeasibleError(msg)
         x = res.x
         self.objective_value = float(res.fun)
         selected: dict[fx.Node, int] = {}

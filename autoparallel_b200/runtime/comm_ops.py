@@ -33,6 +33,9 @@ lib.define("local_chunk(Tensor x, int dim, str group, int group_size) -> Tensor"
 
 #: group name -> symmetric-memory communicator (set by runtime.symm.enable_for_group)
 _symm_backends: dict[str, object] = {}
+#: group name -> copy-engine communicator (set by runtime.dma.enable_for_mesh): gathers of tensors that live in the
+#: peer arena and fp32 reduce-scatters on the leading dim move with the copy engines and take no SM
+_dma_backends: dict[str, object] = {}
 #: False = stand-alone collectives stay on NCCL even where a communicator exists (fused nodes still use it)
 _symm_standalone = True
 
@@ -77,6 +80,9 @@ def _rank_in_group(group: str) -> int:
 
 
 def _all_gather(x, dim, group, n):
+    dma = _dma_backends.get(group)
+    if dma is not None and dma.can_gather(x, dim):
+        return dma.all_gather(x, dim)
     be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_gather(x, dim)
@@ -93,6 +99,9 @@ def _all_gather(x, dim, group, n):
 
 
 def _reduce_scatter(x, dim, group, n):
+    dma = _dma_backends.get(group)
+    if dma is not None and dma.can_reduce(x, dim):
+        return dma.reduce_scatter(x, dim)
     be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.reduce_scatter(x, dim)
@@ -239,6 +248,9 @@ def _request_sms(x) -> None:
 
 
 def _ag_start(x, dim, group, n):
+    dma = _dma_backends.get(group)
+    if dma is not None and dma.can_gather(x, dim):
+        return dma.all_gather_start(x, dim)
     be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_gather_start(x, dim)
@@ -249,6 +261,9 @@ def _ag_start(x, dim, group, n):
 
 
 def _rs_start(x, dim, group, n):
+    dma = _dma_backends.get(group)
+    if dma is not None and dma.can_reduce(x, dim):
+        return dma.reduce_scatter_start(x, dim)
     be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.reduce_scatter_start(x, dim)

@@ -57,9 +57,13 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="debugging only: override the layer count (invalidates the metric)")
     ap.add_argument("--ac", default="auto", choices=["auto", "none", "selective", "full"])
     ap.add_argument("--executor", default="streams", choices=["graph", "streams"])
-    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "symm", "hybrid"],
+    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "symm", "hybrid", "dma", "dma_ag", "dma_fused"],
                     help="nccl: NCCL collectives under the overlap scheduler; symm: own NVLink kernels for everything, GEMMs fused "
-                         "with their collective; hybrid: fused GEMM+collective kernels, stand-alone collectives on NCCL")
+                         "with their collective; hybrid: fused GEMM+collective kernels, stand-alone collectives on NCCL; "
+                         "dma: parameter gathers and gradient reduce-scatters on the copy engines (no SM); dma_ag: copy-engine "
+                         "gathers, NCCL reductions; dma_fused: copy-engine gathers, weight-gradient GEMM fused with its reduce-scatter")
+    ap.add_argument("--dma-ring", type=int, default=4, help="copy-engine reduce-scatter: staging entries in flight")
+    ap.add_argument("--dma-sum-ctas", type=int, default=48, help="copy-engine reduce-scatter: CTAs of the kernel that adds the slots")
     ap.add_argument("--reduction-group", default="separate", choices=["separate", "shared"],
                     help="separate: gradient reductions run on a second NCCL communicator so that parameter gathers never queue behind them")
     ap.add_argument("--dynamic-tiles", default=None, choices=["on", "off"],
@@ -161,6 +165,15 @@ def write_kernel_table(path, step_fn, rank):
         json.dump({"sum_of_kernel_us": round(sum(r["total_us"] for r in rows), 1), "kernels": rows}, f, indent=1)
 
 
+def _dma_stats():
+    try:
+        from autoparallel_b200.runtime import dma
+
+        return dma.stats() if dma.arena() is not None else {}
+    except Exception:
+        return {}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -225,6 +238,7 @@ def run_ours(args):
     if ac == "auto":
         # one GPU holds fp32 params + grads + Adam moments (16 B/param): recompute cheap ops there
         ac = "selective" if world == 1 and cfg.num_params() > 4e9 else "none"
+    fuse_arg = None
     comm_mode = args.comm
     if comm_mode == "auto":
         # Measured on this model (ms/step, nccl vs hybrid on the same box): N=2 468 / 472, N=4 491 / 504,
@@ -232,13 +246,31 @@ def run_ours(args):
         # fused kernel spins on its peers while NCCL kernels of the same step compete for SMs, which is only
         # safe with SMs set aside for NCCL (--reserve-sms), and that configuration has not been timed.
         comm_mode = os.environ.get("APB200_COMM", "nccl")
-    if world > 1 and comm_mode in ("symm", "hybrid"):
+    shadow_arena = None
+    if world > 1 and comm_mode.startswith("dma"):
+        from autoparallel_b200.runtime import dma
+
+        local_param_bytes = sum(p.numel() for p in model.parameters()) * 2 // world
+        # one staging slot holds one rank's chunk of the largest per-layer weight gradient (fp32)
+        layer_max = max((p.numel() for n_, p in model.named_parameters() if "layers." in n_), default=0)
+        slot = ((layer_max * 4 // world + 4095) // 4096) * 4096 if comm_mode == "dma" else 0
+        arena_bytes = local_param_bytes + (64 << 20) + args.dma_ring * world * slot
+        try:
+            shadow_arena = dma.enable_for_mesh(mesh, arena_bytes, ring=args.dma_ring, slot_bytes=slot, sum_ctas=args.dma_sum_ctas,
+                                               reductions=(comm_mode == "dma"))
+        except Exception as e:  # no peer access / symmetric memory on this machine
+            if rank == 0:
+                print(f"peer arena unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr, flush=True)
+            dma.disable_all()
+            comm_mode = "nccl"
+    if world > 1 and comm_mode in ("symm", "hybrid", "dma_fused"):
         # communicators first: the planner fuses a GEMM with its collective only where they exist
         from autoparallel_b200.runtime import symm
 
         try:
             symm.enable_for_mesh(mesh)
             symm.route_standalone_collectives(comm_mode == "symm")
+            fuse_arg = "reductions" if comm_mode == "dma_fused" else None
         except Exception as e:  # no peer access / symmetric memory on this machine: NCCL carries everything
             if rank == 0:
                 print(f"symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr, flush=True)
@@ -249,7 +281,8 @@ def run_ours(args):
 
         comm_ops.use_separate_reduction_groups(mesh, pg_options=pg_opts)
     t0 = time.perf_counter()
-    with AutoParallel(model, input_fn, mesh, MPPolicy(torch.bfloat16, torch.float32), activation_checkpointing=ac) as ap:
+    with AutoParallel(model, input_fn, mesh, MPPolicy(torch.bfloat16, torch.float32), activation_checkpointing=ac,
+                      fuse_collectives=fuse_arg) as ap:
         ap.add_parameter_memory_constraint()
         ap.add_input_constraints([(Shard(0),)] * 2)
         ap.optimize_placement()
@@ -271,7 +304,7 @@ def run_ours(args):
     plan_s = time.perf_counter() - t0
     pm.to_empty(device="cuda")
     pm.init_weights(seed=0)
-    opt = AdamW(pm.parameters(), lr=3e-4, weight_decay=0.1, emit_bf16=(args.emit_bf16 == "on"))
+    opt = AdamW(pm.parameters(), lr=3e-4, weight_decay=0.1, emit_bf16=(args.emit_bf16 == "on"), shadow_arena=shadow_arena)
 
     g = torch.Generator(device="cpu").manual_seed(1234 + rank)
     n_sets = 4
@@ -365,11 +398,13 @@ def run_ours(args):
                 "reduction_group": args.reduction_group if world > 1 else "none",
                 "fused_nodes": fused_nodes,
                 "collectives_in_graph": n_coll,
+                "copy_engine_collectives": _dma_stats(),
                 "l2": "no explicit flush: per-step working set (>=16 GB of weights + activations) >> 126 MB L2",
             },
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": 2 * S * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
+            "library_fallbacks": dict(cuda_impl.library_fallbacks),
             "clocks": clocks,
             "ilp_solve_s": ilp_solve_s,
             "plan_s": {k: round(v, 3) for k, v in timings.items()},
@@ -392,6 +427,10 @@ def run_reference(args):
 
 if __name__ == "__main__":
     a = parse()
+    if a.comm.startswith("dma") or a.comm == "auto":
+        # one hardware queue per stream: a bounded flag wait on a communication stream must never sit in front
+        # of compute kernels of another stream in a shared queue (read once, when the CUDA context is created)
+        os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
     if a.impl == "reference":
         run_reference(a)
     else:

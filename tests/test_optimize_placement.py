@@ -132,9 +132,19 @@ def test_contradictory_constraints_are_reported(mesh_1d):
         ap.add_output_constraints([(Shard(0),)])
         # the output gradient twin must match the output: pin it differently to make it infeasible
         t = ap.joint.tangent_nodes[0]
-        ap.sharding_optimizer.add_node_constraint(t, (Replicate(),))
-        with pytest.raises(RuntimeError, match="feasible"):
+        bad = ap.sharding_optimizer.add_node_constraint(t, (Replicate(),))
+        with pytest.raises(RuntimeError, match="feasible") as err:
             ap.optimize_placement()
+        # the report names the clashing pair (output pinned Shard(0), its gradient pinned Replicate) and
+        # leaves the input constraint, which is compatible with either, out of it
+        rep = ap.sharding_optimizer.infeasibility_report
+        names = {c["name"] for c in rep["conflict"]}
+        assert bad in names and len(names) == 2 and any(n.startswith("output:") for n in names)
+        assert not any(n.startswith("input:") for n in names)
+        assert "conflicting constraints (2 of 3" in str(err.value)
+        # removing one member of the reported set is enough
+        ap.sharding_optimizer.remove_constraints([bad])
+        assert ap.optimize_placement() is not None
 
 
 def test_mixed_precision_orders_casts_and_collectives(mesh_1d):
@@ -173,3 +183,35 @@ def test_clustering_shares_variables_between_layers(mesh_1d):
             ap.optimize_placement()
             sizes[layers] = ap.sharding_optimizer.problem_size["variables"]
     assert sizes[6] < 1.3 * sizes[2]  # four more layers add almost nothing to the ILP
+
+
+def test_parameter_budget_in_bytes_decides_between_replication_and_sharding(mesh_1d):
+    """The bytes form of the parameter-memory constraint: a generous budget leaves the cheaper replicated
+    (data-parallel) plan in place, a budget below the replicated state forces sharded parameters."""
+    d = 1024
+    n_elems = 2 * d * 4 * d
+    replicated_bytes = n_elems * 16.0
+
+    def plan(budget):
+        with torch.device("meta"):
+            m = FFN(d, 4 * d)
+        with AutoParallel(m, lambda: torch.randn(512, 128, d), mesh_1d, plan_device="B200") as ap:
+            ap.add_parameter_memory_constraint(budget_bytes=budget, bytes_per_element=16.0)
+            ap.add_input_constraints([(Shard(0),)])
+            sol = ap.optimize_placement()
+            held = 0
+            for p in ap.joint.param_nodes.values():
+                pl = _out_placements(sol[p])
+                held += p.meta["val"].numel() // (8 if any(isinstance(x, Shard) for x in pl) else 1)
+            return held * 16.0
+
+    assert plan(2 * replicated_bytes) == replicated_bytes       # budget not binding: replicate
+    tight = plan(replicated_bytes / 4)
+    assert tight <= replicated_bytes / 4                          # both weights sharded eightfold
+    with pytest.raises(RuntimeError, match="feasible"):
+        plan(replicated_bytes / 64)                                # below the fully sharded state: no plan
+    with torch.device("meta"):
+        m = FFN(d, 4 * d)
+    with AutoParallel(m, lambda: torch.randn(512, 128, d), mesh_1d, plan_device="B200") as ap:
+        with pytest.raises(ValueError, match="either"):
+            ap.add_parameter_memory_constraint(high=0.5, budget_bytes=1e9)
