@@ -63,7 +63,7 @@ int apb_dma_rs_sum(const void* src, void* dst, const unsigned long long* bases, 
 int apb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Sk, int H, int Hkv,
                       int D, int causal, float scale, uint32_t* status, cudaStream_t stream);
 int apb_adamw(const void* tensors_dev, const void* chunks_dev, int num_chunks, float lr, float beta1, float beta2, float eps,
-              float wd, float bc1, float bc2, float grad_scale, cudaStream_t st);
+              float wd, float bc1, float bc2, float grad_scale, const float* hyper_dev, cudaStream_t st);
 }
 
 namespace {
@@ -204,10 +204,15 @@ void embedding_bwd(const at::Tensor& dy, const at::Tensor& ids, at::Tensor& out_
 }
 
 void adamw(const at::Tensor& table, const at::Tensor& chunks, int64_t num_chunks, double lr, double b1, double b2, double eps,
-           double wd, double bc1, double bc2, double grad_scale) {
+           double wd, double bc1, double bc2, double grad_scale, const c10::optional<at::Tensor>& hyper) {
   c10::cuda::CUDAGuard g(table.device());
+  const float* hp = nullptr;
+  if (hyper.has_value()) {
+    TORCH_CHECK(hyper->scalar_type() == at::kFloat && hyper->numel() >= 3 && hyper->is_cuda(), "adamw: hyper = fp32 [3] on the device");
+    hp = hyper->data_ptr<float>();
+  }
   check(apb_adamw(table.data_ptr(), chunks.data_ptr(), (int)num_chunks, (float)lr, (float)b1, (float)b2, (float)eps, (float)wd,
-                  (float)bc1, (float)bc2, (float)grad_scale, stream()),
+                  (float)bc1, (float)bc2, (float)grad_scale, hp, stream()),
         "apb_adamw");
 }
 

@@ -79,42 +79,79 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 }
 
 // ------------------------------------------------------------------------------------ RMSNorm
-// one block per row; D % 8 == 0
-template <typename T>
+// Forward.  A group of ``TPR`` threads owns a row and keeps its NVEC x 8 elements per thread in registers between the
+// sum of squares and the scaling, so x is read once.  TPR = 32: one warp per row, reduction by shuffles only, no
+// block barrier; several rows per block keep enough loads in flight.  TPR = blockDim.x: one block per row for wide rows.
+// D % 8 == 0 and D <= TPR * 8 * NVEC.
+template <typename T, int NVEC, bool WARP_ROWS>
 __global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
-                                    float* __restrict__ rstd, int D, float eps) {
+                                    float* __restrict__ rstd, long long rows, int D, float eps) {
   __shared__ float red[32];
-  const long long row = blockIdx.x;
-  const T* xr = x + row * D;
-  T* yr = y + row * D;
-  float ss = 0.f;
-  for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
-    Vec8<T> v; v.load(xr + c);
-    float f[8]; v.to_float(f);
+  const int tpr = WARP_ROWS ? 32 : blockDim.x;
+  const int t = WARP_ROWS ? (threadIdx.x & 31) : threadIdx.x;
+  const long long rows_per_block = WARP_ROWS ? (blockDim.x >> 5) : 1;
+  const long long first = (long long)blockIdx.x * rows_per_block + (WARP_ROWS ? (threadIdx.x >> 5) : 0);
+  const long long step = (long long)gridDim.x * rows_per_block;
+  for (long long row = first; WARP_ROWS ? (row < rows) : (row - (WARP_ROWS ? (threadIdx.x >> 5) : 0) < rows); row += step) {
+    if (!WARP_ROWS && row >= rows) break;
+    const T* xr = x + row * D;
+    T* yr = y + row * D;
+    Vec8<T> v[NVEC];
+    float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
-  }
-  ss = block_sum(ss, red);
-  const float r = rsqrtf(ss / D + eps);
-  if (threadIdx.x == 0) rstd[row] = r;
-  for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
-    Vec8<T> v, wv; v.load(xr + c); wv.load(w + c);
-    float f[8], g[8]; v.to_float(f); wv.to_float(g);
+    for (int j = 0; j < NVEC; ++j) {
+      const int c = (t + j * tpr) * 8;
+      if (c < D) {
+        v[j].load(xr + c);
+        float f[8]; v[j].to_float(f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = f[i] * r * g[i];
-    v.from_float(f); v.store(yr + c);
+        for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+      }
+    }
+    ss = WARP_ROWS ? warp_sum(ss) : block_sum(ss, red);
+    const float r = rsqrtf(ss / D + eps);
+    if (t == 0) rstd[row] = r;
+#pragma unroll
+    for (int j = 0; j < NVEC; ++j) {
+      const int c = (t + j * tpr) * 8;
+      if (c < D) {
+        Vec8<T> wv; wv.load(w + c);
+        float f[8], g[8]; v[j].to_float(f); wv.to_float(g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = f[i] * r * g[i];
+        Vec8<T> o; o.from_float(f); o.store(yr + c);
+      }
+    }
   }
 }
 
-// Persistent blocks over rows.  dx per row; dw partial sums per thread-owned columns are added
-// into ``dw_acc`` (fp32 [D], zeroed by the caller) with one atomicAdd per column per block.
-// Requires D <= blockDim.x * 8 * RMS_BWD_MAX_VEC.
+// block-wide sums of R values at once (one barrier pair for all of them); ``red`` holds 32 * R floats
+template <int R>
+__device__ __forceinline__ void block_sum_multi(float (&v)[R], float* red) {
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int k = 0; k < R; ++k) v[k] = warp_sum(v[k]);
+  __syncthreads();
+  if (l == 0) {
+#pragma unroll
+    for (int k = 0; k < R; ++k) red[k * 32 + w] = v[k];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < R; ++k) v[k] = warp_sum(l < nw ? red[k * 32 + l] : 0.f);
+}
+
+// Backward.  Persistent blocks; every iteration takes ROWS rows at once: all their loads are issued before the first
+// use (ROWS x NVEC x 2 sixteen-byte loads in flight per thread) and their ROWS dot products share one block reduction,
+// so the row loop is bound by memory bandwidth rather than by one load-reduce-store round trip per row.
+// dx per row; dw partial sums per thread-owned columns are added into ``dw_acc`` (fp32 [D], zeroed by the caller) with
+// one atomicAdd per column per block.  Requires D <= blockDim.x * 8 * RMS_BWD_MAX_VEC.
 constexpr int RMS_BWD_MAX_VEC = 4;
-template <typename T, int NVEC>
-__global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+template <typename T, int NVEC, int ROWS>
+__global__ void __launch_bounds__(512) rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                                     const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_acc,
                                     long long rows, int D) {
-  __shared__ float red[32];
+  __shared__ float red[32 * ROWS];
   float wreg[NVEC][8];
   float dwreg[NVEC][8];
 #pragma unroll
@@ -126,36 +163,54 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
       Vec8<T> wv; wv.load(w + c); wv.to_float(wreg[j]);
     }
   }
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const T* xr = x + row * D;
-    const T* gr = dy + row * D;
-    const float r = rstd[row];
-    float xh[NVEC][8], g[NVEC][8];
-    float dot = 0.f;
+  for (long long row0 = (long long)blockIdx.x * ROWS; row0 < rows; row0 += (long long)gridDim.x * ROWS) {
+    Vec8<T> xv[ROWS][NVEC], gv[ROWS][NVEC];
+    float r[ROWS];
 #pragma unroll
-    for (int j = 0; j < NVEC; ++j) {
-      const int c = (threadIdx.x + j * blockDim.x) * 8;
-      if (c < D) {
-        Vec8<T> xv, gv; xv.load(xr + c); gv.load(gr + c);
-        float xf[8], gf[8]; xv.to_float(xf); gv.to_float(gf);
+    for (int k = 0; k < ROWS; ++k) {
+      const long long row = row0 + k;
+      r[k] = row < rows ? rstd[row] : 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          xh[j][i] = xf[i] * r;
-          dwreg[j][i] += gf[i] * xh[j][i];
-          g[j][i] = gf[i] * wreg[j][i];
-          dot += g[j][i] * xh[j][i];
+      for (int j = 0; j < NVEC; ++j) {
+        const int c = (threadIdx.x + j * blockDim.x) * 8;
+        if (row < rows && c < D) {
+          xv[k][j].load(x + row * D + c);
+          gv[k][j].load(dy + row * D + c);
         }
       }
     }
-    dot = block_sum(dot, red) / D;
+    float dot[ROWS];
 #pragma unroll
-    for (int j = 0; j < NVEC; ++j) {
-      const int c = (threadIdx.x + j * blockDim.x) * 8;
-      if (c < D) {
-        float o[8];
+    for (int k = 0; k < ROWS; ++k) {
+      dot[k] = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = r * (g[j][i] - xh[j][i] * dot);
-        Vec8<T> ov; ov.from_float(o); ov.store(dx + row * D + c);
+      for (int j = 0; j < NVEC; ++j) {
+        const int c = (threadIdx.x + j * blockDim.x) * 8;
+        if (row0 + k < rows && c < D) {
+          float xf[8], gf[8]; xv[k][j].to_float(xf); gv[k][j].to_float(gf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float xh = xf[i] * r[k];
+            dwreg[j][i] += gf[i] * xh;
+            dot[k] += gf[i] * wreg[j][i] * xh;
+          }
+        }
+      }
+    }
+    block_sum_multi<ROWS>(dot, red);
+#pragma unroll
+    for (int k = 0; k < ROWS; ++k) {
+      const long long row = row0 + k;
+      const float dk = dot[k] / D;
+#pragma unroll
+      for (int j = 0; j < NVEC; ++j) {
+        const int c = (threadIdx.x + j * blockDim.x) * 8;
+        if (row < rows && c < D) {
+          float xf[8], gf[8], o[8]; xv[k][j].to_float(xf); gv[k][j].to_float(gf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = r[k] * (gf[i] * wreg[j][i] - xf[i] * r[k] * dk);
+          Vec8<T> ov; ov.from_float(o); ov.store(dx + row * D + c);
+        }
       }
     }
   }
@@ -319,8 +374,16 @@ struct AdamTensor {
   long long n;
 };
 constexpr int ADAM_CHUNK = 65536;
+// ``hyper`` (optional, device memory): {lr, bc1, bc2} read at run time instead of the launch arguments, so that a step
+// captured in a CUDA graph follows the learning-rate schedule and the bias corrections of the step it is replayed for.
 __global__ void adamw_kernel(const AdamTensor* __restrict__ tensors, const int2* __restrict__ chunks, float lr,
-                             float beta1, float beta2, float eps, float wd, float bc1, float bc2, float grad_scale) {
+                             float beta1, float beta2, float eps, float wd, float bc1, float bc2, float grad_scale,
+                             const float* __restrict__ hyper) {
+  if (hyper != nullptr) {
+    lr = hyper[0];
+    bc1 = hyper[1];
+    bc2 = hyper[2];
+  }
   const int2 ch = chunks[blockIdx.x];
   const AdamTensor t = tensors[ch.x];
   const long long base = (long long)ch.y * ADAM_CHUNK;
@@ -369,15 +432,23 @@ template <typename T>
 static inline int launch_rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_acc,
                                       long long rows, int D, int num_sms, cudaStream_t st) {
   int threads = 128;
-  while (threads * 8 < D && threads < 1024) threads *= 2;
+  while (threads * 8 < D && threads < 512) threads *= 2;  // at most 512 threads: 128 registers each
   const int nvec = (D + threads * 8 - 1) / (threads * 8);
   if (nvec > RMS_BWD_MAX_VEC) return 3;
-  const int per_sm = threads >= 1024 ? 2 : (threads >= 512 ? 4 : 8);
+  const int per_sm = threads >= 512 ? 2 : 4;
   const long long cap = (long long)num_sms * per_sm;
-  const int grid = (int)(rows < cap ? rows : cap);
-  if (nvec == 1) rms_norm_bwd_kernel<T, 1><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_acc, rows, D);
-  else if (nvec == 2) rms_norm_bwd_kernel<T, 2><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_acc, rows, D);
-  else rms_norm_bwd_kernel<T, 4><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_acc, rows, D);
+  // rows per iteration: as many as the registers hold (16-byte vectors for bf16, two per vector for fp32)
+  constexpr bool wide = sizeof(T) == 4;
+#define APB_RMS_BWD(NV, RW)                                                                                              \
+  {                                                                                                                      \
+    const long long iters = (rows + RW - 1) / RW;                                                                        \
+    const int grid = (int)(iters < cap ? iters : cap);                                                                   \
+    rms_norm_bwd_kernel<T, NV, RW><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_acc, rows, D); \
+  }
+  if (nvec == 1) { if constexpr (wide) APB_RMS_BWD(1, 4) else APB_RMS_BWD(1, 8) }
+  else if (nvec == 2) { if constexpr (wide) APB_RMS_BWD(2, 2) else APB_RMS_BWD(2, 4) }
+  else APB_RMS_BWD(4, 1)  // (nvec 3 runs as 4 with the last vector masked)
+#undef APB_RMS_BWD
   return 0;
 }
 
@@ -407,8 +478,28 @@ int apb_rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, long lo
                      cudaStream_t st) {
   if (D % 8) return 3;
   if (rows == 0) return 0;
-  const int threads = D >= 2048 ? 256 : 128;
-  DISPATCH(is_bf16, rms_norm_fwd_kernel<T><<<(unsigned)rows, threads, 0, st>>>((const T*)x, (const T*)w, (T*)y, rstd, D, eps));
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (D <= 32 * 8 * 4) {
+    // one warp per row, eight rows per block
+    const int nvec = (D + 255) / 256;
+    const long long blocks = (rows + 7) / 8, cap = (long long)sms * 8;
+    const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
+#define APB_RMS_FWD_W(NV) DISPATCH(is_bf16, rms_norm_fwd_kernel<T, NV, true><<<grid, 256, 0, st>>>((const T*)x, (const T*)w, (T*)y, rstd, rows, D, eps))
+    if (nvec == 1) { APB_RMS_FWD_W(1); } else if (nvec == 2) { APB_RMS_FWD_W(2); } else { APB_RMS_FWD_W(4); }
+#undef APB_RMS_FWD_W
+  } else {
+    int threads = 256;
+    while (threads * 8 * 4 < D && threads < 1024) threads *= 2;
+    const int nvec = (D + threads * 8 - 1) / (threads * 8);
+    if (nvec > 4) return 3;
+    const long long cap = (long long)sms * (threads >= 1024 ? 2 : (threads >= 512 ? 4 : 8));
+    const unsigned grid = (unsigned)(rows < cap ? rows : cap);
+#define APB_RMS_FWD_B(NV) DISPATCH(is_bf16, rms_norm_fwd_kernel<T, NV, false><<<grid, threads, 0, st>>>((const T*)x, (const T*)w, (T*)y, rstd, rows, D, eps))
+    if (nvec == 1) { APB_RMS_FWD_B(1); } else if (nvec == 2) { APB_RMS_FWD_B(2); } else { APB_RMS_FWD_B(4); }
+#undef APB_RMS_FWD_B
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
@@ -416,7 +507,7 @@ int apb_rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, long lo
 int apb_rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw, float* dw_acc,
                      long long rows, int D, int is_bf16, int num_sms, cudaStream_t st) {
   if (D % 8) return 3;
-  if (D > 1024 * 8 * RMS_BWD_MAX_VEC) return 3;
+  if (D > 512 * 8 * RMS_BWD_MAX_VEC) return 3;
   cudaMemsetAsync(dw_acc, 0, sizeof(float) * D, st);
   if (rows > 0) {
     int e;
@@ -489,10 +580,10 @@ int apb_embedding_bwd(const void* dy, const long long* ids, float* out_f32, long
 }
 
 int apb_adamw(const void* tensors_dev, const void* chunks_dev, int num_chunks, float lr, float beta1, float beta2, float eps,
-              float wd, float bc1, float bc2, float grad_scale, cudaStream_t st) {
+              float wd, float bc1, float bc2, float grad_scale, const float* hyper_dev, cudaStream_t st) {
   if (num_chunks == 0) return 0;
   adamw_kernel<<<num_chunks, 256, 0, st>>>((const AdamTensor*)tensors_dev, (const int2*)chunks_dev, lr, beta1, beta2, eps, wd,
-                                           bc1, bc2, grad_scale);
+                                           bc1, bc2, grad_scale, hyper_dev);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

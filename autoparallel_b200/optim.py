@@ -20,6 +20,10 @@ def _local(t):
     return t._local_tensor if isinstance(t, DTensor) else t
 
 
+def lp_dev_capturing() -> bool:
+    return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
+
+
 class AdamW(torch.optim.Optimizer):
     CHUNK = 65536
 
@@ -37,6 +41,10 @@ class AdamW(torch.optim.Optimizer):
         self.shadow_arena = shadow_arena if emit_bf16 else None
         self._shadows: dict = {}
         self._tables: dict = {}
+        #: per parameter group: {"host": pinned fp32[3], "dev": fp32[3]} = (lr, bias correction 1, bias correction 2), read
+        #: by the kernel at run time when a step has been captured in a CUDA graph (``runtime.graph_step``)
+        self._hyper: dict = {}
+        self._graph_keepalive: list = []
 
     def _shadow_of(self, p):
         lp = _local(p)
@@ -81,6 +89,7 @@ class AdamW(torch.optim.Optimizer):
         # pinned memory and copy asynchronously (a pageable copy would stall the host until the GPU has
         # drained the whole backward pass).  The chunk list only depends on the sizes and is kept.
         nbytes = len(recs)
+        capturing = lp_dev_capturing()
         stage = cached[4] if cached is not None and cached[4].numel() == nbytes else None
         if stage is None:
             stage = {"host": torch.empty(nbytes, dtype=torch.uint8, pin_memory=True),
@@ -88,15 +97,61 @@ class AdamW(torch.optim.Optimizer):
             ch = torch.tensor(chunks, dtype=torch.int32).reshape(-1, 2).to(dev)
         else:
             stage, ch = cached[5], cached[2]
-        if stage["ev"] is not None:
+        if stage["ev"] is not None and not capturing:
             stage["ev"].synchronize()  # the previous copy out of the pinned buffer has completed
         stage["host"].copy_(torch.frombuffer(recs, dtype=torch.uint8))
         stage["dev"].copy_(stage["host"], non_blocking=True)
-        stage["ev"] = torch.cuda.Event()
-        stage["ev"].record()
+        if not capturing:  # (a captured copy re-reads the pinned table on every replay: it must stay as written here)
+            stage["ev"] = torch.cuda.Event()
+            stage["ev"].record()
         table = stage["dev"]
-        self._tables[gi] = (key, table, ch, len(chunks), stage["host"], stage)
+        if capturing:
+            # the captured copy re-reads this pinned table on every replay: keep it (and the chunk list) alive and out
+            # of reach of later eager steps, which build their own
+            self._graph_keepalive.append((stage, ch))
+            self._tables.pop(gi, None)
+        else:
+            self._tables[gi] = (key, table, ch, len(chunks), stage["host"], stage)
         return table, ch, len(chunks)
+
+    def _hyper_buffers(self, gi: int, device):
+        h = self._hyper.get(gi)
+        if h is None:
+            h = {"host": torch.zeros(3, dtype=torch.float32, pin_memory=True), "dev": torch.zeros(3, dtype=torch.float32, device=device)}
+            self._hyper[gi] = h
+        return h
+
+    def prepare_capture(self) -> None:
+        """Allocate, ahead of a stream capture, what ``step()`` would otherwise allocate inside it (pinned memory
+        cannot be obtained while a stream is capturing).  Needs one eager ``step()`` to have run."""
+        for gi, group in enumerate(self.param_groups):
+            plist = [p for p in group["params"]]
+            if plist:
+                self._hyper_buffers(gi, _local(plist[0]).device)
+            if gi not in self._tables:
+                raise RuntimeError("run one eager optimizer step before capturing (the pointer table is sized by it)")
+
+    @torch.no_grad()
+    def advance_for_replay(self) -> None:
+        """Before replaying a captured step: count the step and hand the kernel this step's learning rate and bias
+        corrections (12 bytes per parameter group, copied on the current stream ahead of the graph launch)."""
+        for gi, group in enumerate(self.param_groups):
+            plist = [p for p in group["params"] if p in self.state and len(self.state[p])]
+            if not plist:
+                continue
+            b1, b2 = group["betas"]
+            for p in plist:
+                self.state[p]["step"] += 1
+            step = float(self.state[plist[0]]["step"])
+            h = self._hyper_buffers(gi, _local(plist[0]).device)
+            if h.get("ev") is not None:
+                h["ev"].synchronize()  # the previous step's copy has read the pinned values (host runs at most one step ahead)
+            h["host"][0] = group["lr"]
+            h["host"][1] = 1 - b1**step
+            h["host"][2] = 1 - b2**step
+            h["dev"].copy_(h["host"], non_blocking=True)
+            h["ev"] = torch.cuda.Event()
+            h["ev"].record()
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -108,11 +163,14 @@ class AdamW(torch.optim.Optimizer):
             for p in plist:
                 self._init_state(p)
             b1, b2 = group["betas"]
+            capturing = lp_dev_capturing()
             step = None
             for p in plist:
                 st = self.state[p]
-                st["step"] += 1
+                if not capturing:  # a captured step is counted when it is replayed (``advance_for_replay``)
+                    st["step"] += 1
                 step = float(st["step"]) if step is None else step
+            step = max(step, 1.0)
             bc1, bc2 = 1 - b1**step, 1 - b2**step
             lp0 = _local(plist[0])
             fast = lp0.is_cuda and all(
@@ -127,8 +185,9 @@ class AdamW(torch.optim.Optimizer):
                 table, ch, n = self._table(gi, plist)
                 if self.shadow_arena is not None:
                     self.shadow_arena.barrier()  # every rank has finished reading the old shards
+                hyper = self._hyper_buffers(gi, lp0.device)["dev"] if capturing else None
                 cuda_impl.extension().adamw(table, ch, n, group["lr"], b1, b2, group["eps"], group["weight_decay"], bc1, bc2,
-                                            self.grad_scale)
+                                            self.grad_scale, hyper)
                 cuda_impl._count()
                 if self.shadow_arena is not None:
                     self.shadow_arena.barrier()  # the new shards are complete on every rank before anyone pulls

@@ -125,6 +125,21 @@ def _run(args, shimmed) -> None:
     plan_s = time.perf_counter() - t0
     parallel_mod.to_empty(device="cuda")
     parallel_mod.init_weights()
+    # The reference's own model leaves every transformer block uninitialised: ``TransformerBlock.init_weights``
+    # returns on its first line (autoparallel/_testing/models/llama3.py:424-425), so after ``to_empty`` the
+    # projection weights are whatever the allocator hands out (zeros on a fresh device).  A GEMM on zeros draws far
+    # less power than one on real values, and under the 1 kW cap that decides the clock of the whole step, so the
+    # harness gives those parameters the random values the benchmark names (N(0, 0.02), norms at one) through the
+    # public ``torch.nn.init`` API.  The reference's code is not touched and nothing else is initialised here.
+    harness_init = 0
+    with torch.no_grad():
+        for name, prm in parallel_mod.named_parameters():
+            if ".layers." in "." + name or name.startswith("layers."):
+                if "norm" in name:
+                    torch.nn.init.ones_(prm)
+                else:
+                    torch.nn.init.trunc_normal_(prm, mean=0.0, std=0.02)
+                harness_init += 1
     try:
         opt = torch.optim.AdamW(parallel_mod.parameters(), lr=3e-4, weight_decay=0.1, fused=True)
         opt_name = "torch.optim.AdamW(fused=True)"
@@ -221,6 +236,8 @@ def _run(args, shimmed) -> None:
                        "execution": mode_ran, "modes_that_failed": errors,
                        "optimizer": opt_name, "ilp_backend": "HiGHS behind a PuLP-compatible shim (CBC/PuLP absent offline)",
                        "torch_compat_shims": shimmed,
+                       "weights": f"{harness_init} transformer-block parameters initialised by the harness with N(0, 0.02) / ones "
+                                  "(the reference model's TransformerBlock.init_weights returns before initialising them)",
                        "l2": "no explicit flush: per-step working set >> 126 MB L2"},
             "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": 2 * S * 8, "d2h_bytes_per_step": 4},

@@ -49,6 +49,9 @@ def parse():
     ap.add_argument("--ref-mode", default="auto", choices=["auto", "compile", "compile_ac", "eager"],
                     help="reference arm only: auto tries the reference driver's torch.compile backend, then the same with its "
                          "activation-checkpointing pass, then the eager module")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="capture forward + backward + optimizer in one CUDA graph and replay it (runtime/graph_step.py); auto: on "
+                         "where every collective of the step can be replayed (one GPU, NCCL, copy-engine gathers)")
     ap.add_argument("--kernel-table", default=None, metavar="PATH",
                     help="after the timed regions, run ONE more step under torch.profiler and write the device time per "
                          "kernel name (JSON) to PATH; never part of a reported number")
@@ -335,6 +338,38 @@ def run_ours(args):
     torch.cuda.synchronize()
     cuda_impl.check_status()
 
+    graphed = None
+    replayable = world == 1 or comm_mode in ("nccl", "dma_ag")
+    if args.graph == "on" or (args.graph == "auto" and replayable):
+        from autoparallel_b200.runtime.graph_step import GraphedTrainStep
+
+        try:
+            graphed = GraphedTrainStep(pm, opt, (devs[0][0],), {"labels": devs[0][1]})
+        except Exception as e:  # capture refused (a collective that cannot be replayed, memory): stay eager
+            if args.graph == "on":
+                raise
+            if rank == 0:
+                print(f"CUDA-graph capture unavailable ({type(e).__name__}: {str(e)[:200]}); eager step", file=sys.stderr, flush=True)
+            graphed = None
+        if world > 1:
+            ok = torch.tensor([1 if graphed is not None else 0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                graphed = None
+    if graphed is not None:
+        def step_device(i):  # noqa: F811
+            tok, lab = devs[i % n_sets]
+            return graphed(tok, labels=lab)
+
+        def step_e2e(i):  # noqa: F811
+            t, l = host[i % n_sets]
+            return graphed(t, labels=l).item()  # pinned host -> static device buffers, replay, loss read back
+
+        for i in range(2):
+            step_device(i)
+        torch.cuda.synchronize()
+        cuda_impl.check_status()
+
     def timed(fn, steps):
         dist.barrier()
         torch.cuda.synchronize()
@@ -385,7 +420,7 @@ def run_ours(args):
                 "parallelism": f"dp{world} (plan chosen by the ILP: FSDP, bf16 compute, fp32 grad reduce)",
                 "optimizer": "AdamW (fp32 state, in the timed region)",
                 "activation_checkpointing": ac,
-                "executor": args.executor,
+                "executor": args.executor + (" + whole-step CUDA graph" if graphed is not None else ""),
                 "comm": comm_mode if world > 1 else "none",
                 "reserved_sms_for_comm": reserve,
                 "overlap": {"prefetch_depth": ocfg.prefetch_depth, "max_in_flight_gib": round(ocfg.max_in_flight_bytes / 2**30, 2),
