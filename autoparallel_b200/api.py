@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import contextlib
 import logging
+import json
 import time
 from typing import Any, Callable, Optional, Sequence
 
@@ -50,6 +51,18 @@ def _mesh_device(mesh) -> torch.device:
     if mesh.device_type == "cuda":
         return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
     return torch.device(mesh.device_type)
+
+
+def _artifact(name: str, encoding: str, payload_fn) -> None:
+    """Structured-trace artifact (``TORCH_TRACE=<dir>`` + tlparse): the joint graph, the optimizer's log, the solution
+    and the parallel graph are dumped under the names the reference uses (autoparallel/api.py:212-221, 409-418,
+    430-437, 481-490), so existing tooling finds them.  The payload is only built when a trace is being written."""
+    try:
+        from torch._logging import trace_structured
+
+        trace_structured("artifact", metadata_fn=lambda: {"name": name, "encoding": encoding}, payload_fn=payload_fn)
+    except Exception as e:  # tracing must never break planning
+        logger.debug("structured trace artifact %s not written: %s", name, e)
 
 
 class AutoParallel:
@@ -85,7 +98,12 @@ class AutoParallel:
         bucket_collectives: bool = False,
         ordered_sharding: bool = True,
         uneven_sharding: bool = False,
+        pattern_ops: bool = True,
     ):
+        # pattern_ops=True: stock-PyTorch idioms of the model (nn.RMSNorm, F.silu(a) * b, rotary embedding by complex
+        # multiplication, F.scaled_dot_product_attention) are rewritten to this framework's operators while tracing
+        # (parallel/passes/pattern_ops.py); False keeps the traced ATen operators.
+        self.pattern_ops = bool(pattern_ops)
         # uneven_sharding=True: a tensor dim may be sharded although the mesh dim does not divide it.  Shards are
         # ceil-sized chunks (the last non-empty one shorter, later ones empty); every rank lowers the graph with
         # its own shard shapes and collectives on such dims pad to the chunk size and cut the result.
@@ -133,9 +151,10 @@ class AutoParallel:
             self._install_cost_models()
             self._stack.enter_context(self.mesh)
             t0 = time.perf_counter()
-            self.joint = build_joint_graph(self.model, self.input_fn, self.fake_mode)
+            self.joint = build_joint_graph(self.model, self.input_fn, self.fake_mode, pattern_ops=self.pattern_ops)
             self.gm = self.joint.gm
             self.timings["trace"] = time.perf_counter() - t0
+            _artifact("autoparallel_joint_graph", "string", lambda: self.gm.print_readable(print_output=False))
             t0 = time.perf_counter()
             self.sharding_optimizer = self._new_optimizer(self.joint)
             self.timings["build_optimizer"] = time.perf_counter() - t0
@@ -252,6 +271,8 @@ class AutoParallel:
         self.timings["solve"] = time.perf_counter() - t0
         if verbose:
             logger.info(self.sharding_optimizer.get_log(verbose=True))
+        _artifact("autoparallel_sharding_optimizer_log", "string", lambda: self.sharding_optimizer.get_log(verbose=True, colored=False))
+        _artifact("autoparallel_solution", "json", lambda: json.dumps(self.sharding_optimizer.get_json()))
         return self.sharding_placement
 
     def lower(self, sharding_placement=None) -> LoweredGraph:
@@ -262,6 +283,7 @@ class AutoParallel:
         self.timings["lower"] = time.perf_counter() - t0
         self.lowered = lowered
         self.parallel_gm = lowered.gm
+        _artifact("autoparallel_parallel_graph", "string", lambda: lowered.gm.print_readable(print_output=False))
         return lowered
 
     def _lower(self, joint: JointGraph, sol) -> LoweredGraph:
@@ -426,7 +448,7 @@ class AutoParallel:
         try:
             self._install_cost_models()
             with self.mesh:
-                joint = build_joint_graph(self.model, input_fn, self.fake_mode)
+                joint = build_joint_graph(self.model, input_fn, self.fake_mode, pattern_ops=self.pattern_ops)
                 opt = self._new_optimizer(joint)
                 sol = _transfer_solution(solved, opt)
                 lowered = self._lower(joint, sol)

@@ -38,6 +38,8 @@ int apb_xent_bwd(const float* dloss, const void* logits, const long long* labels
                  long long rows, int V, int is_bf16, cudaStream_t st);
 int apb_embedding_bwd(const void* dy, const long long* ids, float* out_f32, long long tokens, int D, int is_bf16,
                       cudaStream_t st);
+int apb_embedding_fwd(const void* weight, const long long* ids, void* out, long long tokens, int D, long long num_rows,
+                      int is_bf16, cudaStream_t st);
 int apb_symm_header_bytes();
 int apb_symm_wait_probe(const uint32_t* flag, unsigned target, unsigned limit_ms, uint32_t* status, cudaStream_t st);
 void apb_symm_use_multicast_once(unsigned long long workspace_multicast_ptr);
@@ -196,6 +198,15 @@ void xent_bwd(const at::Tensor& dloss, const at::Tensor& logits, const at::Tenso
         "apb_xent_bwd");
 }
 
+void embedding_fwd(const at::Tensor& weight, const at::Tensor& ids, at::Tensor& out) {
+  c10::cuda::CUDAGuard g(weight.device());
+  TORCH_CHECK(weight.dim() == 2 && weight.is_contiguous() && ids.scalar_type() == at::kLong && ids.is_contiguous() && out.is_contiguous(),
+              "embedding_fwd: contiguous [V, D] table, int64 ids");
+  check(apb_embedding_fwd(weight.data_ptr(), reinterpret_cast<const long long*>(ids.data_ptr()), out.data_ptr(), ids.numel(),
+                          (int)weight.size(1), weight.size(0), is_bf16(weight), stream()),
+        "apb_embedding_fwd");
+}
+
 void embedding_bwd(const at::Tensor& dy, const at::Tensor& ids, at::Tensor& out_f32) {
   c10::cuda::CUDAGuard g(dy.device());
   check(apb_embedding_bwd(dy.data_ptr(), (const long long*)ids.data_ptr<int64_t>(), out_f32.data_ptr<float>(), ids.numel(),
@@ -341,6 +352,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("xent_fwd", &xent_fwd);
   m.def("xent_bwd", &xent_bwd);
   m.def("embedding_bwd", &embedding_bwd);
+  m.def("embedding_fwd", &embedding_fwd);
   m.def("adamw", &adamw);
   m.def("symm_header_bytes", &symm_header_bytes);
   m.def("symm_wait_probe", &symm_wait_probe);

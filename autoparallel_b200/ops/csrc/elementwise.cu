@@ -353,6 +353,20 @@ __global__ void xent_bwd_kernel(const float* __restrict__ dloss, const T* __rest
   }
 }
 
+// ------------------------------------------------------------------------------------ embedding forward
+// out[token] = weight[ids[token]]: one block per token, 16-byte vectors (D % 8 == 0 for bf16, % 4 for fp32).
+template <typename T>
+__global__ void embedding_fwd_kernel(const T* __restrict__ weight, const long long* __restrict__ ids, T* __restrict__ out, int D,
+                                     long long num_rows) {
+  const long long tok = blockIdx.x;
+  long long r = ids[tok];
+  r = r < 0 ? 0 : (r >= num_rows ? num_rows - 1 : r);  // (an id outside the table is the caller's bug; never read outside)
+  const uint4* src = reinterpret_cast<const uint4*>(weight + r * D);
+  uint4* dst = reinterpret_cast<uint4*>(out + tok * D);
+  const int nvec = D * (int)sizeof(T) / 16;
+  for (int c = threadIdx.x; c < nvec; c += blockDim.x) dst[c] = src[c];
+}
+
 // ------------------------------------------------------------------------------------ embedding backward
 // out fp32 [rows, D] (zeroed by caller) += dy[token] for each token; one block per token.
 template <typename T>
@@ -569,6 +583,14 @@ int apb_xent_bwd(const float* dloss, const void* logits, const long long* labels
   if (rows == 0) return 0;
   const int threads = V >= 8192 ? 1024 : 256;
   DISPATCH(is_bf16, xent_bwd_kernel<T><<<(unsigned)rows, threads, 0, st>>>(dloss, (const T*)logits, labels, lse, (T*)dlogits, V));
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int apb_embedding_fwd(const void* weight, const long long* ids, void* out, long long tokens, int D, long long num_rows,
+                      int is_bf16, cudaStream_t st) {
+  if (tokens == 0) return 0;
+  if ((D * (is_bf16 ? 2 : 4)) % 16) return 3;
+  DISPATCH(is_bf16, embedding_fwd_kernel<T><<<(unsigned)tokens, 128, 0, st>>>((const T*)weight, ids, (T*)out, D, num_rows));
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

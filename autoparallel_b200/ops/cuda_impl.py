@@ -270,6 +270,16 @@ def _cross_entropy_bwd(dloss, logits, labels, lse):
     return out
 
 
+def _embedding(weight, ids):
+    if weight.dtype not in (torch.bfloat16, torch.float32) or (weight.shape[1] * weight.element_size()) % 16 or ids.dtype != torch.long:
+        _fallback("embedding", f"table {weight.dtype} {tuple(weight.shape)}, ids {ids.dtype}")
+        return torch.nn.functional.embedding(ids, weight)
+    out = torch.empty((*ids.shape, weight.shape[1]), dtype=weight.dtype, device=weight.device)
+    _C.embedding_fwd(weight.contiguous(), ids.contiguous(), out)
+    _count()
+    return out
+
+
 def _embedding_bwd(dy, ids, num_rows):
     dy = dy.contiguous()
     out = torch.zeros(num_rows, dy.shape[-1], dtype=torch.float32, device=dy.device)
@@ -375,6 +385,7 @@ def _register() -> None:
     R("swiglu_bwd", _swiglu_bwd)
     R("cross_entropy", _cross_entropy)
     R("cross_entropy_bwd", _cross_entropy_bwd)
+    R("embedding", _embedding)
     R("embedding_bwd", _embedding_bwd)
     R("attention", _attention)
     R("attention_bwd", _attention_bwd)

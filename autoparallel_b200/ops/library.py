@@ -64,6 +64,7 @@ lib.define("cross_entropy(Tensor logits, Tensor labels) -> (Tensor, Tensor)")
 lib.define("cross_entropy_bwd(Tensor dloss, Tensor logits, Tensor labels, Tensor lse) -> Tensor")
 # C[M,N] = op(A) @ op(B); trans flags are about the *stored* layout (row-major storage).
 lib.define("gemm(Tensor a, Tensor b, bool trans_a, bool trans_b, ScalarType out_dtype) -> Tensor")
+lib.define("embedding(Tensor weight, Tensor ids) -> Tensor")
 lib.define("embedding_bwd(Tensor dy, Tensor ids, int num_rows) -> Tensor")
 
 
@@ -202,6 +203,7 @@ _CPU_IMPLS = {
     "cross_entropy": _cross_entropy_ref,
     "cross_entropy_bwd": _cross_entropy_bwd_ref,
     "gemm": _gemm_ref,
+    "embedding": lambda weight, ids: torch.nn.functional.embedding(ids, weight),
     "embedding_bwd": _embedding_bwd_ref,
 }
 for _name, _fn in _CPU_IMPLS.items():
@@ -242,6 +244,7 @@ _META_IMPLS = {
     ),
     "cross_entropy_bwd": lambda dloss, logits, labels, lse: _meta_like(logits),
     "gemm": _gemm_meta,
+    "embedding": lambda weight, ids: weight.new_empty((*ids.shape, weight.shape[1])),
     "embedding_bwd": lambda dy, ids, num_rows: dy.new_empty((num_rows, dy.shape[-1])),
 }
 for _name, _fn in _META_IMPLS.items():
@@ -389,6 +392,20 @@ def _gemm_bwd(ctx, dc):
 _ag("gemm", _gemm_bwd, _gemm_setup)
 
 
+def _emb_setup(ctx, inputs, output):
+    weight, ids = inputs
+    ctx.save_for_backward(ids)
+    ctx.num_rows = weight.shape[0]
+
+
+def _emb_bwd(ctx, dy):
+    (ids,) = ctx.saved_tensors
+    return ops.embedding_bwd(dy, ids, ctx.num_rows), None
+
+
+_ag("embedding", _emb_bwd, _emb_setup)
+
+
 # --------------------------------------------------------------------------------------
 # thin functional front-ends used by the model zoo
 # --------------------------------------------------------------------------------------
@@ -408,6 +425,11 @@ def attention(q, k, v, causal: bool = True, scale: float | None = None) -> torch
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     return ops.attention(q, k, v, causal, float(scale))[0]
+
+
+def embedding(weight: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """Rows ``ids`` of ``weight`` ([V, D]); the gradient is scattered back by ``embedding_bwd``."""
+    return ops.embedding(weight, ids)
 
 
 def cross_entropy(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:

@@ -196,7 +196,7 @@ def _add_unused_state(model: nn.Module, gm: fx.GraphModule) -> None:
 
 
 def build_joint_graph(
-    model: nn.Module, input_fn: Callable, fake_mode: FakeTensorMode, canonicalize: bool = True
+    model: nn.Module, input_fn: Callable, fake_mode: FakeTensorMode, canonicalize: bool = True, pattern_ops: bool = True
 ) -> JointGraph:
     from torch._dynamo.functional_export import _dynamo_graph_capture_for_export
     from torch._functorch.aot_autograd import aot_export_joint_with_descriptors
@@ -212,6 +212,13 @@ def build_joint_graph(
             captured = _dynamo_graph_capture_for_export(model)(*traced_inputs.args, **traced_inputs.kwargs)
             _restore_state_dict(model, captured)
             _add_unused_state(model, captured)
+            pattern_stats = {}
+            if pattern_ops:
+                # stock-PyTorch idioms (nn.RMSNorm, F.silu * x, complex RoPE, F.scaled_dot_product_attention) become this
+                # framework's operators before differentiation, so their backward is the operators' own
+                from ..passes.pattern_ops import rewrite_to_framework_ops
+
+                pattern_stats = rewrite_to_framework_ops(captured)
             jd = aot_export_joint_with_descriptors(
                 stack,
                 captured,
@@ -226,7 +233,9 @@ def build_joint_graph(
 
         _canon(gm)
     joint = index_joint_graph(gm, traced_inputs, out_spec)
-    logger.info("joint graph captured in %.3fs (%d nodes)", time.perf_counter() - t0, len(gm.graph.nodes))
+    joint.pattern_stats = pattern_stats
+    logger.info("joint graph captured in %.3fs (%d nodes); idioms rewritten to framework operators: %s",
+                time.perf_counter() - t0, len(gm.graph.nodes), pattern_stats)
     return joint
 
 

@@ -237,6 +237,16 @@ def _grouped_mm_wgrad(ctx):
     return expand_rows(ctx, [(S(0), S(0), S(0)), (P, S(1), S(1)), (S(1), S(2), R), (S(2), R, S(2))])
 
 
+@register_rule(apb.embedding.default)
+def _embedding(ctx):
+    # (out [*ids, D], weight [V, D], ids): split the tokens, or the hidden dim of the table; a table split by rows
+    # would need a masked lookup and a reduction and is not offered (the table is gathered instead)
+    weight, ids = ctx.in_vals
+    rows = [(S(i), R, S(i)) for i in range(ids.ndim)]
+    rows.append((S(ids.ndim), S(1), R))
+    return expand_rows(ctx, rows)
+
+
 @register_rule(apb.embedding_bwd.default)
 def _embedding_bwd(ctx):
     dy, ids = ctx.in_vals

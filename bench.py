@@ -46,6 +46,13 @@ def parse():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5],
+                    help="benchmark configuration: 2 = Llama-3 8B on a 1-D dp mesh (the headline; default), 3 = Llama-3 8B on "
+                         "dp=2 x tp=4 with global batch 4 x 8192, 4 = MoE decoder (64 experts, top-8, shared expert) with expert "
+                         "parallelism through local_map and global batch 16 x 4096, 5 = Llama-3 70B on dp=2 x tp=4 with activation "
+                         "checkpointing, a parameter-memory budget and global batch 8 x 4096.  3-5 need 8 GPUs and print their own "
+                         "metric name, never the headline's")
+    ap.add_argument("--zipf", type=float, default=None, help="config 4: Zipf(s) router bias over the experts (skewed load)")
     ap.add_argument("--ref-mode", default="auto", choices=["auto", "compile", "compile_ac", "eager"],
                     help="reference arm only: auto tries the reference driver's torch.compile backend, then the same with its "
                          "activation-checkpointing pass, then the eager module")
@@ -209,7 +216,15 @@ def run_ours(args):
         pg_opts = dist.ProcessGroupNCCL.Options()
         pg_opts.is_high_priority_stream = True
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank), pg_options=pg_opts)
-    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    if args.config in (3, 5):
+        assert world == 8, f"config {args.config} is defined on a dp=2 x tp=4 mesh: launch on 8 GPUs"
+        mesh = init_device_mesh("cuda", (2, 4), mesh_dim_names=("dp", "tp"))
+    elif args.config == 4:
+        mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("ep",))
+    else:
+        mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    data_ranks = mesh.shape[0]            # ranks the batch is split over (the first mesh dim)
+    data_rank = mesh.get_local_rank(0)
     cuda_impl.ensure_loaded()
     cuda_impl.extension().gemm_set_reserved_sms(reserve)
     if args.gemm_stages is not None:
@@ -223,15 +238,36 @@ def run_ours(args):
 
         _co.set_sm_yield(yield_pairs)
 
-    cfg = {"llama3_8b": llama3.llama3_8b, "llama3_debug": llama3.llama3_debug,
-           "llama3_1b": lambda **kw: llama3.llama3_8b(dim=2048, n_layers=16, n_heads=16, n_kv_heads=8, ffn_hidden=8192, **kw)}[args.model](
-        max_seq_len=args.seq_len)
-    if args.layers is not None:
-        cfg.n_layers = args.layers
-    S = args.seq_len
-    B_global = world  # one sequence per GPU (weak scaling); dp=8 gives the named global batch of 8
-    with torch.device("meta"):
-        model = llama3.Transformer(cfg)
+    model_name = args.model
+    if args.config == 4:
+        from autoparallel_b200.models import moe
+
+        S = 4096 if args.seq_len == 8192 else args.seq_len
+        cfg = moe.moe_reference_config(max_seq_len=S, ep_axis="ep", router_bias_zipf=args.zipf)
+        if args.layers is not None:
+            cfg.n_layers = args.layers
+        B_global = 2 * world  # 16 sequences of 4096 on 8 ranks
+        model_name = "moe_64e_top8" + (f"_zipf{args.zipf:g}" if args.zipf else "")
+        with torch.device("meta"):
+            model = moe.MoETransformer(cfg)
+    else:
+        if args.config == 5:
+            model_name = "llama3_70b"
+            S = 4096 if args.seq_len == 8192 else args.seq_len
+            cfg = llama3.llama3_70b(max_seq_len=S)
+            B_global = 8
+        else:
+            cfg = {"llama3_8b": llama3.llama3_8b, "llama3_debug": llama3.llama3_debug,
+                   "llama3_1b": lambda **kw: llama3.llama3_8b(dim=2048, n_layers=16, n_heads=16, n_kv_heads=8, ffn_hidden=8192, **kw)}[args.model](
+                max_seq_len=args.seq_len)
+            S = args.seq_len
+            # config 2: one sequence per GPU (weak scaling; dp=8 gives the named global batch of 8); config 3: 4 x 8192
+            B_global = 4 if args.config == 3 else world
+        if args.layers is not None:
+            cfg.n_layers = args.layers
+        with torch.device("meta"):
+            model = llama3.Transformer(cfg)
+    B_local = B_global // data_ranks
 
     def input_fn():
         return ForwardInputs((torch.randint(0, cfg.vocab_size, (B_global, S)),),
@@ -240,7 +276,8 @@ def run_ours(args):
     ac = args.ac
     if ac == "auto":
         # one GPU holds fp32 params + grads + Adam moments (16 B/param): recompute cheap ops there
-        ac = "selective" if world == 1 and cfg.num_params() > 4e9 else "none"
+        n_params = sum(p.numel() for p in model.parameters())
+        ac = "full" if args.config == 5 else ("selective" if world == 1 and n_params > 4e9 else "none")
     fuse_arg = None
     comm_mode = args.comm
     if comm_mode == "auto":
@@ -253,7 +290,7 @@ def run_ours(args):
     if world > 1 and comm_mode.startswith("dma"):
         from autoparallel_b200.runtime import dma
 
-        local_param_bytes = sum(p.numel() for p in model.parameters()) * 2 // world
+        local_param_bytes = sum(p.numel() for p in model.parameters()) * 2 // world + (256 << 10) * len(list(model.parameters()))
         # one staging slot holds one rank's chunk of the largest per-layer weight gradient (fp32)
         layer_max = max((p.numel() for n_, p in model.named_parameters() if "layers." in n_), default=0)
         slot = ((layer_max * 4 // world + 4095) // 4096) * 4096 if comm_mode == "dma" else 0
@@ -286,8 +323,14 @@ def run_ours(args):
     t0 = time.perf_counter()
     with AutoParallel(model, input_fn, mesh, MPPolicy(torch.bfloat16, torch.float32), activation_checkpointing=ac,
                       fuse_collectives=fuse_arg) as ap:
-        ap.add_parameter_memory_constraint()
-        ap.add_input_constraints([(Shard(0),)] * 2)
+        from torch.distributed.tensor.placement_types import Replicate
+
+        if args.config == 5:
+            # 180 GB per GPU: fp32 master + gradient + two Adam moments (16 B per element held) may take 150 GB of it
+            ap.add_parameter_memory_constraint(budget_bytes=150e9, bytes_per_element=16.0)
+        else:
+            ap.add_parameter_memory_constraint()
+        ap.add_input_constraints([(Shard(0),) + (Replicate(),) * (mesh.ndim - 1)] * 2)
         ap.optimize_placement()
         from autoparallel_b200.parallel.passes.overlap import OverlapConfig
 
@@ -307,12 +350,14 @@ def run_ours(args):
     plan_s = time.perf_counter() - t0
     pm.to_empty(device="cuda")
     pm.init_weights(seed=0)
-    opt = AdamW(pm.parameters(), lr=3e-4, weight_decay=0.1, emit_bf16=(args.emit_bf16 == "on"), shadow_arena=shadow_arena)
+    # config 5 (70B on 8 GPUs) has no room for a second, bf16 copy of the parameters: 16 B/element already take 140 GB
+    emit = args.emit_bf16 == "on" and args.config != 5
+    opt = AdamW(pm.parameters(), lr=3e-4, weight_decay=0.1, emit_bf16=emit, shadow_arena=shadow_arena)
 
-    g = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    g = torch.Generator(device="cpu").manual_seed(1234 + data_rank)  # ranks that share a batch shard draw the same tokens
     n_sets = 4
-    host = [(torch.randint(0, cfg.vocab_size, (1, S), generator=g).pin_memory(),
-             torch.randint(0, cfg.vocab_size, (1, S), generator=g).pin_memory()) for _ in range(n_sets)]
+    host = [(torch.randint(0, cfg.vocab_size, (B_local, S), generator=g).pin_memory(),
+             torch.randint(0, cfg.vocab_size, (B_local, S), generator=g).pin_memory()) for _ in range(n_sets)]
     devs = [(t.cuda(), l.cuda()) for t, l in host]
 
     def step_device(i):
@@ -398,9 +443,11 @@ def run_ours(args):
     value = tokens / (ms_dev / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
     if rank == 0:
-        flops_tok = cfg.flops_per_token(S)
+        flops_tok = cfg.flops_per_token(S) if hasattr(cfg, "flops_per_token") else 0
+        headline = args.config == 2 and args.model == "llama3_8b" and args.layers is None
+        mesh_desc = " x ".join(f"{n}={s_}" for n, s_ in zip(mesh.mesh_dim_names, mesh.shape))
         out = {
-            "metric": "Llama-3-8B train tokens/s (auto plan)" if args.model == "llama3_8b" and args.layers is None else f"{args.model} train tokens/s (auto plan; NOT the headline config)",
+            "metric": "Llama-3-8B train tokens/s (auto plan)" if headline else f"{model_name} train tokens/s on {mesh_desc} (auto plan; config {args.config}, NOT the headline config)",
             "value": value,
             "unit": "tokens/s",
             "n_gpus": world,
@@ -414,10 +461,11 @@ def run_ours(args):
             "data": "synthetic",
             "impl": "ours",
             "config": {
-                "model": args.model if args.layers is None else f"{args.model}[{args.layers} layers]",
+                "model": model_name if args.layers is None else f"{model_name}[{args.layers} layers]",
                 "global_batch": B_global,
                 "seq_len": S,
-                "parallelism": f"dp{world} (plan chosen by the ILP: FSDP, bf16 compute, fp32 grad reduce)",
+                "parallelism": (f"dp{world} (plan chosen by the ILP: FSDP, bf16 compute, fp32 grad reduce)" if args.config == 2
+                                else f"{mesh_desc} (plan chosen by the ILP, bf16 compute, fp32 grad reduce)"),
                 "optimizer": "AdamW (fp32 state, in the timed region)",
                 "activation_checkpointing": ac,
                 "executor": args.executor + (" + whole-step CUDA graph" if graphed is not None else ""),
@@ -426,7 +474,7 @@ def run_ours(args):
                 "overlap": {"prefetch_depth": ocfg.prefetch_depth, "max_in_flight_gib": round(ocfg.max_in_flight_bytes / 2**30, 2),
                             "pending_reductions": ocfg.max_pending_reductions},
                 "sm_pairs_yielded_per_collective": yield_pairs if world > 1 and dynamic_tiles else 0,
-                "optimizer_emits_bf16_params": args.emit_bf16 == "on",
+                "optimizer_emits_bf16_params": emit,
                 "gemm_stages": cuda_impl.extension().gemm_get_pair_stages(),
                 "gemm_dynamic_tiles": bool(cuda_impl.extension().gemm_get_dynamic_tiles()),
                 "nccl_stream_priority": args.nccl_priority if world > 1 else "none",
@@ -437,14 +485,14 @@ def run_ours(args):
                 "l2": "no explicit flush: per-step working set (>=16 GB of weights + activations) >> 126 MB L2",
             },
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": 2 * S * 8, "d2h_bytes_per_step": 4},
+                    "h2d_bytes_per_step": 2 * B_local * S * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
             "library_fallbacks": dict(cuda_impl.library_fallbacks),
             "clocks": clocks,
             "ilp_solve_s": ilp_solve_s,
             "plan_s": {k: round(v, 3) for k, v in timings.items()},
             "plan_total_s": round(plan_s, 2),
-            "mfu_vs_nominal_2250": value / world * flops_tok / 2.25e15,
+            "mfu_vs_nominal_2250": (value / world * flops_tok / 2.25e15) if flops_tok else None,
             "peak_mem_gib": round(peak_mem, 1),
             "final_loss": float(last_e2e),
         }

@@ -168,3 +168,47 @@ def test_shipped_measured_table_changes_the_prices(mesh_1d):
         assert ap.sharding_optimizer.objective_value > 0
     finally:
         ap.__exit__(None, None, None)
+
+
+def test_estimate_against_measurement_helpers(mesh_1d):
+    """benchmark_strategy_runtime_cost / compare_estimated_with_benchmarked_throughput run the nodes with their local shapes."""
+    from autoparallel_b200.parallel.cost.compute import benchmark_strategy_runtime_cost, compare_estimated_with_benchmarked_throughput
+
+    ap = _llama(mesh_1d)
+    try:
+        sol = ap.optimize_placement()
+        data = compare_estimated_with_benchmarked_throughput(ap.gm.graph, sol, device=torch.device("cpu"))
+        assert len(data) >= 7
+        for node, (real_us, est_us, tflops, peak, eff) in data.items():
+            assert node.target in (apb.mm_nd.default, apb.mm_wgrad.default)
+            assert real_us > 0 and est_us > 0 and tflops > 0 and peak > 0 and eff == tflops / peak
+        norm = next(n for n in ap.gm.graph.nodes if n.target is apb.rms_norm.default)
+        assert benchmark_strategy_runtime_cost(norm, sol[norm], torch.device("cpu")) > 0
+        view = next(n for n in ap.gm.graph.nodes if n.op == "call_function" and "view" in str(n.target))
+        assert benchmark_strategy_runtime_cost(view, sol[view], torch.device("cpu")) == 0.0
+    finally:
+        ap.__exit__(None, None, None)
+
+
+def test_structured_trace_artifacts(mesh_1d, tmp_path, monkeypatch):
+    """With a structured trace being written, planning dumps the four artifacts under the reference's names."""
+    import torch._logging._internal as tl
+
+    seen = {}
+
+    def fake(name, metadata_fn=None, payload_fn=None, **kw):
+        md = metadata_fn() if metadata_fn else {}
+        seen[md.get("name")] = (md.get("encoding"), payload_fn())
+
+    import autoparallel_b200.api as api_mod
+
+    monkeypatch.setattr("torch._logging.trace_structured", fake)
+    ap = _llama(mesh_1d)
+    try:
+        ap.lower()
+    finally:
+        ap.__exit__(None, None, None)
+    assert set(seen) >= {"autoparallel_joint_graph", "autoparallel_sharding_optimizer_log", "autoparallel_solution",
+                         "autoparallel_parallel_graph"}
+    assert seen["autoparallel_solution"][0] == "json" and json.loads(seen["autoparallel_solution"][1])
+    assert "apb200.mm_nd" in seen["autoparallel_joint_graph"][1] and "apb200_comm" in seen["autoparallel_parallel_graph"][1]

@@ -357,3 +357,18 @@ def test_graphed_train_step_matches_eager_steps():
     finally:
         if own_pg:
             dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_embedding_forward_and_backward(K, dtype):
+    L, _ = K
+    torch.manual_seed(0)
+    V, D = 1000, 256
+    w = torch.randn(V, D, device="cuda", dtype=dtype, requires_grad=True)
+    ids = torch.randint(0, V, (3, 77), device="cuda")
+    out = L.embedding(w, ids)
+    assert torch.equal(out, torch.nn.functional.embedding(ids, w))
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref = torch.zeros(V, D, dtype=torch.float32).index_add_(0, ids.reshape(-1).cpu(), g.reshape(-1, D).float().cpu())
+    _close(w.grad, ref, 2e-2 if dtype == torch.bfloat16 else 1e-5, 2e-2 if dtype == torch.bfloat16 else 1e-5)

@@ -155,7 +155,21 @@ def test_save_load_json_log_html_and_metrics(mesh_1d, tmp_path):
         json.dumps(plan)
         assert plan["mesh"]["shape"] == [8] and {n["phase"] for n in plan["nodes"]} == {"forward", "backward"}
         html = generate_visualization_html(plan)
-        assert "<table" in html and "Module tree" in html
+        assert "<table" in html and "id=treemap" in html
+        # the three views the reference's report has: module treemap, parameter tree, simulated-step timeline
+        from autoparallel_b200.utils.visualizer import module_tree, parameter_tree, write_report
+
+        mt = module_tree(plan["nodes"])
+        assert mt["name"] == "model" and mt["children"] and abs(mt["compute"] - plan["summary"]["compute_us"]) < 1e-3 * max(1, mt["compute"])
+        pt = parameter_tree(plan["nodes"], plan["mesh"]["shape"])
+        assert pt["count"] == len(ap.joint.param_nodes) and 0 < pt["local_bytes"] <= pt["bytes"]
+        low = ap.lower()
+        report = write_report(str(tmp_path / "plan.html"), opt, low.gm, ap.mesh)
+        doc = open(report).read()
+        for marker in ("id=modules", "id=parameters", "id=timeline", "drawTreemap", "traceEvents", "download Chrome-trace JSON"):
+            assert marker in doc, marker
+        embedded = json.loads(doc.split("const DATA=", 1)[1].split(";\nfunction show", 1)[0])
+        assert embedded["trace"]["traceEvents"] and embedded["modules"]["n"] == len(plan["nodes"])
         p1, p2 = str(tmp_path / "opt.pt"), str(tmp_path / "pl.json")
         opt.save(p1)
         opt.save_placements(p2)
