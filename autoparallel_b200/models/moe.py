@@ -10,7 +10,12 @@ expert FFN on the local experts → combine all-to-all → weighted scatter-add 
 
 Dispatch is **capacity based**: each (source rank, expert) pair owns a fixed slot count
 ``C = ceil(capacity_factor · tokens · top_k / num_experts)``; assignments beyond the slot count are
-dropped (their gate weight contributes nothing).  Shapes are therefore static – no device→host
+dropped (their gate weight contributes nothing).  ``capacity_factor=None`` is the **dropless** setting: every
+(source rank, expert) pair gets as many slots as the rank has tokens - the most it can ever need, since a token
+names an expert at most once - so no assignment is ever dropped and the numerics equal the single-device model
+under any routing skew, at the price of moving and multiplying the padding (exact, not fast: a transport and a
+grouped GEMM that skip the padding through device-side counts are not built).  ``MoEFFN.dropped_assignments``
+counts what a given batch would lose under the configured capacity.  Shapes are therefore static – no device→host
 sync for split sizes in any layer and the step is CUDA-graph capturable – where the reference
 exchanges counts and then syncs to the host for variable all-to-all splits
 (autoparallel/_testing/models/dsv3.py:552-616; routing :388-444; region :620-703).
@@ -42,7 +47,7 @@ class MoEConfig:
     top_k: int = 8
     expert_hidden: int = 1408
     shared_hidden: int = 1408
-    capacity_factor: float = 1.25
+    capacity_factor: Optional[float] = 1.25  # None: dropless (capacity = tokens per rank)
     norm_eps: float = 1e-5
     rope_theta: float = 10000.0
     max_seq_len: int = 4096
@@ -196,7 +201,7 @@ class MoEFFN(nn.Module):
             return shared + self._routed_planner(x.reshape(b * s, d), gate_w.to(x.dtype).reshape(b * s, -1),
                                                  gate_idx.reshape(b * s, -1)).view(b, s, d)
         tokens_per_rank = (b * s) // axis_size(cfg.ep_axis)
-        capacity = max(1, math.ceil(cfg.capacity_factor * tokens_per_rank * cfg.top_k / cfg.num_experts))
+        capacity = self.capacity(tokens_per_rank)
 
         # Argument order = order of first use inside the region: the graph capture lists the region's
         # inputs in that order and insists that the declared placements line up with it.
@@ -208,12 +213,30 @@ class MoEFFN(nn.Module):
             gate_idx.reshape(b * s, -1), x.reshape(b * s, d), self.w1, self.w3, self.w2, gate_w.to(x.dtype).reshape(b * s, -1))
         return shared + routed.view(b, s, d)
 
+    def capacity(self, tokens: int) -> int:
+        """Slots of one (token block, expert) pair; ``tokens`` = tokens of the block (a rank, or a dispatch block)."""
+        cfg = self.cfg
+        if cfg.capacity_factor is None:
+            return max(1, tokens)  # dropless: a block never sends more than one assignment per token to an expert
+        return max(1, math.ceil(cfg.capacity_factor * tokens * cfg.top_k / cfg.num_experts))
+
+    @torch.no_grad()
+    def dropped_assignments(self, x: torch.Tensor, blocks: int) -> int:
+        """How many of the ``tokens x top_k`` assignments of ``x`` [b, s, d] the configured capacity drops when the
+        tokens are split into ``blocks`` equal blocks (ranks of the expert-parallel axis, or dispatch blocks)."""
+        cfg = self.cfg
+        scores = torch.softmax(self.router(x).float() + self.router_bias, dim=-1)
+        idx = torch.topk(scores, cfg.top_k, dim=-1).indices.reshape(blocks, -1)          # [blocks, tokens/block * k]
+        cap = self.capacity(idx.shape[1] // cfg.top_k)
+        counts = torch.zeros(blocks, cfg.num_experts, dtype=torch.long, device=x.device).scatter_add_(1, idx, torch.ones_like(idx))
+        return int((counts - cap).clamp_min(0).sum().item())
+
     def _routed_planner(self, xf, gate_w, gate_idx):
         """Routed experts as graph nodes the solver places: slots -> scatter -> 3 grouped GEMMs -> gather."""
         cfg = self.cfg
         T, d = xf.shape
         E, nb = cfg.num_experts, cfg.dispatch_blocks
-        capacity = max(1, math.ceil(cfg.capacity_factor * (T // nb) * cfg.top_k / E))
+        capacity = self.capacity(T // nb)
         slot = K.moe_slots(gate_idx, E, capacity, nb)
         h = K.moe_dispatch(xf, slot, E, capacity, nb).view(E, nb * capacity, d)
         y = K.grouped_mm(K.swiglu(K.grouped_mm(h, self.w1), K.grouped_mm(h, self.w3)), self.w2)

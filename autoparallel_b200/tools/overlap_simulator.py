@@ -2,6 +2,13 @@
 
     python -m autoparallel_b200.tools.overlap_simulator --model llama3_8b --mesh 8 [--layers 4]
         [--prefetch-depth 12] [--max-in-flight-gb 2] [--bucket] [--table colls.json] [--trace out.json]
+        [--save-capture step.capture.json]
+    python -m autoparallel_b200.tools.overlap_simulator --replay step.capture.json [--table colls16_8.table] ...
+
+The second form needs no model and no process group: it reloads the per-rank graphs a previous run (or a training
+job, ``tools.graph_capture.save_capture``) wrote, prices the collectives through the capture's own group-name ->
+mesh-dim mapping with the alpha-beta model or a measured table (this framework's JSON tables or the reference's
+``colls*.table`` text tables), and reports the same numbers.
 
 Plans the model on fake ranks (no GPU, no process group traffic), lowers it, partitions it, applies
 the bucketing / overlap passes with the given knobs and reports, for forward and backward: number
@@ -32,7 +39,11 @@ def main(argv=None):
     ap.add_argument("--table", default=None)
     ap.add_argument("--trace", default=None)
     ap.add_argument("--device", default="B200")
+    ap.add_argument("--save-capture", default=None, help="write the partitioned per-rank graphs to this file for later --replay")
+    ap.add_argument("--replay", default=None, help="simulate a saved capture instead of planning a model")
     args = ap.parse_args(argv)
+    if args.replay:
+        return replay(args)
 
     import torch
     import torch.distributed as dist
@@ -72,6 +83,10 @@ def main(argv=None):
         apx.optimize_placement()
         lowered = apx.lower()
         parts = partition_joint(lowered.joint)
+        if args.save_capture:
+            from .graph_capture import save_capture
+
+            save_capture(args.save_capture, parts.fw, parts.bw, mesh, {"model": args.model, "layers": cfg.n_layers, "seq_len": args.seq_len})
         ocfg = OverlapConfig(args.prefetch_depth, int(args.max_in_flight_gb * 2**30), args.max_pending_reductions)
         report = {"plan": {"collectives": lowered.num_collectives, "fused": apx.fusion_stats, "buckets": apx.bucket_stats,
                            "ilp_solve_s": apx.sharding_optimizer.timings.get("solve")}}
@@ -85,6 +100,40 @@ def main(argv=None):
             }
             if args.trace:
                 create_execution_trace(sched, mesh, args.trace.replace(".json", f"_{name}.json"), args.device)
+    print(json.dumps(report, indent=1, default=float))
+    return report
+
+
+def replay(args) -> dict:
+    """Simulate a saved capture: no model, no process group."""
+    from ..parallel.cost import comm as comm_cost
+    from ..parallel.passes.overlap import OverlapConfig, exposed_collectives, schedule_for_streams
+    from ..utils.trace_sim import make_runtime_estimator, simulate
+    from .graph_capture import load_capture, load_colls_table
+
+    cap = load_capture(args.replay)
+    topo = comm_cost.Topology([comm_cost.NVLINK5] * len(cap["mesh_shape"]))
+    if args.table:
+        if args.table.endswith(".table"):
+            topo.tables.update(load_colls_table(args.table))
+        else:
+            topo.load_table(args.table)
+    est = make_runtime_estimator(None, args.device, group_dim=cap["group_dim"], topology=topo)
+    ocfg = OverlapConfig(args.prefetch_depth, int(args.max_in_flight_gb * 2**30), args.max_pending_reductions)
+    report = {"capture": {"mesh_shape": cap["mesh_shape"], "group_dim": cap["group_dim"], **cap.get("extra", {})},
+              "table": args.table or "alpha-beta NVLink 5 model"}
+    for name, gm in (("forward", cap["forward_gm"]), ("backward", cap["backward_gm"])):
+        if gm is None:
+            continue
+        before = simulate(gm, est)
+        sched = schedule_for_streams(copy.deepcopy(gm), None, ocfg)
+        events: list = []
+        after = simulate(sched, est, events)
+        report[name] = {"before": before.__dict__, "after": after.__dict__, "exposed_collectives_after": exposed_collectives(sched)}
+        if args.trace:
+            with open(args.trace.replace(".json", f"_{name}.json"), "w") as f:
+                json.dump({"traceEvents": events, "displayTimeUnit": "ms"}, f)
+    report["step_ms_after"] = sum(report[k]["after"]["total_us"] for k in ("forward", "backward") if k in report) / 1e3
     print(json.dumps(report, indent=1, default=float))
     return report
 

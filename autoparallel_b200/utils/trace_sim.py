@@ -42,14 +42,18 @@ def _nbytes(v) -> int:
     return 0
 
 
-def make_runtime_estimator(mesh, plan_device: Optional[str] = None) -> Callable[[fx.Node], float]:
+def make_runtime_estimator(mesh, plan_device: Optional[str] = None, group_dim: Optional[dict] = None,
+                           topology=None) -> Callable[[fx.Node], float]:
     """node -> microseconds.  Collectives are priced by the active topology through their group
-    name (resolved to a mesh dim), everything else by FLOPs / bytes on local shapes."""
+    name (resolved to a mesh dim), everything else by FLOPs / bytes on local shapes.
+    ``group_dim`` / ``topology``: replaying a saved graph needs no live mesh - the capture records which mesh dim
+    each group name stood for, and the topology (formula or measured table) is passed in."""
     from ..parallel.cost.device import DEVICE_LIMITS
 
-    limit = DEVICE_LIMITS[plan_device] if plan_device else get_device_limit(mesh.device_type)
-    topo = comm_cost.get_topology(mesh)
-    group_dim = {mesh.get_group(i).group_name: i for i in range(mesh.ndim)}
+    limit = DEVICE_LIMITS[plan_device] if plan_device else get_device_limit(mesh.device_type if mesh is not None else "cuda")
+    topo = topology if topology is not None else comm_cost.get_topology(mesh)
+    if group_dim is None:
+        group_dim = {mesh.get_group(i).group_name: i for i in range(mesh.ndim)}
     C = comm_ops.ops
 
     def flops_of(node):
@@ -174,7 +178,13 @@ def simulate(gm: fx.GraphModule, estimate: Callable[[fx.Node], float], events: O
     return GraphMetrics(total, compute_us, comm_us, exposed, peak, n_coll)
 
 
-def estimate_graph_metrics(gm: fx.GraphModule, mesh, plan_device: Optional[str] = None) -> GraphMetrics:
+def estimate_graph_metrics(gm: fx.GraphModule, mesh, plan_device: Optional[str] = None, estimator=None) -> GraphMetrics:
+    if estimator is not None:
+        return simulate(gm, estimator)
+    return _estimate_graph_metrics(gm, mesh, plan_device)
+
+
+def _estimate_graph_metrics(gm: fx.GraphModule, mesh, plan_device: Optional[str] = None) -> GraphMetrics:
     return simulate(gm, make_runtime_estimator(mesh, plan_device))
 
 

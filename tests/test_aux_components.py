@@ -212,3 +212,37 @@ def test_structured_trace_artifacts(mesh_1d, tmp_path, monkeypatch):
                          "autoparallel_parallel_graph"}
     assert seen["autoparallel_solution"][0] == "json" and json.loads(seen["autoparallel_solution"][1])
     assert "apb200.mm_nd" in seen["autoparallel_joint_graph"][1] and "apb200_comm" in seen["autoparallel_parallel_graph"][1]
+
+
+def test_overlap_simulator_replays_a_capture_with_a_measured_table(fake_world, tmp_path, capsys):
+    """A saved per-rank graph is simulated again without model or process group, priced by a measured table in the
+    reference's text format."""
+    from autoparallel_b200.tools import overlap_simulator
+    from autoparallel_b200.tools.graph_capture import load_capture, load_colls_table
+
+    cap = tmp_path / "step.capture.json"
+    overlap_simulator.main(["--model", "llama3_debug", "--mesh", "8", "--layers", "2", "--seq-len", "64", "--save-capture", str(cap)])
+    live = json.loads(capsys.readouterr().out)
+    doc = load_capture(str(cap))
+    assert doc["mesh_shape"] == [8] and len(doc["group_dim"]) == 1
+    n_coll = sum(1 for d in doc["forward"] if "apb200_comm" in d["target"])
+    assert n_coll == sum(live["plan"]["collectives"].values()) or n_coll > 0
+    table = tmp_path / "colls.table"
+    table.write_text(
+        "  Group    Group Size  Collective                    1MB (ms)    64MB (ms)    1024MB (ms)\n"
+        "-------  ------------  --------------------------  ----------  -----------  -------------\n"
+        "      0             8  all_gather_into_tensor          0.0495       1.3371        20.9105\n"
+        "      0             8  reduce_scatter_tensor           0.0173       0.1953         2.6420\n"
+        "      0             8  all_reduce                      0.0280       0.3822         5.2756\n")
+    t = load_colls_table(str(table))
+    assert t[("all_gather", 8)][0] == (8 * 2**20, 49.5) and t[("reduce_scatter", 8)][1] == (64 * 2**20, 195.3)
+    rep = overlap_simulator.main(["--replay", str(cap), "--table", str(table)])
+    capsys.readouterr()
+    assert rep["forward"]["after"]["num_collectives"] == live["forward"]["after"]["num_collectives"]
+    assert rep["step_ms_after"] > 0
+    # a slower table makes the replayed step slower: the table really prices the collectives
+    slow = tmp_path / "slow.table"
+    slow.write_text(table.read_text().replace("0.0495", "9.0495").replace("0.0173", "9.0173").replace("0.0280", "9.0280"))
+    rep2 = overlap_simulator.main(["--replay", str(cap), "--table", str(slow)])
+    capsys.readouterr()
+    assert rep2["forward"]["before"]["comm_us"] > rep["forward"]["before"]["comm_us"]

@@ -561,3 +561,56 @@ def test_dcp_moves_a_checkpoint_between_shard_nestings(tmp_path):
 def test_dcp_round_trip_of_sharded_params_and_optimizer_state(tmp_path):
     want, got = _run(_dcp_worker, 2, str(tmp_path / "ckpt"))
     assert abs(want - got) < 1e-5
+
+
+def _moe_dropless_worker(rank, ws, port, q):
+    """Skewed routing (Zipf router bias) with the dropless setting: every assignment is served on any rank count."""
+    _init(rank, ws, port)
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Shard
+
+    from autoparallel_b200 import AutoParallel, ForwardInputs
+    from autoparallel_b200.models.moe import MoETransformer, moe_debug
+
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("ep",))
+    B, S = 4, 32
+    out = {}
+    for label, cf in (("dropless", None), ("tight", 1.0)):
+        cfg = moe_debug(capacity_factor=cf, router_bias_zipf=1.2)
+        with torch.device("meta"):
+            m = MoETransformer(cfg)
+
+        def input_fn():
+            return ForwardInputs((torch.randint(0, cfg.vocab_size, (B, S)),), {"labels": torch.randint(0, cfg.vocab_size, (B, S))})
+
+        with AutoParallel(m, input_fn, mesh) as ap:
+            ap.add_parameter_memory_constraint()
+            ap.add_input_constraints([(Shard(0),)] * 2)
+            ap.optimize_placement()
+            pm = ap.apply_placement()
+        pm.to_empty(device="cpu")
+        pm.init_weights(seed=0)
+        torch.manual_seed(1)
+        tok = torch.randint(0, cfg.vocab_size, (B, S))
+        lab = torch.randint(0, cfg.vocab_size, (B, S))
+        loss = pm(tok.chunk(ws, 0)[rank], labels=lab.chunk(ws, 0)[rank])
+        loss.backward()
+        gn = sum(p.grad.full_tensor().float().pow(2).sum() for p in pm.parameters()).sqrt().item()
+        ref = MoETransformer(cfg)
+        ref.init_weights(seed=0)
+        x = torch.randn(B, S, cfg.dim)
+        dropped = ref.layers["0"].moe.dropped_assignments(x, blocks=2)
+        out[label] = (loss.item(), gn, dropped)
+    if rank == 0:
+        q.put(out)
+    dist.destroy_process_group()
+
+
+def test_moe_dropless_capacity_matches_one_rank_under_skewed_routing():
+    two, one = _run(_moe_dropless_worker, 2), _run(_moe_dropless_worker, 1)
+    # dropless: identical on one and two ranks although the router prefers a few experts, and nothing would be dropped
+    assert abs(two["dropless"][0] - one["dropless"][0]) < 1e-4
+    assert abs(two["dropless"][1] - one["dropless"][1]) / one["dropless"][1] < 1e-3
+    assert two["dropless"][2] == 0
+    # the same model with a tight capacity does drop assignments under that skew (and says how many)
+    assert two["tight"][2] > 0
