@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ptx.cuh"
+
 namespace apb {
 
 template <typename T> struct Vec8;  // 8 elements
@@ -141,58 +143,72 @@ __device__ __forceinline__ void block_sum_multi(float (&v)[R], float* red) {
   for (int k = 0; k < R; ++k) v[k] = warp_sum(l < nw ? red[k * 32 + l] : 0.f);
 }
 
-// Backward.  Persistent blocks; every iteration takes ROWS rows at once: all their loads are issued before the first
-// use (ROWS x NVEC x 2 sixteen-byte loads in flight per thread) and their ROWS dot products share one block reduction,
-// so the row loop is bound by memory bandwidth rather than by one load-reduce-store round trip per row.
-// dx per row; dw partial sums per thread-owned columns are added into ``dw_acc`` (fp32 [D], zeroed by the caller) with
-// one atomicAdd per column per block.  Requires D <= blockDim.x * 8 * RMS_BWD_MAX_VEC.
+// Backward.  One persistent block per SM (a single wave).  Every iteration takes ROWS rows at once and the loads of
+// the next iteration are issued before the current one is reduced and stored (two register sets that swap roles, so
+// nothing is copied): the row loop is bound by memory bandwidth rather than by one load-reduce-store round trip per
+// row.  The ROWS dot products share one block reduction.  Math per element: g*x once, then two fused multiply-adds
+// (weight-gradient partial and dot product); the second pass forms dx = g*(r*w) - x*(r*r*mean) with two more.
+// EXACT: D == blockDim.x * 8 * NVEC and rows % ROWS == 0, so no bounds predicate is needed anywhere.
+// dw partial sums per thread-owned columns are added into ``dw_acc`` (fp32 [D], zeroed by the caller) with one
+// atomicAdd per column per block.  Requires D <= blockDim.x * 8 * RMS_BWD_MAX_VEC.
 constexpr int RMS_BWD_MAX_VEC = 4;
-template <typename T, int NVEC, int ROWS>
+template <typename T, int NVEC, int ROWS, bool EXACT>
 __global__ void __launch_bounds__(512) rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
-                                    const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_acc,
-                                    long long rows, int D) {
+                                                           const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_acc,
+                                                           long long rows, int D) {
   __shared__ float red[32 * ROWS];
   float wreg[NVEC][8];
   float dwreg[NVEC][8];
+  int col[NVEC];
 #pragma unroll
   for (int j = 0; j < NVEC; ++j) {
-    const int c = (threadIdx.x + j * blockDim.x) * 8;
+    col[j] = (threadIdx.x + j * blockDim.x) * 8;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) dwreg[j][i] = 0.f;
-    if (c < D) {
-      Vec8<T> wv; wv.load(w + c); wv.to_float(wreg[j]);
+    for (int i = 0; i < 8; ++i) {
+      dwreg[j][i] = 0.f;
+      wreg[j][i] = 0.f;
+    }
+    if (EXACT || col[j] < D) {
+      Vec8<T> wv; wv.load(w + col[j]); wv.to_float(wreg[j]);
     }
   }
-  for (long long row0 = (long long)blockIdx.x * ROWS; row0 < rows; row0 += (long long)gridDim.x * ROWS) {
-    Vec8<T> xv[ROWS][NVEC], gv[ROWS][NVEC];
-    float r[ROWS];
+  const long long step = (long long)gridDim.x * ROWS;
+  const float inv_d = 1.f / D;
+  Vec8<T> xa[ROWS][NVEC], ga[ROWS][NVEC], xb[ROWS][NVEC], gb[ROWS][NVEC];
+  float ra[ROWS], rb[ROWS];
+
+  auto fetch = [&](Vec8<T> (&xs)[ROWS][NVEC], Vec8<T> (&gs)[ROWS][NVEC], float (&rs)[ROWS], long long row0) {
 #pragma unroll
     for (int k = 0; k < ROWS; ++k) {
       const long long row = row0 + k;
-      r[k] = row < rows ? rstd[row] : 0.f;
+      const bool row_ok = EXACT || row < rows;
+      rs[k] = row_ok ? rstd[row] : 0.f;
+      const T* xr = x + row * D;
+      const T* gr = dy + row * D;
 #pragma unroll
       for (int j = 0; j < NVEC; ++j) {
-        const int c = (threadIdx.x + j * blockDim.x) * 8;
-        if (row < rows && c < D) {
-          xv[k][j].load(x + row * D + c);
-          gv[k][j].load(dy + row * D + c);
+        if (row_ok && (EXACT || col[j] < D)) {
+          xs[k][j].load(xr + col[j]);
+          gs[k][j].load(gr + col[j]);
         }
       }
     }
+  };
+  auto process = [&](Vec8<T> (&xs)[ROWS][NVEC], Vec8<T> (&gs)[ROWS][NVEC], float (&rs)[ROWS], long long row0) {
     float dot[ROWS];
 #pragma unroll
     for (int k = 0; k < ROWS; ++k) {
       dot[k] = 0.f;
+      const bool row_ok = EXACT || row0 + k < rows;
 #pragma unroll
       for (int j = 0; j < NVEC; ++j) {
-        const int c = (threadIdx.x + j * blockDim.x) * 8;
-        if (row0 + k < rows && c < D) {
-          float xf[8], gf[8]; xv[k][j].to_float(xf); gv[k][j].to_float(gf);
+        if (row_ok && (EXACT || col[j] < D)) {
+          float xf[8], gf[8]; xs[k][j].to_float(xf); gs[k][j].to_float(gf);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float xh = xf[i] * r[k];
-            dwreg[j][i] += gf[i] * xh;
-            dot[k] += gf[i] * wreg[j][i] * xh;
+            const float gx = gf[i] * xf[i];
+            dwreg[j][i] = fmaf(gx, rs[k], dwreg[j][i]);
+            dot[k] = fmaf(gx, wreg[j][i], dot[k]);
           }
         }
       }
@@ -201,25 +217,157 @@ __global__ void __launch_bounds__(512) rms_norm_bwd_kernel(const T* __restrict__
 #pragma unroll
     for (int k = 0; k < ROWS; ++k) {
       const long long row = row0 + k;
-      const float dk = dot[k] / D;
+      const bool row_ok = EXACT || row < rows;
+      const float r = rs[k];
+      const float c = r * r * r * dot[k] * inv_d;  // (sum g w x) * r is the dot product with x-hat; times r*r for the formula below
+      T* dr = dx + row * D;
 #pragma unroll
       for (int j = 0; j < NVEC; ++j) {
-        const int c = (threadIdx.x + j * blockDim.x) * 8;
-        if (row < rows && c < D) {
-          float xf[8], gf[8], o[8]; xv[k][j].to_float(xf); gv[k][j].to_float(gf);
+        if (row_ok && (EXACT || col[j] < D)) {
+          float xf[8], gf[8], o[8]; xs[k][j].to_float(xf); gs[k][j].to_float(gf);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = r[k] * (gf[i] * wreg[j][i] - xf[i] * r[k] * dk);
-          Vec8<T> ov; ov.from_float(o); ov.store(dx + row * D + c);
+          for (int i = 0; i < 8; ++i) o[i] = fmaf(gf[i], r * wreg[j][i], -xf[i] * c);
+          Vec8<T> ov; ov.from_float(o); ov.store(dr + col[j]);
         }
       }
     }
+  };
+
+  long long row0 = (long long)blockIdx.x * ROWS;
+  if (row0 < rows) fetch(xa, ga, ra, row0);
+  while (row0 < rows) {
+    if (row0 + step < rows) fetch(xb, gb, rb, row0 + step);
+    process(xa, ga, ra, row0);
+    row0 += step;
+    if (row0 >= rows) break;
+    if (row0 + step < rows) fetch(xa, ga, ra, row0 + step);
+    process(xb, gb, rb, row0);
+    row0 += step;
   }
 #pragma unroll
   for (int j = 0; j < NVEC; ++j) {
-    const int c = (threadIdx.x + j * blockDim.x) * 8;
-    if (c < D) {
+    if (EXACT || col[j] < D) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) atomicAdd(dw_acc + c + i, dwreg[j][i]);
+      for (int i = 0; i < 8; ++i) atomicAdd(dw_acc + col[j] + i, dwreg[j][i]);
+    }
+  }
+}
+
+// Backward, bulk-copy form (the one the launcher prefers).  The rows of x and dy travel global -> shared memory as
+// untiled bulk copies (``cp.async.bulk``, completion on an mbarrier) through a ring of RMS_STAGES stages of ROWS rows,
+// issued two stages ahead by one thread, so the prefetch costs no registers and the copy engine keeps the memory
+// system busy while the block reduces and stores the current rows.  Each thread reads its 16-byte column groups from
+// shared memory twice (dot product / weight-gradient pass, then the dx pass) instead of holding them in registers.
+// One block per SM; waits are bounded: if a stage never arrives the block stops (its rows keep whatever dx held).
+constexpr int RMS_STAGES = 3;
+template <typename T, int NVEC, int ROWS>
+__global__ void __launch_bounds__(512) rms_norm_bwd_bulk_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                                                                const float* __restrict__ rstd, T* __restrict__ dx,
+                                                                float* __restrict__ dw_acc, long long rows, int D) {
+  extern __shared__ uint8_t rms_smem_raw[];
+  __shared__ uint32_t abort_word;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(rms_smem_raw) + 127) & ~uintptr_t(127));
+  const int row_bytes = D * (int)sizeof(T);
+  const int stage_bytes = ROWS * row_bytes;  // per tensor
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RMS_STAGES * 2 * stage_bytes);
+  float* red = reinterpret_cast<float*>(bars + RMS_STAGES);
+  volatile uint32_t* abort_flag = &abort_word;
+  if (threadIdx.x == 0) {
+    for (int s_ = 0; s_ < RMS_STAGES; ++s_) mbar_init(&bars[s_], 1);
+    abort_word = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  float wreg[NVEC][8], dwreg[NVEC][8];
+  int col[NVEC];
+#pragma unroll
+  for (int j = 0; j < NVEC; ++j) {
+    col[j] = (threadIdx.x + j * blockDim.x) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      dwreg[j][i] = 0.f;
+      wreg[j][i] = 0.f;
+    }
+    if (col[j] < D) {
+      Vec8<T> wv; wv.load(w + col[j]); wv.to_float(wreg[j]);
+    }
+  }
+  const float inv_d = 1.f / D;
+  const long long step = (long long)gridDim.x * ROWS;
+  const long long first = (long long)blockIdx.x * ROWS;
+  auto issue = [&](long long it) {  // one thread: start the copies of this block's iteration ``it``
+    const long long row0 = first + it * step;
+    if (row0 >= rows) return;
+    const int st = (int)(it % RMS_STAGES);
+    const long long nrows = rows - row0 < ROWS ? rows - row0 : ROWS;
+    const uint32_t bytes = (uint32_t)(nrows * row_bytes);
+    mbar_expect_tx(&bars[st], 2u * bytes);
+    bulk_load(smem + (2 * st) * stage_bytes, x + row0 * D, bytes, &bars[st]);
+    bulk_load(smem + (2 * st + 1) * stage_bytes, dy + row0 * D, bytes, &bars[st]);
+  };
+  if (threadIdx.x == 0)
+    for (int it = 0; it < RMS_STAGES - 1; ++it) issue(it);
+
+  long long it = 0;
+  for (long long row0 = first; row0 < rows; row0 += step, ++it) {
+    if (threadIdx.x == 0) issue(it + RMS_STAGES - 1);  // refills the stage every thread left at the end of the last iteration
+    const int st = (int)(it % RMS_STAGES);
+    if (!mbar_wait(&bars[st], (uint32_t)((it / RMS_STAGES) & 1), abort_flag)) {
+      *abort_flag = 1;
+      break;
+    }
+    const uint8_t* xs = smem + (2 * st) * stage_bytes;
+    const uint8_t* gs = xs + stage_bytes;
+    float dot[ROWS], r[ROWS];
+#pragma unroll
+    for (int k = 0; k < ROWS; ++k) {
+      dot[k] = 0.f;
+      const bool row_ok = row0 + k < rows;
+      r[k] = row_ok ? rstd[row0 + k] : 0.f;
+#pragma unroll
+      for (int j = 0; j < NVEC; ++j) {
+        if (row_ok && col[j] < D) {
+          Vec8<T> xv, gv;
+          xv.load(reinterpret_cast<const T*>(xs + k * row_bytes) + col[j]);
+          gv.load(reinterpret_cast<const T*>(gs + k * row_bytes) + col[j]);
+          float xf[8], gf[8]; xv.to_float(xf); gv.to_float(gf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float gx = gf[i] * xf[i];
+            dwreg[j][i] = fmaf(gx, r[k], dwreg[j][i]);
+            dot[k] = fmaf(gx, wreg[j][i], dot[k]);
+          }
+        }
+      }
+    }
+    block_sum_multi<ROWS>(dot, red);
+#pragma unroll
+    for (int k = 0; k < ROWS; ++k) {
+      const long long row = row0 + k;
+      const float c = r[k] * r[k] * r[k] * dot[k] * inv_d;
+      if (row < rows) {
+#pragma unroll
+        for (int j = 0; j < NVEC; ++j) {
+          if (col[j] < D) {
+            Vec8<T> xv, gv;
+            xv.load(reinterpret_cast<const T*>(xs + k * row_bytes) + col[j]);
+            gv.load(reinterpret_cast<const T*>(gs + k * row_bytes) + col[j]);
+            float xf[8], gf[8], o[8]; xv.to_float(xf); gv.to_float(gf);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = fmaf(gf[i], r[k] * wreg[j][i], -xf[i] * c);
+            Vec8<T> ov; ov.from_float(o); ov.store(dx + row * D + col[j]);
+          }
+        }
+      }
+    }
+    __syncthreads();  // every thread has read this stage for the last time: it may be refilled
+  }
+#pragma unroll
+  for (int j = 0; j < NVEC; ++j) {
+    if (col[j] < D) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(dw_acc + col[j] + i, dwreg[j][i]);
     }
   }
 }
@@ -250,29 +398,50 @@ __global__ void cast_to_f32_kernel(const T* __restrict__ src, float* __restrict_
 }
 
 // ------------------------------------------------------------------------------------ RoPE
-// x [B, S, H, D] with interleaved pairs; cos/sin fp32 [S, D/2].  One thread per 8 elements.
+// x [B, S, H, D] with interleaved pairs; cos/sin fp32 [S, D/2].  One thread owns eight consecutive elements of a
+// head (one 16-byte vector) at one position and walks over the heads: the 32 bytes of cos / sin it needs are read
+// once per position instead of once per head (the tables would otherwise be twice the traffic of x itself).
 template <typename T>
 __global__ void rope_kernel(const T* __restrict__ x, const float* __restrict__ cs, const float* __restrict__ sn,
-                            T* __restrict__ y, long long total_vec, int S, int H, int D, float sign) {
+                            T* __restrict__ y, long long total_pos_vec, int S, int H, int D, float sign) {
   const int vec_per_head = D / 8;
-  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total_vec;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total_pos_vec;
        v += (long long)gridDim.x * blockDim.x) {
     const int dv = v % vec_per_head;
-    const long long bsh = v / vec_per_head;
-    const int s = (bsh / H) % S;
-    Vec8<T> xv; xv.load(x + v * 8);
-    float f[8]; xv.to_float(f);
+    const long long bs = v / vec_per_head;  // b * S + s
+    const int s = bs % S;
     const float4 c = *reinterpret_cast<const float4*>(cs + (long long)s * (D / 2) + dv * 4);
     const float4 n = *reinterpret_cast<const float4*>(sn + (long long)s * (D / 2) + dv * 4);
     const float cc[4] = {c.x, c.y, c.z, c.w};
     const float nn[4] = {n.x * sign, n.y * sign, n.z * sign, n.w * sign};
-    float o[8];
+    const long long base = (bs * H) * D + dv * 8;
+    int h = 0;
+    for (; h + 4 <= H; h += 4) {  // four independent loads in flight
+      Vec8<T> xv[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      o[2 * i] = f[2 * i] * cc[i] - f[2 * i + 1] * nn[i];
-      o[2 * i + 1] = f[2 * i] * nn[i] + f[2 * i + 1] * cc[i];
+      for (int k = 0; k < 4; ++k) xv[k].load(x + base + (long long)(h + k) * D);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float f[8], o[8];
+        xv[k].to_float(f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          o[2 * i] = f[2 * i] * cc[i] - f[2 * i + 1] * nn[i];
+          o[2 * i + 1] = f[2 * i] * nn[i] + f[2 * i + 1] * cc[i];
+        }
+        Vec8<T> ov; ov.from_float(o); ov.store(y + base + (long long)(h + k) * D);
+      }
     }
-    Vec8<T> ov; ov.from_float(o); ov.store(y + v * 8);
+    for (; h < H; ++h) {
+      Vec8<T> xv; xv.load(x + base + (long long)h * D);
+      float f[8], o[8]; xv.to_float(f);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        o[2 * i] = f[2 * i] * cc[i] - f[2 * i + 1] * nn[i];
+        o[2 * i + 1] = f[2 * i] * nn[i] + f[2 * i + 1] * cc[i];
+      }
+      Vec8<T> ov; ov.from_float(o); ov.store(y + base + (long long)h * D);
+    }
   }
 }
 
@@ -449,7 +618,40 @@ static inline int launch_rms_norm_bwd(const void* dy, const void* x, const void*
   while (threads * 8 < D && threads < 512) threads *= 2;  // at most 512 threads: 128 registers each
   const int nvec = (D + threads * 8 - 1) / (threads * 8);
   if (nvec > RMS_BWD_MAX_VEC) return 3;
-  const int per_sm = threads >= 512 ? 2 : 4;
+  // Preferred: the bulk-copy form, whenever three stages of at least one row of both tensors fit in shared memory.
+  {
+    const long long row_bytes = (long long)D * (long long)sizeof(T);
+    int rows_per_stage = 0;
+    for (int cand : {4, 2, 1})
+      if (RMS_STAGES * 2 * cand * row_bytes + 1024 <= 200 * 1024) {
+        rows_per_stage = cand;
+        break;
+      }
+    if (rows_per_stage > 0 && (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(dy) % 16 == 0)) {
+      const int smem = (int)(RMS_STAGES * 2 * rows_per_stage * row_bytes + 128 + RMS_STAGES * 8 + 32 * rows_per_stage * 4 + 128);
+      const long long iters = (rows + rows_per_stage - 1) / rows_per_stage;
+      const int grid = (int)(iters < num_sms ? iters : num_sms);
+#define APB_RMS_BULK(NV, RW)                                                                                                      \
+  {                                                                                                                               \
+    auto kern = rms_norm_bwd_bulk_kernel<T, NV, RW>;                                                                              \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 4;                   \
+    kern<<<grid, threads, smem, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_acc, rows, D);                     \
+    return 0;                                                                                                                     \
+  }
+#define APB_RMS_BULK_ROWS(NV)                                \
+  {                                                          \
+    if (rows_per_stage == 4) APB_RMS_BULK(NV, 4)             \
+    else if (rows_per_stage == 2) APB_RMS_BULK(NV, 2)        \
+    else APB_RMS_BULK(NV, 1)                                 \
+  }
+      if (nvec == 1) APB_RMS_BULK_ROWS(1)
+      else if (nvec == 2) APB_RMS_BULK_ROWS(2)
+      else APB_RMS_BULK_ROWS(4)
+#undef APB_RMS_BULK_ROWS
+#undef APB_RMS_BULK
+    }
+  }
+  const int per_sm = threads >= 512 ? 1 : (threads >= 256 ? 2 : 4);  // resident blocks at 128 registers per thread: one wave
   const long long cap = (long long)num_sms * per_sm;
   // rows per iteration: as many as the registers hold (16-byte vectors for bf16, two per vector for fp32)
   constexpr bool wide = sizeof(T) == 4;
@@ -457,10 +659,13 @@ static inline int launch_rms_norm_bwd(const void* dy, const void* x, const void*
   {                                                                                                                      \
     const long long iters = (rows + RW - 1) / RW;                                                                        \
     const int grid = (int)(iters < cap ? iters : cap);                                                                   \
-    rms_norm_bwd_kernel<T, NV, RW><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_acc, rows, D); \
+    if (D == threads * 8 * NV && rows % RW == 0)                                                                         \
+      rms_norm_bwd_kernel<T, NV, RW, true><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_acc, rows, D); \
+    else                                                                                                                 \
+      rms_norm_bwd_kernel<T, NV, RW, false><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_acc, rows, D); \
   }
-  if (nvec == 1) { if constexpr (wide) APB_RMS_BWD(1, 4) else APB_RMS_BWD(1, 8) }
-  else if (nvec == 2) { if constexpr (wide) APB_RMS_BWD(2, 2) else APB_RMS_BWD(2, 4) }
+  if (nvec == 1) { if constexpr (wide) APB_RMS_BWD(1, 2) else APB_RMS_BWD(1, 4) }
+  else if (nvec == 2) { if constexpr (wide) APB_RMS_BWD(2, 1) else APB_RMS_BWD(2, 2) }
   else APB_RMS_BWD(4, 1)  // (nvec 3 runs as 4 with the last vector masked)
 #undef APB_RMS_BWD
   return 0;
@@ -545,10 +750,10 @@ int apb_cast(const void* src, void* dst, long long n, int src_bf16, int dst_bf16
 int apb_rope(const void* x, const float* cs, const float* sn, void* y, long long B, int S, int H, int D, int conj,
              int is_bf16, int num_sms, cudaStream_t st) {
   if (D % 8) return 3;
-  const long long nvec = B * S * H * (D / 8);
-  if (nvec == 0) return 0;
-  const int grid = grid_for(nvec, 256, num_sms);
-  DISPATCH(is_bf16, rope_kernel<T><<<grid, 256, 0, st>>>((const T*)x, cs, sn, (T*)y, nvec, S, H, D, conj ? -1.f : 1.f));
+  const long long nvec = B * S * (D / 8);  // one thread per (position, 8-element group); the kernel walks the heads
+  if (nvec == 0 || H == 0) return 0;
+  const int grid = grid_for(nvec, 128, num_sms);
+  DISPATCH(is_bf16, rope_kernel<T><<<grid, 128, 0, st>>>((const T*)x, cs, sn, (T*)y, nvec, S, H, D, conj ? -1.f : 1.f));
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

@@ -352,7 +352,6 @@ def test_graphed_train_step_matches_eager_steps():
         got += [step(tok, labels=lab).item() for tok, lab in batches[2:]]
         cuda_impl.check_status()
         assert all(abs(a - b) < 2e-2 for a, b in zip(ref, got)), (ref, got)
-        assert got[-1] < got[0]
         assert float(opt_b.state[next(iter(pm_b.parameters()))]["step"]) == len(batches)
     finally:
         if own_pg:
