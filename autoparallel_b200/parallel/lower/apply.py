@@ -378,8 +378,18 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
                 new_args = tuple(_INT_ARG_LOCALIZERS[node.target](list(new_args), val, lval))
             from ..strategies.local_map_rules import is_local_map_node, local_map_body
 
+            rng_key = _sharded_rng_key(node, out_spec, mesh)
             if is_local_map_node(node):
                 nn_ = _inline_region(new_g, local_map_body(node), new_args)
+            elif rng_key is not None:
+                # a random operator whose output is sharded: every rank draws from the stream of ITS shard
+                # (runtime/rng.py); ranks that hold the same shard share the stream
+                from ...runtime import rng
+
+                if node.target is aten.native_dropout.default:
+                    nn_ = new_g.call_function(rng.sharded_dropout, (new_args[0], new_args[1], new_args[2] if len(new_args) > 2 else True, rng_key))
+                else:
+                    nn_ = new_g.call_function(rng.sharded_rand, (new_args[0], rng_key, node.target is aten.randn.default), dict(new_kwargs))
             else:
                 target = node.target
                 if target in (aten.view.default, aten._unsafe_view.default):
@@ -422,6 +432,29 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
         output_placements=[pl(n) for n in joint.fwd_outputs],
         num_collectives=dict(redis.counts),
     )
+
+
+_RANDOM_OPS = (aten.native_dropout.default, aten.rand.default, aten.randn.default)
+
+
+def _sharded_rng_key(node: fx.Node, out_spec, mesh):
+    """((mesh dim, this rank's coordinate), ...) over the mesh dims that shard the output of a random operator, or
+    None when the operator is not random or its output is replicated (then every rank must draw the same numbers)."""
+    if node.target not in _RANDOM_OPS:
+        return None
+    spec = out_spec if isinstance(out_spec, DTensorSpec) else next((s for s in out_spec if s is not None), None)
+    if spec is None:
+        return None
+    from torch.distributed.tensor.placement_types import Shard as _Shard
+
+    dims = [i for i, p in enumerate(spec.placements) if isinstance(p, _Shard)]
+    if not dims:
+        return None
+    try:
+        coords = [mesh.get_local_rank(i) for i in dims]
+    except Exception:
+        coords = [0 for _ in dims]
+    return tuple(zip(dims, coords))
 
 
 def sink_input_chains(gm: fx.GraphModule) -> int:

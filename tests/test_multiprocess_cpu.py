@@ -614,3 +614,54 @@ def test_moe_dropless_capacity_matches_one_rank_under_skewed_routing():
     assert two["dropless"][2] == 0
     # the same model with a tight capacity does drop assignments under that skew (and says how many)
     assert two["tight"][2] > 0
+
+
+def _dropout_worker(rank, ws, port, q):
+    """Dropout on a batch-sharded activation and a replicated random tensor: shards draw different masks, replicas agree."""
+    _init(rank, ws, port)
+    import torch.nn as nn
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Replicate, Shard
+
+    from autoparallel_b200 import AutoParallel
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = nn.Linear(32, 32, bias=False)
+
+        def forward(self, x):
+            noise = torch.rand(32)                                   # no tensor input: may be replicated
+            return torch.nn.functional.dropout(self.lin(x), p=0.5, training=True), noise
+
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("dp",))
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.ones(8, 32), mesh) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.add_output_constraints([(Shard(0),), (Replicate(),)])
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+        targets = [str(n.target) for n in ap.lowered.gm.graph.nodes if n.op == "call_function"]
+    pm.to_empty(device="cpu")
+    with torch.no_grad():
+        pm.lin.weight.copy_(torch.distributed.tensor.distribute_tensor(torch.eye(32), mesh, pm.lin.weight.placements))
+    torch.manual_seed(123)                                           # the same seed on every rank, as training scripts do
+    out, noise = pm(torch.ones(4, 32))
+    mask = (out != 0).to(torch.int64)
+    masks = [torch.empty_like(mask) for _ in range(ws)]
+    noises = [torch.empty_like(noise) for _ in range(ws)]
+    dist.all_gather(masks, mask)
+    dist.all_gather(noises, noise.contiguous())
+    if rank == 0:
+        q.put((bool(torch.equal(masks[0], masks[1])), bool(torch.equal(noises[0], noises[1])), any("sharded_dropout" in t for t in targets),
+               float(mask.float().mean())))
+    dist.destroy_process_group()
+
+
+def test_sharded_random_ops_draw_per_shard_and_replicated_ones_agree():
+    same_mask, same_noise, routed, keep = _run(_dropout_worker, 2)
+    assert routed            # the dropout of the sharded activation went through the per-shard stream
+    assert not same_mask     # the two shards did not repeat one mask
+    assert same_noise        # the replicated draw is identical on both ranks
+    assert 0.3 < keep < 0.7
