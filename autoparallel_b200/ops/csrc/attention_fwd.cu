@@ -386,12 +386,10 @@ extern "C" int apb_attention_fwd(const void* q, const void* k, const void* v, vo
   p.causal = causal ? 1 : 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM_BYTES) != cudaSuccess)
-      return 20;
-    configured = true;
-  }
+  // (the attribute belongs to the current device's instance of the kernel: set on every launch, so a second device of
+  // the same process is configured too)
+  if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM_BYTES) != cudaSuccess)
+    return 20;
   const long long ctas = (long long)(S / (NQ * TQ)) * H * B;
   if (ctas >= (1ll << 31)) return 3;
   attn_fwd_kernel<<<(unsigned)ctas, ATTN_THREADS, ATTN_SMEM_BYTES, stream>>>(tmQ, tmK, tmV, p);

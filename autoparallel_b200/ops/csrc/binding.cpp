@@ -42,10 +42,9 @@ int apb_embedding_fwd(const void* weight, const long long* ids, void* out, long 
                       int is_bf16, cudaStream_t st);
 int apb_symm_header_bytes();
 int apb_symm_wait_probe(const uint32_t* flag, unsigned target, unsigned limit_ms, uint32_t* status, cudaStream_t st);
-void apb_symm_use_multicast_once(unsigned long long workspace_multicast_ptr);
 int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank, int n, unsigned epoch, const void* src,
                         void* dst, long long outer, long long inner_bytes, int elem_kind, float scale, long long stage_capacity,
-                        uint32_t* status, int num_ctas, unsigned target0, unsigned target1, cudaStream_t st);
+                        uint32_t* status, int num_ctas, unsigned target0, unsigned target1, unsigned long long multicast_base, cudaStream_t st);
 int apb_gemm_fused(int fuse, const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                    long long ldc, int a_mn_major, int b_mn_major, int out_fp32, const unsigned long long* peer_ptrs, int rank,
                    int n, unsigned epoch, int rows_per_shard, const void* shard_src, void* gbuf, long long shard_bytes,
@@ -241,13 +240,14 @@ void symm_wait_probe(const at::Tensor& flag, int64_t target, int64_t limit_ms, a
 // One collective on a symmetric workspace (see symm_comm.cu).  src/dst are ordinary device tensors.
 void symm_collective(int64_t mode, const std::vector<int64_t>& peer_ptrs, int64_t rank, int64_t epoch, const at::Tensor& src,
                      at::Tensor& dst, int64_t outer, int64_t inner_bytes, int64_t elem_kind, double scale,
-                     int64_t stage_capacity, at::Tensor& status, int64_t num_ctas, int64_t target0, int64_t target1) {
+                     int64_t stage_capacity, at::Tensor& status, int64_t num_ctas, int64_t target0, int64_t target1,
+                     int64_t multicast_base) {
   c10::cuda::CUDAGuard g(src.device());
   std::vector<unsigned long long> ptrs(peer_ptrs.begin(), peer_ptrs.end());
   check(apb_symm_collective((int)mode, ptrs.data(), (int)rank, (int)ptrs.size(), (unsigned)epoch, src.data_ptr(), dst.data_ptr(),
                             outer, inner_bytes, (int)elem_kind, (float)scale, stage_capacity,
                             reinterpret_cast<uint32_t*>(status.data_ptr()), (int)num_ctas, (unsigned)target0, (unsigned)target1,
-                            stream()),
+                            (unsigned long long)multicast_base, stream()),
         "apb_symm_collective");
 }
 
@@ -357,7 +357,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_header_bytes", &symm_header_bytes);
   m.def("symm_wait_probe", &symm_wait_probe);
   m.def("symm_collective", &symm_collective);
-  m.def("symm_use_multicast_once", [](int64_t ptr) { apb_symm_use_multicast_once((unsigned long long)ptr); });
   m.def("gemm_fused", &gemm_fused);
   m.def("gemm_fused_ctas", [](int64_t fuse, int64_t M, int64_t N, int64_t comm_ctas) {
     return (int64_t)apb_gemm_fused_ctas((int)fuse, (int)M, (int)N, (int)comm_ctas, num_sms());

@@ -225,15 +225,13 @@ int apb_symm_wait_probe(const uint32_t* flag, unsigned target, unsigned limit_ms
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
-// Multicast address of the workspace that the NEXT reduce-scatter call should sum through (0 = plain peer loads).
-static unsigned long long g_multicast_base = 0ull;
-void apb_symm_use_multicast_once(unsigned long long workspace_multicast_ptr) { g_multicast_base = workspace_multicast_ptr; }
-
 // peer_ptrs: host array of n workspace base pointers (this process's mappings of every rank's buffer).
-// mode: 0 all-gather, 1 reduce-scatter (sum), 2 all-to-all.  Returns 0 or an error code.
+// mode: 0 all-gather, 1 reduce-scatter (sum), 2 all-to-all.  ``multicast_base``: multicast address of the workspace for
+// the reduce-scatter to sum through (NVLS), or 0 for plain peer loads.  Returns 0 or an error code.
 int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank, int n, unsigned epoch, const void* src,
                         void* dst, long long outer, long long inner_bytes, int elem_kind, float scale, long long stage_capacity,
-                        uint32_t* status, int num_ctas, unsigned target0, unsigned target1, cudaStream_t st) {
+                        uint32_t* status, int num_ctas, unsigned target0, unsigned target1, unsigned long long multicast_base,
+                        cudaStream_t st) {
   if (n > MAX_RANKS || n < 1) return 3;
   if ((inner_bytes & 15) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return 3;
   const long long in_bytes = (mode == ALL_GATHER) ? outer * inner_bytes : outer * inner_bytes * n;
@@ -243,9 +241,8 @@ int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank,
   p.rank = rank; p.n = n; p.epoch = epoch;
   p.src = static_cast<const uint8_t*>(src); p.dst = static_cast<uint8_t*>(dst);
   p.outer = outer; p.inner_bytes = inner_bytes; p.elem_kind = elem_kind; p.scale = scale; p.status = status; p.target0 = target0; p.target1 = target1;
-  p.mc_stage = (mode == REDUCE_SCATTER && g_multicast_base != 0ull)
-                   ? reinterpret_cast<const uint8_t*>(g_multicast_base) + HEADER_BYTES : nullptr;
-  g_multicast_base = 0ull;  // one call only: the caller names the workspace's multicast address per collective
+  p.mc_stage = (mode == REDUCE_SCATTER && multicast_base != 0ull)
+                   ? reinterpret_cast<const uint8_t*>(multicast_base) + HEADER_BYTES : nullptr;
   if (mode == ALL_GATHER) symm_collective_kernel<ALL_GATHER><<<num_ctas, 512, 0, st>>>(p);
   else if (mode == REDUCE_SCATTER) symm_collective_kernel<REDUCE_SCATTER><<<num_ctas, 512, 0, st>>>(p);
   else if (mode == ALL_TO_ALL) symm_collective_kernel<ALL_TO_ALL><<<num_ctas, 512, 0, st>>>(p);

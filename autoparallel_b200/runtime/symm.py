@@ -70,11 +70,9 @@ class SymmGroup:
         self.epoch += 1
         self.arrivals[0] += self.num_ctas
         self.arrivals[1] += self.num_ctas
-        if mode == MODE_RS and self.multicast_ptr:
-            self._C.symm_use_multicast_once(self.multicast_ptr)
         self._C.symm_collective(mode, self.peer_ptrs, self.rank, self.epoch, src, dst, outer, inner_bytes, elem_kind, scale,
                                 self.capacity, self.status, self.num_ctas, self.arrivals[0] & 0xFFFFFFFF,
-                                self.arrivals[1] & 0xFFFFFFFF)
+                                self.arrivals[1] & 0xFFFFFFFF, self.multicast_ptr if mode == MODE_RS else 0)
         cuda_impl._count()
 
     def _split(self, shape, dim, itemsize):
