@@ -64,6 +64,15 @@ class GraphedTrainStep:
         self.kernels_per_replay = cuda_impl.launch_count - before
         self.replays = 0
 
+    def release(self) -> None:
+        """Drop the captured graph and its memory pool.  Call before ``destroy_process_group`` when the step contains
+        collectives: a communicator must not be torn down while a graph still holds its kernels."""
+        torch.cuda.synchronize()
+        if self.graph is not None:
+            self.graph.reset()
+        self.graph = None
+        self._static_loss = None
+
     def _eager_step(self) -> torch.Tensor:
         out = self.module(*self._static_args, **self._static_kwargs)
         loss = self.loss_of(out) if self.loss_of is not None else out

@@ -246,4 +246,4 @@ def _run(args, shimmed) -> None:
         }), flush=True)
     if getattr(args, "kernel_table", None):
         bench.write_kernel_table(args.kernel_table, step_device, rank)
-    dist.destroy_process_group()
+    bench._teardown(None)

@@ -58,7 +58,7 @@ def parse():
                          "activation-checkpointing pass, then the eager module")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="capture forward + backward + optimizer in one CUDA graph and replay it (runtime/graph_step.py); auto: on "
-                         "where every collective of the step can be replayed (one GPU, NCCL, copy-engine gathers)")
+                         "one GPU; on: also with NCCL collectives or copy-engine gathers inside the graph")
     ap.add_argument("--kernel-table", default=None, metavar="PATH",
                     help="after the timed regions, run ONE more step under torch.profiler and write the device time per "
                          "kernel name (JSON) to PATH; never part of a reported number")
@@ -184,6 +184,30 @@ def _dma_stats():
         return {}
 
 
+def _teardown(graphed=None, limit_s: float = 20.0) -> None:
+    """Leave the job: release the captured step first (a CUDA graph that holds collective kernels must be gone before
+    its communicator is destroyed), then the process group.  The result line has been printed by now; if the
+    teardown itself does not finish within ``limit_s`` the process exits anyway instead of holding the GPUs."""
+    import threading
+
+    import torch
+    import torch.distributed as dist
+
+    sys.stdout.flush()
+    sys.stderr.flush()
+    timer = threading.Timer(limit_s, lambda: os._exit(0))
+    timer.daemon = True
+    timer.start()
+    try:
+        if graphed is not None:
+            graphed.release()
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.destroy_process_group()
+    finally:
+        timer.cancel()
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -281,11 +305,11 @@ def run_ours(args):
     fuse_arg = None
     comm_mode = args.comm
     if comm_mode == "auto":
-        # Measured on this model (ms/step, nccl vs hybrid on the same box): N=2 468 / 472, N=4 491 / 504,
-        # N=8 496 / 490.  NCCL under the overlap scheduler is the default at every N: in hybrid mode a
-        # fused kernel spins on its peers while NCCL kernels of the same step compete for SMs, which is only
-        # safe with SMs set aside for NCCL (--reserve-sms), and that configuration has not been timed.
-        comm_mode = os.environ.get("APB200_COMM", "nccl")
+        # Measured on this model, one box per row (ms/step, NCCL under the overlap scheduler vs copy-engine collectives):
+        # N=2 453.1 / 453.7, N=8 477.7 / 460.3.  The copy-engine mode is the default above one GPU: parameter gathers
+        # and gradient reduce-scatters move with the copy engines and take no SM from the persistent GEMMs; tensors it
+        # does not cover (and a machine without peer access) fall back to NCCL.
+        comm_mode = os.environ.get("APB200_COMM", "dma" if world > 1 else "nccl")
     shadow_arena = None
     if world > 1 and comm_mode.startswith("dma"):
         from autoparallel_b200.runtime import dma
@@ -384,7 +408,9 @@ def run_ours(args):
     cuda_impl.check_status()
 
     graphed = None
-    replayable = world == 1 or comm_mode in ("nccl", "dma_ag")
+    # auto: one GPU only.  With collectives inside the graph the device-side gain is under one per cent (the step is
+    # energy-bound) and a communicator must not be destroyed while a graph holds its kernels: --graph on asks for it.
+    replayable = world == 1
     if args.graph == "on" or (args.graph == "auto" and replayable):
         from autoparallel_b200.runtime.graph_step import GraphedTrainStep
 
@@ -499,7 +525,7 @@ def run_ours(args):
         print(json.dumps(out), flush=True)
     if args.kernel_table:
         write_kernel_table(args.kernel_table, step_device, rank)
-    dist.destroy_process_group()
+    _teardown(graphed)
 
 
 def run_reference(args):
