@@ -64,6 +64,7 @@ def main():
                     help="run a single small case (what a profiler capture is taken on)")
     ap.add_argument("--pair", default=None, choices=["on", "off"], help="force the CTA-pair (cta_group::2) GEMM kernel on or off")
     ap.add_argument("--gemm-only", action="store_true", help="stop after the GEMM rows")
+    ap.add_argument("--skip-gemm", action="store_true", help="bandwidth-bound kernels only (a short run for profiler captures)")
     args = ap.parse_args()
     from autoparallel_b200.ops import cuda_impl, library as L
 
@@ -111,7 +112,7 @@ def main():
     shapes = [(M, 4096, 4096), (M, 14336, 4096), (M, 4096, 14336), (M, 1024, 4096)]
     if not args.quick:
         shapes.append((M, 128256, 4096))
-    for (m, n, k) in shapes:
+    for (m, n, k) in ([] if args.skip_gemm else shapes):
         for tag, ta, tb in (("nt", False, True), ("nn", False, False), ("tn", True, False)):
             if tag == "tn":
                 mk = lambda: (torch.randn(k, m, device=dev, dtype=bf), torch.randn(k, n, device=dev, dtype=bf))
@@ -151,9 +152,39 @@ def main():
         mk = lambda: (torch.randn(M, V, device=dev, dtype=bf), torch.randint(0, V, (M,), device=dev))
         ms, best = time_fn(mk, lambda lg, lb: L.ops.cross_entropy(lg, lb), pool=2)
         rec("cross_entropy fwd 8192x128256", ms, best, nbytes=M * V * 2)
+    # cross-entropy backward, casts, embedding, multi-tensor AdamW, grouped expert GEMM
+    V2 = 32064
+    mk = lambda: (torch.randn(M, device=dev), torch.randn(M, V2, device=dev, dtype=bf), torch.randint(0, V2, (M,), device=dev), torch.rand(M, device=dev) + 10)
+    ms, best = time_fn(mk, lambda g, lg, lb, lse: L.ops.cross_entropy_bwd(g, lg, lb, lse), pool=4)
+    rec("cross_entropy bwd 8192x32064", ms, best, nbytes=2 * M * V2 * 2)
+    mk = lambda: (torch.randn(M, H, device=dev),)
+    ms, best = time_fn(mk, lambda x: L.ops.dtype_cast(x, bf), pool=3)
+    rec("cast fp32->bf16 8192x14336", ms, best, nbytes=M * H * 6)
+    mk = lambda: (torch.randn(M, H, device=dev, dtype=bf),)
+    ms, best = time_fn(mk, lambda x: L.ops.dtype_cast(x, torch.float32), pool=3)
+    rec("cast bf16->fp32 8192x14336", ms, best, nbytes=M * H * 6)
+    tab = torch.randn(128256, D, device=dev, dtype=bf)
+    mk = lambda: (torch.randint(0, 128256, (1, M), device=dev),)
+    ms, best = time_fn(mk, lambda ids: L.ops.embedding(tab, ids), pool=4)
+    rec("embedding fwd 8192 of 128256x4096", ms, best, nbytes=2 * M * D * 2)
+    from autoparallel_b200.optim import AdamW
+
+    ps = [torch.nn.Parameter(torch.randn(H, D, device=dev)) for _ in range(4)]
+    for p_ in ps:
+        p_.grad = torch.randn_like(p_)
+    opt = AdamW(ps, lr=1e-3, emit_bf16=True)
+    opt.step()  # state and tables exist before timing
+    opt.prepare_capture()
+    ms, best = time_fn(lambda: (), lambda: opt.step(), pool=2)
+    rec("adamw 4 x 14336x4096 fp32 (+bf16 copy)", ms, best, nbytes=4 * H * D * (16 + 12 + 2))
+    if not args.quick:
+        E, Me, Ne, Ke = 8, 8192, 1408, 2048
+        mk = lambda: (torch.randn(E, Me, Ke, device=dev, dtype=bf) * 0.05, torch.randn(E, Ke, Ne, device=dev, dtype=bf) * 0.05)
+        ms, best = time_fn(mk, lambda a, b: torch.ops.apb200.grouped_mm(a, b, False, bf), pool=3)
+        rec(f"grouped_mm {E}x{Me}x{Ne}x{Ke}", ms, best, flops=2.0 * E * Me * Ne * Ke)
     mk = lambda: (torch.randn(1, M, 32, 128, device=dev, dtype=bf), torch.randn(1, M, 8, 128, device=dev, dtype=bf), torch.randn(1, M, 8, 128, device=dev, dtype=bf))
     ms, best = time_fn(mk, lambda q, k, v: L.ops.attention(q, k, v, True, 128 ** -0.5), pool=2)
-    rec("attention fwd causal 8192 32q/8kv", ms, best, flops=4.0 * M * M * 4096 * 0.5)
+    rec("attention fwd causal 8192 32q/8kv (library kernel unless APB200_ATTENTION_FWD=own)", ms, best, flops=4.0 * M * M * 4096 * 0.5)
     if args.json:
         json.dump({"peaks": {"hbm_gbs": hbm, "bf16_tflops": tf_burst, "bf16_tflops_sustained": tf_sus, "source": src}, "rows": rows}, open(args.json, "w"), indent=1)
 
