@@ -62,6 +62,34 @@ for nb in (1 << 20, 16 << 20, 128 << 20):
     tr = timeit(lambda: C.reduce_scatter(big, 0, name, n)); trn = timeit(unfused(lambda: C.reduce_scatter(big, 0, name, n)))
     if rank == 0: print(f"U1 {nb>>20:4d} MiB/rank: all_gather ours {ta:.3f} ms nccl {tn:.3f} ms | reduce_scatter ours {tr:.3f} ms nccl {trn:.3f} ms", flush=True)
     rows.append(dict(case=f"U1 {nb>>20}MiB", ag_ms=ta, ag_nccl_ms=tn, rs_ms=tr, rs_nccl_ms=trn))
+# copy-engine collectives (runtime/dma.py): gathers of arena-resident shards and fp32 reduce-scatters, against NCCL
+try:
+    from torch.distributed.device_mesh import init_device_mesh
+    from autoparallel_b200.runtime import dma
+    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    slot = 128 << 20
+    arena = dma.enable_for_mesh(mesh, arena_bytes=(256 << 20) + 3 * world * slot + (1 << 20), ring=3, slot_bytes=slot, sum_ctas=48)
+    dname = mesh.get_group(0).group_name
+    def no_dma(fn):
+        def run():
+            be = comm_ops._dma_backends.pop(dname); sb = comm_ops._symm_backends.pop(name, None)
+            try: return fn()
+            finally:
+                comm_ops._dma_backends[dname] = be
+                if sb is not None: comm_ops._symm_backends[name] = sb
+        return run
+    for nb in (1 << 20, 16 << 20, 128 << 20):
+        shard = arena.alloc((nb // 2,), bf); shard.copy_(R(nb // 2)); arena.barrier()
+        ta = timeit(lambda: C.all_gather(shard, 0, dname, n)); tn = timeit(no_dma(lambda: C.all_gather(shard, 0, dname, n)))
+        full = torch.randn(nb // 4 * n, device="cuda", dtype=f32) if nb * n <= (1 << 30) else None
+        if full is not None and nb <= slot:
+            tr = timeit(lambda: C.reduce_scatter(full, 0, dname, n)); trn = timeit(no_dma(lambda: C.reduce_scatter(full, 0, dname, n)))
+        else:
+            tr = trn = float("nan")
+        if rank == 0: print(f"CE {nb>>20:4d} MiB/rank: all_gather copy-engine {ta:.3f} ms nccl {tn:.3f} ms | reduce_scatter(fp32) copy-engine+sum {tr:.3f} ms nccl {trn:.3f} ms", flush=True)
+        rows.append(dict(case=f"CE {nb>>20}MiB", ag_ms=ta, ag_nccl_ms=tn, rs_ms=tr, rs_nccl_ms=trn))
+except Exception as e:
+    if rank == 0: print("copy-engine rows skipped:", type(e).__name__, str(e)[:200], flush=True)
 torch.cuda.synchronize(); cuda_impl.check_status()
 out = next((a.split("=", 1)[1] for a in sys.argv if a.startswith("--out=")), None)
 if rank == 0 and out: json.dump(rows, open(out, "w"), indent=1)

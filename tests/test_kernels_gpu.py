@@ -216,10 +216,6 @@ def test_attention(K, causal):
     _close(dv, rdv, 5e-2, 5e-2)
 
 
-@pytest.mark.skipif(
-    __import__("os").environ.get("APB200_TEST_OWN_ATTENTION") != "1",
-    reason="own attention forward: opt-in (APB200_TEST_OWN_ATTENTION=1) until it has been validated on hardware",
-)
 @pytest.mark.parametrize("causal,S,Sk,H,Hkv", [(True, 256, 256, 2, 1), (True, 1024, 1024, 4, 2), (False, 256, 384, 2, 2)])
 def test_own_attention_forward(K, causal, S, Sk, H, Hkv):
     lib, impl = K
