@@ -63,6 +63,7 @@ class Runtime:
             else:
                 self._order.append(("input", self._tensor_input_pos[n]))
         self._n_in = flat_tensor_counter
+        self._graph_device = torch.device("cpu")  # device constants inside the graphs (planning happens on CPU fake tensors)
         self._fn = _make_function(self)
         if self.executor == "streams":
             from ..parallel.passes.overlap import schedule_for_streams
@@ -70,12 +71,37 @@ class Runtime:
             self.fw = schedule_for_streams(self.fw, mesh, overlap_config)
             self.bw = schedule_for_streams(self.bw, mesh, overlap_config)
 
+    def _retarget(self, device: torch.device) -> None:
+        """Planning runs on CPU fake tensors, so factory operators traced with an explicit ``device=`` (``torch.zeros(...,
+        device=x.device)`` inside a user region, ``arange`` for index arithmetic) carry "cpu" as a constant.  Before the
+        first run on another device the constant is replaced in every graph of this runtime."""
+        if device == self._graph_device:
+            return
+        for gm in (self.fw, self.bw, self.fwd_only):
+            changed = False
+            for n in gm.graph.nodes:
+                if n.op != "call_function":
+                    continue
+                if isinstance(n.kwargs.get("device"), torch.device) and n.kwargs["device"] != device:
+                    n.kwargs = {**n.kwargs, "device": device}
+                    changed = True
+                new_args = tuple(device if isinstance(a, torch.device) and a != device else a for a in n.args)
+                if any(x is not y for x, y in zip(new_args, n.args)):
+                    n.args = new_args
+                    changed = True
+            if changed:
+                gm.recompile()
+        self._graph_device = device
+
     def gather_inputs(self, params, buffers, inputs):
         src = {"param": params, "buffer": buffers, "input": inputs}
         return [src[k][i] for k, i in self._order]
 
     def __call__(self, params: Sequence[torch.Tensor], buffers, inputs, grad_enabled: bool):
         flat = self.gather_inputs(params, buffers, inputs)
+        dev = next((t.device for t in flat if isinstance(t, torch.Tensor)), None)
+        if dev is not None and dev != self._graph_device:
+            self._retarget(dev)
         if not grad_enabled:
             with torch.no_grad():
                 return tuple(self.fwd_only(*flat))

@@ -367,3 +367,49 @@ def test_embedding_forward_and_backward(K, dtype):
     out.backward(g)
     ref = torch.zeros(V, D, dtype=torch.float32).index_add_(0, ids.reshape(-1).cpu(), g.reshape(-1, D).float().cpu())
     _close(w.grad, ref, 2e-2 if dtype == torch.bfloat16 else 1e-5, 2e-2 if dtype == torch.bfloat16 else 1e-5)
+
+
+def test_factory_ops_traced_on_cpu_follow_the_module_to_the_gpu():
+    """A region that builds index tensors with ``device=x.device`` is planned on CPU fake tensors; at run time the
+    device constant inside the graphs follows the module (the MoE dispatch does exactly this)."""
+    import torch.distributed as dist
+    import torch.nn as nn
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Shard
+
+    from autoparallel_b200 import AutoParallel
+    from conftest import free_port
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = nn.Linear(32, 32, bias=False)
+
+        def forward(self, x):
+            idx = torch.arange(x.shape[0], device=x.device) % 4
+            acc = torch.zeros(4, 32, device=x.device, dtype=x.dtype).index_add(0, idx, self.lin(x))
+            return acc.sum()
+
+    own_pg = not dist.is_initialized()
+    if own_pg:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()))
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    try:
+        mesh = init_device_mesh("cuda", (1,), mesh_dim_names=("dp",))
+        with torch.device("meta"):
+            m = M()
+        with AutoParallel(m, lambda: torch.rand(16, 32), mesh) as ap:
+            ap.add_input_constraints([(Shard(0),)])
+            ap.optimize_placement()
+            pm = ap.apply_placement()
+        pm.to_empty(device="cuda")
+        with torch.no_grad():
+            pm.lin.weight.copy_(torch.eye(32))
+        x = torch.rand(16, 32, device="cuda")
+        out = pm(x)
+        out.backward()
+        assert torch.allclose(out, x.sum(), rtol=1e-4)
+        assert pm.lin.weight.grad is not None
+    finally:
+        if own_pg:
+            dist.destroy_process_group()
