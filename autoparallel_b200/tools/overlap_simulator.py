@@ -39,6 +39,10 @@ def main(argv=None):
     ap.add_argument("--table", default=None)
     ap.add_argument("--trace", default=None)
     ap.add_argument("--device", default="B200")
+    ap.add_argument("--ac", default="none", choices=["none", "selective", "full"], help="activation checkpointing mode of the plan")
+    ap.add_argument("--optimizer-bytes-per-param", type=float, default=30.0,
+                    help="HBM traffic of the optimizer step per local parameter element (AdamW on fp32 state with a bf16 copy: "
+                         "reads p, g, m, v = 16 B, writes p, m, v + bf16 = 14 B); 0 leaves the optimizer out")
     ap.add_argument("--save-capture", default=None, help="write the partitioned per-rank graphs to this file for later --replay")
     ap.add_argument("--replay", default=None, help="simulate a saved capture instead of planning a model")
     args = ap.parse_args(argv)
@@ -77,7 +81,7 @@ def main(argv=None):
                              {"labels": torch.randint(0, cfg.vocab_size, (batch, args.seq_len))})
 
     with AutoParallel(model, input_fn, mesh, MPPolicy(torch.bfloat16, torch.float32), plan_device=args.device,
-                      cost_model=args.table or "auto", bucket_collectives=args.bucket) as apx:
+                      cost_model=args.table or "auto", bucket_collectives=args.bucket, activation_checkpointing=args.ac) as apx:
         apx.add_parameter_memory_constraint()
         apx.add_input_constraints([(Shard(0),) + (Replicate(),) * (mesh.ndim - 1)] * 2)
         apx.optimize_placement()
@@ -100,6 +104,14 @@ def main(argv=None):
             }
             if args.trace:
                 create_execution_trace(sched, mesh, args.trace.replace(".json", f"_{name}.json"), args.device)
+        # the optimizer is not part of the traced graphs: a bandwidth-bound pass over the local shards of the state
+        from ..parallel.cost.device import DEVICE_LIMITS
+
+        local_params = sum(p.numel() for p in model.parameters()) / world
+        opt_us = args.optimizer_bytes_per_param * local_params / DEVICE_LIMITS[args.device].bytes_per_us()
+        report["optimizer_us"] = opt_us
+        report["step_ms_after"] = (report["forward"]["after"]["total_us"] + report["backward"]["after"]["total_us"] + opt_us) / 1e3
+        report["kernel_ms"] = (report["forward"]["after"]["compute_us"] + report["backward"]["after"]["compute_us"] + opt_us) / 1e3
     print(json.dumps(report, indent=1, default=float))
     return report
 

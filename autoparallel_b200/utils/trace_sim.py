@@ -107,6 +107,12 @@ def make_runtime_estimator(mesh, plan_device: Optional[str] = None, group_dim: O
         if isinstance(v0, torch.Tensor) and v0.dtype.is_floating_point:
             dt = v0.dtype
         fl = flops_of(node)
+        if fl > 0:
+            # a contraction runs at the rate of its operands (bf16 weight gradients accumulate into fp32 outputs)
+            a0 = next((a.meta.get("val") for a in node.all_input_nodes if isinstance(a.meta.get("val"), torch.Tensor)
+                       and a.meta["val"].dtype.is_floating_point), None)
+            if a0 is not None:
+                dt = a0.dtype
         t_us = max(fl / limit.flops_per_us(dt), nb / limit.bytes_per_us(), limit.launch_us)
         if t in comm_ops.FUSED_OPS:
             g, n = node.args[-2], node.args[-1]
