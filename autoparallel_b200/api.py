@@ -95,7 +95,7 @@ class AutoParallel:
         activation_checkpointing: str = "none",
         plan_device: Optional[str] = None,
         fuse_collectives: Any = None,
-        bucket_collectives: bool = False,
+        bucket_collectives: Any = False,
         ordered_sharding: bool = True,
         uneven_sharding: bool = False,
         pattern_ops: bool = True,
@@ -126,7 +126,11 @@ class AutoParallel:
         self.ac_stats: dict = {}
         self.plan_device = plan_device
         self.fuse_collectives = fuse_collectives
+        # False: every collective stays its own node; True: collectives below 4 MiB are merged up to fixed caps;
+        # "auto": the bucket plan is made from priced collectives, a compute window and a memory headroom
         self.bucket_collectives = bucket_collectives
+        #: "auto" bucketing: bytes a bucket may keep alive beyond what the separate collectives would
+        self.bucket_headroom_bytes: int = 2 << 30
         self.ordered_sharding = ordered_sharding
         self.bucket_stats = {}
         self.fusion_stats = {}
@@ -313,7 +317,14 @@ class AutoParallel:
         if self.bucket_collectives:
             from .parallel.passes.bucketing import bucket_collectives
 
-            self.bucket_stats = bucket_collectives(lowered.gm)
+            cost = None
+            if self.bucket_collectives == "auto":
+                # sizes decided by the priced collectives (a calibrated table when ``cost_model`` names one) and by the
+                # memory left on the device next to parameters, gradients and optimizer state
+                from .parallel.passes.bucketing import BucketCost
+
+                cost = BucketCost.from_mesh(self.mesh, self.plan_device, headroom_bytes=self.bucket_headroom_bytes)
+            self.bucket_stats = bucket_collectives(lowered.gm, cost=cost)
             changed += self.bucket_stats["members"]
         if changed:
             lowered.joint = index_joint_graph(lowered.gm, joint.traced_inputs, joint.out_spec)

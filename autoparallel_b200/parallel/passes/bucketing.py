@@ -13,6 +13,20 @@ between its first and last member (keeping members close preserves the prefetch 
 how long the first member's data waits).  Dim-0 shardings only, fp32 / bf16 only – the same limits
 as the reference's bucketing (autoparallel/graph_passes/autobucketing_inductor/bucket_utils.py:
 487-764, size and span rules in autoparallel/graph_passes/auto_bucketing.py:19-188, 294-314).
+
+Two ways to decide what goes into a bucket:
+
+* static (``BucketConfig`` alone): collectives below ``small_bytes`` are merged up to the caps above;
+* cost driven (``BucketCost``, ``AutoParallel(bucket_collectives="auto")``): collectives of any size are
+  candidates and a member joins a bucket only if (i) the priced collective gets cheaper by at least
+  ``min_saving_us`` after paying for the member's copies into and out of the packed buffers (prices come
+  from the active topology, i.e. from a table calibrated on the machine when one is loaded), (ii) a gather bucket still finishes inside the compute window in front of its first
+  consumer, so that merging never turns hidden communication into exposed communication, (iii) the bytes
+  the bucket keeps alive longer than the separate collectives would (earlier gathered outputs, gradients
+  held until the last member exists, the packed buffers) fit the memory headroom, and (iv) the bucket stays
+  below ``max_fraction`` of all candidate bytes of its kind, so that a step never degenerates into one
+  collective.  Reference: autoparallel/graph_passes/autobucketing_inductor/bucket_plan.py:60-330 (greedy plan
+  from calibrated estimates with a memory check), estimation_utils.py:73-147.
 """
 from __future__ import annotations
 
@@ -34,6 +48,44 @@ class BucketConfig:
     max_bucket_bytes: int = 64 << 20
     small_bytes: int = 4 << 20  # only collectives below this size are bucketed
     max_span: int = 1500
+
+
+@dataclasses.dataclass
+class BucketCost:
+    """Prices for the cost-driven plan.  ``collective_us(kind, nbytes, n_ranks, group)`` with ``kind`` in
+    {"all_gather", "reduce_scatter"} and ``nbytes`` the size of the full (gathered / pre-scatter) tensor;
+    ``compute_us(node)`` for everything else."""
+
+    collective_us: callable
+    compute_us: callable
+    copy_us: callable = lambda nbytes: 0.0  # device time of moving ``nbytes`` (read + write counted by the caller)
+    headroom_bytes: int = 2 << 30
+    min_saving_us: float = 1.0
+    window_nodes: int = 12  # compute nodes in front of a consumer that a prefetched gather can hide under
+    max_fraction: float = 0.2
+
+    @classmethod
+    def from_mesh(cls, mesh, plan_device=None, headroom_bytes: int = 2 << 30, **kw) -> "BucketCost":
+        """Prices from the topology that is active for ``mesh`` (formula, NCCL model or a measured table)."""
+        from ...parallel.cost import comm as comm_cost
+        from ...utils.trace_sim import make_runtime_estimator
+
+        topo = comm_cost.get_topology(mesh)
+        group_dim = {mesh.get_group(i).group_name: i for i in range(mesh.ndim)}
+        est = make_runtime_estimator(mesh, plan_device)
+
+        def collective_us(kind, nbytes, n, group):
+            dim = group_dim.get(group, 0)
+            return (topo.all_gather if kind == "all_gather" else topo.reduce_scatter)(dim, n, nbytes)
+
+        from ...parallel.cost.device import DEVICE_LIMITS, get_device_limit
+
+        limit = DEVICE_LIMITS[plan_device] if plan_device else get_device_limit(mesh.device_type)
+
+        def copy_us(nbytes):
+            return max(limit.launch_us, nbytes / limit.bytes_per_us())
+
+        return cls(collective_us, est, copy_us, headroom_bytes, **kw)
 
 
 def _nbytes(n: fx.Node) -> int:
@@ -72,8 +124,10 @@ def _unpack_scatter(buf, shapes, n):
     return tuple(outs)
 
 
-def bucket_collectives(gm: fx.GraphModule, config: BucketConfig | None = None) -> dict:
+def bucket_collectives(gm: fx.GraphModule, config: BucketConfig | None = None, cost: BucketCost | None = None) -> dict:
     cfg = config or BucketConfig()
+    if cost is not None and config is None:
+        cfg = BucketConfig(max_bucket_bytes=1 << 40, small_bytes=1 << 40)  # sizes are decided by the prices
     g = gm.graph
     order = {n: i for i, n in enumerate(g.nodes)}
     placeholders = {n for n in g.nodes if n.op == "placeholder"}
@@ -85,6 +139,80 @@ def bucket_collectives(gm: fx.GraphModule, config: BucketConfig | None = None) -
             input_only.add(n)
     out_node = next(n for n in g.nodes if n.op == "output")
     stats = {"all_gather_buckets": 0, "reduce_scatter_buckets": 0, "members": 0}
+    if cost is not None:
+        stats.update({"saved_us": 0.0, "rejected_saving": 0, "rejected_window": 0, "rejected_memory": 0, "rejected_fraction": 0})
+    nodes_in_order = list(g.nodes)
+    _compute_cache: dict = {}
+
+    def compute_us(n):
+        if n not in _compute_cache:
+            t = 0.0
+            if n.op == "call_function" and n.target not in comm_ops.COLLECTIVE_OPS and n.target not in comm_ops.START_OPS:
+                try:
+                    t = float(cost.compute_us(n))
+                except Exception:
+                    t = 0.0
+            _compute_cache[n] = t
+        return _compute_cache[n]
+
+    def window_us(user):
+        """Compute time of the ``window_nodes`` kernels in front of ``user``: what a prefetched gather can hide under."""
+        i = order[user] - 1
+        seen, t = 0, 0.0
+        while i >= 0 and seen < cost.window_nodes:
+            d = compute_us(nodes_in_order[i])
+            if d > 0:
+                t += d
+                seen += 1
+            i -= 1
+        return t
+
+    def size_of(kind, n):
+        # priced mode counts the full tensor a collective moves (gathered output / pre-scatter input); the static caps
+        # are defined on the node's own output
+        return _nbytes(n.args[0]) if (cost is not None and kind == "rs") else _nbytes(n)
+
+    def accept(kind, bucket, size, n, total_bytes):
+        """May ``n`` join ``bucket`` (current full-tensor bytes ``size``)?"""
+        nb = size_of(kind, n)
+        if size + nb > cfg.max_bucket_bytes or order[n] - order[bucket[0]] > cfg.max_span:
+            return False
+        if cost is None:
+            return True
+        group, n_ranks = n.args[2], n.args[3]
+        name = "all_gather" if kind == "ag" else "reduce_scatter"
+        if total_bytes > 0 and size + nb > cost.max_fraction * total_bytes and len(bucket) >= 2:
+            stats["rejected_fraction"] += 1
+            return False
+        merged = cost.collective_us(name, size + nb, n_ranks, group)
+        saving = cost.collective_us(name, size, n_ranks, group) + cost.collective_us(name, nb, n_ranks, group) - merged
+        # a member of a bucket is copied into the packed buffer and (gathers) out of the gathered one; alone it is not
+
+        def packing(nbytes):
+            if kind == "ag":
+                return cost.copy_us(2 * nbytes // n_ranks) + cost.copy_us(2 * nbytes)
+            return cost.copy_us(2 * nbytes)
+
+        saving -= packing(nb) + (packing(size) if len(bucket) == 1 else 0.0)
+        if saving < cost.min_saving_us:
+            stats["rejected_saving"] += 1
+            return False
+        if kind == "ag":
+            first_user = min((u for m in bucket for u in m.users), key=lambda u: order[u])
+            latency = cost.collective_us(name, 0, n_ranks, group)
+            if merged > max(window_us(first_user), 4.0 * latency):  # latency-bound buckets are always worth it
+                stats["rejected_window"] += 1
+                return False
+            held = sum(_nbytes(m) for m in bucket[1:]) + nb  # gathered earlier than they would be
+            extra = held + (size + nb) + (size + nb) // n_ranks  # + gathered buffer + packed shards
+        else:
+            held = sum(_nbytes(m.args[0]) for m in bucket)  # gradients wait for the last member
+            extra = held + (size + nb) + (size + nb) // n_ranks
+        if extra > cost.headroom_bytes:
+            stats["rejected_memory"] += 1
+            return False
+        stats["saved_us"] += saving
+        return True
 
     def candidates(target, pred):
         res = []
@@ -136,19 +264,23 @@ def bucket_collectives(gm: fx.GraphModule, config: BucketConfig | None = None) -
         stats["all_gather_buckets" if kind == "ag" else "reduce_scatter_buckets"] += 1
         stats["members"] += len(members)
 
-    def run(kind, cands):
+    def plan(kind, cands):
+        """Buckets (lists of members, graph order) of one kind; nothing in the graph is touched."""
         by_group: dict = {}
         for n in cands:
             by_group.setdefault((n.args[2], n.meta["val"].dtype), []).append(n)
+        buckets = []
         for members in by_group.values():
             bucket, size = [], 0
+            total_bytes = sum(size_of(kind, m) for m in members)
             for n in members:
-                if bucket and (size + _nbytes(n) > cfg.max_bucket_bytes or order[n] - order[bucket[0]] > cfg.max_span):
-                    close(kind, bucket)
+                if bucket and not accept(kind, bucket, size, n, total_bytes):
+                    buckets.append(bucket)
                     bucket, size = [], 0
                 bucket.append(n)
-                size += _nbytes(n)
-            close(kind, bucket)
+                size += size_of(kind, n)
+            buckets.append(bucket)
+        return [b for b in buckets if len(b) >= 2]
 
     # Gathers of graph-input-derived shards (parameter -> cast -> gather chains).  Such a chain can
     # run anywhere after the placeholders, so the members of a bucket are first hoisted – chain and
@@ -166,6 +298,7 @@ def bucket_collectives(gm: fx.GraphModule, config: BucketConfig | None = None) -
         by_group.setdefault((n.args[2], n.meta["val"].dtype), []).append(n)
     for members in by_group.values():
         bucket, size = [], 0
+        total_bytes = sum(_nbytes(m) for m in members)
 
         def flush():
             if len(bucket) >= 2:
@@ -179,26 +312,23 @@ def bucket_collectives(gm: fx.GraphModule, config: BucketConfig | None = None) -
                 close("ag", list(bucket))
 
         for n in members:
-            if bucket and (size + _nbytes(n) > cfg.max_bucket_bytes or order[n] - order[bucket[0]] > cfg.max_span):
+            if bucket and not accept("ag", bucket, size, n, total_bytes):
                 flush()
                 bucket, size = [], 0
             bucket.append(n)
             size += _nbytes(n)
         flush()
     order = {n: i for i, n in enumerate(g.nodes)}
+    nodes_in_order = list(g.nodes)
     rs = candidates(C.reduce_scatter.default, lambda n: all(u is out_node for u in n.users))
 
-    def rs_runs(nodes):
-        # reductions feeding only the output can be delayed to the position of the last member
-        return [nodes] if nodes else []
-
-    for r in rs_runs(rs):
-        # move every member (and nothing else) to the position of the last one
-        last = r[-1]
-        for m in r[:-1]:
+    # Reductions that feed only the graph's outputs can be delayed: the members of a bucket (and nothing else) move to
+    # the position of its last member.  Reductions that stay alone keep their place.
+    for bucket in plan("rs", rs):
+        last = bucket[-1]
+        for m in bucket[:-1]:
             last.prepend(m)
-        order = {n: i for i, n in enumerate(g.nodes)}
-        run("rs", r)
+        close("rs", bucket)
     g.lint()
     gm.recompile()
     return stats

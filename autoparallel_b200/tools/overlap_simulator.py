@@ -35,7 +35,8 @@ def main(argv=None):
     ap.add_argument("--prefetch-depth", type=int, default=12)
     ap.add_argument("--max-in-flight-gb", type=float, default=2.0)
     ap.add_argument("--max-pending-reductions", type=int, default=6)
-    ap.add_argument("--bucket", action="store_true")
+    ap.add_argument("--bucket", nargs="?", const="static", default=None, choices=["static", "auto"],
+                    help="merge collectives: static size caps, or 'auto' = plan from priced collectives / compute window / memory headroom")
     ap.add_argument("--table", default=None)
     ap.add_argument("--trace", default=None)
     ap.add_argument("--device", default="B200")
@@ -81,7 +82,8 @@ def main(argv=None):
                              {"labels": torch.randint(0, cfg.vocab_size, (batch, args.seq_len))})
 
     with AutoParallel(model, input_fn, mesh, MPPolicy(torch.bfloat16, torch.float32), plan_device=args.device,
-                      cost_model=args.table or "auto", bucket_collectives=args.bucket, activation_checkpointing=args.ac) as apx:
+                      cost_model=args.table or "auto",
+                      bucket_collectives={None: False, "static": True, "auto": "auto"}[args.bucket], activation_checkpointing=args.ac) as apx:
         apx.add_parameter_memory_constraint()
         apx.add_input_constraints([(Shard(0),) + (Replicate(),) * (mesh.ndim - 1)] * 2)
         apx.optimize_placement()

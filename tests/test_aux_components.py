@@ -269,3 +269,121 @@ def test_simulated_llama3_8b_step_is_close_to_the_measured_one():
     assert rep["step_ms_after"] <= 445.6
     # AdamW over 8.03e9 fp32 parameters with a bf16 copy: measured 39.9 ms
     assert abs(rep["optimizer_us"] / 1e3 - 39.9) / 39.9 < 0.15
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# cost-driven bucket plan (reference behaviours: tests/test_auto_bucketing_patches.py - merge within caps, split on
+# bytes, split on span, skip what depends on a member - restated for the priced planner)
+# ---------------------------------------------------------------------------------------------------------------
+def _gather_chain_graph(sizes, compute_between=1, group="g0", n_ranks=4, lead=0):
+    """placeholders p_i -> all_gather(p_i) -> relu-consumer chain; ``compute_between`` compute nodes before each use,
+    ``lead`` compute nodes in front of everything."""
+    import torch.fx as fx
+
+    from autoparallel_b200.runtime import comm_ops
+
+    C = comm_ops.ops
+    g = fx.Graph()
+    x = g.placeholder("x")
+    x.meta["val"] = torch.empty(1024, 1024)
+    ps = []
+    for i, sz in enumerate(sizes):
+        p = g.placeholder(f"p{i}")
+        p.meta["val"] = torch.empty(sz // n_ranks, dtype=torch.float32)
+        ps.append(p)
+    cur = x
+    for _ in range(lead):
+        cur = g.call_function(torch.ops.aten.relu.default, (cur,))
+        cur.meta["val"] = torch.empty(1024, 1024)
+    gathers = []
+    for i, p in enumerate(ps):
+        ag = g.call_function(C.all_gather.default, (p, 0, group, n_ranks))
+        ag.meta["val"] = torch.empty(sizes[i], dtype=torch.float32)
+        gathers.append(ag)
+        for _ in range(compute_between):
+            cur = g.call_function(torch.ops.aten.relu.default, (cur,))
+            cur.meta["val"] = torch.empty(1024, 1024)
+        s = g.call_function(torch.ops.aten.sum.default, (ag,))
+        s.meta["val"] = torch.empty(())
+        cur = g.call_function(torch.ops.aten.add.Tensor, (cur, s))
+        cur.meta["val"] = torch.empty(1024, 1024)
+    g.output((cur,))
+    return fx.GraphModule(torch.nn.Module(), g), gathers
+
+
+def _priced(alpha_us=10.0, gbps=100.0, compute_us=5.0, **kw):
+    from autoparallel_b200.parallel.passes.bucketing import BucketCost
+
+    return BucketCost(lambda kind, nb, n, group: alpha_us + nb / (gbps * 1e3), lambda node: compute_us, **kw)
+
+
+def _count(gm, target):
+    return sum(1 for n in gm.graph.nodes if n.op == "call_function" and n.target is target)
+
+
+def test_priced_bucket_plan_merges_latency_bound_gathers_and_leaves_bandwidth_bound_ones():
+    from autoparallel_b200.parallel.passes.bucketing import bucket_collectives
+    from autoparallel_b200.runtime import comm_ops
+
+    C = comm_ops.ops
+    # eight 4 KiB gathers: each costs ~alpha; merging two saves one alpha
+    gm, _ = _gather_chain_graph([1024] * 8)
+    stats = bucket_collectives(gm, cost=_priced(max_fraction=1.0))
+    assert stats["all_gather_buckets"] == 1 and stats["members"] == 8 and _count(gm, C.all_gather.default) == 1
+    assert stats["saved_us"] == pytest.approx(7 * 10.0, rel=1e-3)
+    gm.graph.lint()
+    # the same gathers when latency is free: nothing to gain, nothing merged
+    gm, _ = _gather_chain_graph([1024] * 8)
+    stats = bucket_collectives(gm, cost=_priced(alpha_us=0.0, max_fraction=1.0))
+    assert stats["members"] == 0 and stats["rejected_saving"] >= 1 and _count(gm, C.all_gather.default) == 8
+
+
+def test_priced_bucket_plan_respects_window_memory_and_fraction():
+    from autoparallel_b200.parallel.passes.bucketing import bucket_collectives
+    from autoparallel_b200.runtime import comm_ops
+
+    C = comm_ops.ops
+    # 4 MiB gathers at 100 GB/s take ~52 us each; the window in front of the first consumer is 12 nodes x 5 us = 60 us,
+    # so a second member (94 us merged) would expose communication: every gather stays alone
+    gm, _ = _gather_chain_graph([1 << 20] * 6, lead=12)
+    stats = bucket_collectives(gm, cost=_priced(max_fraction=1.0))
+    assert stats["members"] == 0 and stats["rejected_window"] >= 1
+    # a long compute window admits them ...
+    gm, _ = _gather_chain_graph([1 << 20] * 6, lead=12)
+    stats = bucket_collectives(gm, cost=_priced(compute_us=100.0, max_fraction=1.0))
+    assert stats["members"] == 6 and _count(gm, C.all_gather.default) == 1
+    # ... unless the memory the bucket keeps alive does not fit the headroom (4 MiB members, 6 MiB headroom)
+    gm, _ = _gather_chain_graph([1 << 20] * 6, lead=12)
+    stats = bucket_collectives(gm, cost=_priced(compute_us=100.0, max_fraction=1.0, headroom_bytes=6 << 20))
+    assert stats["members"] == 0 and stats["rejected_memory"] >= 1
+    # ... and no bucket takes more than the given fraction of all candidate bytes (0.5 of six members = three each)
+    gm, _ = _gather_chain_graph([1 << 20] * 6, lead=12)
+    stats = bucket_collectives(gm, cost=_priced(compute_us=100.0, max_fraction=0.5))
+    assert stats["all_gather_buckets"] == 2 and stats["members"] == 6 and stats["rejected_fraction"] >= 1
+
+
+def test_priced_bucket_plan_on_llama_keeps_numerics_and_reduces_collectives(mesh_1d):
+    """End to end: ``bucket_collectives="auto"`` prices the collectives with the mesh's topology; the lowered graph has
+    fewer collectives and a simulated step that is not slower."""
+    from autoparallel_b200.runtime import comm_ops
+    from autoparallel_b200.utils.trace_sim import estimate_graph_metrics
+
+    C = comm_ops.ops
+    ap = _llama(mesh_1d, fuse_collectives=False)
+    try:
+        plain = ap.lower()
+        n_plain = _count(plain.gm, C.all_gather.default) + _count(plain.gm, C.reduce_scatter.default)
+        t_plain = estimate_graph_metrics(plain.gm, mesh_1d, "B200").total_us
+    finally:
+        ap.__exit__(None, None, None)
+    ap = _llama(mesh_1d, fuse_collectives=False, bucket_collectives="auto")
+    try:
+        low = ap.lower()
+        low.gm.graph.lint()
+        n_auto = _count(low.gm, C.all_gather.default) + _count(low.gm, C.reduce_scatter.default)
+        t_auto = estimate_graph_metrics(low.gm, mesh_1d, "B200").total_us
+        assert ap.bucket_stats["members"] >= 2 and ap.bucket_stats["saved_us"] > 0
+        assert n_auto < n_plain
+        assert t_auto <= t_plain * 1.001
+    finally:
+        ap.__exit__(None, None, None)

@@ -26,6 +26,8 @@ def _llama_worker(rank, ws, shape, executor, mp_policy, port, q):
     from autoparallel_b200.parallel.frontend.mp_cast import MPPolicy
 
     mesh = init_device_mesh("cpu", shape, mesh_dim_names=("dp", "tp")[: len(shape)])
+    executor, _, bucket = executor.partition("+")  # "graph+auto": cost-driven bucketing, "graph+static": size caps
+    bucket = {"": False, "static": True, "auto": "auto"}[bucket]
     if executor == "streams":
         # reductions on a second communicator per mesh dim (what the training entry point does)
         from autoparallel_b200.runtime import comm_ops
@@ -41,11 +43,13 @@ def _llama_worker(rank, ws, shape, executor, mp_policy, port, q):
         return ForwardInputs((torch.randint(0, cfg.vocab_size, (B, S)),), {"labels": torch.randint(0, cfg.vocab_size, (B, S))})
 
     pol = MPPolicy(torch.bfloat16, torch.float32) if mp_policy else None
-    with AutoParallel(m, input_fn, mesh, pol) as ap:
+    with AutoParallel(m, input_fn, mesh, pol, bucket_collectives=bucket) as ap:
         ap.add_parameter_memory_constraint()
         ap.add_input_constraints([(Shard(0),) + (Replicate(),) * (mesh.ndim - 1)] * 2)
         ap.optimize_placement()
         pm = ap.apply_placement(executor=executor)
+        if bucket:
+            assert ap.bucket_stats["members"] >= 2, ap.bucket_stats
     pm.to_empty(device="cpu")
     pm.init_weights(seed=0)
     torch.manual_seed(1)
@@ -89,6 +93,15 @@ def test_llama_matches_single_device(shape, executor):
     assert worst < 1e-4
     assert abs(inf - ref) < 1e-5  # forward-only graph under no_grad agrees with the training graph
     assert is_user_class
+
+
+@pytest.mark.parametrize("mode", ["graph+static", "streams+auto"])
+def test_llama_with_bucketed_collectives_matches_single_device(mode):
+    """Merged parameter gathers / gradient reductions (fixed caps or the priced plan) change no value."""
+    loss, ref, worst, inf, _ = _run(_llama_worker, 2, (2,), mode, False)
+    assert abs(loss - ref) < 1e-5
+    assert worst < 1e-4
+    assert abs(inf - ref) < 1e-5
 
 
 def test_llama_mixed_precision_close_to_fp32():
