@@ -160,6 +160,28 @@ def _mm_wgrad(a, b, out_dtype):
     return gemm_raw(_as2d(a), _as2d(b), True, True, out_dtype)
 
 
+def _scaled_mm(a, b, scale_a, scale_b, trans_b, out_dtype):
+    """fp8 operands with tensor-wise or row-wise scales: the library's fp8 GEMM (cuBLASLt through ``torch._scaled_mm``),
+    counted as a library call - this framework has no fp8 tensor-core kernel of its own."""
+    _fallback("scaled_mm", f"fp8 GEMM {tuple(a.shape)} x {tuple(b.shape)}")
+    lead = a.shape[:-1]
+    a2 = a.reshape(-1, a.shape[-1])
+    if a2.stride(-1) != 1:
+        a2 = a2.contiguous()
+    bk = b.t() if trans_b else b  # [K, N]; the library wants it column-major
+    if bk.stride(0) != 1:
+        bk = bk.t().contiguous().t()
+    n = bk.shape[1]
+    sa = scale_a.float().reshape(-1, 1) if scale_a.numel() > 1 else scale_a.float().reshape(())
+    sb = scale_b.float().reshape(1, -1) if scale_b.numel() > 1 else scale_b.float().reshape(())
+    if (sa.ndim == 0) != (sb.ndim == 0):  # the library takes both scales tensor-wise or both row-wise
+        sa = sa.expand(a2.shape[0], 1).contiguous() if sa.ndim == 0 else sa
+        sb = sb.expand(1, n).contiguous() if sb.ndim == 0 else sb
+    out = torch._scaled_mm(a2, bk, scale_a=sa.contiguous() if sa.ndim else sa, scale_b=sb.contiguous() if sb.ndim else sb,
+                           out_dtype=out_dtype if out_dtype in (torch.bfloat16, torch.float16, torch.float32) else torch.bfloat16)
+    return out.view(*lead, n).to(out_dtype)
+
+
 def _grouped_ok(*ts):
     return all(t.dtype == torch.bfloat16 and t.shape[-1] % 8 == 0 for t in ts)
 
@@ -374,6 +396,7 @@ def _register() -> None:
     R = L.register_cuda_impl
     R("gemm", _gemm)
     R("mm_nd", _mm_nd)
+    R("scaled_mm", _scaled_mm)
     R("mm_wgrad", _mm_wgrad)
     R("grouped_mm", _grouped_mm)
     R("grouped_mm_wgrad", _grouped_mm_wgrad)

@@ -479,6 +479,36 @@ reference_impls["mm_nd"] = _mm_nd_ref
 reference_impls["mm_wgrad"] = _mm_wgrad_ref
 
 
+# --------------------------------------------------------------------------------------
+# fp8 projection with scales: ``(a * scale_a) @ (b * scale_b)`` accumulated in fp32.  ``a`` [..., K] and ``b``
+# ([N, K] when ``trans_b`` else [K, N]) are float8 tensors; a scale is a scalar (tensor-wise) or, row-wise, has the
+# operand's shape with the contraction dim reduced to 1 (``scale_a`` [..., 1]; ``scale_b`` [N, 1] / [1, N]).
+# The planner sees it like ``mm_nd`` with the scales sharded along with the rows they belong to.  No autograd
+# formula: float8 training wraps it in its own autograd function, as with ``torch._scaled_mm`` (reference:
+# autoparallel/graph_passes/async_tp/asynctp_ops.py:363-393 for the scale modes).
+# --------------------------------------------------------------------------------------
+lib.define("scaled_mm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, bool trans_b, ScalarType out_dtype) -> Tensor")
+
+
+def _scaled_mm_ref(a, b, scale_a, scale_b, trans_b, out_dtype):
+    af = a.float() * scale_a.float()
+    bf = b.float() * scale_b.float()
+    lead = af.shape[:-1]
+    out = af.reshape(-1, af.shape[-1]) @ (bf.t() if trans_b else bf)
+    return out.reshape(*lead, out.shape[-1]).to(out_dtype)
+
+
+def _scaled_mm_meta(a, b, scale_a, scale_b, trans_b, out_dtype):
+    n = b.shape[0] if trans_b else b.shape[1]
+    return a.new_empty((*a.shape[:-1], n), dtype=out_dtype)
+
+
+lib.impl("scaled_mm", _scaled_mm_ref, "CPU")
+lib.impl("scaled_mm", _scaled_mm_meta, "Meta")
+lib.impl("scaled_mm", _make_cuda_entry("scaled_mm"), "CUDA")
+reference_impls["scaled_mm"] = _scaled_mm_ref
+
+
 def _mm_nd_setup(ctx, inputs, output):
     a, b, tb, _ = inputs
     ctx.save_for_backward(a, b)

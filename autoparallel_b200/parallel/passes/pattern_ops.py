@@ -314,6 +314,43 @@ def _rewrite_embedding(g: fx.Graph) -> int:
     return count
 
 
+# ------------------------------------------------------------------------------------------ fp8 projection
+def _rewrite_scaled_mm(g: fx.Graph) -> int:
+    """``torch._scaled_mm(a, b, scale_a, scale_b, out_dtype=..)`` without bias or result scale -> ``apb200::scaled_mm``.
+    A second operand written as ``w.t()`` (how float8 linears pass a row-major weight) is folded into ``trans_b``, so
+    the planner sees the weight as stored and its row-wise scale [N, 1] as a per-row tensor of it."""
+    count = 0
+    for n in list(g.nodes):
+        if not _is_fn(n, torch._scaled_mm):
+            continue
+        a, b, sa, sb = _arg(n, 0, "self"), _arg(n, 1, "mat2"), _arg(n, 2, "scale_a"), _arg(n, 3, "scale_b")
+        if _arg(n, 4, "bias") is not None or _arg(n, 5, "scale_result") is not None:
+            continue
+        out_dtype = _arg(n, 6, "out_dtype")
+        av, bv, sav, sbv = _val(a), _val(b), _val(sa), _val(sb)
+        if av is None or bv is None or sav is None or sbv is None or av.ndim != 2 or bv.ndim != 2:
+            continue
+        if out_dtype is None:
+            out_dtype = av.dtype
+        trans_b = False
+        if _is_method(b, "t") or (_is_method(b, "transpose") and set(b.args[1:]) in ({0, 1}, {-1, -2}, {0, -1}, {1, -2})):
+            src = b.args[0]
+            if _val(src) is not None and _val(src).ndim == 2:
+                # scale_b [1, N] belongs to the columns of b = rows of the stored weight: hand it over as [N, 1]
+                with g.inserting_before(n):
+                    sb_t = g.call_method("reshape", (sb, -1, 1)) if sbv.numel() > 1 else sb
+                if sb_t is not sb and "example_value" in sb.meta:
+                    sb_t.meta["example_value"] = sbv.reshape(-1, 1)
+                b, sb, trans_b = src, sb_t, True
+        with g.inserting_before(n):
+            y = g.call_function(apb.scaled_mm.default, (a, b, sa, sb, trans_b, out_dtype))
+        _copy_meta(y, n)
+        n.replace_all_uses_with(y)
+        g.erase_node(n)
+        count += 1
+    return count
+
+
 def rewrite_to_framework_ops(gm: fx.GraphModule) -> dict:
     """Apply every pattern to a Dynamo-level (torch IR) graph in place; returns how many of each were rewritten."""
     g = gm.graph
@@ -323,6 +360,7 @@ def rewrite_to_framework_ops(gm: fx.GraphModule) -> dict:
         "attention": _rewrite_sdpa(g),
         "rope": _rewrite_complex_rope(g),
         "embedding": _rewrite_embedding(g),
+        "scaled_mm": _rewrite_scaled_mm(g),
     }
     if any(stats.values()):
         g.lint()

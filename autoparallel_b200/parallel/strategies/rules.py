@@ -178,6 +178,21 @@ def _mm_nd(ctx):
     return expand_rows(ctx, rows)
 
 
+@register_rule(apb.scaled_mm.default)
+def _scaled_mm(ctx):
+    # (out, a, b, scale_a, scale_b): rows of ``a`` carry their row-wise scale, columns of the result carry ``scale_b``;
+    # a split of the contraction dim leaves both scales whole (they do not depend on k) and yields partial sums
+    a, b, sa, sb = ctx.in_vals[:4]
+    trans_b = ctx.args[4]
+    last = a.ndim - 1
+    kdim, ndim = (1, 0) if trans_b else (0, 1)
+    row_a = sa.ndim == a.ndim and sa.numel() > 1
+    row_b = sb.ndim == 2 and sb.numel() > 1
+    rows = [(S(i), S(i), R, S(i) if row_a and sa.shape[i] == a.shape[i] else R, R) for i in range(last)]
+    rows += [(S(last), R, S(ndim), R, S(ndim) if row_b else R), (P, S(last), S(kdim), R, R)]
+    return expand_rows(ctx, rows)
+
+
 @register_rule(apb.mm_wgrad.default)
 def _mm_wgrad(ctx):
     a, b = ctx.in_vals

@@ -80,6 +80,9 @@ def _rank_in_group(group: str) -> int:
 
 
 def _all_gather(x, dim, group, n):
+    if x.dtype.is_floating_point and x.dtype.itemsize == 1:
+        # float8: data movement only, and not every transport knows the dtype
+        return _all_gather(x.view(torch.uint8), dim, group, n).view(x.dtype)
     dma = _dma_backends.get(group)
     if dma is not None and dma.can_gather(x, dim):
         return dma.all_gather(x, dim)
@@ -125,6 +128,8 @@ def _all_reduce(x, group, n):
 def _all_to_all(x, split_dim, concat_dim, group, n):
     """Each rank splits ``x`` into n chunks along ``split_dim``, sends chunk r to rank r, and
     concatenates what it receives along ``concat_dim`` (Shard(concat_dim) -> Shard(split_dim))."""
+    if x.dtype.is_floating_point and x.dtype.itemsize == 1:
+        return _all_to_all(x.view(torch.uint8), split_dim, concat_dim, group, n).view(x.dtype)
     be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_to_all(x, split_dim, concat_dim)
@@ -389,9 +394,61 @@ def _mm_rs_meta(a, b, mode, dim, out_dtype, scale, group, n):
     return a.new_empty((*lead, b.shape[0] if mode == 0 else b.shape[1]), dtype=out_dtype)
 
 
+# fp8 forms.  The float8 operand and, when it is row-wise, its scale travel together; the product runs on
+# ``apb200::scaled_mm``.  Modes as above restricted to the cases float8 training produces:
+#   ag_scaled_mm  mode 0: y = x @ all_gather(w, 0)^T (w [N/n, K]; a row-wise scale_w [N/n, 1] is gathered with it)
+#                 mode 2: y = all_gather(x, rows) @ w^T     mode 3: y = all_gather(x, rows) @ w
+#                         (a row-wise scale_x [..., 1] is gathered with x)
+#   scaled_mm_rs  mode 0 / 1: reduce_scatter((a * sa) @ (b * sb)^T | (a * sa) @ (b * sb), rows)
+# Reference: autoparallel/graph_passes/async_tp/asynctp_ops.py:948-1026 (gather), :1189-1424 (reduce-scatter).
+lib.define("ag_scaled_mm(Tensor x, Tensor w, Tensor scale_x, Tensor scale_w, int mode, int dim, ScalarType out_dtype, "
+           "str group, int group_size) -> (Tensor, Tensor)")
+lib.define("scaled_mm_rs(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, int mode, int dim, ScalarType out_dtype, "
+           "str group, int group_size) -> Tensor")
+
+
+def _ag_scaled_mm(x, w, sx, sw, mode, dim, out_dtype, group, n):
+    if mode == 0:
+        wf = _all_gather(w, 0, group, n)
+        swf = _all_gather(sw.contiguous(), 0, group, n) if sw.numel() > 1 else sw
+        return _apb.scaled_mm(x, wf, sx, swf, True, out_dtype), wf
+    xf = _all_gather(x, dim, group, n)
+    sxf = _all_gather(sx.contiguous(), dim, group, n) if sx.numel() > 1 else sx
+    return _apb.scaled_mm(xf, w, sxf, sw, mode == 2, out_dtype), xf
+
+
+def _scaled_mm_rs(a, b, sa, sb, mode, dim, out_dtype, group, n):
+    # partial products are summed in fp32 (the reference stacks and sums the partials in the output dtype's accumulator)
+    full = _apb.scaled_mm(a, b, sa, sb, mode == 0, torch.float32)
+    return _reduce_scatter(full, dim, group, n).to(out_dtype)
+
+
+def _ag_scaled_mm_meta(x, w, sx, sw, mode, dim, out_dtype, group, n):
+    if mode == 0:
+        wf = w.new_empty((w.shape[0] * n, w.shape[1]))
+        return x.new_empty((*x.shape[:-1], wf.shape[0]), dtype=out_dtype), wf
+    lead = list(x.shape[:-1])
+    lead[dim] *= n
+    return x.new_empty((*lead, w.shape[0] if mode == 2 else w.shape[1]), dtype=out_dtype), x.new_empty((*lead, x.shape[-1]))
+
+
+def _scaled_mm_rs_meta(a, b, sa, sb, mode, dim, out_dtype, group, n):
+    lead = list(a.shape[:-1])
+    lead[dim] //= n
+    return a.new_empty((*lead, b.shape[0] if mode == 0 else b.shape[1]), dtype=out_dtype)
+
+
+for _name, _fn in (("ag_scaled_mm", _ag_scaled_mm), ("scaled_mm_rs", _scaled_mm_rs)):
+    lib.impl(_name, _fn, "CPU")
+    lib.impl(_name, _fn, "CUDA")
+lib.impl("ag_scaled_mm", _ag_scaled_mm_meta, "Meta")
+lib.impl("scaled_mm_rs", _scaled_mm_rs_meta, "Meta")
+
 for _name, _fn in (("ag_mm", _ag_mm), ("mm_rs", _mm_rs)):
     lib.impl(_name, _fn, "CPU")
     lib.impl(_name, _fn, "CUDA")
 lib.impl("ag_mm", _ag_mm_meta, "Meta")
 lib.impl("mm_rs", _mm_rs_meta, "Meta")
 FUSED_OPS = {ops.ag_mm.default, ops.mm_rs.default}
+#: fp8 forms: compositions of a collective and the library's fp8 GEMM (no single-kernel implementation)
+SCALED_FUSED_OPS = {ops.ag_scaled_mm.default, ops.scaled_mm_rs.default}
