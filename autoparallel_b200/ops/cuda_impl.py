@@ -177,8 +177,15 @@ def _scaled_mm(a, b, scale_a, scale_b, trans_b, out_dtype):
     if (sa.ndim == 0) != (sb.ndim == 0):  # the library takes both scales tensor-wise or both row-wise
         sa = sa.expand(a2.shape[0], 1).contiguous() if sa.ndim == 0 else sa
         sb = sb.expand(1, n).contiguous() if sb.ndim == 0 else sb
-    out = torch._scaled_mm(a2, bk, scale_a=sa.contiguous() if sa.ndim else sa, scale_b=sb.contiguous() if sb.ndim else sb,
-                           out_dtype=out_dtype if out_dtype in (torch.bfloat16, torch.float16, torch.float32) else torch.bfloat16)
+    sa = sa.contiguous() if sa.ndim else sa
+    sb = sb.contiguous() if sb.ndim else sb
+    want = out_dtype if out_dtype in (torch.bfloat16, torch.float16, torch.float32) else torch.bfloat16
+    try:
+        out = torch._scaled_mm(a2, bk, scale_a=sa, scale_b=sb, out_dtype=want)
+    except RuntimeError:
+        if want == torch.bfloat16:
+            raise
+        out = torch._scaled_mm(a2, bk, scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)  # row-wise scales: bf16 results only
     return out.view(*lead, n).to(out_dtype)
 
 

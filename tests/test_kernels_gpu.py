@@ -413,3 +413,26 @@ def test_factory_ops_traced_on_cpu_follow_the_module_to_the_gpu():
     finally:
         if own_pg:
             dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("rowwise", [False, True])
+def test_scaled_mm_on_the_gpu_matches_the_cpu_reference(rowwise):
+    """fp8 projection: the CUDA entry (the library's fp8 GEMM, counted as a library call) against the dequantised product."""
+    from autoparallel_b200.ops import cuda_impl
+
+    torch.manual_seed(0)
+    x, w = torch.randn(256, 512), torch.randn(384, 512)
+    f8 = torch.float8_e4m3fn
+    if rowwise:
+        sx = x.abs().amax(-1, keepdim=True) / 448.0
+        sw = w.abs().amax(-1, keepdim=True) / 448.0
+    else:
+        sx, sw = x.abs().max() / 448.0, w.abs().max() / 448.0
+    xq, wq = (x / sx).to(f8), (w / sw).to(f8)
+    ref = (xq.float() * sx) @ (wq.float() * sw).t()
+    before = cuda_impl.library_fallbacks.get("scaled_mm", 0)
+    y = torch.ops.apb200.scaled_mm(xq.cuda(), wq.cuda(), sx.cuda(), sw.cuda(), True, torch.bfloat16)
+    assert cuda_impl.library_fallbacks.get("scaled_mm", 0) == before + 1
+    assert y.shape == (256, 384) and y.dtype == torch.bfloat16
+    err = (y.float().cpu() - ref).abs().max() / ref.abs().max()
+    assert err < 2e-2, err
