@@ -388,6 +388,8 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
 
                 if node.target is aten.native_dropout.default:
                     nn_ = new_g.call_function(rng.sharded_dropout, (new_args[0], new_args[1], new_args[2] if len(new_args) > 2 else True, rng_key))
+                elif node.target in _RANDOM_LIKE_OPS:
+                    nn_ = new_g.call_function(rng.sharded_like, (node.target, rng_key) + tuple(new_args), dict(new_kwargs))
                 else:
                     nn_ = new_g.call_function(rng.sharded_rand, (new_args[0], rng_key, node.target is aten.randn.default), dict(new_kwargs))
             else:
@@ -434,7 +436,9 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
     )
 
 
-_RANDOM_OPS = (aten.native_dropout.default, aten.rand.default, aten.randn.default)
+_RANDOM_LIKE_OPS = (aten.uniform.default, aten.normal_functional.default, aten.bernoulli.p, aten.bernoulli.default,
+                    aten.rand_like.default, aten.randn_like.default)
+_RANDOM_OPS = (aten.native_dropout.default, aten.rand.default, aten.randn.default) + _RANDOM_LIKE_OPS
 
 
 def _sharded_rng_key(node: fx.Node, out_spec, mesh):

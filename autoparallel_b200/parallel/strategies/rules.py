@@ -361,6 +361,15 @@ def _native_dropout(ctx):
     return expand_rows(ctx, [(S(i), S(i), S(i)) for i in range(x.ndim)])
 
 
+@register_rule(aten.uniform.default, aten.normal_functional.default, aten.bernoulli.p, aten.bernoulli.default,
+               aten.rand_like.default, aten.randn_like.default)
+def _random_like(ctx):
+    """Random values with the shape of the input (``x.uniform_()``, ``bernoulli``, ``rand_like``): the output follows any
+    sharding of the input; a sharded output is drawn per shard from the shard's own stream (runtime/rng.py)."""
+    x = ctx.in_vals[0]
+    return expand_rows(ctx, [(S(i), S(i)) for i in range(x.ndim)])
+
+
 @register_rule(aten.native_dropout_backward.default)
 def _native_dropout_bwd(ctx):
     g = ctx.in_vals[0]

@@ -56,3 +56,26 @@ def sharded_dropout(x: torch.Tensor, p: float, train, key):
     noise = torch.rand(x.shape, generator=_generator(x.device, key), dtype=torch.float32, device=x.device)
     mask = noise >= p
     return x * mask.to(x.dtype) * (1.0 / (1.0 - p)), mask
+
+
+def sharded_like(op, key, x: torch.Tensor, *args, **kwargs):
+    """``uniform`` / ``normal`` / ``bernoulli`` / ``rand_like`` / ``randn_like`` on a shard, drawn from the shard's stream."""
+    aten = torch.ops.aten
+    g = _generator(x.device, key)
+    kwargs = {k: v for k, v in kwargs.items() if k != "generator"}
+    if op is aten.uniform.default:
+        lo = args[0] if len(args) > 0 else kwargs.get("from", 0.0)
+        hi = args[1] if len(args) > 1 else kwargs.get("to", 1.0)
+        return torch.empty_like(x).uniform_(lo, hi, generator=g)
+    if op is aten.normal_functional.default:
+        mean = args[0] if len(args) > 0 else kwargs.get("mean", 0.0)
+        std = args[1] if len(args) > 1 else kwargs.get("std", 1.0)
+        return torch.empty_like(x).normal_(mean, std, generator=g)
+    if op is aten.bernoulli.p:
+        p = args[0] if args else kwargs.get("p", 0.5)
+        return torch.empty_like(x).bernoulli_(p, generator=g)
+    if op is aten.bernoulli.default:
+        return torch.bernoulli(x, generator=g)
+    dtype = kwargs.get("dtype") or x.dtype
+    fn = torch.randn if op is aten.randn_like.default else torch.rand
+    return fn(x.shape, generator=g, dtype=dtype, device=x.device)

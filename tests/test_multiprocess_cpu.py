@@ -678,3 +678,52 @@ def test_sharded_random_ops_draw_per_shard_and_replicated_ones_agree():
     assert not same_mask     # the two shards did not repeat one mask
     assert same_noise        # the replicated draw is identical on both ranks
     assert 0.3 < keep < 0.7
+
+
+def _random_like_worker(rank, ws, port, q):
+    """``uniform_`` / ``bernoulli`` / ``randn_like`` of a batch-sharded activation: a rule (no replicate fallback) and per-shard draws."""
+    _init(rank, ws, port)
+    import torch.nn as nn
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Shard
+
+    from autoparallel_b200 import AutoParallel
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = nn.Linear(32, 32, bias=False)
+
+        def forward(self, x):
+            y = self.lin(x)
+            u = torch.empty_like(y).uniform_(-1.0, 1.0)
+            b = torch.bernoulli(torch.full_like(y, 0.5))
+            n = torch.randn_like(y)
+            return y, u, b, n
+
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("dp",))
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.ones(8, 32), mesh) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.add_output_constraints([(Shard(0),)] * 4)
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+        targets = [str(n.target) for n in ap.lowered.gm.graph.nodes if n.op == "call_function"]
+    pm.to_empty(device="cpu")
+    torch.manual_seed(7)
+    _, u, b, n = pm(torch.ones(4, 32))
+    same = []
+    for t in (u, b, n):
+        parts = [torch.empty_like(t) for _ in range(ws)]
+        dist.all_gather(parts, t.contiguous())
+        same.append(bool(torch.equal(parts[0], parts[1])))
+    if rank == 0:
+        q.put((same, sum("sharded_like" in t or "sharded_rand" in t for t in targets), float(u.min().detach()), float(u.max().detach()), float(b.mean().detach()), float(n.std().detach())))
+    dist.destroy_process_group()
+
+
+def test_random_like_ops_follow_the_input_sharding_and_draw_per_shard():
+    same, routed, lo, hi, keep, std = _run(_random_like_worker, 2)
+    assert routed >= 3 and same == [False, False, False]
+    assert -1.0 <= lo < -0.5 and 0.5 < hi <= 1.0 and 0.3 < keep < 0.7 and 0.7 < std < 1.3
