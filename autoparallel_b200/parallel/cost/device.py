@@ -47,6 +47,16 @@ DEVICE_LIMITS = {
     "A10G": DeviceLimit("A10G", 600.0, {_bf16: 70.0, _f16: 70.0, _f32: 31.2, _f64: 0.5}, 0.7, 7.0, 80, 24.0),
     "V100": DeviceLimit("V100", 900.0, {_f16: 125.0, _bf16: 125.0, _f32: 15.7, _f64: 7.8}, 0.7, 7.0, 80, 32.0),
     "T4": DeviceLimit("T4", 300.0, {_f16: 65.0, _bf16: 65.0, _f32: 8.1, _f64: 0.25}, 0.7, 7.0, 40, 16.0),
+    "A30": DeviceLimit("A30", 933.0, {_bf16: 165.0, _f16: 165.0, _f32: 10.3, _f64: 5.2}, 0.7, 7.0, 56, 24.0),
+    "P100": DeviceLimit("P100", 732.0, {_f16: 21.2, _bf16: 21.2, _f32: 10.6, _f64: 5.3}, 0.7, 7.0, 56, 16.0),
+    # planning only (the kernels of this package are sm_100a): nominal figures of other vendors' parts, so that a plan
+    # can be made for them and compared
+    "MI200X": DeviceLimit("MI200X", 3276.8, {_bf16: 383.0, _f16: 383.0, _f32: 47.9, _f64: 47.9}, 0.7, 7.0, 220, 128.0),
+    "MI300X": DeviceLimit("MI300X", 5300.0, {_bf16: 1307.4, _f16: 1307.4, _f32: 163.4, _f64: 81.7}, 0.7, 7.0, 304, 192.0),
+    "MI325X": DeviceLimit("MI325X", 6000.0, {_bf16: 1307.4, _f16: 1307.4, _f32: 163.4, _f64: 81.7}, 0.7, 7.0, 304, 256.0),
+    "MI350X": DeviceLimit("MI350X", 8000.0, {_bf16: 2300.0, _f16: 2300.0, _f32: 144.2, _f64: 72.1}, 0.7, 7.0, 256, 288.0),
+    "MI355X": DeviceLimit("MI355X", 8000.0, {_bf16: 2500.0, _f16: 2500.0, _f32: 157.3, _f64: 78.6}, 0.7, 7.0, 256, 288.0),
+    "Max1550": DeviceLimit("Max1550", 3276.8, {_bf16: 832.0, _f16: 832.0, _f32: 52.0, _f64: 52.0}, 0.7, 7.0, 128, 128.0),
     "cpu": DeviceLimit("cpu", 100.0, {_f32: 2.0, _bf16: 2.0, _f16: 2.0, _f64: 1.0}, 0.7, 1.0, 0, 64.0),
 }
 
@@ -77,7 +87,8 @@ def get_device_limit(device_type: str = "cuda") -> DeviceLimit:
         return DEVICE_LIMITS[env]
     if device_type == "cuda" and torch.cuda.is_available():
         name = torch.cuda.get_device_name(0)
-        for key in ("GB200", "B200", "H200", "H100", "A100", "A10G", "V100", "T4"):
+        for key in ("GB200", "B200", "H200", "H100", "A100", "A10G", "A30", "V100", "P100", "T4",
+                    "MI355X", "MI350X", "MI325X", "MI300X", "MI200X", "Max1550"):
             if key in name:
                 return DEVICE_LIMITS[key]
         return DEVICE_LIMITS["A100"]
