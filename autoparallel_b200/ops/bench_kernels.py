@@ -60,7 +60,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--only", default=None, choices=["gemm_nt", "gemm_tn", "rms_norm_bwd", "xent_bwd"],
+    ap.add_argument("--only", default=None, choices=["gemm_nt", "gemm_tn", "rms_norm_bwd", "xent_bwd", "grouped_mm"],
                     help="run a single small case (what a profiler capture is taken on)")
     ap.add_argument("--pair", default=None, choices=["on", "off"], help="force the CTA-pair (cta_group::2) GEMM kernel on or off")
     ap.add_argument("--gemm-only", action="store_true", help="stop after the GEMM rows")
@@ -98,6 +98,11 @@ def main():
                 (lambda: (torch.randn(M, 4096, device=dev, dtype=bf), torch.randn(4096, 4096, device=dev, dtype=bf)))
             ms, best = time_fn(mk, lambda a, b: L.ops.gemm(a, b, ta, not ta, bf), iters=3, pool=2)
             rec(f"{args.only} 8192x4096x4096", ms, best, flops=2.0 * M * 4096 * 4096)
+        elif args.only == "grouped_mm":
+            E, Me, Ne, Ke = 8, 4096, 1408, 2048  # the expert projection of the MoE configuration at half its token count
+            mk = lambda: (torch.randn(E, Me, Ke, device=dev, dtype=bf) * 0.05, torch.randn(E, Ke, Ne, device=dev, dtype=bf) * 0.05)
+            ms, best = time_fn(mk, lambda a, b: torch.ops.apb200.grouped_mm(a, b, False, bf), iters=3, pool=2)
+            rec(f"grouped_mm {E}x{Me}x{Ne}x{Ke}", ms, best, flops=2.0 * E * Me * Ne * Ke)
         elif args.only == "rms_norm_bwd":
             mk = lambda: (torch.randn(M, 4096, device=dev, dtype=bf), torch.randn(M, 4096, device=dev, dtype=bf), torch.randn(4096, device=dev, dtype=bf), torch.rand(M, device=dev))
             ms, best = time_fn(mk, lambda dy, x, w, r: L.ops.rms_norm_bwd(dy, x, w, r), iters=3, pool=2)
