@@ -294,9 +294,58 @@ def strip_redistribution_points(gm: fx.GraphModule) -> None:
     gm.recompile()
 
 
+def rewrite_means_as_scaled_sums(gm: fx.GraphModule) -> int:
+    """``mean(x, dims)`` -> ``sum(x, dims) * (1 / count)``.
+
+    A mean over a sharded dim has no exact placement of its own (the mean of shard means needs an averaging reduction),
+    so as a single node it forces the operand to be gathered first - ``loss = out.mean()`` on batch-sharded activations
+    would gather every activation.  Written as a sum, the sharded reduction yields ``Partial(sum)``, which a scalar-sized
+    all-reduce completes; the count is that of the global tensor, so the scaling is exact for any sharding.  (The
+    reference reaches the same plans through DTensor's ``Partial("avg")`` strategies.)"""
+    aten = torch.ops.aten
+    g = gm.graph
+    count = 0
+    for n in list(g.nodes):
+        if n.op != "call_function" or n.target not in (aten.mean.default, aten.mean.dim):
+            continue
+        x = n.args[0]
+        xv, ov = _meta_val(x), _meta_val(n)
+        if not isinstance(xv, torch.Tensor) or not isinstance(ov, torch.Tensor) or not ov.dtype.is_floating_point:
+            continue
+        if n.target is aten.mean.default:
+            dims, keepdim = list(range(xv.ndim)), False
+        else:
+            dims = n.args[1] if len(n.args) > 1 else n.kwargs.get("dim")
+            dims = list(range(xv.ndim)) if dims is None or len(dims) == 0 else [d % xv.ndim for d in dims]
+            keepdim = n.args[2] if len(n.args) > 2 else n.kwargs.get("keepdim", False)
+        dtype = n.kwargs.get("dtype")
+        if any(not isinstance(xv.shape[d], int) for d in dims):
+            continue
+        numel = 1
+        for d in dims:
+            numel *= xv.shape[d]
+        if numel == 0:
+            continue
+        with g.inserting_before(n):
+            s = g.call_function(aten.sum.dim_IntList, (x, dims, keepdim), {"dtype": dtype} if dtype is not None else {})
+            _copy_meta(s, n)
+            s.meta["val"] = ov
+            y = g.call_function(aten.mul.Tensor, (s, 1.0 / numel))
+            _copy_meta(y, n)
+            y.meta["val"] = ov
+        n.replace_all_uses_with(y)
+        g.erase_node(n)
+        count += 1
+    if count:
+        g.lint()
+        gm.recompile()
+    return count
+
+
 def canonicalize(gm: fx.GraphModule, *, linear_patterns: bool = True, aliases: bool = True) -> None:
     assert_has_no_collectives(gm)
     cleanup_graph(gm)
+    rewrite_means_as_scaled_sums(gm)
     if linear_patterns:
         rewrite_linear_patterns(gm)
     if aliases:
