@@ -46,12 +46,29 @@ class AdamW(torch.optim.Optimizer):
         self._hyper: dict = {}
         self._graph_keepalive: list = []
 
+    @staticmethod
+    def _even_shards(p) -> bool:
+        """True when every rank holds a shard of the same shape.  Only then do all ranks make the same arena allocations
+        in the same order, which is what keeps the arena's offsets equal on every rank (a peer's shard is read at this
+        rank's own offset)."""
+        spec = getattr(p, "_spec", None)
+        if spec is None:
+            return True
+        shape = list(p.shape)
+        for i, pl in enumerate(spec.placements):
+            if pl.is_shard():
+                n = spec.mesh.size(i)
+                if shape[pl.dim] % n:
+                    return False
+                shape[pl.dim] //= n
+        return True
+
     def _shadow_of(self, p):
         lp = _local(p)
         sh = self._shadows.get(id(p))
         if sh is None or sh.shape != lp.shape or sh.device != lp.device:
             sh = None
-            if self.shadow_arena is not None and lp.is_cuda:
+            if self.shadow_arena is not None and lp.is_cuda and self._even_shards(p):
                 try:
                     sh = self.shadow_arena.alloc(tuple(lp.shape), torch.bfloat16)
                 except MemoryError:

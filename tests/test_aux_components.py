@@ -386,3 +386,27 @@ def test_priced_bucket_plan_on_llama_keeps_numerics_and_reduces_collectives(mesh
         assert t_auto <= t_plain * 1.001
     finally:
         ap.__exit__(None, None, None)
+
+
+def test_arena_shadows_are_only_for_evenly_sharded_parameters(mesh_1d, mesh_2d):
+    """The peer arena hands out offsets by allocation order; a peer's shard is read at the reader's own offset, so only
+    parameters whose shards have the same shape on every rank may live there."""
+    from torch.distributed.tensor import DTensor
+    from torch.distributed.tensor.placement_types import Replicate
+
+    from autoparallel_b200.optim import AdamW
+
+    def dt(shape, mesh, placements):
+        local = list(shape)
+        for i, p in enumerate(placements):
+            if p.is_shard():
+                local[p.dim] = -(-local[p.dim] // mesh.size(i))
+        return DTensor.from_local(torch.zeros(local), mesh, placements, run_check=False, shape=torch.Size(shape),
+                                  stride=torch.zeros(shape).stride())
+
+    assert AdamW._even_shards(torch.zeros(3, 5))                                   # a plain tensor
+    assert AdamW._even_shards(dt((16, 4), mesh_1d, (Shard(0),)))
+    assert not AdamW._even_shards(dt((20, 4), mesh_1d, (Shard(0),)))               # 20 rows over 8 ranks
+    assert AdamW._even_shards(dt((16, 4), mesh_2d, (Shard(0), Shard(0))))          # nested: 16 / 2 / 4
+    assert not AdamW._even_shards(dt((12, 4), mesh_2d, (Shard(0), Shard(0))))      # 12 / 2 = 6, not divisible by 4
+    assert AdamW._even_shards(dt((12, 4), mesh_2d, (Shard(0), Replicate())))
