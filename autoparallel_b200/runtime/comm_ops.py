@@ -253,6 +253,8 @@ def _request_sms(x) -> None:
 
 
 def _ag_start(x, dim, group, n):
+    if x.dtype.is_floating_point and x.dtype.itemsize == 1:
+        return _all_gather(x, dim, group, n)  # float8 moves as bytes (synchronous form)
     dma = _dma_backends.get(group)
     if dma is not None and dma.can_gather(x, dim):
         return dma.all_gather_start(x, dim)
