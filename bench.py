@@ -52,6 +52,9 @@ def parse():
                          "parallelism through local_map and global batch 16 x 4096, 5 = Llama-3 70B on dp=2 x tp=4 with activation "
                          "checkpointing, a parameter-memory budget and global batch 8 x 4096.  3-5 need 8 GPUs and print their own "
                          "metric name, never the headline's")
+    ap.add_argument("--prefetch-discount", type=float, default=None,
+                    help="scale the planner's price of parameter gathers (0 = free: they are prefetched by the copy engines / the "
+                         "overlap scheduler); default: not applied")
     ap.add_argument("--zipf", type=float, default=None, help="config 4: Zipf(s) router bias over the experts (skewed load)")
     ap.add_argument("--ref-mode", default="auto", choices=["auto", "compile", "compile_ac", "eager"],
                     help="reference arm only: auto tries the reference driver's torch.compile backend, then the same with its "
@@ -356,6 +359,8 @@ def run_ours(args):
         else:
             ap.add_parameter_memory_constraint()
         ap.add_input_constraints([(Shard(0),) + (Replicate(),) * (mesh.ndim - 1)] * 2)
+        if args.prefetch_discount is not None:
+            ap.sharding_optimizer.apply_prefetch_discount(args.prefetch_discount)
         ap.optimize_placement()
         from autoparallel_b200.parallel.passes.overlap import OverlapConfig
 
@@ -500,6 +505,7 @@ def run_ours(args):
                 "reserved_sms_for_comm": reserve,
                 "overlap": {"prefetch_depth": ocfg.prefetch_depth, "max_in_flight_gib": round(ocfg.max_in_flight_bytes / 2**30, 2),
                             "pending_reductions": ocfg.max_pending_reductions},
+                "planner_prefetch_discount": args.prefetch_discount,
                 "sm_pairs_yielded_per_collective": yield_pairs if world > 1 and dynamic_tiles else 0,
                 "optimizer_emits_bf16_params": emit,
                 "gemm_stages": cuda_impl.extension().gemm_get_pair_stages(),
