@@ -404,7 +404,7 @@ def test_factory_ops_traced_on_cpu_follow_the_module_to_the_gpu():
             pm = ap.apply_placement()
         pm.to_empty(device="cuda")
         with torch.no_grad():
-            pm.lin.weight.copy_(torch.eye(32))
+            pm.lin.weight.to_local().copy_(torch.eye(32))
         x = torch.rand(16, 32, device="cuda")
         out = pm(x)
         out.backward()
