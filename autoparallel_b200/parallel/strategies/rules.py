@@ -407,6 +407,27 @@ def _index_tensor(ctx):
     return expand_rows(ctx, rows)
 
 
+@register_rule(aten.index_select.default)
+def _index_select(ctx):
+    """``x.index_select(dim, index)``: every other dim of ``x`` shards through; or the 1-D index is sharded and the
+    result is sharded along ``dim`` (``x`` whole along it)."""
+    x = ctx.in_vals[0]
+    dim = ctx.args[1] % max(x.ndim, 1)
+    rows = [(S(d), S(d), R) for d in range(x.ndim) if d != dim]
+    rows.append((S(dim), R, S(0)))
+    return expand_rows(ctx, rows)
+
+
+@register_rule(aten.index_add.default)
+def _index_add(ctx):
+    """``x.index_add(dim, index, source)``: dims other than ``dim`` shard through ``x``, ``source`` and the result
+    alike; a sharded index with the matching slice of ``source`` yields partial sums of a zero-based accumulation only
+    when ``x`` itself is partial, which is not offered."""
+    x = ctx.in_vals[0]
+    dim = ctx.args[1] % max(x.ndim, 1)
+    return expand_rows(ctx, [(S(d), S(d), R, S(d)) for d in range(x.ndim) if d != dim])
+
+
 # ------------------------------------------------------------------------------ view / reshape
 def _view_groups(in_shape, out_shape):
     """Split both shapes into aligned groups with equal element counts:
