@@ -106,7 +106,7 @@ def test_plain_pytorch_llama_traces_into_framework_operators(mesh_1d):
         model = PlainLlama()
     with AutoParallel(model, lambda: torch.randint(0, 256, (8, 32)), mesh_1d) as ap:
         stats = ap.joint.pattern_stats
-        assert stats == {"rms_norm": 5, "swiglu": 2, "attention": 2, "rope": 4, "embedding": 1}
+        assert stats == {"rms_norm": 5, "swiglu": 2, "attention": 2, "rope": 4, "embedding": 1, "scaled_mm": 0}
         t = _targets(ap.gm)
         assert t.count(apb.rms_norm.default) == 5 and t.count(apb.rms_norm_bwd.default) == 5
         assert t.count(apb.attention.default) == 2 and t.count(apb.attention_bwd.default) == 2
