@@ -60,7 +60,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--only", default=None, choices=["gemm_nt", "gemm_tn", "rms_norm_bwd", "xent_bwd", "grouped_mm"],
+    ap.add_argument("--only", default=None, choices=["gemm_nt", "gemm_tn", "rms_norm_bwd", "xent_bwd", "grouped_mm", "attention"],
                     help="run a single small case (what a profiler capture is taken on)")
     ap.add_argument("--pair", default=None, choices=["on", "off"], help="force the CTA-pair (cta_group::2) GEMM kernel on or off")
     ap.add_argument("--gemm-only", action="store_true", help="stop after the GEMM rows")
@@ -98,6 +98,14 @@ def main():
                 (lambda: (torch.randn(M, 4096, device=dev, dtype=bf), torch.randn(4096, 4096, device=dev, dtype=bf)))
             ms, best = time_fn(mk, lambda a, b: L.ops.gemm(a, b, ta, not ta, bf), iters=3, pool=2)
             rec(f"{args.only} 8192x4096x4096", ms, best, flops=2.0 * M * 4096 * 4096)
+        elif args.only == "attention":
+            # causal, 8192 tokens, 32 query / 8 key-value heads of 128: the library kernel, or this package's own forward
+            # kernel when APB200_ATTENTION_FWD=own is set
+            mk = lambda: (torch.randn(1, M, 32, 128, device=dev, dtype=bf), torch.randn(1, M, 8, 128, device=dev, dtype=bf),
+                          torch.randn(1, M, 8, 128, device=dev, dtype=bf))
+            ms, best = time_fn(mk, lambda q, k, v: L.ops.attention(q, k, v, True, 128 ** -0.5), iters=3, pool=2)
+            rec(f"attention fwd causal 8192 32q/8kv ({os.environ.get('APB200_ATTENTION_FWD', 'library')})", ms, best,
+                flops=4.0 * M * M * 4096 * 0.5)
         elif args.only == "grouped_mm":
             E, Me, Ne, Ke = 8, 4096, 1408, 2048  # the expert projection of the MoE configuration at half its token count
             mk = lambda: (torch.randn(E, Me, Ke, device=dev, dtype=bf) * 0.05, torch.randn(E, Ke, Ne, device=dev, dtype=bf) * 0.05)
