@@ -111,7 +111,7 @@ def cleanup_graph(gm: fx.GraphModule) -> None:
             if t in (aten.sum.dim_IntList, aten.mean.dim) and len(n.args) > 1 and n.args[1] is not None and len(n.args[1]) == 0:
                 # an empty dim list means "all dims" to ATen but "no dims" to DTensor's reduction rule
                 src = n.args[0]
-                if _is_tensor_node(src):
+                if _is_tensor_node(src) and src.meta["val"].ndim > 0:  # (a 0-d operand has no dims to list)
                     n.update_arg(1, list(range(src.meta["val"].ndim)))
                     changed = True
             if t in (aten.alias.default, aten.detach.default, aten.lift_fresh_copy.default):

@@ -74,8 +74,26 @@ def _localize_moe_scatter(args, val, lval):
     return args
 
 
+def _localize_group_norm(args, val, lval):
+    # native_group_norm(x, weight, bias, N, C, HxW, groups, eps): N is the batch extent of the (possibly batch-sharded) input
+    x = args[0].meta.get("val") if isinstance(args[0], fx.Node) else None
+    if isinstance(x, torch.Tensor):
+        args[3] = x.shape[0]
+    return args
+
+
+def _localize_group_norm_bwd(args, val, lval):
+    # native_group_norm_backward(dy, x, mean, rstd, weight, N, C, HxW, groups, mask)
+    x = args[1].meta.get("val") if isinstance(args[1], fx.Node) else None
+    if isinstance(x, torch.Tensor):
+        args[5] = x.shape[0]
+    return args
+
+
 # op -> rewrite of integer arguments that describe a global extent (args list, global value, local value)
 _INT_ARG_LOCALIZERS = {
+    aten.native_group_norm.default: _localize_group_norm,
+    aten.native_group_norm_backward.default: _localize_group_norm_bwd,
     torch.ops.apb200.moe_slots.default: _localize_moe_slots,
     torch.ops.apb200.moe_scatter.default: _localize_moe_scatter,
 }
@@ -374,7 +392,7 @@ def lower_to_local_graph(joint: JointGraph, solution: dict[fx.Node, OpSpec], mes
                     if node.target in _STRIDED_FACTORIES:
                         new_args[pos + 1] = _strides_like(list(node.args[pos + 1]), list(lval.shape))
                 new_args = tuple(new_args)
-            if node.target in _INT_ARG_LOCALIZERS and isinstance(lval, torch.Tensor):
+            if node.target in _INT_ARG_LOCALIZERS and isinstance(lval, (torch.Tensor, tuple, list)):
                 new_args = tuple(_INT_ARG_LOCALIZERS[node.target](list(new_args), val, lval))
             from ..strategies.local_map_rules import is_local_map_node, local_map_body
 

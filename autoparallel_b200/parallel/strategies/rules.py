@@ -537,6 +537,55 @@ def _layer_norm(ctx):
     return expand_rows(ctx, rows)
 
 
+@register_rule(aten.max.dim, aten.min.dim)
+def _max_min_dim(ctx):
+    """``x.max(dim)`` / ``x.min(dim)`` -> (values, indices): every dim but the reduced one shards through (renumbered
+    when the reduced dim is dropped).  DTensor's strategy for these describes one output only."""
+    x = ctx.in_vals[0]
+    dim = ctx.args[1] % max(x.ndim, 1)
+    keepdim = bool(ctx.args[2]) if len(ctx.args) > 2 else False
+    rows = []
+    for d in range(x.ndim):
+        if d == dim:
+            continue
+        od = d if keepdim or d < dim else d - 1
+        rows.append((S(od), S(od), S(d)))
+    return expand_rows(ctx, rows)
+
+
+@register_rule(aten.flip.default)
+def _flip(ctx):
+    x = ctx.in_vals[0]
+    flipped = {d % max(x.ndim, 1) for d in ctx.args[1]}
+    return expand_rows(ctx, [(S(d), S(d)) for d in range(x.ndim) if d not in flipped])
+
+
+@register_rule(aten.cumsum.default, aten.cumprod.default, aten.logcumsumexp.default)
+def _scan(ctx):
+    """Prefix scans: every dim but the scanned one may be sharded."""
+    x = ctx.in_vals[0]
+    dim = ctx.args[1] % max(x.ndim, 1)
+    return expand_rows(ctx, [(S(d), S(d)) for d in range(x.ndim) if d != dim])
+
+
+@register_rule(aten.native_group_norm.default)
+def _group_norm(ctx):
+    """(x [N, C, *], weight?, bias?, N, C, HxW, groups, eps) -> (out [N, C, *], mean [N, G], rstd [N, G]): statistics are
+    per sample and group, so the batch dim shards through."""
+    n_extra = len(ctx.in_vals) - 1
+    return expand_rows(ctx, [(S(0), S(0), S(0), S(0)) + (R,) * n_extra])
+
+
+@register_rule(aten.native_group_norm_backward.default)
+def _group_norm_bwd(ctx):
+    """(dy, x, mean, rstd, weight?, N, C, HxW, groups, mask) -> (dx, dw?, db?): batch-sharded operands give the input
+    gradient batch-sharded and partial sums for the affine parameters."""
+    outs = ctx.out_vals
+    n_extra = len(ctx.in_vals) - 4
+    o = [S(0)] + [P if isinstance(v, torch.Tensor) else None for v in outs[1:]]
+    return expand_rows(ctx, [tuple(o) + (S(0), S(0), S(0), S(0)) + (R,) * n_extra])
+
+
 @register_rule(aten.native_layer_norm_backward.default)
 def _layer_norm_bwd(ctx):
     """(dy, x, normalized_shape, mean, rstd, weight?, bias?, mask) -> (dx, dw?, db?)."""
@@ -641,6 +690,37 @@ def _max_pool(ctx):
         return expand_rows(ctx, [])
     n = len(ctx.out_vals) + len(ctx.in_vals)
     return expand_rows(ctx, [(S(0),) * n, (S(1),) * n])  # windows never cross samples or channels
+
+
+@register_rule(aten.avg_pool2d.default, aten.avg_pool2d_backward.default, aten._adaptive_avg_pool2d.default,
+               aten._adaptive_avg_pool2d_backward.default)
+def _avg_pool(ctx):
+    """Average pooling (plain and adaptive, forward and backward): windows never cross samples or channels, so the batch
+    and channel dims of a 4-D operand (the channel dim of a 3-D one) shard through every tensor of the node."""
+    x = ctx.in_vals[0]
+    n = len(ctx.out_vals) + len(ctx.in_vals)
+    if x.ndim == 4:
+        return expand_rows(ctx, [(S(0),) * n, (S(1),) * n])
+    if x.ndim == 3:
+        return expand_rows(ctx, [(S(0),) * n])
+    return expand_rows(ctx, [])
+
+
+@register_rule(aten.any.dims, aten.any.dim, aten.all.dims, aten.all.dim)
+def _any_all(ctx):
+    """Logical reductions over some dims: the surviving dims shard through (no partial form of "or" / "and")."""
+    x = ctx.in_vals[0]
+    dims = ctx.args[1] if len(ctx.args) > 1 else None
+    dims = list(range(x.ndim)) if dims is None else ([dims] if isinstance(dims, int) else list(dims))
+    dims = {d % max(x.ndim, 1) for d in dims}
+    keepdim = bool(ctx.args[2]) if len(ctx.args) > 2 else False
+    rows = []
+    for d in range(x.ndim):
+        if d in dims:
+            continue
+        od = d if keepdim else d - sum(1 for r in dims if r < d)
+        rows.append((S(od), S(d)))
+    return expand_rows(ctx, rows)
 
 
 @register_rule(aten.index_put.default)

@@ -1,0 +1,114 @@
+"""Sharding rules for operators that otherwise run replicated or could not be planned: ``max`` / ``min`` over a dim (two
+outputs), ``flip``, prefix scans, group norm, average pooling, logical reductions.  Each is pinned to a batch split and the
+parallel module is compared with the single-device model on two gloo ranks; a scalar ``.sum()`` must not stall planning."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+import torch.nn as nn
+import torch.nn.functional as F
+from conftest import free_port
+from torch.distributed.tensor.placement_types import Shard
+
+aten = torch.ops.aten
+
+
+class Zoo(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.lin = nn.Linear(16, 16)
+        self.gn = nn.GroupNorm(2, 4)
+
+    def forward(self, x):                       # x [B, 16]
+        y = self.lin(x)
+        mx, arg = y.max(dim=-1)                 # two outputs
+        mn = y.min(dim=1, keepdim=True)[0]
+        sc = y.cumsum(-1) + y.flip(-1) + (y * 0.1 + 1.0).cumprod(-1)
+        img = y.view(-1, 4, 2, 2)
+        g = self.gn(img)
+        pooled = F.avg_pool2d(g, 2).flatten(1) + F.adaptive_avg_pool2d(img, 1).flatten(1)   # [B, 4]
+        flag = (y > 0).any(dim=-1).to(y.dtype) + (y > -10).all(dim=1).to(y.dtype)
+        out = sc.sum(-1) + mx + mn.squeeze(1) + pooled.sum(-1) + flag + arg.to(y.dtype) * 0.0
+        return out                              # [B]
+
+
+PINNED = (aten.max.dim, aten.min.dim, aten.flip.default, aten.cumsum.default, aten.cumprod.default, aten.native_group_norm.default,
+          aten.avg_pool2d.default, aten._adaptive_avg_pool2d.default, aten.any.dim, aten.any.dims, aten.all.dim, aten.all.dims)
+
+
+def _worker(rank, ws, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(ws))
+    dist.init_process_group("gloo", rank=rank, world_size=ws)
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from autoparallel_b200 import AutoParallel
+    from autoparallel_b200.parallel.lower.init_weights import _distribute
+
+    torch.manual_seed(0)
+    ref = Zoo()
+    with torch.device("meta"):
+        m = Zoo()
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("dp",))
+    with AutoParallel(m, lambda: torch.randn(8, 16), mesh) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.add_output_constraints([(Shard(0),)])
+        pinned = set()
+        for n in ap.joint.gm.graph.nodes:
+            if n.op == "call_function" and n.target in PINNED and not n.meta.get("autograd_backward"):
+                v = n.meta["val"]
+                v0 = v[0] if isinstance(v, (tuple, list)) else v
+                if v0.ndim >= 1 and v0.shape[0] == 8:
+                    ap.sharding_optimizer.add_node_constraint(n, (Shard(0),))  # (of a multi-output node: its first output)
+                    pinned.add(str(n.target))
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    pm.to_empty(device="cpu")
+    state = dict(ref.named_parameters())
+    state.update(dict(ref.named_buffers()))
+    with torch.no_grad():
+        for n, t in list(pm.named_parameters()) + list(pm.named_buffers()):
+            t._local_tensor.copy_(_distribute(state[n].detach().clone(), mesh, t.placements)._local_tensor)
+    torch.manual_seed(1)
+    x = torch.randn(8, 16)
+    w = torch.linspace(-1, 1, 8)
+    y = pm(x.chunk(ws, 0)[rank])
+    (y * w.chunk(ws)[rank]).sum().backward()
+    yr = ref(x)
+    (yr * w).sum().backward()
+    err = (y - yr.chunk(ws, 0)[rank]).abs().max().item()
+    g = max((p.grad.full_tensor() - state[n].grad).abs().max().item() for n, p in pm.named_parameters())
+    if rank == 0:
+        q.put((sorted(pinned), err, g))
+    dist.destroy_process_group()
+
+
+def test_batch_split_through_less_common_operators_on_two_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    mp.spawn(_worker, args=(2, free_port(), q), nprocs=2, join=True)
+    pinned, err, grad = q.get()
+    assert len(pinned) >= 8, pinned
+    assert err < 1e-5 and grad < 1e-5
+
+
+def test_sum_of_a_scalar_does_not_stall_planning(mesh_1d):
+    """``loss.sum()`` on a 0-d tensor traces to a reduction over an empty dim list of a tensor without dims; the graph
+    clean-up must leave it alone instead of rewriting it for ever."""
+    from autoparallel_b200 import AutoParallel
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.l = nn.Linear(16, 16)
+
+        def forward(self, x):
+            return F.mse_loss(self.l(x), torch.zeros(x.shape[0], 16)).sum()
+
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.randn(64, 16), mesh_1d) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.optimize_placement()
+        assert ap.lower() is not None
