@@ -667,7 +667,7 @@ def _channel_row(ctx):
 # split would have to combine means and variances across ranks inside the op); with fixed statistics the batch may
 # be split as well.
 @register_rule(aten._native_batch_norm_legit_functional.default, aten._native_batch_norm_legit.default,
-               aten.native_batch_norm.default, aten.native_batch_norm_backward.default)
+               aten._native_batch_norm_legit.no_stats, aten.native_batch_norm.default, aten.native_batch_norm_backward.default)
 def _batch_norm_training(ctx):
     training = next((a for a in ctx.args if isinstance(a, bool)), True)
     rows = [_channel_row(ctx)]
@@ -704,6 +704,113 @@ def _avg_pool(ctx):
     if x.ndim == 3:
         return expand_rows(ctx, [(S(0),) * n])
     return expand_rows(ctx, [])
+
+
+def _pointwise_rows(ctx):
+    """Rows of an elementwise operator with broadcasting: an output dim shards together with the matching dim of every
+    operand that has it in full (aligned from the right); operands that broadcast along it stay whole."""
+    out = ctx.out_vals[0]
+    rows = []
+    for d in range(out.ndim):
+        row = [S(d) if isinstance(v, torch.Tensor) else None for v in ctx.out_vals]
+        for v in ctx.in_vals:
+            vd = d - (out.ndim - v.ndim)
+            row.append(S(vd) if vd >= 0 and v.shape[vd] == out.shape[d] and out.shape[d] != 1 else R)
+        rows.append(tuple(row))
+    return rows
+
+
+@register_rule(aten.hardtanh.default, aten.hardtanh_backward.default, aten.leaky_relu.default, aten.leaky_relu_backward.default,
+               aten.elu.default, aten.elu_backward.default, aten.softplus.default, aten.softplus_backward.default,
+               aten.hardswish.default, aten.hardswish_backward.default, aten.hardsigmoid.default, aten.hardsigmoid_backward.default,
+               aten.mish.default, aten.mish_backward.default, aten.threshold.default, aten.threshold_backward.default,
+               aten.softshrink.default, aten.hardshrink.default, aten.logit.default, aten.special_expm1.default)
+def _pointwise(ctx):
+    """Elementwise activations (and their backward forms) that have no registered strategy."""
+    return expand_rows(ctx, _pointwise_rows(ctx))
+
+
+@register_rule(aten.var_mean.correction, aten.var.correction, aten.std.correction, aten.std_mean.correction)
+def _var_mean(ctx):
+    """Variance / standard deviation (optionally with the mean) over some dims: no partial form, the surviving dims
+    shard through every output."""
+    x = ctx.in_vals[0]
+    kwargs = ctx.kwargs or {}
+    dims = ctx.args[1] if len(ctx.args) > 1 else kwargs.get("dim")
+    dims = list(range(x.ndim)) if dims is None else ([dims] if isinstance(dims, int) else list(dims))
+    dims = {d % max(x.ndim, 1) for d in dims} if dims else set(range(x.ndim))
+    keepdim = bool(kwargs.get("keepdim", False))
+    rows = []
+    for d in range(x.ndim):
+        if d in dims:
+            continue
+        od = d if keepdim else d - sum(1 for r in dims if r < d)
+        rows.append(tuple(S(od) if isinstance(v, torch.Tensor) else None for v in ctx.out_vals) + (S(d),))
+    return expand_rows(ctx, rows)
+
+
+@register_rule(aten.median.dim, aten.nanmedian.dim, aten.mode.default, aten.kthvalue.default, aten.cummax.default, aten.cummin.default)
+def _order_statistic(ctx):
+    """(values, indices) of an order statistic along one dim: every other dim shards through."""
+    x = ctx.in_vals[0]
+    pos = 2 if ctx.op is aten.kthvalue.default else 1
+    dim = (ctx.args[pos] if len(ctx.args) > pos else -1) % max(x.ndim, 1)
+    scan = ctx.op in (aten.cummax.default, aten.cummin.default)
+    keepdim = scan or (bool(ctx.args[pos + 1]) if len(ctx.args) > pos + 1 else False)
+    rows = []
+    for d in range(x.ndim):
+        if d == dim:
+            continue
+        od = d if keepdim or d < dim else d - 1
+        rows.append((S(od), S(od), S(d)))
+    return expand_rows(ctx, rows)
+
+
+@register_rule(aten.searchsorted.Tensor)
+def _searchsorted(ctx):
+    """``searchsorted(sorted_sequence, values)``: with an N-d sequence the leading dims pair up with those of ``values``
+    and shard through; the searched (last) dim of the sequence stays whole."""
+    seq, vals = ctx.in_vals[0], ctx.in_vals[1]
+    if seq.ndim == 1:
+        return expand_rows(ctx, [(S(d), R, S(d)) for d in range(vals.ndim)])
+    return expand_rows(ctx, [(S(d), S(d), S(d)) for d in range(seq.ndim - 1)])
+
+
+@register_rule(aten._cdist_forward.default)
+def _cdist(ctx):
+    """``cdist(x1 [.., P, M], x2 [.., R, M]) -> [.., P, R]``: batch dims shard through both; rows of either side alone."""
+    x1 = ctx.in_vals[0]
+    nb = x1.ndim - 2
+    rows = [(S(d), S(d), S(d)) for d in range(nb)]
+    rows += [(S(nb), S(nb), R), (S(nb + 1), R, S(nb))]
+    return expand_rows(ctx, rows)
+
+
+@register_rule(aten._cdist_backward.default)
+def _cdist_bwd(ctx):
+    """(grad [.., P, R], x1 [.., P, M], x2 [.., R, M], p, cdist [.., P, R]) -> dx1 [.., P, M]: batch dims and the rows of
+    ``x1`` shard through; ``x2`` must be whole along its rows (every row of it contributes to every dx1 row)."""
+    x1 = ctx.in_vals[1]
+    nb = x1.ndim - 2
+    rows = [(S(d), S(d), S(d), S(d), S(d)) for d in range(nb)]
+    rows.append((S(nb), S(nb), S(nb), R, S(nb)))
+    return expand_rows(ctx, rows)
+
+
+@register_rule(aten.diagonal_scatter.default)
+def _diagonal_scatter(ctx):
+    """``diagonal_scatter(x, src, offset, dim1, dim2)``: dims of ``x`` outside the diagonal plane shard through; in ``src``
+    they come first, in order, followed by the diagonal itself."""
+    x = ctx.in_vals[0]
+    d1 = (ctx.args[3] if len(ctx.args) > 3 else 0) % x.ndim
+    d2 = (ctx.args[4] if len(ctx.args) > 4 else 1) % x.ndim
+    rows, k = [], 0
+    for d in range(x.ndim):
+        if d in (d1, d2):
+            continue
+        rows.append((S(d), S(d), S(k)))
+        k += 1
+    return expand_rows(ctx, rows)
 
 
 @register_rule(aten.any.dims, aten.any.dim, aten.all.dims, aten.all.dim)

@@ -112,3 +112,81 @@ def test_sum_of_a_scalar_does_not_stall_planning(mesh_1d):
         ap.add_input_constraints([(Shard(0),)])
         ap.optimize_placement()
         assert ap.lower() is not None
+
+
+class Zoo2(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.lin = nn.Linear(16, 16)
+
+    def forward(self, x):                       # x [B, 16]
+        y = self.lin(x)
+        a = F.hardtanh(y) + F.leaky_relu(y, 0.1) + F.elu(y) + F.softplus(y) + F.hardswish(y) + F.mish(y)
+        var, mean = torch.var_mean(y, dim=-1)
+        sd = y.std(dim=1)
+        med = y.median(dim=-1)[0] + y.kthvalue(3, dim=-1)[0]
+        pos = torch.searchsorted(y.detach().sort(-1)[0], y.detach()).to(y.dtype).sum(-1)
+        m = y.view(-1, 4, 4)
+        dist_ = torch.cdist(m, m + 1.0).sum((1, 2))
+        diag = m.diagonal(dim1=1, dim2=2).sum(-1)
+        return a.sum(-1) + var + mean + sd + med + pos * 0.0 + dist_ + diag
+
+
+PINNED2 = (aten.hardtanh.default, aten.leaky_relu.default, aten.elu.default, aten.softplus.default, aten.hardswish.default,
+           aten.mish.default, aten.var_mean.correction, aten.std.correction, aten.median.dim, aten.kthvalue.default,
+           aten.searchsorted.Tensor, aten._cdist_forward.default, aten.diagonal_scatter.default, aten._cdist_backward.default,
+           aten.hardtanh_backward.default, aten.leaky_relu_backward.default, aten.elu_backward.default)
+
+
+def _worker2(rank, ws, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(ws))
+    dist.init_process_group("gloo", rank=rank, world_size=ws)
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from autoparallel_b200 import AutoParallel
+    from autoparallel_b200.parallel.lower.init_weights import _distribute
+
+    torch.manual_seed(0)
+    ref = Zoo2()
+    with torch.device("meta"):
+        m = Zoo2()
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("dp",))
+    with AutoParallel(m, lambda: torch.randn(8, 16), mesh) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.add_output_constraints([(Shard(0),)])
+        pinned = set()
+        for n in ap.joint.gm.graph.nodes:
+            if n.op == "call_function" and n.target in PINNED2:
+                v = n.meta["val"]
+                v0 = v[0] if isinstance(v, (tuple, list)) else v
+                if v0.ndim >= 1 and v0.shape[0] == 8:
+                    ap.sharding_optimizer.add_node_constraint(n, (Shard(0),))
+                    pinned.add(str(n.target))
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    pm.to_empty(device="cpu")
+    state = dict(ref.named_parameters())
+    with torch.no_grad():
+        for n, t in pm.named_parameters():
+            t._local_tensor.copy_(_distribute(state[n].detach().clone(), mesh, t.placements)._local_tensor)
+    torch.manual_seed(1)
+    x = torch.randn(8, 16)
+    w = torch.linspace(-1, 1, 8)
+    y = pm(x.chunk(ws, 0)[rank])
+    (y * w.chunk(ws)[rank]).sum().backward()
+    yr = ref(x)
+    (yr * w).sum().backward()
+    err = (y - yr.chunk(ws, 0)[rank]).abs().max().item()
+    g = max((p.grad.full_tensor() - state[n].grad).abs().max().item() for n, p in pm.named_parameters())
+    if rank == 0:
+        q.put((sorted(pinned), err, g))
+    dist.destroy_process_group()
+
+
+def test_batch_split_through_activations_statistics_and_distances_on_two_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    mp.spawn(_worker2, args=(2, free_port(), q), nprocs=2, join=True)
+    pinned, err, grad = q.get()
+    assert len(pinned) >= 10, pinned
+    assert err < 1e-4 and grad < 1e-4
