@@ -813,6 +813,59 @@ def _diagonal_scatter(ctx):
     return expand_rows(ctx, rows)
 
 
+@register_rule(aten.adaptive_max_pool2d.default, aten.adaptive_max_pool2d_backward.default, aten.avg_pool3d.default,
+               aten.avg_pool3d_backward.default, aten.max_pool3d_with_indices.default, aten.max_pool3d_with_indices_backward.default,
+               aten._adaptive_avg_pool3d.default, aten._adaptive_avg_pool3d_backward.default, aten.adaptive_max_pool3d.default,
+               aten.adaptive_max_pool3d_backward.default)
+def _pool_nc(ctx):
+    """Pooling over the spatial dims of [N, C, spatial...] operands (forward and backward forms, with or without index
+    outputs): windows never cross samples or channels."""
+    x = ctx.in_vals[0]
+    n = len(ctx.out_vals) + len(ctx.in_vals)
+    if x.ndim >= 4 and all(v.ndim == x.ndim for v in ctx.in_vals):
+        return expand_rows(ctx, [(S(0),) * n, (S(1),) * n])
+    return expand_rows(ctx, [])
+
+
+@register_rule(aten.grid_sampler_2d.default)
+def _grid_sampler(ctx):
+    """``grid_sample(input [N, C, H, W], grid [N, Ho, Wo, 2]) -> [N, C, Ho, Wo]``: samples (input and grid together) or
+    channels (grid whole)."""
+    return expand_rows(ctx, [(S(0), S(0), S(0)), (S(1), S(1), R)])
+
+
+@register_rule(aten.grid_sampler_2d_backward.default)
+def _grid_sampler_bwd(ctx):
+    """(grad, input, grid, ...) -> (dinput, dgrid): per-sample work."""
+    o = tuple(S(0) if isinstance(v, torch.Tensor) else None for v in ctx.out_vals)
+    return expand_rows(ctx, [o + (S(0), S(0), S(0))])
+
+
+@register_rule(aten._fft_r2c.default, aten._fft_c2r.default, aten._fft_c2c.default)
+def _fft(ctx):
+    """Fourier transforms along ``dim``: every other dim shards through."""
+    x = ctx.in_vals[0]
+    dims = {d % max(x.ndim, 1) for d in ctx.args[1]}
+    return expand_rows(ctx, [(S(d), S(d)) for d in range(x.ndim) if d not in dims])
+
+
+@register_rule(aten._embedding_bag.default, aten._embedding_bag_forward_only.default)
+def _embedding_bag(ctx):
+    """(weight [V, D], indices, offsets, ...) -> (out [B, D], offset2bag, bag_size, max_indices): the embedding width may be
+    split (every rank reduces its columns of the same rows); bags are not split - their boundaries are data."""
+    n_in = len(ctx.in_vals)
+    outs = ctx.out_vals
+    row = (S(1),) + tuple(R if isinstance(v, torch.Tensor) else None for v in outs[1:]) + (S(1),) + (R,) * (n_in - 1)
+    return expand_rows(ctx, [row])
+
+
+@register_rule(aten._embedding_bag_backward.default, aten._embedding_bag_dense_backward.default)
+def _embedding_bag_bwd(ctx):
+    """(grad [B, D], indices, ...) -> dweight [V, D]: columns of the gradient give columns of the weight gradient."""
+    n_in = len(ctx.in_vals)
+    return expand_rows(ctx, [(S(1), S(1)) + (R,) * (n_in - 1)])
+
+
 @register_rule(aten.any.dims, aten.any.dim, aten.all.dims, aten.all.dim)
 def _any_all(ctx):
     """Logical reductions over some dims: the surviving dims shard through (no partial form of "or" / "and")."""

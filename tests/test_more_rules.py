@@ -190,3 +190,78 @@ def test_batch_split_through_activations_statistics_and_distances_on_two_ranks()
     pinned, err, grad = q.get()
     assert len(pinned) >= 10, pinned
     assert err < 1e-4 and grad < 1e-4
+
+
+class Zoo3(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.conv = nn.Conv2d(2, 4, 3, padding=1)
+        self.gru = nn.GRU(16, 8, batch_first=True)
+
+    def forward(self, x):                                   # x [B, 2, 4, 4]
+        y = self.conv(x)                                    # [B, 4, 4, 4]
+        p = F.adaptive_max_pool2d(y, 2).flatten(1).sum(-1)
+        v = F.avg_pool3d(y.unsqueeze(1), 2).flatten(1).sum(-1)
+        grid = torch.zeros(x.shape[0], 3, 3, 2) + 0.25
+        s = F.grid_sample(y, grid, align_corners=False).flatten(1).sum(-1)
+        f = torch.fft.rfft(y.flatten(2), dim=-1).abs().flatten(1).sum(-1)
+        seq, _ = self.gru(y.flatten(2))                     # [B, 4, 8]
+        return p + v + s + f + seq.sum((1, 2))
+
+
+PINNED3 = (aten.adaptive_max_pool2d.default, aten.avg_pool3d.default, aten.grid_sampler_2d.default, aten._fft_r2c.default,
+           aten.adaptive_max_pool2d_backward.default, aten.avg_pool3d_backward.default, aten.grid_sampler_2d_backward.default)
+
+
+def _worker3(rank, ws, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(ws))
+    dist.init_process_group("gloo", rank=rank, world_size=ws)
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from autoparallel_b200 import AutoParallel
+    from autoparallel_b200.parallel.lower.init_weights import _distribute
+
+    torch.manual_seed(0)
+    ref = Zoo3()
+    with torch.device("meta"):
+        m = Zoo3()
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("dp",))
+    with AutoParallel(m, lambda: torch.randn(8, 2, 4, 4), mesh) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.add_output_constraints([(Shard(0),)])
+        pinned = set()
+        for n in ap.joint.gm.graph.nodes:
+            if n.op == "call_function" and n.target in PINNED3:
+                v = n.meta["val"]
+                v0 = next(t for t in (v if isinstance(v, (tuple, list)) else [v]) if isinstance(t, torch.Tensor))
+                if v0.ndim >= 1 and v0.shape[0] == 8:
+                    ap.sharding_optimizer.add_node_constraint(n, (Shard(0),))
+                    pinned.add(str(n.target))
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    pm.to_empty(device="cpu")
+    state = dict(ref.named_parameters())
+    with torch.no_grad():
+        for n, t in pm.named_parameters():
+            t._local_tensor.copy_(_distribute(state[n].detach().clone(), mesh, t.placements)._local_tensor)
+    torch.manual_seed(1)
+    x = torch.randn(8, 2, 4, 4)
+    w = torch.linspace(-1, 1, 8)
+    y = pm(x.chunk(ws, 0)[rank])
+    (y * w.chunk(ws)[rank]).sum().backward()
+    yr = ref(x)
+    (yr * w).sum().backward()
+    err = (y - yr.chunk(ws, 0)[rank]).abs().max().item()
+    g = max((p.grad.full_tensor() - state[n].grad).abs().max().item() for n, p in pm.named_parameters())
+    if rank == 0:
+        q.put((sorted(pinned), err, g))
+    dist.destroy_process_group()
+
+
+def test_batch_split_through_pooling_sampling_fft_and_a_gru_on_two_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    mp.spawn(_worker3, args=(2, free_port(), q), nprocs=2, join=True)
+    pinned, err, grad = q.get()
+    assert len(pinned) >= 4, pinned
+    assert err < 1e-4 and grad < 1e-4
