@@ -72,6 +72,8 @@ def worker(rank, ws, names, port, mesh_shape):
             for n, p in pm.named_parameters():
                 if p.grad is None: continue
                 g = p.grad.full_tensor() * (1.0 / dp); rg = state[n].grad
+                if rg is None:  # a parameter the single-device model's loss does not reach: its gradient here must be zero
+                    rg = torch.zeros_like(g)
                 e = ((g - rg).abs().max() / (rg.abs().max() + 1e-6)).item()
                 if e > worst: worst, who = e, n
             if rank == 0: print(f"{name:12s} out {err:.2e} grad {worst:.2e} ({who})", flush=True)

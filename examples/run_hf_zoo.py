@@ -91,12 +91,62 @@ ZOO = {
                                                     pad_token_id=0, bos_token_id=1, eos_token_id=2, decoder_start_token_id=1)),
     "distilbert": ("masked-lm", lambda T: T.DistilBertConfig(dim=D, n_layers=L, n_heads=H, hidden_dim=4 * D, vocab_size=V,
                                                              max_position_embeddings=512)),
+    # further families: decoders, encoders, seq2seq and vision models with less common building blocks (grouped linear layers,
+    # relative-position attention, shifted windows, depthwise convolutions, spatial-reduction attention, pooling mixers)
+    "openai_gpt": _dec("OpenAIGPTConfig", n_embd=D, n_layer=L, n_head=H, vocab_size=V, n_positions=512),
+    "ctrl": _dec("CTRLConfig", n_embd=D, n_layer=L, n_head=H, dff=4 * D, vocab_size=V, n_positions=512),
+    "glm": _dec("GlmConfig", hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=4,
+                head_dim=32, vocab_size=V, max_position_embeddings=512, pad_token_id=0),
+    "nemotron": _dec("NemotronConfig", hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H,
+                     num_key_value_heads=4, head_dim=32, vocab_size=V, max_position_embeddings=512),
+    "helium": _dec("HeliumConfig", hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=4,
+                   head_dim=32, vocab_size=V, max_position_embeddings=512),
+    "smollm3": _dec("SmolLM3Config", pad_token_id=0, hidden_size=D, intermediate_size=704, num_hidden_layers=L, num_attention_heads=H,
+                    num_key_value_heads=4, vocab_size=V, max_position_embeddings=512),
+    "biogpt": _dec("BioGptConfig", hidden_size=D, num_hidden_layers=L, num_attention_heads=H, intermediate_size=4 * D, vocab_size=V,
+                   max_position_embeddings=512),
+    "xglm": _dec("XGLMConfig", d_model=D, num_layers=L, attention_heads=H, ffn_dim=4 * D, vocab_size=V, max_position_embeddings=512),
+    "mt5": ("seq2seq", lambda T: T.MT5Config(d_model=D, d_ff=4 * D, num_layers=L, num_decoder_layers=L, num_heads=H, d_kv=D // H, vocab_size=V)),
+    "mbart": ("seq2seq", lambda T: T.MBartConfig(d_model=D, encoder_layers=L, decoder_layers=L, encoder_attention_heads=H,
+                                                 decoder_attention_heads=H, encoder_ffn_dim=4 * D, decoder_ffn_dim=4 * D, vocab_size=V,
+                                                 max_position_embeddings=512)),
+    "pegasus": ("seq2seq", lambda T: T.PegasusConfig(d_model=D, encoder_layers=L, decoder_layers=L, encoder_attention_heads=H,
+                                                     decoder_attention_heads=H, encoder_ffn_dim=4 * D, decoder_ffn_dim=4 * D, vocab_size=V,
+                                                     max_position_embeddings=512)),
+    "marian": ("seq2seq", lambda T: T.MarianConfig(d_model=D, encoder_layers=L, decoder_layers=L, encoder_attention_heads=H,
+                                                   decoder_attention_heads=H, encoder_ffn_dim=4 * D, decoder_ffn_dim=4 * D, vocab_size=V,
+                                                   max_position_embeddings=512, pad_token_id=0, decoder_start_token_id=0)),
+    "deberta_v2": ("masked-lm", lambda T: T.DebertaV2Config(hidden_size=D, num_hidden_layers=L, num_attention_heads=H,
+                                                            intermediate_size=4 * D, vocab_size=V, max_position_embeddings=512)),
+    "mobilebert": ("masked-lm", lambda T: T.MobileBertConfig(hidden_size=D, embedding_size=128, num_hidden_layers=L, num_attention_heads=4,
+                                                             intermediate_size=4 * D, intra_bottleneck_size=128, vocab_size=V,
+                                                             max_position_embeddings=512)),
+    "squeezebert": ("masked-lm", lambda T: T.SqueezeBertConfig(hidden_size=D, embedding_size=D, num_hidden_layers=L, num_attention_heads=H,
+                                                               intermediate_size=4 * D, vocab_size=V, max_position_embeddings=512,
+                                                               q_groups=2, k_groups=2, v_groups=2, post_attention_groups=1,
+                                                               intermediate_groups=2, output_groups=2)),
+    "xlm_roberta": ("masked-lm", lambda T: T.XLMRobertaConfig(hidden_size=D, num_hidden_layers=L, num_attention_heads=H,
+                                                              intermediate_size=4 * D, vocab_size=V, max_position_embeddings=514)),
+    "mpnet": ("masked-lm", lambda T: T.MPNetConfig(hidden_size=D, num_hidden_layers=L, num_attention_heads=H, intermediate_size=4 * D,
+                                                   vocab_size=V, max_position_embeddings=514)),
+    "roformer": ("masked-lm", lambda T: T.RoFormerConfig(hidden_size=D, embedding_size=D, num_hidden_layers=L, num_attention_heads=H,
+                                                         intermediate_size=4 * D, vocab_size=V, max_position_embeddings=512)),
+    "beit": ("image-cls", lambda T: T.BeitConfig(hidden_size=D, num_hidden_layers=L, num_attention_heads=H, intermediate_size=4 * D,
+                                                 image_size=64, patch_size=8, num_labels=16)),
+    "swin": ("image-cls", lambda T: T.SwinConfig(image_size=64, patch_size=4, embed_dim=32, depths=[1, 1], num_heads=[2, 4], window_size=4,
+                                                 num_labels=16)),
+    "mobilenet_v2": ("image-cls", lambda T: T.MobileNetV2Config(image_size=64, num_labels=16, depth_multiplier=0.35)),
+    "regnet": ("image-cls", lambda T: T.RegNetConfig(embedding_size=32, hidden_sizes=[32, 64], depths=[1, 1], groups_width=8, num_labels=16)),
+    "segformer": ("image-cls", lambda T: T.SegformerConfig(num_encoder_blocks=2, depths=[1, 1], sr_ratios=[2, 1], hidden_sizes=[32, 64],
+                                                           patch_sizes=[7, 3], strides=[4, 2], num_attention_heads=[1, 2], num_labels=16)),
+    "poolformer": ("image-cls", lambda T: T.PoolFormerConfig(num_encoder_blocks=2, depths=[1, 1], hidden_sizes=[32, 64], patch_sizes=[7, 3],
+                                                             strides=[4, 2], padding=[2, 1], num_labels=16)),
 }
 
 
 # LayerDrop draws a random number per layer and branches on it in Python while training: not capturable as one
 # graph.  These families are planned in eval mode (the branch is skipped; dropout is off).
-EVAL_MODE = {"opt", "bart", "whisper"}
+EVAL_MODE = {"opt", "bart", "whisper", "biogpt", "xglm", "mbart", "pegasus", "marian"}
 
 
 def plan_one(name, mesh, batch, seq, execute, bf16=False, uneven=False):

@@ -13,7 +13,8 @@ pytest.importorskip("transformers")
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-@pytest.mark.parametrize("name", ["gpt2", "gptj", "falcon", "t5", "bert", "gemma2", "opt", "vit", "resnet"])
+@pytest.mark.parametrize("name", ["gpt2", "gptj", "falcon", "t5", "bert", "gemma2", "opt", "vit", "resnet", "swin", "deberta_v2",
+                                  "mobilenet_v2", "marian"])
 def test_family_plans_lowers_and_executes(mesh_1d, name):
     from examples.run_hf_zoo import plan_one
 
