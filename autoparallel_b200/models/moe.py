@@ -95,32 +95,19 @@ def _expert_region(x, gate_w, gate_idx, w1, w3, w2, *, ep_axis: str, num_experts
     """Runs on local shards.  x [T, d] tokens of this rank; gate_w / gate_idx [T, k]; w1, w3
     [E_loc, d, h], w2 [E_loc, h, d] local experts.  Returns [T, d]."""
     T, d = x.shape
-    k = gate_idx.shape[1]
     n = axis_size(ep_axis)
     e_loc = num_experts // n
-    flat_e = gate_idx.reshape(-1)                                   # [T*k] expert of each assignment
-    order = torch.argsort(flat_e, stable=True)
-    sorted_e = flat_e[order]
-    counts = torch.zeros(num_experts, dtype=torch.long, device=x.device).index_add(0, flat_e, torch.ones_like(flat_e))
-    starts = torch.cumsum(counts, 0) - counts
-    pos_sorted = torch.arange(T * k, device=x.device) - starts[sorted_e]
-    pos = torch.empty_like(pos_sorted)
-    pos[order] = pos_sorted                                         # slot of each assignment inside its expert
-    keep = pos < capacity
-    slot = torch.where(keep, flat_e * capacity + pos, torch.full_like(pos, num_experts * capacity))
-    tok = torch.arange(T * k, device=x.device) // k
-    send = x.new_zeros(num_experts * capacity + 1, d)
-    send = send.index_copy(0, slot, x[tok])[:-1]                    # [E*C, d]; dropped rows land in the spare row
-    send = send.view(n, e_loc * capacity, d)
+    # slot of every (token, choice) in this rank's [E * C] send buffer (E * C = beyond the capacity: dropped), the rows
+    # written expert-major, and after the expert FFN read back weighted by the gate: three operators with kernels and
+    # gradients of their own (ops/moe_ops.py) instead of a sort, a dozen index operators and a [T * k, d] intermediate
+    slot = K.moe_slots(gate_idx, num_experts, capacity, 1)
+    send = K.moe_dispatch(x, slot, num_experts, capacity, 1)        # [E, 1, C, d]
     recv = all_to_all(send.reshape(n * e_loc * capacity, d), ep_axis, 0, 0).view(n, e_loc, capacity, d)
     h = recv.permute(1, 0, 2, 3).reshape(e_loc, n * capacity, d)    # expert-major
     y = K.grouped_mm(K.swiglu(K.grouped_mm(h, w1), K.grouped_mm(h, w3)), w2)   # [E_loc, n*C, d]: one grouped GEMM launch each
     back = y.view(e_loc, n, capacity, d).permute(1, 0, 2, 3).reshape(n * e_loc * capacity, d)
     got = all_to_all(back, ep_axis, 0, 0)                           # [E*C, d] in this rank's slot order
-    got = torch.cat([got, got.new_zeros(1, d)], 0)
-    per_assign = got[slot] * (gate_w.reshape(-1, 1) * keep.unsqueeze(1)).to(got.dtype)
-    out = torch.zeros_like(x).index_add(0, tok, per_assign)
-    return out
+    return K.moe_combine(got.view(num_experts, 1, capacity, d), slot, gate_w)
 
 
 class MLAttention(nn.Module):

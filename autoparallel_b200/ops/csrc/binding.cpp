@@ -40,6 +40,14 @@ int apb_embedding_bwd(const void* dy, const long long* ids, float* out_f32, long
                       cudaStream_t st);
 int apb_embedding_fwd(const void* weight, const long long* ids, void* out, long long tokens, int D, long long num_rows,
                       int is_bf16, cudaStream_t st);
+int apb_moe_slots_max_experts(int threads);
+int apb_moe_slots(const long long* gate_idx, long long* slot, int num_blocks, int per_block, int E, int C, cudaStream_t st);
+int apb_moe_scatter(const void* src, const long long* slot, const float* w, void* buf, long long T, int k, int d, int E, int C, int nb,
+                    int is_bf16, cudaStream_t st);
+int apb_moe_gather(const void* buf, const long long* slot, const float* w, void* out, long long T, int k, int d, int E, int C, int nb,
+                   int is_bf16, cudaStream_t st);
+int apb_moe_gate_grad(const void* buf, const long long* slot, const void* g, float* dw, long long T, int k, int d, int E, int C, int nb,
+                      int is_bf16, cudaStream_t st);
 int apb_symm_header_bytes();
 int apb_symm_wait_probe(const uint32_t* flag, unsigned target, unsigned limit_ms, uint32_t* status, cudaStream_t st);
 int apb_symm_collective(int mode, const unsigned long long* peer_ptrs, int rank, int n, unsigned epoch, const void* src,
@@ -213,6 +221,65 @@ void embedding_bwd(const at::Tensor& dy, const at::Tensor& ids, at::Tensor& out_
         "apb_embedding_bwd");
 }
 
+// Mixture-of-experts dispatch (ops/moe_ops.py): gate_idx / slot [T, k] int64, w [T, k] fp32, buf [E, nb, C, d], src / out / g [T, d].
+static void moe_check(const at::Tensor& x, const char* what) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous(), what, ": contiguous CUDA tensor expected");
+}
+
+int64_t moe_slots_max_experts(int64_t per_block) {
+  int threads = per_block >= 1024 ? 1024 : (int)((per_block + 31) / 32) * 32;
+  return apb_moe_slots_max_experts(threads);
+}
+
+void moe_slots(const at::Tensor& gate_idx, at::Tensor& slot, int64_t E, int64_t C, int64_t nb) {
+  c10::cuda::CUDAGuard g(gate_idx.device());
+  moe_check(gate_idx, "moe_slots");
+  moe_check(slot, "moe_slots");
+  TORCH_CHECK(gate_idx.scalar_type() == at::kLong && slot.scalar_type() == at::kLong && gate_idx.dim() == 2 &&
+                  gate_idx.numel() == slot.numel() && nb > 0 && gate_idx.size(0) % nb == 0,
+              "moe_slots: int64 [T, k] with T a multiple of the block count");
+  const int64_t per_block = gate_idx.size(0) / nb * gate_idx.size(1);
+  check(apb_moe_slots((const long long*)gate_idx.data_ptr<int64_t>(), (long long*)slot.data_ptr<int64_t>(), (int)nb, (int)per_block,
+                      (int)E, (int)C, stream()),
+        "apb_moe_slots");
+}
+
+void moe_scatter(const at::Tensor& src, const at::Tensor& slot, const at::Tensor& w, at::Tensor& buf, int64_t E, int64_t C, int64_t nb) {
+  c10::cuda::CUDAGuard g(src.device());
+  moe_check(src, "moe_scatter"); moe_check(slot, "moe_scatter"); moe_check(w, "moe_scatter"); moe_check(buf, "moe_scatter");
+  TORCH_CHECK(src.dim() == 2 && slot.dim() == 2 && slot.scalar_type() == at::kLong && w.scalar_type() == at::kFloat &&
+                  w.numel() == slot.numel() && slot.size(0) == src.size(0) && buf.scalar_type() == src.scalar_type() &&
+                  buf.numel() == E * nb * C * src.size(1),
+              "moe_scatter: src [T, d], slot [T, k] int64, w [T, k] fp32, buf [E, nb, C, d] of src's dtype");
+  check(apb_moe_scatter(src.data_ptr(), (const long long*)slot.data_ptr<int64_t>(), w.data_ptr<float>(), buf.data_ptr(), src.size(0),
+                        (int)slot.size(1), (int)src.size(1), (int)E, (int)C, (int)nb, is_bf16(src), stream()),
+        "apb_moe_scatter");
+}
+
+void moe_gather(const at::Tensor& buf, const at::Tensor& slot, const at::Tensor& w, at::Tensor& out) {
+  c10::cuda::CUDAGuard g(buf.device());
+  moe_check(buf, "moe_gather"); moe_check(slot, "moe_gather"); moe_check(w, "moe_gather"); moe_check(out, "moe_gather");
+  TORCH_CHECK(buf.dim() == 4 && slot.dim() == 2 && slot.scalar_type() == at::kLong && w.scalar_type() == at::kFloat &&
+                  w.numel() == slot.numel() && out.dim() == 2 && out.size(0) == slot.size(0) && out.size(1) == buf.size(3) &&
+                  out.scalar_type() == buf.scalar_type(),
+              "moe_gather: buf [E, nb, C, d], slot [T, k] int64, w [T, k] fp32, out [T, d] of buf's dtype");
+  check(apb_moe_gather(buf.data_ptr(), (const long long*)slot.data_ptr<int64_t>(), w.data_ptr<float>(), out.data_ptr(), slot.size(0),
+                       (int)slot.size(1), (int)buf.size(3), (int)buf.size(0), (int)buf.size(2), (int)buf.size(1), is_bf16(buf), stream()),
+        "apb_moe_gather");
+}
+
+void moe_gate_grad(const at::Tensor& buf, const at::Tensor& slot, const at::Tensor& g_, at::Tensor& dw) {
+  c10::cuda::CUDAGuard g(buf.device());
+  moe_check(buf, "moe_gate_grad"); moe_check(slot, "moe_gate_grad"); moe_check(g_, "moe_gate_grad"); moe_check(dw, "moe_gate_grad");
+  TORCH_CHECK(buf.dim() == 4 && slot.dim() == 2 && slot.scalar_type() == at::kLong && g_.dim() == 2 && g_.size(0) == slot.size(0) &&
+                  g_.size(1) == buf.size(3) && g_.scalar_type() == buf.scalar_type() && dw.scalar_type() == at::kFloat &&
+                  dw.numel() == slot.numel(),
+              "moe_gate_grad: buf [E, nb, C, d], slot [T, k] int64, g [T, d] of buf's dtype, dw [T, k] fp32");
+  check(apb_moe_gate_grad(buf.data_ptr(), (const long long*)slot.data_ptr<int64_t>(), g_.data_ptr(), dw.data_ptr<float>(), slot.size(0),
+                          (int)slot.size(1), (int)buf.size(3), (int)buf.size(0), (int)buf.size(2), (int)buf.size(1), is_bf16(buf), stream()),
+        "apb_moe_gate_grad");
+}
+
 void adamw(const at::Tensor& table, const at::Tensor& chunks, int64_t num_chunks, double lr, double b1, double b2, double eps,
            double wd, double bc1, double bc2, double grad_scale, const c10::optional<at::Tensor>& hyper) {
   c10::cuda::CUDAGuard g(table.device());
@@ -354,6 +421,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_bwd", &embedding_bwd);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("adamw", &adamw);
+  m.def("moe_slots_max_experts", &moe_slots_max_experts);
+  m.def("moe_slots", &moe_slots);
+  m.def("moe_scatter", &moe_scatter);
+  m.def("moe_gather", &moe_gather);
+  m.def("moe_gate_grad", &moe_gate_grad);
   m.def("symm_header_bytes", &symm_header_bytes);
   m.def("symm_wait_probe", &symm_wait_probe);
   m.def("symm_collective", &symm_collective);

@@ -220,6 +220,68 @@ def _grouped_mm_wgrad(a, b, out_dtype):
     return c
 
 
+# ----------------------------------------------------------------------------------- mixture-of-experts dispatch
+_MOE_KERNELS = os.environ.get("APB200_MOE_KERNELS", "1") != "0"
+
+
+def _moe_ok(*ts) -> bool:
+    return _MOE_KERNELS and all(t.is_cuda for t in ts)
+
+
+def _moe_slots(gate_idx, num_experts, capacity, num_blocks):
+    from . import moe_ops
+
+    T, k = gate_idx.shape
+    if not (_moe_ok(gate_idx) and gate_idx.dtype == torch.long and T % num_blocks == 0 and T > 0
+            and num_experts <= _C.moe_slots_max_experts(T // num_blocks * k) and num_experts * capacity < 2**31):
+        _fallback("moe_index", f"moe_slots {tuple(gate_idx.shape)} E={num_experts}")
+        return moe_ops._moe_slots(gate_idx, num_experts, capacity, num_blocks)
+    slot = torch.empty_like(gate_idx, memory_format=torch.contiguous_format)
+    _C.moe_slots(gate_idx.contiguous(), slot, num_experts, capacity, num_blocks)
+    _count()
+    return slot
+
+
+def _moe_scatter(src, slot, w, num_experts, capacity, num_blocks):
+    from . import moe_ops
+
+    if not (_moe_ok(src, slot, w) and src.dtype in (torch.bfloat16, torch.float32) and src.dim() == 2 and src.shape[0] % num_blocks == 0
+            and src.shape[0] > 0):
+        _fallback("moe_index", f"moe_scatter {tuple(src.shape)} {src.dtype}")
+        return moe_ops._moe_scatter(src, slot, w, num_experts, capacity, num_blocks)
+    buf = torch.zeros((num_experts, num_blocks, capacity, src.shape[1]), dtype=src.dtype, device=src.device)
+    # the gate weight is applied in the operand's precision (as the reference formula does), then widened for the kernel
+    _C.moe_scatter(src.contiguous(), slot.contiguous(), w.to(src.dtype).float().contiguous(), buf, num_experts, capacity, num_blocks)
+    _count()
+    return buf
+
+
+def _moe_gather(buf, slot, w):
+    from . import moe_ops
+
+    if not (_moe_ok(buf, slot, w) and buf.dtype in (torch.bfloat16, torch.float32) and buf.dim() == 4 and slot.shape[0] % buf.shape[1] == 0
+            and slot.shape[0] > 0):
+        _fallback("moe_index", f"moe_gather {tuple(buf.shape)} {buf.dtype}")
+        return moe_ops._moe_gather(buf, slot, w)
+    out = torch.empty((slot.shape[0], buf.shape[3]), dtype=buf.dtype, device=buf.device)
+    _C.moe_gather(buf.contiguous(), slot.contiguous(), w.to(buf.dtype).float().contiguous(), out)
+    _count()
+    return out
+
+
+def _moe_gate_grad(buf, slot, g):
+    from . import moe_ops
+
+    if not (_moe_ok(buf, slot, g) and buf.dtype in (torch.bfloat16, torch.float32) and buf.dim() == 4 and g.dtype == buf.dtype
+            and slot.shape[0] % buf.shape[1] == 0 and slot.shape[0] > 0):
+        _fallback("moe_index", f"moe_gate_grad {tuple(buf.shape)} {buf.dtype}")
+        return moe_ops._moe_gate_grad(buf, slot, g)
+    dw = torch.empty(slot.shape, dtype=torch.float32, device=buf.device)
+    _C.moe_gate_grad(buf.contiguous(), slot.contiguous(), g.contiguous(), dw)
+    _count()
+    return dw
+
+
 # ----------------------------------------------------------------------------------- pointwise etc.
 def _dtype_cast(x, dtype):
     if x.dtype == dtype:
@@ -406,6 +468,10 @@ def _register() -> None:
     R("scaled_mm", _scaled_mm)
     R("mm_wgrad", _mm_wgrad)
     R("grouped_mm", _grouped_mm)
+    R("moe_slots", _moe_slots)
+    R("moe_scatter", _moe_scatter)
+    R("moe_gather", _moe_gather)
+    R("moe_gate_grad", _moe_gate_grad)
     R("grouped_mm_wgrad", _grouped_mm_wgrad)
     R("dtype_cast", _dtype_cast)
     R("rms_norm", _rms_norm)

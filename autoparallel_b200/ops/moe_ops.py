@@ -27,7 +27,7 @@ from __future__ import annotations
 
 import torch
 
-from .library import _ag, _make_cuda_entry, lib, ops, reference_impls, register_cuda_impl
+from .library import _ag, _make_cuda_entry, lib, ops, reference_impls
 
 lib.define("moe_slots(Tensor gate_idx, int num_experts, int capacity, int num_blocks) -> Tensor")
 lib.define("moe_scatter(Tensor src, Tensor slot, Tensor w, int num_experts, int capacity, int num_blocks) -> Tensor")
@@ -124,9 +124,8 @@ for _name, _fn in _REFS.items():
     lib.impl(_name, _META[_name], "Meta")
     lib.impl(_name, _make_cuda_entry(_name), "CUDA")
     reference_impls[_name] = _fn
-# the index-shuffling ops run as PyTorch index kernels on the GPU too; the GEMMs get their own kernel
-for _name in ("moe_slots", "moe_scatter", "moe_gather", "moe_gate_grad"):
-    register_cuda_impl(_name, _REFS[_name])
+# On a GPU every operator above resolves to a kernel wrapper of ``ops/cuda_impl.py`` (``csrc/moe_kernels.cu`` for the four index
+# operators, the grouped tcgen05 GEMM for the products); the formulas in this file are their CPU semantics and the GPU tests' oracle.
 
 
 # ------------------------------------------------------------------------------------ autograd
@@ -181,7 +180,7 @@ def moe_slots(gate_idx, num_experts: int, capacity: int, num_blocks: int):
 
 def moe_dispatch(x, slot, num_experts: int, capacity: int, num_blocks: int):
     """Tokens into per-(expert, block) buffers: ``[T, d] -> [E, num_blocks, capacity, d]``."""
-    return ops.moe_scatter(x, slot, torch.ones(slot.shape, dtype=x.dtype, device=x.device), num_experts, capacity, num_blocks)
+    return ops.moe_scatter(x, slot, x.new_ones(slot.shape), num_experts, capacity, num_blocks)
 
 
 def moe_combine(y, slot, gate_w):

@@ -436,3 +436,34 @@ def test_scaled_mm_on_the_gpu_matches_the_cpu_reference(rowwise):
     assert y.shape == (256, 384) and y.dtype == torch.bfloat16
     err = (y.float().cpu() - ref).abs().max() / ref.abs().max()
     assert err < 2e-2, err
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("T,k,E,C,nb,d", [(64, 2, 8, 5, 2, 48), (4096, 8, 64, 700, 4, 256), (96, 3, 7, 100, 1, 40)])
+def test_moe_dispatch_kernels_match_the_cpu_formulas(K, dtype, T, k, E, C, nb, d):
+    """moe_slots / moe_scatter / moe_gather / moe_gate_grad (csrc/moe_kernels.cu) against the formulas of ops/moe_ops.py,
+    with capacities tight enough to drop assignments in the first case."""
+    from autoparallel_b200.ops import cuda_impl, moe_ops  # noqa: F401
+
+    torch.manual_seed(0)
+    gi = torch.stack([torch.randperm(E)[:k] for _ in range(T)])
+    src = torch.randn(T, d).to(dtype)
+    w = torch.rand(T, k)
+    g = torch.randn(T, d).to(dtype)
+    before = cuda_impl.library_fallbacks.get("moe_index", 0)
+    ops = torch.ops.apb200
+    slot_ref = moe_ops._moe_slots(gi, E, C, nb)
+    slot = ops.moe_slots(gi.cuda(), E, C, nb)
+    assert torch.equal(slot.cpu(), slot_ref)
+    buf_ref = moe_ops._moe_scatter(src, slot_ref, w, E, C, nb)
+    buf = ops.moe_scatter(src.cuda(), slot, w.cuda(), E, C, nb)
+    assert buf.shape == buf_ref.shape and torch.equal(buf.cpu(), buf_ref)
+    out_ref = moe_ops._moe_gather(buf_ref.float(), slot_ref, w.to(dtype).float())
+    out = ops.moe_gather(buf, slot, w.cuda())
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    assert torch.allclose(out.float().cpu(), out_ref, rtol=tol, atol=tol)
+    dw_ref = moe_ops._moe_gate_grad(buf_ref, slot_ref, g)
+    dw = ops.moe_gate_grad(buf, slot, g.cuda())
+    assert dw.dtype == torch.float32 and torch.allclose(dw.cpu(), dw_ref, rtol=1e-3, atol=1e-3 * d ** 0.5)
+    assert cuda_impl.library_fallbacks.get("moe_index", 0) == before  # the kernels ran, not the composite formulas
+    cuda_impl.check_status()
