@@ -60,7 +60,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--only", default=None, choices=["gemm_nt", "gemm_tn", "rms_norm_bwd", "xent_bwd", "grouped_mm", "attention"],
+    ap.add_argument("--only", default=None, choices=["gemm_nt", "gemm_tn", "rms_norm_bwd", "xent_bwd", "grouped_mm", "attention", "moe_dispatch"],
                     help="run a single small case (what a profiler capture is taken on)")
     ap.add_argument("--pair", default=None, choices=["on", "off"], help="force the CTA-pair (cta_group::2) GEMM kernel on or off")
     ap.add_argument("--gemm-only", action="store_true", help="stop after the GEMM rows")
@@ -106,6 +106,28 @@ def main():
             ms, best = time_fn(mk, lambda q, k, v: L.ops.attention(q, k, v, True, 128 ** -0.5), iters=3, pool=2)
             rec(f"attention fwd causal 8192 32q/8kv ({os.environ.get('APB200_ATTENTION_FWD', 'library')})", ms, best,
                 flops=4.0 * M * M * 4096 * 0.5)
+        elif args.only == "moe_dispatch":
+            # the dispatch of the MoE configuration on one rank: 8192 tokens, top-8 of 64 experts, capacity factor 1.25, d = 2048;
+            # this package's kernels against the index-operator formulas they replace (ops/moe_ops.py)
+            from autoparallel_b200.ops import moe_ops
+
+            T_, k_, E_, d_ = 8192, 8, 64, 2048
+            C_ = int(1.25 * T_ * k_ / E_)
+            gi = torch.stack([torch.randperm(E_, device=dev)[:k_] for _ in range(T_)])
+            x = torch.randn(T_, d_, device=dev, dtype=bf)
+            w = torch.rand(T_, k_, device=dev)
+            slot = torch.ops.apb200.moe_slots(gi, E_, C_, 1)
+            buf = torch.ops.apb200.moe_scatter(x, slot, w, E_, C_, 1)
+            moved = 2 * T_ * k_ * d_ * 2
+            for name, fn, ref, nb_ in (
+                    ("moe_slots", lambda: torch.ops.apb200.moe_slots(gi, E_, C_, 1), lambda: moe_ops._moe_slots(gi, E_, C_, 1), T_ * k_ * 16),
+                    ("moe_scatter", lambda: torch.ops.apb200.moe_scatter(x, slot, w, E_, C_, 1), lambda: moe_ops._moe_scatter(x, slot, w, E_, C_, 1),
+                     moved + E_ * C_ * d_ * 2),
+                    ("moe_gather", lambda: torch.ops.apb200.moe_gather(buf, slot, w), lambda: moe_ops._moe_gather(buf, slot, w), moved)):
+                ms, best = time_fn(lambda: (), fn, iters=3, pool=2)
+                rec(f"{name} {T_}x{k_} E={E_} C={C_} d={d_} (kernel)", ms, best, nbytes=nb_)
+                ms, best = time_fn(lambda: (), ref, iters=3, pool=2)
+                rec(f"{name} (index-operator formula)", ms, best, nbytes=nb_)
         elif args.only == "grouped_mm":
             E, Me, Ne, Ke = 8, 4096, 1408, 2048  # the expert projection of the MoE configuration at half its token count
             mk = lambda: (torch.randn(E, Me, Ke, device=dev, dtype=bf) * 0.05, torch.randn(E, Ke, Ne, device=dev, dtype=bf) * 0.05)
