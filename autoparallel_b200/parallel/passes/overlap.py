@@ -20,6 +20,7 @@ for graphs whose nodes are its own kernels.
 from __future__ import annotations
 
 import dataclasses
+import operator
 from typing import Optional
 
 import torch
@@ -201,3 +202,31 @@ def exposed_collectives(gm: fx.GraphModule) -> int:
         if a.op == "call_function" and a.target in comm_ops.START_OPS and b.target is comm_ops.ops.comm_wait.default and b.args[0] is a:
             n_exposed += 1
     return n_exposed
+
+
+def max_compute_run_between_reductions(gm: fx.GraphModule) -> int:
+    """Longest run of compute nodes between two consecutive reduce-scatter / all-reduce issues (or graph ends).
+
+    A regression metric for the scheduler: gradient reductions that are deferred too far bunch up at the end of the
+    backward, where nothing is left to hide them; a small value means they are spread through the compute.
+    (Reference: the ``_max_consec_compute_between_rs`` check of autoparallel/graph_passes/auto_bucketing.py:191-210.)"""
+    C = comm_ops.ops
+    reductions = {C.reduce_scatter.default, C.reduce_scatter_start.default, C.all_reduce.default, C.all_reduce_start.default,
+                  C.mm_rs.default, C.scaled_mm_rs.default}
+    passive = {C.comm_wait.default}
+    longest = run = 0
+    for n in gm.graph.nodes:
+        if n.op != "call_function":
+            continue
+        if n.target in reductions:
+            longest, run = max(longest, run), 0
+        elif n.target in passive or n.target in comm_ops.COLLECTIVE_OPS or n.target in comm_ops.START_OPS:
+            continue
+        elif isinstance(n.meta.get("val"), (torch.Tensor, tuple, list)) and n.target not in _FREE_OPS:
+            run += 1
+    return max(longest, run)
+
+
+_FREE_OPS = {torch.ops.aten.view.default, torch.ops.aten.reshape.default, torch.ops.aten._unsafe_view.default, torch.ops.aten.permute.default,
+             torch.ops.aten.t.default, torch.ops.aten.alias.default, torch.ops.aten.expand.default, torch.ops.aten.unsqueeze.default,
+             torch.ops.aten.squeeze.dim, torch.ops.aten.slice.Tensor, operator.getitem}

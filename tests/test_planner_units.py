@@ -226,5 +226,12 @@ def test_overlap_schedule_prefetches_and_defers(mesh_1d):
         rs = [i for i, n in enumerate(bn) if n.target is comm_ops.ops.reduce_scatter_start.default]
         rs_waits = {n.args[0]: i for i, n in enumerate(bn) if n.target is comm_ops.ops.comm_wait.default}
         assert any(rs_waits[bn[i]] - i > 3 for i in rs)  # gradient reductions overlap later compute
+        # and they are spread through the backward, not bunched at its end: the longest stretch of compute without a
+        # reduction being issued is a fraction of the graph (about one layer)
+        from autoparallel_b200.parallel.passes.overlap import max_compute_run_between_reductions
+
+        n_compute = sum(1 for n in bn if n.op == "call_function")
+        assert 0 < max_compute_run_between_reductions(bw) < n_compute // 2
+        assert max_compute_run_between_reductions(fw) > 0
     finally:
         ap.__exit__(None, None, None)
