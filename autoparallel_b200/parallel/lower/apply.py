@@ -152,8 +152,15 @@ class _Redistributor:
         for k in ("stack_trace", "nn_module_stack", "seq_nr", "autograd_backward", "apb200_phase"):
             if k in like.meta:
                 n.meta[k] = like.meta[k]
-        self.counts[kind] += 1
+        self.counts["all_reduce" if kind == "all_reduce_op" else kind] += 1
         return n
+
+    def _emit_all_reduce(self, cur, st, gname, n, like, shape) -> fx.Node:
+        """Sums use ``all_reduce`` (own kernels, split-phase forms); a pending maximum / minimum its own operator."""
+        if getattr(st, "op", "sum") == "sum":
+            return self._emit("all_reduce", (cur, gname, n), like, shape)
+        node = self._emit("all_reduce_op", (cur, st.op, gname, n), like, shape)
+        return node
 
     def _local(self, target, args: tuple, like: fx.Node, shape) -> fx.Node:
         n = self.g.call_function(target, args)
@@ -194,7 +201,7 @@ class _Redistributor:
             gname, n = self.groups[st.mesh_dim]
             m, me = st.mesh_dim, coord[st.mesh_dim]
             if st.kind == "all_reduce":
-                cur = self._emit("all_reduce", (cur, gname, n), like, shape)
+                cur = self._emit_all_reduce(cur, st, gname, n, like, shape)
                 pl[m] = Replicate()
             elif st.kind == "all_gather":
                 d = st.dim
@@ -269,7 +276,7 @@ class _Redistributor:
                 shape[st.dim] *= n
                 cur = self._emit("all_gather", (cur, st.dim, gname, n), x, shape)
             elif st.kind == "all_reduce":
-                cur = self._emit("all_reduce", (cur, gname, n), x, shape)
+                cur = self._emit_all_reduce(cur, st, gname, n, x, shape)
             elif st.kind == "reduce_scatter":
                 shape[st.dim] //= n
                 cur = self._emit("reduce_scatter", (cur, st.dim, gname, n), x, shape)

@@ -26,6 +26,7 @@ class Step(NamedTuple):
     mesh_dim: int
     dim: Optional[int] = None  # gather / scatter / chunk dim (all_to_all: new shard dim)
     dim2: Optional[int] = None  # all_to_all: old shard dim (concat dim)
+    op: str = "sum"  # all_reduce: the pending reduction it completes ("sum" | "max" | "min")
 
 
 class RedistributeError(RuntimeError):
@@ -92,9 +93,13 @@ def plan_redistribution(src: Sequence[Placement], dst: Sequence[Placement], mesh
             cur[i] = q
             continue
         if isinstance(p, Partial) and isinstance(q, Replicate):
-            steps.append(Step("all_reduce", i))
+            steps.append(Step("all_reduce", i, op=p.reduce_op))
         elif isinstance(p, Partial) and isinstance(q, Shard):
-            steps.append(Step("reduce_scatter", i, q.dim))
+            if p.reduce_op == "sum":
+                steps.append(Step("reduce_scatter", i, q.dim))
+            else:  # a pending maximum / minimum: complete it everywhere, then keep this rank's slice
+                steps.append(Step("all_reduce", i, op=p.reduce_op))
+                steps.append(Step("local_chunk", i, q.dim))
         elif isinstance(p, Replicate) and isinstance(q, Shard):
             steps.append(Step("local_chunk", i, q.dim))
         else:

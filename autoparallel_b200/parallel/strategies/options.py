@@ -168,7 +168,7 @@ def _filter(strat: OpStrategy, mesh, even_only: bool, op=None) -> OpStrategy:
             if op in _RESHAPES and s.input_specs and not _view_keeps_counts(s, mesh):
                 continue
         if not all(_plain_placements(x) for x in list(outs) + list(s.input_specs)):
-            continue  # masked / avg / max partials need op-specific local math; not lowered
+            continue  # masked / averaging partials need op-specific local math; not lowered
         key = (_fp_spec(s.output_specs), _fp_spec(s.input_specs))
         if key in seen:
             continue
@@ -181,8 +181,8 @@ def _plain_placements(spec) -> bool:
     if spec is None:
         return True
     for p in spec.placements:
-        if isinstance(p, Partial) and (type(p) is not Partial or p.reduce_op != "sum"):
-            return False
+        if isinstance(p, Partial) and (type(p) is not Partial or p.reduce_op not in ("sum", "max", "min")):
+            return False  # masked / averaging partials need op-specific local math; sums, maxima and minima are lowered
         if not isinstance(p, (Partial, Replicate, Shard)) or type(p).__name__ == "_StridedShard":
             return False
     return True

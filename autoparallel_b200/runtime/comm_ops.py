@@ -310,6 +310,22 @@ lib.impl("reduce_scatter_start", lambda x, dim, group, n: _shape_div(x, dim, n),
 lib.impl("all_reduce_start", lambda x, group, n: torch.empty_like(x), "Meta")
 lib.impl("comm_wait", lambda x: torch.empty_like(x), "Meta")
 
+# A pending maximum / minimum (``Partial("max")``: the result of ``amax`` over a sharded dim, say) is completed by an
+# all-reduce with that operator.  Kept apart from ``all_reduce`` (sums: gradients, partial products), which has kernels of
+# its own and split-phase forms; this one always runs on the process group's library collective.
+lib.define("all_reduce_op(Tensor x, str op, str group, int group_size) -> Tensor")
+
+
+def _all_reduce_op(x, op, group, n):
+    out = torch.ops._c10d_functional.all_reduce(x.contiguous(), op, group)
+    return torch.ops._c10d_functional.wait_tensor(out)
+
+
+lib.impl("all_reduce_op", _all_reduce_op, "CPU")
+lib.impl("all_reduce_op", _all_reduce_op, "CUDA")
+lib.impl("all_reduce_op", lambda x, op, group, n: torch.empty_like(x), "Meta")
+COLLECTIVE_OPS.add(ops.all_reduce_op.default)
+
 START_OF = {
     ops.all_gather.default: ops.all_gather_start.default,
     ops.reduce_scatter.default: ops.reduce_scatter_start.default,

@@ -92,7 +92,7 @@ def make_runtime_estimator(mesh, plan_device: Optional[str] = None, group_dim: O
                 return topo.all_gather(dim, n, nb)
             if t in (C.reduce_scatter.default, C.reduce_scatter_start.default):
                 return topo.reduce_scatter(dim, n, nb * n)
-            if t in (C.all_reduce.default, C.all_reduce_start.default):
+            if t in (C.all_reduce.default, C.all_reduce_start.default, C.all_reduce_op.default):
                 return topo.all_reduce(dim, n, nb)
             return topo.all_to_all(dim, n, nb)
         if t is C.comm_wait.default or not isinstance(t, torch._ops.OpOverload):

@@ -265,3 +265,69 @@ def test_batch_split_through_pooling_sampling_fft_and_a_gru_on_two_ranks():
     pinned, err, grad = q.get()
     assert len(pinned) >= 4, pinned
     assert err < 1e-4 and grad < 1e-4
+
+
+class Extremes(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.lin = nn.Linear(16, 16)
+
+    def forward(self, x):
+        y = self.lin(x)                      # [B, 16], batch sharded
+        spread = y.amax(dim=0) - y.amin(dim=0)   # extremes over the sharded dim
+        return y / (spread + 1.0)
+
+
+def _extremes_worker(rank, ws, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(ws))
+    dist.init_process_group("gloo", rank=rank, world_size=ws)
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.placement_types import Partial
+
+    from autoparallel_b200 import AutoParallel
+    from autoparallel_b200.parallel.lower.init_weights import _distribute
+    from autoparallel_b200.runtime import comm_ops
+
+    torch.manual_seed(0)
+    ref = Extremes()
+    with torch.device("meta"):
+        m = Extremes()
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("dp",))
+    with AutoParallel(m, lambda: torch.randn(8, 16), mesh) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.add_output_constraints([(Shard(0),)])
+        for n in ap.joint.gm.graph.nodes:
+            if n.op == "call_function" and n.target is aten.amax.default:
+                ap.sharding_optimizer.add_node_constraint(n, (Partial("max"),))
+            if n.op == "call_function" and n.target is aten.amin.default:
+                ap.sharding_optimizer.add_node_constraint(n, (Partial("min"),))
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+        n_op = sum(1 for n in ap.lowered.gm.graph.nodes if n.op == "call_function" and n.target is comm_ops.ops.all_reduce_op.default)
+    pm.to_empty(device="cpu")
+    state = dict(ref.named_parameters())
+    with torch.no_grad():
+        for n, t in pm.named_parameters():
+            t._local_tensor.copy_(_distribute(state[n].detach().clone(), mesh, t.placements)._local_tensor)
+    torch.manual_seed(1)
+    x = torch.randn(8, 16)
+    w = torch.linspace(-1, 1, 16)
+    y = pm(x.chunk(ws, 0)[rank])
+    (y * w).sum().backward()
+    yr = ref(x)
+    (yr * w).sum().backward()
+    err = (y - yr.chunk(ws, 0)[rank]).abs().max().item()
+    g = max((p.grad.full_tensor() - state[n].grad).abs().max().item() for n, p in pm.named_parameters())
+    if rank == 0:
+        q.put((n_op, err, g))
+    dist.destroy_process_group()
+
+
+def test_pending_maximum_and_minimum_are_completed_by_their_own_all_reduce():
+    """``amax`` / ``amin`` over a sharded dim give ``Partial("max")`` / ``Partial("min")``; the lowering completes them with an
+    all-reduce of that operator (a few elements) instead of gathering the operand."""
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    mp.spawn(_extremes_worker, args=(2, free_port(), q), nprocs=2, join=True)
+    n_op, err, grad = q.get()
+    assert n_op == 2 and err < 1e-6 and grad < 1e-5
