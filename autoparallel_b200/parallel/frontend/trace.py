@@ -195,6 +195,45 @@ def _add_unused_state(model: nn.Module, gm: fx.GraphModule) -> None:
         gm.recompile()
 
 
+def _unalias_outputs(captured: fx.GraphModule) -> int:
+    """Outputs that share storage with an earlier output (``return y, y.t()``) get a copy of their own.
+
+    AOTAutograd leaves such an output out of the differentiated graph - it has no tangent there - and expects a run-time
+    wrapper to rebuild it as a view of the other output so that autograd reaches it that way.  The per-rank graphs of this
+    framework run without that wrapper (and a view recorded with global sizes would be wrong on a shard anyway), so
+    gradients arriving through the second output would be dropped without an error.  A copy is a node of the graph like
+    any other: it gets its own tangent."""
+    from torch.multiprocessing.reductions import StorageWeakRef
+    from torch.utils import _pytree as pytree
+
+    g = captured.graph
+    out = next(n for n in g.nodes if n.op == "output")
+    flat, spec = pytree.tree_flatten(out.args[0])
+    seen: set = set()
+    count = 0
+    for i, v in enumerate(flat):
+        ev = v.meta.get("example_value", v.meta.get("val")) if isinstance(v, fx.Node) else None
+        if not isinstance(ev, torch.Tensor):
+            continue
+        try:
+            key = StorageWeakRef(ev.untyped_storage())
+        except Exception:
+            continue
+        if key in seen:
+            with g.inserting_before(out):
+                c = g.call_function(torch.clone, (v,))
+            c.meta = dict(v.meta)
+            flat[i] = c
+            count += 1
+        else:
+            seen.add(key)
+    if count:
+        out.args = (pytree.tree_unflatten(flat, spec),)
+        g.lint()
+        captured.recompile()
+    return count
+
+
 def build_joint_graph(
     model: nn.Module, input_fn: Callable, fake_mode: FakeTensorMode, canonicalize: bool = True, pattern_ops: bool = True
 ) -> JointGraph:
@@ -214,6 +253,7 @@ def build_joint_graph(
             captured = _dynamo_graph_capture_for_export(model)(*traced_inputs.args, **traced_inputs.kwargs)
             _restore_state_dict(model, captured)
             _add_unused_state(model, captured)
+            _unalias_outputs(captured)
             pattern_stats = {}
             if pattern_ops:
                 # stock-PyTorch idioms (nn.RMSNorm, F.silu * x, complex RoPE, F.scaled_dot_product_attention) become this

@@ -32,7 +32,7 @@ def worker(rank, ws, names, port, mesh_shape):
             cfg = make(T); cfg.use_cache = False
             if name == "deit": cfg.architectures = ["DeiTForImageClassification"]
             auto = {"causal-lm": T.AutoModelForCausalLM, "seq2seq": T.AutoModelForSeq2SeqLM, "masked-lm": T.AutoModelForMaskedLM,
-                    "image-cls": T.AutoModelForImageClassification, "speech": T.AutoModelForSpeechSeq2Seq}[task]
+                    "image-cls": T.AutoModelForImageClassification, "speech": T.AutoModelForSpeechSeq2Seq, "contrastive": T.AutoModel}[task]
             try:
                 cfg._attn_implementation = "sdpa"; torch.manual_seed(0); ref = auto.from_config(cfg)
             except ValueError:
@@ -47,6 +47,8 @@ def worker(rank, ws, names, port, mesh_shape):
                 full = {"pixel_values": torch.randn(B, 3, 64, 64)}
             elif task == "speech":
                 full = {"input_features": torch.randn(B, 16, 128), "decoder_input_ids": torch.randint(0, cfg.vocab_size, (B, S))}
+            elif task == "contrastive":
+                full = {"input_ids": torch.randint(0, cfg.text_config.vocab_size, (B, S)), "pixel_values": torch.randn(B, 3, 64, 64)}
             else:
                 full = {"input_ids": torch.randint(0, cfg.vocab_size, (B, S))}
                 if task == "seq2seq": full["decoder_input_ids"] = torch.randint(0, cfg.vocab_size, (B, S))
@@ -62,10 +64,11 @@ def worker(rank, ws, names, port, mesh_shape):
                 for n, t in list(pm.named_parameters()) + list(pm.named_buffers()):
                     t._local_tensor.copy_(_distribute(state[n].detach().clone(), mesh, t.placements)._local_tensor)
             out = pm(**{k: v.chunk(dp, 0)[me] for k, v in full.items()})
-            logits = out.logits
+            logits = out.logits if hasattr(out, "logits") else out.logits_per_image
             w = torch.linspace(-1, 1, logits.shape[-1])
             (logits.float() * w).mean().backward()
-            rl = ref(**full).logits
+            ro = ref(**full)
+            rl = ro.logits if hasattr(ro, "logits") else ro.logits_per_image
             (rl.float() * w).mean().backward()
             err = (logits - rl.chunk(dp, 0)[me]).abs().max().item()
             worst, who = 0.0, ""

@@ -139,6 +139,12 @@ ZOO = {
     "regnet": ("image-cls", lambda T: T.RegNetConfig(embedding_size=32, hidden_sizes=[32, 64], depths=[1, 1], groups_width=8, num_labels=16)),
     "segformer": ("image-cls", lambda T: T.SegformerConfig(num_encoder_blocks=2, depths=[1, 1], sr_ratios=[2, 1], hidden_sizes=[32, 64],
                                                            patch_sizes=[7, 3], strides=[4, 2], num_attention_heads=[1, 2], num_labels=16)),
+    "clip": ("contrastive", lambda T: T.CLIPConfig(
+        text_config=T.CLIPTextConfig(hidden_size=D, num_hidden_layers=L, num_attention_heads=H, intermediate_size=4 * D, vocab_size=V,
+                                     max_position_embeddings=128, projection_dim=64).to_dict(),
+        vision_config=T.CLIPVisionConfig(hidden_size=D, num_hidden_layers=L, num_attention_heads=H, intermediate_size=4 * D,
+                                         image_size=64, patch_size=8, projection_dim=64).to_dict(),
+        projection_dim=64)),
     "poolformer": ("image-cls", lambda T: T.PoolFormerConfig(num_encoder_blocks=2, depths=[1, 1], hidden_sizes=[32, 64], patch_sizes=[7, 3],
                                                              strides=[4, 2], padding=[2, 1], num_labels=16)),
 }
@@ -158,7 +164,7 @@ def plan_one(name, mesh, batch, seq, execute, bf16=False, uneven=False):
     if name == "deit":
         cfg.architectures = ["DeiTForImageClassification"]  # the auto class maps this config to two heads
     auto = {"causal-lm": T.AutoModelForCausalLM, "seq2seq": T.AutoModelForSeq2SeqLM, "masked-lm": T.AutoModelForMaskedLM,
-            "image-cls": T.AutoModelForImageClassification, "speech": T.AutoModelForSpeechSeq2Seq}[task]
+            "image-cls": T.AutoModelForImageClassification, "speech": T.AutoModelForSpeechSeq2Seq, "contrastive": T.AutoModel}[task]
     with torch.device("meta"):
         try:
             cfg._attn_implementation = "sdpa"
@@ -177,12 +183,14 @@ def plan_one(name, mesh, batch, seq, execute, bf16=False, uneven=False):
             return ForwardInputs((), {"pixel_values": torch.randn(batch, 3, 64, 64)})
         if task == "speech":  # log-mel frames in (two per encoder position), decoder tokens
             return ForwardInputs((), {"input_features": torch.randn(batch, 16, 128), "decoder_input_ids": ids()})
+        if task == "contrastive":  # one caption per image
+            return ForwardInputs((), {"input_ids": torch.randint(0, V, (batch, min(seq, 64))), "pixel_values": torch.randn(batch, 3, 64, 64)})
         kw = {"input_ids": ids()}
         if task == "seq2seq":
             kw["decoder_input_ids"] = ids()
         return ForwardInputs((), kw)
 
-    n_in = 2 if task in ("seq2seq", "speech") else 1
+    n_in = 2 if task in ("seq2seq", "speech", "contrastive") else 1
     t0 = time.perf_counter()
     policy = None
     if bf16:
@@ -208,7 +216,7 @@ def plan_one(name, mesh, batch, seq, execute, bf16=False, uneven=False):
                 loc.normal_(0.0, 0.02) if loc.dtype.is_floating_point else loc.zero_()
         local = {k: v[: batch // mesh.shape[0]] for k, v in input_fn().kwargs.items()}
         out = pm(**local)
-        logits = out.logits if hasattr(out, "logits") else out[0]
+        logits = out.logits if hasattr(out, "logits") else (out.logits_per_image if hasattr(out, "logits_per_image") else out[0])
         logits.float().sum().backward()
     return secs, cost, lowered.num_collectives
 

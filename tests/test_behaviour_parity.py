@@ -267,3 +267,40 @@ def test_strided_factories_get_local_sizes_and_strides(mesh_1d):
     out = pm(torch.rand(2, 16))
     assert out.shape == (2, 16)
     out.sum().backward()
+
+
+def test_gradients_flow_through_an_output_that_is_a_view_of_another_output(mesh_1d):
+    """``return y.t(), y``: the differentiated graph has no tangent for an output that aliases another one (a run-time wrapper
+    is expected to rebuild it as a view); here such an output gets a copy of its own, so a loss on it reaches the parameters."""
+    import torch.nn as nn
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.l = nn.Linear(8, 8)
+
+        def forward(self, x):
+            y = self.l(x)
+            return y.t(), y, x.t()          # a view of another output, the output itself, a view of an input
+
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.randn(16, 8), mesh_1d) as ap:
+        assert len(ap.joint.tangent_nodes) >= 2
+        ap.add_input_constraints([(Shard(0),)])
+        ap.add_output_constraints([(Shard(1),), (Shard(0),), None])
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    pm.to_empty(device="cpu")
+    with torch.no_grad():
+        for p in pm.parameters():
+            p.to_local().normal_()
+    x = torch.randn(16 // mesh_1d.size(0), 8)
+    a, b, c = pm(x)
+    assert torch.equal(a, b.t())
+    a.sum().backward()
+    g_view = pm.l.weight.grad.to_local().clone()
+    pm.l.weight.grad = None
+    a, b, c = pm(x)
+    b.sum().backward()
+    assert g_view.abs().sum() > 0 and torch.allclose(g_view, pm.l.weight.grad.to_local())
