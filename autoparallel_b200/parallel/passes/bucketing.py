@@ -131,7 +131,9 @@ def bucket_collectives(gm: fx.GraphModule, config: BucketConfig | None = None, c
     g = gm.graph
     order = {n: i for i, n in enumerate(g.nodes)}
     placeholders = {n for n in g.nodes if n.op == "placeholder"}
-    input_only = set(placeholders)
+    # chains that start at a tangent belong to the backward; a bucket holding one would make the forward depend on it
+    tangents = {n for n in placeholders if (n.meta.get("apb200_kind") or (None,))[0] == "tangent" or n.name.startswith("tangents")}
+    input_only = set(placeholders) - tangents
     for n in g.nodes:
         # single-input chains only (cast / gather / view of one graph input): anything that joins two
         # tensors is real computation, not parameter preparation
@@ -264,11 +266,22 @@ def bucket_collectives(gm: fx.GraphModule, config: BucketConfig | None = None, c
         stats["all_gather_buckets" if kind == "ag" else "reduce_scatter_buckets"] += 1
         stats["members"] += len(members)
 
+    backward_nodes = set(tangents)
+    for n in g.nodes:
+        if n.op == "call_function" and any(i in backward_nodes for i in n.all_input_nodes):
+            backward_nodes.add(n)
+
+    def phase(n) -> bool:
+        """True for a collective that only the backward consumes (the re-gather of a parameter, say).  It must not share a
+        bucket with one the forward waits for: it would run, and its result stay alive, from the forward on."""
+        users = list(n.users)
+        return bool(users) and all(u in backward_nodes for u in users)
+
     def plan(kind, cands):
         """Buckets (lists of members, graph order) of one kind; nothing in the graph is touched."""
         by_group: dict = {}
         for n in cands:
-            by_group.setdefault((n.args[2], n.meta["val"].dtype), []).append(n)
+            by_group.setdefault((n.args[2], n.meta["val"].dtype, phase(n)), []).append(n)
         buckets = []
         for members in by_group.values():
             bucket, size = [], 0
@@ -295,7 +308,7 @@ def bucket_collectives(gm: fx.GraphModule, config: BucketConfig | None = None, c
     ag = candidates(C.all_gather.default, lambda n: n.args[0] in input_only and all(len(c.users) == 1 for c in chain_of(n)))
     by_group: dict = {}
     for n in ag:
-        by_group.setdefault((n.args[2], n.meta["val"].dtype), []).append(n)
+        by_group.setdefault((n.args[2], n.meta["val"].dtype, phase(n)), []).append(n)
     for members in by_group.values():
         bucket, size = [], 0
         total_bytes = sum(_nbytes(m) for m in members)

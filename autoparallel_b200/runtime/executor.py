@@ -63,6 +63,10 @@ class Runtime:
             else:
                 self._order.append(("input", self._tensor_input_pos[n]))
         self._n_in = flat_tensor_counter
+        # forward inputs that the module overwrites after the call (buffers the forward mutates: running statistics and
+        # the like): a backward that reads them - a recomputed batch norm does - must see the value the forward saw
+        self._mutated_inputs = {pos for pos, (kind, i) in enumerate(self._order)
+                                if kind == "buffer" and bnames[i] in getattr(joint, "buffer_updates", {})}
         self._graph_device = torch.device("cpu")  # device constants inside the graphs (planning happens on CPU fake tensors)
         self._fn = _make_function(self)
         if self.executor == "streams":
@@ -117,7 +121,7 @@ def _make_function(rt: Runtime):
         def forward(ctx, *flat):
             outs = rt.fw(*flat)
             fwd_outs, saved = outs[:n_out], outs[n_out:]
-            prim = [flat[i] for kind, i in parts.bw_inputs if kind == "primal"]
+            prim = [flat[i].clone() if i in rt._mutated_inputs else flat[i] for kind, i in parts.bw_inputs if kind == "primal"]
             ctx.save_for_backward(*saved, *prim)
             ctx.n_saved = len(saved)
             for o in fwd_outs:

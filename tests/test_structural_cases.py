@@ -87,7 +87,7 @@ CASES = {
 def flat(o):
     from torch.utils._pytree import tree_flatten
     return [t for t in tree_flatten(o)[0] if isinstance(t, torch.Tensor)]
-def worker(rank, ws, port, names, q):
+def worker(rank, ws, port, names, mode, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(ws))
     dist.init_process_group("gloo", rank=rank, world_size=ws)
     from torch.distributed.device_mesh import init_device_mesh
@@ -106,12 +106,12 @@ def worker(rank, ws, port, names, q):
             torch.manual_seed(0); ref = cls()
             with torch.device("meta"): m = cls()
             torch.manual_seed(1); x = mk()
-            with AutoParallel(m, mk, mesh) as ap:
+            with AutoParallel(m, mk, mesh, activation_checkpointing=mode.get("ac", "none"), bucket_collectives=mode.get("bucket", False)) as ap:
                 ap.add_parameter_memory_constraint()
                 ap.add_input_constraints([(Shard(0),) + rest])
                 nout = ap.joint.num_user_outputs
                 ap.add_output_constraints([(Shard(0),) + rest if name != 'retparam' or i < 2 else None for i in range(nout)])
-                ap.optimize_placement(); pm = ap.apply_placement()
+                ap.optimize_placement(); pm = ap.apply_placement(executor=mode.get("executor", "graph"))
             pm.to_empty(device="cpu")
             state = dict(ref.named_parameters()); state.update(dict(ref.named_buffers()))
             with torch.no_grad():
@@ -137,10 +137,17 @@ def worker(rank, ws, port, names, q):
     dist.destroy_process_group()
 
 
-def test_structural_cases_match_single_device_on_two_ranks():
+@pytest.mark.parametrize("mode", [
+    {},
+    {"ac": "selective"},                              # recomputed operators read buffers the forward has since overwritten
+    {"ac": "full"},
+    {"executor": "streams", "bucket": True},          # buckets must not mix forward gathers with backward-only ones
+    {"bucket": "auto"},
+], ids=["plain", "selective-ac", "full-ac", "streams+buckets", "priced-buckets"])
+def test_structural_cases_match_single_device_on_two_ranks(mode):
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
-    mp.spawn(worker, args=(2, free_port(), list(CASES), q), nprocs=2, join=True)
+    mp.spawn(worker, args=(2, free_port(), list(CASES), mode, q), nprocs=2, join=True)
     results = q.get()
     bad = {k: v for k, v in results.items() if isinstance(v, str) or v[0] > 1e-4 or v[1] > 1e-3}
     assert len(results) == len(CASES) and not bad, bad
