@@ -105,7 +105,7 @@ class AutoParallel:
         # (parallel/passes/pattern_ops.py); False keeps the traced ATen operators.
         self.pattern_ops = bool(pattern_ops)
         # uneven_sharding=True: a tensor dim may be sharded although the mesh dim does not divide it.  Shards are
-        # ceil-sized chunks (the last non-empty one shorter, later ones empty); every rank lowers the graph with
+        # ceil-sized chunks (the last one shorter; splits that would leave a rank empty are not offered); every rank lowers the graph with
         # its own shard shapes and collectives on such dims pad to the chunk size and cut the result.
         self.uneven_sharding = bool(uneven_sharding)
         # dynamic=True: graphs stay specialised to static shapes (every kernel launch has fixed extents), but the

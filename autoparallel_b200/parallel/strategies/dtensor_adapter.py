@@ -92,7 +92,12 @@ def is_valid_spec(spec: Optional[DTensorSpec], mesh, even_only: bool) -> bool:
                 return False
             if even_only and shape[d] % n != 0:
                 return False
-            shape[d] = -(-shape[d] // n)
+            chunk = -(-shape[d] // n)
+            if chunk * (n - 1) >= shape[d]:
+                # ceil-sized chunks would leave the last rank(s) without a row: operators such as convolution refuse empty
+                # operands, and a shard is only offered while every rank holds part of it (the reference's rule)
+                return False
+            shape[d] = chunk
     if not even_only:
         # an uneven tensor dim may be split by one mesh dim only: the shard sizes of a second split would
         # depend on the first coordinate, which the lowered collectives do not handle

@@ -31,10 +31,13 @@ def test_options_with_uneven_shards(mesh_2d):
 
     from autoparallel_b200.parallel.strategies.dtensor_adapter import all_options, is_valid_spec
 
-    val = torch.empty(6, 10)
+    val = torch.empty(7, 10)
     even = {tuple(s.output_spec.placements) for s in all_options(mesh_2d, val, True).strategies}
     uneven = {tuple(s.output_spec.placements) for s in all_options(mesh_2d, val, False).strategies}
-    assert (Replicate(), Shard(0)) not in even and (Replicate(), Shard(0)) in uneven  # 6 rows over tp=4
+    assert (Replicate(), Shard(0)) not in even and (Replicate(), Shard(0)) in uneven  # 7 rows over tp=4: 2, 2, 2, 1
+    # 6 rows over tp=4 would be 2, 2, 2, 0: a shard is only offered while every rank holds part of it
+    six = {tuple(s.output_spec.placements) for s in all_options(mesh_2d, torch.empty(6, 10), False).strategies}
+    assert (Replicate(), Shard(0)) not in six and (Shard(0), Replicate()) in six
     assert (Shard(1), Shard(1)) not in uneven  # 10 columns over 2 x 4 ranks: nested and uneven
     tm = TensorMeta(torch.Size([16, 10]), (10, 1), torch.float32)
     assert is_valid_spec(DTensorSpec(mesh_2d, (Shard(0), Shard(0)), tensor_meta=tm), mesh_2d, False)  # nested but even
@@ -112,7 +115,7 @@ def _worker(rank, ws, mesh_shape, batch, port, q):
 
 @pytest.mark.parametrize(
     "mesh_shape,batch",
-    [((3,), 7), ((4,), 5), ((2, 2), 3)],  # 7 rows over 3 ranks; 5 over 4 (rank 3 holds nothing); 2-D mesh
+    [((3,), 7), ((4,), 7), ((2, 2), 3)],  # 7 rows over 3 ranks (3, 3, 1); over 4 (2, 2, 2, 1); 2-D mesh
 )
 def test_uneven_shards_match_single_device(mesh_shape, batch):
     ws = 1
