@@ -106,7 +106,7 @@ def worker(rank, ws, port, names, mode, q):
             torch.manual_seed(0); ref = cls()
             with torch.device("meta"): m = cls()
             torch.manual_seed(1); x = mk()
-            with AutoParallel(m, mk, mesh, activation_checkpointing=mode.get("ac", "none"), bucket_collectives=mode.get("bucket", False)) as ap:
+            with AutoParallel(m, mk, mesh, activation_checkpointing=mode.get("ac", "none"), bucket_collectives=mode.get("bucket", False), fuse_collectives=mode.get("fuse")) as ap:
                 ap.add_parameter_memory_constraint()
                 ap.add_input_constraints([(Shard(0),) + rest])
                 nout = ap.joint.num_user_outputs
@@ -143,7 +143,8 @@ def worker(rank, ws, port, names, mode, q):
     {"ac": "full"},
     {"executor": "streams", "bucket": True},          # buckets must not mix forward gathers with backward-only ones
     {"bucket": "auto"},
-], ids=["plain", "selective-ac", "full-ac", "streams+buckets", "priced-buckets"])
+    {"fuse": "all", "executor": "streams"},          # GEMM + collective nodes (compositions on CPU ranks)
+], ids=["plain", "selective-ac", "full-ac", "streams+buckets", "priced-buckets", "fused-nodes"])
 def test_structural_cases_match_single_device_on_two_ranks(mode):
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
