@@ -143,7 +143,7 @@ def worker(rank, ws, port, names, mode, q):
     {"ac": "full"},
     {"executor": "streams", "bucket": True},          # buckets must not mix forward gathers with backward-only ones
     {"bucket": "auto"},
-    {"fuse": "all", "executor": "streams"},          # GEMM + collective nodes (compositions on CPU ranks)
+    {"fuse": "all"},                                  # GEMM + collective nodes (compositions on CPU ranks)
 ], ids=["plain", "selective-ac", "full-ac", "streams+buckets", "priced-buckets", "fused-nodes"])
 def test_structural_cases_match_single_device_on_two_ranks(mode):
     ctx = mp.get_context("spawn")
