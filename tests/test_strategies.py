@@ -19,8 +19,9 @@ def test_all_options_respects_divisibility(mesh_1d, mesh_2d):
     assert (Shard(0), Shard(0)) in opts2 and (Shard(1), Shard(1)) not in opts2
     assert (Shard(1), Replicate()) in opts2  # 4 >= 2 on dp
     # uneven shards only when asked for
-    assert (Shard(0),) not in _pl(all_options(mesh_1d, torch.empty(12, 3)))
-    assert (Shard(0),) in _pl(all_options(mesh_1d, torch.empty(12, 3), even_only=False))
+    assert (Shard(0),) not in _pl(all_options(mesh_1d, torch.empty(15, 3)))
+    assert (Shard(0),) in _pl(all_options(mesh_1d, torch.empty(15, 3), even_only=False))       # 2, 2, 2, 2, 2, 2, 2, 1
+    assert (Shard(0),) not in _pl(all_options(mesh_1d, torch.empty(12, 3), even_only=False))   # 2 x 6, then two empty ranks
 
 
 def test_local_shape():
