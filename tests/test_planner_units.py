@@ -233,5 +233,10 @@ def test_overlap_schedule_prefetches_and_defers(mesh_1d):
         n_compute = sum(1 for n in bn if n.op == "call_function")
         assert 0 < max_compute_run_between_reductions(bw) < n_compute // 2
         assert max_compute_run_between_reductions(fw) > 0
+        # every split-phase collective is consumed through its wait, never directly, and none is left un-waited
+        for gm_ in (fw, bw):
+            for n in gm_.graph.nodes:
+                if n.op == "call_function" and n.target in comm_ops.START_OPS:
+                    assert n.users and all(u.target is comm_ops.ops.comm_wait.default for u in n.users), n.name
     finally:
         ap.__exit__(None, None, None)
