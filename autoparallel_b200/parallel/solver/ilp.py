@@ -803,7 +803,7 @@ def _fmt_pl(pl) -> str:
         if isinstance(p, Replicate):
             return "R"
         if isinstance(p, Partial):
-            return "P"
+            return "P" if p.reduce_op == "sum" else f"P({p.reduce_op})"
         return str(p)
 
     return "".join(one(p) for p in pl) if len(pl) == 1 else "(" + ",".join(one(p) for p in pl) + ")"

@@ -58,6 +58,8 @@ def _parse_placement(s: str):
             out.append(Replicate())
         elif it == "P":
             out.append(Partial())
+        elif it.startswith("P(") and it.endswith(")"):
+            out.append(Partial(it[2:-1]))
         elif it.startswith("S(") and it.endswith(")"):
             out.append(Shard(int(it[2:-1])))
         else:
