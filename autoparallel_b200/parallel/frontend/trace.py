@@ -246,9 +246,11 @@ def build_joint_graph(
         traced_inputs = normalize_inputs(input_fn())
 
     with contextlib.ExitStack() as stack:
-        # allow_rnn: nn.RNN / nn.GRU / nn.LSTM are captured as their ATen operators instead of being refused
+        # allow_rnn: nn.RNN / nn.GRU / nn.LSTM are captured as their ATen operators instead of being refused; with the
+        # oneDNN flag off their decomposition takes the generic per-step form rather than a fused CPU-only operator that
+        # the planning host offers but the devices the graph will run on do not have
         with cast_reads(True), _local_map_capture(), _flex_attention_on_fake_cpu(), \
-                torch._dynamo.config.patch(allow_rnn=True), \
+                torch._dynamo.config.patch(allow_rnn=True), torch.backends.mkldnn.flags(enabled=False), \
                 torch._dynamo.utils._disable_saved_tensors_hooks_during_tracing():
             captured = _dynamo_graph_capture_for_export(model)(*traced_inputs.args, **traced_inputs.kwargs)
             _restore_state_dict(model, captured)

@@ -78,14 +78,20 @@ class Runtime:
     def _retarget(self, device: torch.device) -> None:
         """Planning runs on CPU fake tensors, so factory operators traced with an explicit ``device=`` (``torch.zeros(...,
         device=x.device)`` inside a user region, ``arange`` for index arithmetic) carry "cpu" as a constant.  Before the
-        first run on another device the constant is replaced in every graph of this runtime."""
+        first run on another device the constant is replaced in every graph of this runtime, and operators that exist on
+        the planning host only are swapped for device-neutral stand-ins."""
         if device == self._graph_device:
             return
+        from .portable_ops import SWAPS
+
         for gm in (self.fw, self.bw, self.fwd_only):
             changed = False
             for n in gm.graph.nodes:
                 if n.op != "call_function":
                     continue
+                if n.target in SWAPS and device.type != "cpu":
+                    n.target = SWAPS[n.target]  # an operator only the planning host implements (runtime/portable_ops.py)
+                    changed = True
                 if isinstance(n.kwargs.get("device"), torch.device) and n.kwargs["device"] != device:
                     n.kwargs = {**n.kwargs, "device": device}
                     changed = True

@@ -304,3 +304,41 @@ def test_gradients_flow_through_an_output_that_is_a_view_of_another_output(mesh_
     a, b, c = pm(x)
     b.sum().backward()
     assert g_view.abs().sum() > 0 and torch.allclose(g_view, pm.l.weight.grad.to_local())
+
+
+def test_operators_of_the_planning_host_are_swapped_when_the_graphs_move_to_another_device(mesh_1d):
+    """Attention that the pattern pass does not take over is traced (on CPU fake tensors) to operators only the CPU has; when
+    the runtime retargets its graphs they become device-neutral functions, and device constants follow."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from autoparallel_b200.runtime import portable_ops
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.qkv = nn.Linear(64, 192)
+
+        def forward(self, x):
+            q, k, v = self.qkv(x).view(x.shape[0], x.shape[1], 3, 4, 16).permute(2, 0, 3, 1, 4)
+            pos = torch.arange(x.shape[1], device=x.device)
+            bias = -(pos[:, None] - pos[None, :]).abs().to(x.dtype)            # an explicit additive mask
+            return F.scaled_dot_product_attention(q, k, v, attn_mask=bias).sum()
+
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.randn(8, 32, 64), mesh_1d, pattern_ops=False) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    rt = pm.__dict__["_apb200_runtime"]
+    aten = torch.ops.aten
+    before = {n.target for g in (rt.fw, rt.bw) for n in g.graph.nodes if n.op == "call_function"}
+    assert aten._scaled_dot_product_flash_attention_for_cpu.default in before
+    rt._retarget(torch.device("cuda", 0))                                       # graph surgery only: nothing is run
+    after = {n.target for g in (rt.fw, rt.bw, rt.fwd_only) for n in g.graph.nodes if n.op == "call_function"}
+    assert aten._scaled_dot_product_flash_attention_for_cpu.default not in after
+    assert aten._scaled_dot_product_flash_attention_for_cpu_backward.default not in after
+    assert portable_ops.sdpa_forward in after and portable_ops.sdpa_backward in after
+    devs = {n.kwargs["device"] for g in (rt.fw, rt.bw) for n in g.graph.nodes if n.op == "call_function" and "device" in n.kwargs}
+    assert devs == {torch.device("cuda", 0)}

@@ -197,6 +197,7 @@ class Zoo3(nn.Module):
         super().__init__()
         self.conv = nn.Conv2d(2, 4, 3, padding=1)
         self.gru = nn.GRU(16, 8, batch_first=True)
+        self.lstm = nn.LSTM(16, 8, batch_first=True)
 
     def forward(self, x):                                   # x [B, 2, 4, 4]
         y = self.conv(x)                                    # [B, 4, 4, 4]
@@ -206,7 +207,8 @@ class Zoo3(nn.Module):
         s = F.grid_sample(y, grid, align_corners=False).flatten(1).sum(-1)
         f = torch.fft.rfft(y.flatten(2), dim=-1).abs().flatten(1).sum(-1)
         seq, _ = self.gru(y.flatten(2))                     # [B, 4, 8]
-        return p + v + s + f + seq.sum((1, 2))
+        seq2, _ = self.lstm(y.flatten(2))                   # traced into per-step operators (no fused CPU-only operator)
+        return p + v + s + f + seq.sum((1, 2)) + seq2.sum((1, 2))
 
 
 PINNED3 = (aten.adaptive_max_pool2d.default, aten.avg_pool3d.default, aten.grid_sampler_2d.default, aten._fft_r2c.default,
@@ -258,7 +260,7 @@ def _worker3(rank, ws, port, q):
     dist.destroy_process_group()
 
 
-def test_batch_split_through_pooling_sampling_fft_and_a_gru_on_two_ranks():
+def test_batch_split_through_pooling_sampling_fft_a_gru_and_an_lstm_on_two_ranks():
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
     mp.spawn(_worker3, args=(2, free_port(), q), nprocs=2, join=True)

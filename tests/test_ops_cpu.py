@@ -1,5 +1,6 @@
 """CPU reference implementations of the operator library against PyTorch's own autograd."""
 import math
+import pytest
 import torch
 import torch.nn.functional as F
 
@@ -195,3 +196,28 @@ def test_yarn_rope_tables_keep_fast_pairs_and_stretch_slow_ones():
     # factor 1 (or no yarn) is the plain table
     c, s_ = rope_tables(d, n, theta, yarn={"factor": 1.0})
     assert torch.equal(c, cos0) and torch.equal(s_, sin0)
+
+
+@pytest.mark.parametrize("causal,mask", [(True, None), (False, None), (False, "float"), (True, "float")])
+def test_device_neutral_attention_matches_the_planning_hosts_operator(causal, mask, monkeypatch):
+    """``runtime/portable_ops.py``: the stand-ins that replace the CPU-only attention operators when a graph moves to another
+    device compute the same outputs, log-sum-exp and gradients (their generic branch is forced here)."""
+    from autoparallel_b200.runtime import portable_ops as P
+
+    torch.manual_seed(0)
+    B, H, L, D = 2, 3, 16, 8
+    q, k, v, go = (torch.randn(B, H, L, D, dtype=torch.float64) for _ in range(4))
+    m = None
+    if mask == "bool":
+        m = torch.rand(B, 1, L, L) > 0.3
+        m[..., 0] = True  # no row fully masked
+    elif mask == "float":
+        m = torch.randn(B, 1, L, L, dtype=torch.float64)
+    aten = torch.ops.aten
+    ro, rl = aten._scaled_dot_product_flash_attention_for_cpu(q, k, v, 0.0, causal, attn_mask=m)
+    rdq, rdk, rdv = aten._scaled_dot_product_flash_attention_for_cpu_backward(go, q, k, v, ro, rl, 0.0, causal, attn_mask=m)
+    monkeypatch.setattr(P, "FORCE_GENERIC", True)
+    o, l = P.sdpa_forward(q, k, v, 0.0, causal, attn_mask=m)
+    assert torch.allclose(o, ro, atol=1e-9) and torch.allclose(l.to(rl.dtype), rl, atol=1e-6)
+    dq, dk, dv = P.sdpa_backward(go, q, k, v, ro, rl.double(), 0.0, causal, attn_mask=m)
+    assert torch.allclose(dq, rdq, atol=1e-8) and torch.allclose(dk, rdk, atol=1e-8) and torch.allclose(dv, rdv, atol=1e-8)
