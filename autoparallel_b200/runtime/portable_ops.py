@@ -3,9 +3,13 @@
 Planning traces the model on CPU fake tensors, so an attention call that the pattern pass does not take over (an explicit
 attention mask, ``pattern_ops=False``) is decomposed to ``aten._scaled_dot_product_flash_attention_for_cpu`` and its backward
 - operators without a CUDA implementation.  When a runtime's graphs move to another device the executor swaps them for the
-functions below: the same mathematics in ordinary tensor operators (the score matrix is materialised, which is what small
-models with masks can afford; the framework's own attention operator serves the mask-free cases through the pattern
-pass).  Signatures and return values are those of the two ATen operators, so the swap is a change of ``node.target`` only.
+functions below.  Off the CPU the forward is ``torch.nn.functional.scaled_dot_product_attention`` itself (whatever fused
+kernel the device's library picks, mask included) and the backward recomputes that call under autograd, so nothing of
+size L x S is kept; if the library refuses the arguments, the same mathematics runs in ordinary tensor operators with
+the score matrix materialised.  (The framework's own attention operator serves the mask-free cases through the pattern
+pass.)  Signatures and return values are those of the two ATen operators, so the swap is a change of ``node.target``
+only; the log-sum-exp output is exact on the formula path and a placeholder on the library path, whose backward does
+not read it.
 """
 from __future__ import annotations
 
@@ -15,8 +19,10 @@ from typing import Optional
 import torch
 
 aten = torch.ops.aten
-#: tests set this to run the device-neutral formulas on CPU tensors as well
+#: tests set this to run the device-neutral paths on CPU tensors as well
 FORCE_GENERIC = False
+#: skip the library call and use the explicit formulas (tests; a device whose library lacks the fused operator)
+FORMULAS_ONLY = False
 
 
 def _acc(t) -> torch.dtype:
@@ -43,6 +49,12 @@ def sdpa_forward(q, k, v, dropout_p: float = 0.0, is_causal: bool = False, *, at
         return aten._scaled_dot_product_flash_attention_for_cpu(q, k, v, dropout_p, is_causal, attn_mask=attn_mask, scale=scale)
     if dropout_p != 0.0:
         raise NotImplementedError("attention dropout inside the traced attention operator is not supported off the planning device")
+    if not FORMULAS_ONLY:
+        try:
+            out = torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask, is_causal=is_causal, scale=scale)
+            return out, q.new_zeros(q.shape[:-1], dtype=torch.float32)
+        except RuntimeError:
+            pass
     s = _scores(q, k, attn_mask, is_causal, scale)
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse.unsqueeze(-1))
@@ -56,6 +68,14 @@ def sdpa_backward(grad_out, q, k, v, out, lse, dropout_p: float, is_causal: bool
     if q.device.type == "cpu" and not FORCE_GENERIC:
         return aten._scaled_dot_product_flash_attention_for_cpu_backward(grad_out, q, k, v, out, lse, dropout_p, is_causal,
                                                                        attn_mask=attn_mask, scale=scale)
+    if not FORMULAS_ONLY:
+        try:
+            with torch.enable_grad():
+                qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
+                o = torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, attn_mask=attn_mask, is_causal=is_causal, scale=scale)
+                return torch.autograd.grad(o, (qq, kk, vv), grad_out)
+        except RuntimeError:
+            pass
     sc = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     s = _scores(q, k, attn_mask, is_causal, scale)
     p = torch.nan_to_num(torch.exp(s - lse.unsqueeze(-1)), nan=0.0)

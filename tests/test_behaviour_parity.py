@@ -335,6 +335,16 @@ def test_operators_of_the_planning_host_are_swapped_when_the_graphs_move_to_anot
     aten = torch.ops.aten
     before = {n.target for g in (rt.fw, rt.bw) for n in g.graph.nodes if n.op == "call_function"}
     assert aten._scaled_dot_product_flash_attention_for_cpu.default in before
+    # reference run with the host's operators
+    pm.to_empty(device="cpu")
+    with torch.no_grad():
+        for p_ in pm.parameters():
+            p_.to_local().normal_(std=0.2)
+    x = torch.randn(8 // mesh_1d.size(0), 32, 64)
+    ref = pm(x)
+    ref.backward()
+    ref_grad = pm.qkv.weight.grad.to_local().clone()
+    pm.qkv.weight.grad = None
     rt._retarget(torch.device("cuda", 0))                                       # graph surgery only: nothing is run
     after = {n.target for g in (rt.fw, rt.bw, rt.fwd_only) for n in g.graph.nodes if n.op == "call_function"}
     assert aten._scaled_dot_product_flash_attention_for_cpu.default not in after
@@ -342,3 +352,16 @@ def test_operators_of_the_planning_host_are_swapped_when_the_graphs_move_to_anot
     assert portable_ops.sdpa_forward in after and portable_ops.sdpa_backward in after
     devs = {n.kwargs["device"] for g in (rt.fw, rt.bw) for n in g.graph.nodes if n.op == "call_function" and "device" in n.kwargs}
     assert devs == {torch.device("cuda", 0)}
+    # the swapped graphs compute the same thing (run here on the CPU again, with the stand-ins' generic path forced)
+    rt._retarget(torch.device("cpu"))
+    portable_ops.FORCE_GENERIC = True
+    try:
+        for formulas in (False, True):
+            portable_ops.FORMULAS_ONLY = formulas
+            out = pm(x)
+            out.backward()
+            assert torch.allclose(out, ref, rtol=1e-5, atol=1e-3)
+            assert torch.allclose(pm.qkv.weight.grad.to_local(), ref_grad, rtol=1e-4, atol=1e-3)  # values up to a few hundred, fp32
+            pm.qkv.weight.grad = None
+    finally:
+        portable_ops.FORCE_GENERIC = portable_ops.FORMULAS_ONLY = False

@@ -217,7 +217,11 @@ def test_device_neutral_attention_matches_the_planning_hosts_operator(causal, ma
     ro, rl = aten._scaled_dot_product_flash_attention_for_cpu(q, k, v, 0.0, causal, attn_mask=m)
     rdq, rdk, rdv = aten._scaled_dot_product_flash_attention_for_cpu_backward(go, q, k, v, ro, rl, 0.0, causal, attn_mask=m)
     monkeypatch.setattr(P, "FORCE_GENERIC", True)
-    o, l = P.sdpa_forward(q, k, v, 0.0, causal, attn_mask=m)
-    assert torch.allclose(o, ro, atol=1e-9) and torch.allclose(l.to(rl.dtype), rl, atol=1e-6)
-    dq, dk, dv = P.sdpa_backward(go, q, k, v, ro, rl.double(), 0.0, causal, attn_mask=m)
-    assert torch.allclose(dq, rdq, atol=1e-8) and torch.allclose(dk, rdk, atol=1e-8) and torch.allclose(dv, rdv, atol=1e-8)
+    for formulas in (True, False):  # explicit formulas; the library call with a recomputing backward
+        monkeypatch.setattr(P, "FORMULAS_ONLY", formulas)
+        o, l = P.sdpa_forward(q, k, v, 0.0, causal, attn_mask=m)
+        assert torch.allclose(o, ro, atol=1e-9)
+        if formulas:
+            assert torch.allclose(l.to(rl.dtype), rl, atol=1e-6)
+        dq, dk, dv = P.sdpa_backward(go, q, k, v, o, l.double(), 0.0, causal, attn_mask=m)
+        assert torch.allclose(dq, rdq, atol=1e-8) and torch.allclose(dk, rdk, atol=1e-8) and torch.allclose(dv, rdv, atol=1e-8)
