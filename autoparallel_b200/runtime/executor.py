@@ -87,6 +87,12 @@ class Runtime:
         for gm in (self.fw, self.bw, self.fwd_only):
             changed = False
             for n in gm.graph.nodes:
+                if n.op == "get_attr":
+                    # tensor constants the forward creates (``torch.tensor([...])``) were materialised on the planning host
+                    t = getattr(gm, n.target, None) if "." not in n.target else None
+                    if isinstance(t, torch.Tensor) and t.device != device and t.device.type != "meta":
+                        setattr(gm, n.target, t.to(device))
+                    continue
                 if n.op != "call_function":
                     continue
                 if n.target in SWAPS and device.type != "cpu":

@@ -365,3 +365,30 @@ def test_operators_of_the_planning_host_are_swapped_when_the_graphs_move_to_anot
             pm.qkv.weight.grad = None
     finally:
         portable_ops.FORCE_GENERIC = portable_ops.FORMULAS_ONLY = False
+
+
+def test_tensor_constants_created_in_the_forward_follow_the_graphs(mesh_1d):
+    """``torch.tensor([...])`` inside ``forward`` becomes a constant attribute of the traced graphs, materialised on the planning
+    host; it moves with the graphs when they are retargeted (a CPU constant next to device tensors is an error otherwise)."""
+    import torch.nn as nn
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.l = nn.Linear(4, 4)
+
+        def forward(self, x):
+            return self.l(x) * torch.tensor([0.5, 2.0, 1.0, -1.0]) + torch.tensor(3.0)
+
+    with torch.device("meta"):
+        m = M()
+    with AutoParallel(m, lambda: torch.randn(16, 4), mesh_1d) as ap:
+        ap.add_input_constraints([(Shard(0),)])
+        ap.optimize_placement()
+        pm = ap.apply_placement()
+    rt = pm.__dict__["_apb200_runtime"]
+    consts = [b for g in (rt.fw, rt.bw, rt.fwd_only) for _, b in g.named_buffers()]
+    assert consts and all(b.device.type == "cpu" for b in consts)
+    rt._retarget(torch.device("meta"))
+    consts = [b for g in (rt.fw, rt.bw, rt.fwd_only) for _, b in g.named_buffers()]
+    assert consts and all(b.device.type == "meta" for b in consts)
