@@ -90,7 +90,8 @@ class Runtime:
                 if n.op == "get_attr":
                     # tensor constants the forward creates (``torch.tensor([...])``) were materialised on the planning host
                     t = getattr(gm, n.target, None) if "." not in n.target else None
-                    if isinstance(t, torch.Tensor) and t.device != device and t.device.type != "meta":
+                    if (isinstance(t, torch.Tensor) and type(t).__name__ != "FakeTensor" and t.device != device
+                            and t.device.type != "meta"):
                         setattr(gm, n.target, t.to(device))
                     continue
                 if n.op != "call_function":
