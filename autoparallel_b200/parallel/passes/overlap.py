@@ -112,6 +112,10 @@ def schedule_for_streams(gm: fx.GraphModule, mesh=None, config: Optional[Overlap
             cur = users[0]
             if cur.target in comm_ops.START_OPS or cur.target is wait_op:
                 return False
+            if len(cur.all_input_nodes) != 1:
+                # the result joins another tensor on its way out (gradients of a tied parameter are added up): its tail
+                # cannot move as a unit behind this wait alone
+                return False
         return False
 
     deferred_waits = {

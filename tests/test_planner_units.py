@@ -240,3 +240,37 @@ def test_overlap_schedule_prefetches_and_defers(mesh_1d):
                     assert n.users and all(u.target is comm_ops.ops.comm_wait.default for u in n.users), n.name
     finally:
         ap.__exit__(None, None, None)
+
+
+def test_reductions_whose_results_are_added_up_are_not_deferred_as_a_unit(mesh_1d):
+    """A parameter used three times (a tied embedding) gets three reduced gradients that are added on their way out.  The
+    scheduler may defer a reduction together with its tail only when that tail is a unary chain; here every node must still
+    be scheduled exactly once."""
+    import torch.nn as nn
+
+    from autoparallel_b200.parallel.lower.partition import partition_joint
+    from autoparallel_b200.parallel.passes.overlap import schedule_for_streams
+
+    class Tied3(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = nn.Embedding(64, 32)
+            self.mid = nn.Linear(32, 32)
+
+        def forward(self, a, b):
+            h = self.mid(self.emb(a) + self.emb(b))
+            return h @ self.emb.weight.t()
+
+    with torch.device("meta"):
+        m = Tied3()
+    with AutoParallel(m, lambda: (torch.randint(0, 64, (16, 8)), torch.randint(0, 64, (16, 8))), mesh_1d) as ap:
+        ap.add_parameter_memory_constraint()
+        ap.add_input_constraints([(Shard(0),)] * 2)
+        ap.optimize_placement()
+        parts = partition_joint(ap.lower().joint)
+        for gm_ in (parts.fw, parts.bw):
+            n_before = sum(1 for n in gm_.graph.nodes if n.op == "call_function")
+            sched = schedule_for_streams(gm_, mesh_1d)
+            n_after = sum(1 for n in sched.graph.nodes if n.op == "call_function")
+            assert n_after >= n_before  # (split collectives add their waits; nothing is lost or doubled beyond that)
+            sched.graph.lint()
