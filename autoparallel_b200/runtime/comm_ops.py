@@ -18,6 +18,8 @@ ordered_sharding.py:70-102) and wraps them for users in autoparallel/collectives
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 import torch.distributed._functional_collectives as funcol
@@ -252,6 +254,21 @@ def _request_sms(x) -> None:
         cuda_impl.extension().gemm_yield_request(_yield_pairs)
 
 
+#: Host tensors (gloo ranks: the CPU test paths) complete their split-phase collectives at issue.  The schedule - which
+#: node is issued where, which wait is deferred - is the same; only the library call is no longer in flight while the
+#: graph runs on.  With several gloo collectives in flight next to the graph's own operators, about one run in twenty-five
+#: of small multi-model numerics jobs ended in a corrupted heap ("malloc(): unaligned tcache chunk detected"), with
+#: identical schedules on all ranks; the same collectives issued and waited from a plain loop never did, and the cause
+#: was not found.  Device tensors are stream ordered and unaffected.  ``APB200_HOST_ASYNC=1`` restores in-flight issue.
+_HOST_ASYNC = os.environ.get("APB200_HOST_ASYNC", "0") == "1"
+
+
+def _issued(out):
+    if not out.is_cuda and not _HOST_ASYNC:
+        return torch.ops._c10d_functional.wait_tensor(out)
+    return out
+
+
 def _ag_start(x, dim, group, n):
     if x.dtype.is_floating_point and x.dtype.itemsize == 1:
         return _all_gather(x, dim, group, n)  # float8 moves as bytes (synchronous form)
@@ -264,7 +281,7 @@ def _ag_start(x, dim, group, n):
     if dim != 0:
         return _all_gather(x, dim, group, n)  # inner-dim gathers need a post-permute: keep synchronous
     _request_sms(x)
-    return torch.ops._c10d_functional.all_gather_into_tensor(x.contiguous(), n, group)
+    return _issued(torch.ops._c10d_functional.all_gather_into_tensor(x.contiguous(), n, group))
 
 
 def _rs_start(x, dim, group, n):
@@ -279,7 +296,7 @@ def _rs_start(x, dim, group, n):
     shape = list(x.shape)
     shape[0] //= n
     _request_sms(x)
-    out = torch.ops._c10d_functional.reduce_scatter_tensor(x.contiguous().view(-1), "sum", n, _red_group(group))
+    out = _issued(torch.ops._c10d_functional.reduce_scatter_tensor(x.contiguous().view(-1), "sum", n, _red_group(group)))
     return out.view(shape)
 
 
@@ -287,7 +304,7 @@ def _ar_start(x, group, n):
     be = _standalone_backend(group)
     if be is not None and x.is_cuda:
         return be.all_reduce_start(x)
-    return torch.ops._c10d_functional.all_reduce(x.contiguous(), "sum", _red_group(group))
+    return _issued(torch.ops._c10d_functional.all_reduce(x.contiguous(), "sum", _red_group(group)))
 
 
 def _comm_wait(x):
